@@ -1,0 +1,152 @@
+/*
+ * mcb200.h -- C ABI of libmetal_candle_b200.so: the B200 (sm_100a) kernels behind the
+ * custom-op hot path of GarthDB/metal-candle (fused LoRA linear, RMSNorm, row softmax, AdamW).
+ *
+ * Conventions (all entry points):
+ *   - return 0 on success; a negative value for an invalid argument (null pointer, bad shape,
+ *     misalignment, unsupported layout); a positive value for a CUDA runtime error (its
+ *     cudaError_t) or MCB_ERR_DEVICE_TIMEOUT.  Nothing aborts or throws across the boundary.
+ *   - mcb_last_error() returns a thread-local message for the last non-zero status.
+ *   - every pointer named x/W/A/B/y/... is a DEVICE pointer owned by the caller, outputs and
+ *     workspaces included.  The library allocates no device memory in these calls (the one small
+ *     per-device status word is created by mcb_init).  There is no CPU fallback.
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised.
+ *   - matrices are dense row-major.  M = product of the leading dims (batch*seq tokens),
+ *     K = in_features, N = out_features, r = LoRA rank.
+ *
+ * Reference paths are given as file:line within the metal-candle source tree.
+ */
+#ifndef MCB200_H_
+#define MCB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MCB_OK 0
+#define MCB_ERR_NULL (-1)          /* a required pointer is null */
+#define MCB_ERR_SHAPE (-2)         /* a dimension is zero/negative/out of range, or shapes disagree */
+#define MCB_ERR_ALIGN (-3)         /* pointer or row pitch not aligned as the kernel needs */
+#define MCB_ERR_UNSUPPORTED (-4)   /* dtype / layout / rank combination the kernel does not implement */
+#define MCB_ERR_WORKSPACE (-5)     /* workspace missing or too small */
+#define MCB_ERR_NOT_INIT (-6)      /* mcb_init was not called for the current device */
+#define MCB_ERR_DEVICE_TIMEOUT 100001 /* a bounded device-side wait ran out (see mcb_device_status) */
+
+/* Element types.  MCB_F32 is the validation path (CUDA-core FMA, matches the reference's f32 CPU
+ * arithmetic to <=1e-4); MCB_BF16 is the production path (tcgen05 tensor cores, fp32 accumulate). */
+#define MCB_F32 0
+#define MCB_BF16 1
+
+/* Layout of the frozen weight.  candle_nn::Linear stores [out, in] (src/models/transformer.rs:189-192). */
+#define MCB_W_OUT_IN 0 /* W is [N, K]: what the forward consumes  */
+#define MCB_W_IN_OUT 1 /* W is [K, N]: what the backward consumes */
+
+/* ---- library / device ------------------------------------------------------------------ */
+
+/* Replaces Device::new_metal / MetalKernelCompiler::new (src/backend/device.rs:58-87,
+ * src/backend/metal_kernels.rs:70-81): binds the library to CUDA device `device`, checks that it is
+ * compute capability 10.x, resolves the driver's tensor-map encoder, raises the kernels' dynamic
+ * shared-memory limits and allocates the per-device status word.  Idempotent. */
+int mcb_init(int device);
+const char* mcb_last_error(void);
+int mcb_version(void);
+/* Reads (and clears) the device-side status word of the current device: 0, or a code naming the
+ * bounded wait that gave up.  Synchronises the device. */
+int mcb_device_status(int* status_out);
+
+/* ---- fused LoRA -------------------------------------------------------------------------- */
+
+/* Replaces FusedLoRAOp / CustomMetalOps::lora_forward_fused (src/backend/custom_ops.rs:73-431,
+ * src/backend/metal_ops.rs:126-144) and the kernel fused_lora_forward_tiled
+ * (src/backend/kernels.metal:108-159):   out[M,N] = scale * (x[M,K] @ A[K,r]) @ B[r,N].
+ * A and B are float32 (the reference keeps them F32, src/training/lora.rs:238,244); x/out are `dtype`. */
+int mcb_lora_delta_fwd(const void* x, const float* A, const float* B, void* out,
+                       int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Workspace needed by the three mcb_lora_* calls for these sizes. */
+size_t mcb_lora_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int dtype);
+
+/* Frozen linear + LoRA in one pass:  y = x W^T (+ bias) + scale * (x A) B.
+ * Replaces the sequence candle_nn::Linear (src/models/transformer.rs:241-243) + LoRALayer::forward
+ * (src/training/lora.rs:292-342) + the add at src/models/qwen.rs:114-118.
+ *   W      [N,K] (w_layout MCB_W_OUT_IN; the bf16 path accepts only this), dtype
+ *   bias   [N] dtype, or null
+ *   A,B    float32 [K,r], [r,N]; r may be 0 with A=B=null (plain frozen linear)
+ *   y      [M,N] dtype
+ *   h_save [M, mcb_lora_rank_padded(r)] dtype, or null: receives scale*(x A) for the backward. */
+int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const float* A, const float* B,
+                        void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale,
+                        int dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reverse pass of mcb_lora_linear_fwd with W and bias frozen (candle autograd at
+ * src/training/trainer.rs:388 over src/training/lora.rs:323-339):
+ *   dx = dy W + scale (dy B^T) A^T ;  dA = x^T (scale dy B^T) ;  dB = (scale x A)^T dy
+ *   W      [K,N] (w_layout MCB_W_IN_OUT) for bf16; either layout for f32
+ *   h_save from the forward; null makes the call recompute it
+ *   dx     [M,K] dtype, or null to skip;  dA [K,r], dB [r,N] float32, or both null to skip
+ *   accumulate != 0 adds into dA/dB instead of overwriting (gradient accumulation). */
+int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                        const void* h_save, void* dx, float* dA, float* dB, int accumulate,
+                        int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Rank rounded up to the tensor-core K granule (16); the column count of h_save. */
+int64_t mcb_lora_rank_padded(int64_t r);
+
+/* dst[cols,rows] = src[rows,cols]^T; makes the [K,N] copy of a frozen weight for the backward. */
+int mcb_transpose_2d(const void* src, void* dst, int64_t rows, int64_t cols, int dtype, void* stream);
+
+/* ---- RMSNorm ------------------------------------------------------------------------------ */
+
+/* Replaces FusedRMSNormOp / rms_norm_fused (src/backend/custom_ops.rs:443-632, kernels.metal:281-330)
+ * and, with w != null, the model layer's extra broadcast_mul (src/models/qwen.rs:314-325):
+ *   y = x / sqrt(mean(x^2) + eps) (* w).   x,y [rows,D] dtype; w [D] dtype or null;
+ *   rstd [rows] float32 or null (saved 1/sqrt(..) for the backward). */
+int mcb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t rows, int64_t D,
+                    float eps, int dtype, void* stream);
+size_t mcb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t D);
+/* Reverse pass (candle autograd in the reference):  dx [rows,D] dtype; dw [D] float32 or null
+ * (overwritten unless accumulate).  `workspace` holds the per-block partial sums of dw. */
+int mcb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
+                    int64_t rows, int64_t D, float eps, int dtype,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- softmax ------------------------------------------------------------------------------ */
+
+/* Replaces FusedSoftmaxOp / softmax_fused (src/backend/custom_ops.rs:644-824, kernels.metal:187-261)
+ * and TensorExt::softmax_stable (src/backend/tensor.rs:91-98): softmax over the last dim of [rows,D].
+ * -inf entries (an additive causal mask, src/models/transformer.rs:269-273) give 0; a row that is
+ * all -inf gives zeros.  In-place (y == x) is allowed. */
+int mcb_softmax_fwd(const void* x, void* y, int64_t rows, int64_t D, int dtype, void* stream);
+/* dx = y * (dy - sum_j dy_j y_j).  In-place on dy is allowed. */
+int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int dtype,
+                    void* stream);
+
+/* ---- AdamW -------------------------------------------------------------------------------- */
+
+typedef struct {
+  float* p;        /* parameter, updated in place   */
+  const float* g;  /* gradient                      */
+  float* m;        /* first moment, updated         */
+  float* v;        /* second moment, updated        */
+  int64_t n;       /* element count                 */
+  int32_t t;       /* bias-correction step for THIS tensor (the reference's shared counter advances
+                      once per tensor, src/training/optimizer.rs:236-238) */
+  int32_t pad_;
+} mcb_adamw_tensor;
+
+/* Replaces AdamW::step / step_var (src/training/optimizer.rs:227-316) for a list of float32 tensors
+ * in a few launches:  m=b1 m+(1-b1)g; v=b2 v+(1-b2)g^2; p -= lr*(m/(1-b1^t))/(sqrt(v/(1-b2^t))+eps)
+ * + (wd*lr)*p.  `tensors` is a HOST array.  g is multiplied by grad_scale first (1/world size in the
+ * data-parallel step; 1 otherwise). */
+int mcb_adamw_multi(const mcb_adamw_tensor* tensors, int n_tensors, float lr, float beta1, float beta2,
+                    float eps, float weight_decay, float grad_scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MCB200_H_ */

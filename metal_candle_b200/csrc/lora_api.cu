@@ -1,0 +1,87 @@
+// extern "C" entry points of the fused LoRA linear: argument validation (the checks FusedLoRAOp::new
+// and its forward do, src/backend/custom_ops.rs:118-168,283-313) and dispatch to the float32 or the
+// bfloat16 implementation.
+#include "lora_internal.cuh"
+
+using namespace mcb;
+
+namespace {
+
+int check_dims(const char* op, int64_t M, int64_t K, int64_t N, int64_t r, int dtype, bool rank_required) {
+  if (M <= 0 || K <= 0 || N <= 0)
+    return fail(MCB_ERR_SHAPE, "%s: M=%lld K=%lld N=%lld must be positive", op, (long long)M, (long long)K, (long long)N);
+  // The reference range-checks every dimension into u32 (src/backend/custom_ops.rs:283-313).
+  if (M > 0xffffffffll || K > 0xffffffffll || N > 0xffffffffll)
+    return fail(MCB_ERR_SHAPE, "%s: dimension exceeds u32", op);
+  if (r < 0 || (rank_required && r == 0))
+    return fail(MCB_ERR_SHAPE, "%s: LoRA rank must be greater than 0", op);
+  // LoRALayer::new rejects rank > min(in, out) (src/training/lora.rs:222-231).
+  if (r > (K < N ? K : N))
+    return fail(MCB_ERR_SHAPE, "%s: LoRA rank %lld exceeds maximum rank %lld (min of in_features=%lld, out_features=%lld)", op,
+                (long long)r, (long long)(K < N ? K : N), (long long)K, (long long)N);
+  if (dtype != MCB_F32 && dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "%s: dtype %d", op, dtype);
+  return MCB_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t mcb_lora_rank_padded(int64_t r) { return rank_padded(r); }
+
+extern "C" size_t mcb_lora_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int dtype) {
+  if (M <= 0 || K <= 0 || N <= 0 || r <= 0) return 0;
+  return dtype == MCB_F32 ? f32path::workspace_bytes(M, K, N, r) : bf16path::workspace_bytes(M, K, N, r);
+}
+
+extern "C" int mcb_lora_delta_fwd(const void* x, const float* A, const float* B, void* out, int64_t M, int64_t K,
+                                  int64_t N, int64_t r, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+  if (!x || !A || !B || !out) return fail(MCB_ERR_NULL, "lora_delta_fwd: null pointer");
+  if (int rc = check_dims("lora_delta_fwd", M, K, N, r, dtype, true)) return rc;
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  LoraArgs a;
+  a.x = x; a.A = A; a.B = B; a.y = out;
+  a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return dtype == MCB_F32 ? f32path::delta_fwd(a) : bf16path::delta_fwd(a, ds);
+}
+
+extern "C" int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const float* A, const float* B, void* y,
+                                   void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
+                                   int w_layout, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !W || !y) return fail(MCB_ERR_NULL, "lora_linear_fwd: x, W or y is null");
+  if (r > 0 && (!A || !B)) return fail(MCB_ERR_NULL, "lora_linear_fwd: rank %lld but A or B is null", (long long)r);
+  if (int rc = check_dims("lora_linear_fwd", M, K, N, r, dtype, false)) return rc;
+  if (w_layout != MCB_W_OUT_IN && w_layout != MCB_W_IN_OUT) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_fwd: w_layout %d", w_layout);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  LoraArgs a;
+  a.x = x; a.W = W; a.bias = bias; a.A = A; a.B = B; a.y = y; a.h_save = h_save;
+  a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = w_layout;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return dtype == MCB_F32 ? f32path::linear_fwd(a) : bf16path::linear_fwd(a, ds);
+}
+
+extern "C" int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                                   const void* h_save, void* dx, float* dA, float* dB, int accumulate, int64_t M,
+                                   int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  if (!dy) return fail(MCB_ERR_NULL, "lora_linear_bwd: dy is null");
+  if (dx && !W) return fail(MCB_ERR_NULL, "lora_linear_bwd: dx wanted but W is null");
+  if (r > 0 && (!A || !B)) return fail(MCB_ERR_NULL, "lora_linear_bwd: rank %lld but A or B is null", (long long)r);
+  if (r > 0 && (dA || dB) && !x) return fail(MCB_ERR_NULL, "lora_linear_bwd: dA/dB wanted but x is null");
+  if ((dA == nullptr) != (dB == nullptr)) return fail(MCB_ERR_NULL, "lora_linear_bwd: pass both dA and dB, or neither");
+  if (int rc = check_dims("lora_linear_bwd", M, K, N, r, dtype, false)) return rc;
+  if (w_layout != MCB_W_OUT_IN && w_layout != MCB_W_IN_OUT) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_bwd: w_layout %d", w_layout);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  LoraArgs a;
+  a.x = x; a.W = W; a.A = A; a.B = B; a.dy = dy; a.h_save = const_cast<void*>(h_save);
+  a.dx = dx; a.dA = dA; a.dB = dB; a.accumulate = accumulate;
+  a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = w_layout;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return dtype == MCB_F32 ? f32path::linear_bwd(a) : bf16path::linear_bwd(a, ds);
+}

@@ -1,0 +1,46 @@
+// Internal interface between the C-ABI LoRA entry points (lora_api.cu) and the two implementations:
+// the float32 validation path on CUDA cores (sgemm_f32.cu) and the bfloat16 production path on
+// tcgen05 tensor cores (umma_gemm.cu).
+#pragma once
+#include "common.cuh"
+
+namespace mcb {
+
+struct LoraArgs {
+  const void* x = nullptr;     // [M,K]
+  const void* W = nullptr;     // [N,K] or [K,N] per w_layout
+  const void* bias = nullptr;  // [N] or null
+  const float* A = nullptr;    // [K,r] float32
+  const float* B = nullptr;    // [r,N] float32
+  void* y = nullptr;           // [M,N]
+  void* h_save = nullptr;      // [M,rp] scale*(x A), optional
+  const void* dy = nullptr;    // [M,N]
+  void* dx = nullptr;          // [M,K]
+  float* dA = nullptr;         // [K,r]
+  float* dB = nullptr;         // [r,N]
+  int accumulate = 0;
+  int64_t M = 0, K = 0, N = 0, r = 0;
+  float scale = 1.0f;
+  int w_layout = MCB_W_OUT_IN;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  cudaStream_t stream = nullptr;
+};
+
+inline int64_t rank_padded(int64_t r) { return r <= 0 ? 0 : ((r + 15) / 16) * 16; }
+
+namespace f32path {
+size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
+int delta_fwd(const LoraArgs& a);
+int linear_fwd(const LoraArgs& a);
+int linear_bwd(const LoraArgs& a);
+}  // namespace f32path
+
+namespace bf16path {
+size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
+int delta_fwd(const LoraArgs& a, const DeviceState* ds);
+int linear_fwd(const LoraArgs& a, const DeviceState* ds);
+int linear_bwd(const LoraArgs& a, const DeviceState* ds);
+}  // namespace bf16path
+
+}  // namespace mcb

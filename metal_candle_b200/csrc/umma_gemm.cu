@@ -1,0 +1,766 @@
+// bfloat16 production path of the fused LoRA linear on Blackwell tensor cores.
+//
+// One persistent, warp-specialised kernel computes
+//
+//     Y[M,N] = X[M,K] . W[N,K]^T  (+ bias)  +  (scale * X . P[rp,K]^T) . Q[N,rp]^T
+//
+// with every operand K-major (the reduction index is the contiguous one).  The forward uses it with
+// X = x, W = the frozen weight [out,in], P = A^T, Q = B^T; the backward uses the SAME kernel with
+// X = dy, W = the [in,out] copy of the frozen weight, P = B, Q = A, so dx and the rank-r path share one
+// pass over dy.  The rank-r intermediate H = scale * X P^T never goes through HBM on its way to the
+// output: it is accumulated in tensor memory beside the main accumulator, converted to bf16 by the
+// epilogue warps into shared memory, and applied as one more tcgen05.mma onto the main accumulator.
+// (The [M,rp] copy that the weight-gradient kernel needs is written out by the n-tile-0 CTAs only.)
+//
+// Roles per CTA (192 threads, one CTA per SM, grid = min(#tiles, #SMs)):
+//   warp 0    TMA producer: cp.async.bulk.tensor loads of the X / W / P tiles (128B swizzle) into a
+//             multi-stage ring, and of the Q tile (no swizzle, 16-byte columns) once per output tile
+//   warp 1    owns tensor memory (tcgen05.alloc of all 512 columns) and issues tcgen05.mma
+//             (M=128, N=BN and N=rp, K=16, bf16 x bf16 -> fp32) from one thread
+//   warps 2-5 epilogue: tcgen05.ld the accumulators (32 lanes per warp), convert, store
+// Two accumulator buffers (256 columns each: BN main + rp rank columns) let the epilogue of tile i
+// overlap the main loop of tile i+1.
+//
+// Every wait on an mbarrier is bounded (about two seconds); a wait that runs out records a code in
+// the device status word, raises a CTA-wide abort flag, and all roles fall through to the common
+// exit where tensor memory is released.  No loads use cluster multicast.
+#include <cuda.h>
+
+#include "lora_internal.cuh"
+
+namespace mcb {
+namespace bf16path {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kSmemBudget = 227 * 1024 - 1024;  // dynamic shared memory we ask for (minus alignment slack)
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+struct GemmParams {
+  int M, N, K;
+  int BN, rp, has_w, stages;
+  int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;
+  float scale;
+  __nv_bfloat16* Y;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* H;
+  int* status;
+  uint32_t stage_bytes, w_off, p_off;        // within a stage
+  uint32_t q_off, q_bytes, hs_off, hs_bytes; // from the aligned base
+  uint32_t bar_off;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = code;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47).
+//   K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused (=1).
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+//   K-major, no swizzle: 8x16-byte core matrices; LBO = byte step between 16-byte K chunks,
+//   SBO = byte step between 8-row groups.
+__device__ __forceinline__ uint64_t desc_noswz(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo >> 4) << 16) |
+         (static_cast<uint64_t>(sbo >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor for kind::f16: D=f32, A=B=bf16, both K-major, M=128, N=n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& mt, int& nt) {
+  const int per_band = p.group_m * p.num_n_tiles;
+  const int band = t / per_band;
+  const int in = t - band * per_band;
+  const int m_first = band * p.group_m;
+  const int gm = min(p.group_m, p.num_m_tiles - m_first);
+  nt = in / gm;
+  mt = m_first + in % gm;
+}
+
+// Barrier slots (8 bytes each) after the tile buffers.
+struct Bars {
+  uint32_t full0, empty0, d2_full0, h_ready0, d1_full0, acc_empty0, q_full0;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                 const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  Bars b;
+  b.full0 = base + p.bar_off;
+  b.empty0 = b.full0 + 8 * kMaxStages;
+  b.d2_full0 = b.empty0 + 8 * kMaxStages;
+  b.h_ready0 = b.d2_full0 + 16;
+  b.d1_full0 = b.h_ready0 + 16;
+  b.acc_empty0 = b.d1_full0 + 16;
+  b.q_full0 = b.acc_empty0 + 16;
+  const uint32_t tmem_slot = b.q_full0 + 16;
+  const uint32_t abort_addr = tmem_slot + 4;
+  // generic pointers to the two words after the barriers
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(b.full0 + 8 * s, 1);
+      mbar_init(b.empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(b.d2_full0 + 8 * a, 1);
+      mbar_init(b.h_ready0 + 8 * a, 4);
+      mbar_init(b.d1_full0 + 8 * a, 1);
+      mbar_init(b.acc_empty0 + 8 * a, 4);
+      mbar_init(b.q_full0 + 8 * a, 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int nkb = p.num_k_blocks;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int i = 0;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++i) {
+        int mt, nt;
+        tile_coords(p, t, mt, nt);
+        const int m0 = mt * BM, n0 = nt * p.BN;
+        const int a = i & 1;
+        if (p.rp > 0) {
+          if (i >= 2) ok = mbar_wait(b.d1_full0 + 8 * a, ((i - 2) >> 1) & 1, abort_flag, 11, p.status);
+          if (!ok) break;
+          const uint32_t qbar = b.q_full0 + 8 * a;
+          mbar_expect_tx(qbar, p.q_bytes);
+          const uint32_t qs = base + p.q_off + a * p.q_bytes;
+          for (int j = 0; j < p.rp / 8; ++j) tma_load_2d(qs + j * p.BN * 16, &tmQ, qbar, j * 8, n0);
+        }
+        for (int kb = 0; kb < nkb; ++kb) {
+          ok = mbar_wait(b.empty0 + 8 * stage, phase ^ 1, abort_flag, 12, p.status);
+          if (!ok) break;
+          const uint32_t fb = b.full0 + 8 * stage;
+          const uint32_t sb = base + stage * p.stage_bytes;
+          mbar_expect_tx(fb, p.stage_bytes);
+          tma_load_2d(sb, &tmX, fb, kb * BK, m0);
+          if (p.has_w) tma_load_2d(sb + p.w_off, &tmW, fb, kb * BK, n0);
+          if (p.rp > 0) tma_load_2d(sb + p.p_off, &tmP, fb, kb * BK, 0);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_main = make_idesc(p.BN);
+      const uint32_t idesc_rank = make_idesc(p.rp);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int i = 0;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++i) {
+        const int a = i & 1;
+        const uint32_t u = static_cast<uint32_t>(i >> 1);
+        ok = mbar_wait(b.acc_empty0 + 8 * a, (u & 1) ^ 1, abort_flag, 21, p.status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t d1 = tmem_base + a * 256;
+        const uint32_t d2 = d1 + p.BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          ok = mbar_wait(b.full0 + 8 * stage, phase, abort_flag, 22, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t sb = base + stage * p.stage_bytes;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint64_t ad = desc_sw128(sb + k4 * 32);
+            const uint32_t acc = (kb | k4) != 0 ? 1u : 0u;
+            if (p.has_w) umma_bf16(d1, ad, desc_sw128(sb + p.w_off + k4 * 32), idesc_main, acc);
+            if (p.rp > 0) umma_bf16(d2, ad, desc_sw128(sb + p.p_off + k4 * 32), idesc_rank, acc);
+          }
+          umma_commit(b.empty0 + 8 * stage);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (p.rp > 0) {
+          umma_commit(b.d2_full0 + 8 * a);
+          ok = mbar_wait(b.h_ready0 + 8 * a, u & 1, abort_flag, 23, p.status);
+          if (!ok) break;
+          ok = mbar_wait(b.q_full0 + 8 * a, u & 1, abort_flag, 24, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t hs = base + p.hs_off + a * p.hs_bytes;
+          const uint32_t qs = base + p.q_off + a * p.q_bytes;
+          for (int kk = 0; kk < p.rp / 16; ++kk) {
+            const uint64_t hd = desc_noswz(hs + kk * 2 * (BM * 16), BM * 16, 128);
+            const uint64_t qd = desc_noswz(qs + kk * 2 * (p.BN * 16), p.BN * 16, 128);
+            umma_bf16(d1, hd, qd, idesc_main, (p.has_w || kk > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(b.d1_full0 + 8 * a);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    int i = 0;
+    for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++i) {
+      int mt, nt;
+      tile_coords(p, t, mt, nt);
+      const int m0 = mt * BM, n0 = nt * p.BN;
+      const int a = i & 1;
+      const uint32_t u = static_cast<uint32_t>(i >> 1);
+      const int64_t grow = static_cast<int64_t>(m0) + row_in_tile;
+      const uint32_t d1 = tmem_base + lane_addr + a * 256;
+      if (p.rp > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(b.d2_full0 + 8 * a, u & 1, abort_flag, 31, p.status));
+        if (!ok) break;
+        tcgen05_fence_after();
+        uint8_t* hs_gen = gen_base + p.hs_off + a * p.hs_bytes;
+        for (int c = 0; c < p.rp; c += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(d1 + p.BN + c, v);
+          tmem_ld_wait();
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            w[j] = pack_bf16(__uint_as_float(v[2 * j]) * p.scale, __uint_as_float(v[2 * j + 1]) * p.scale);
+          const uint4 lo = make_uint4(w[0], w[1], w[2], w[3]);
+          const uint4 hi = make_uint4(w[4], w[5], w[6], w[7]);
+          // no-swizzle K-major operand: 16-byte K chunk j of row m lives at j*(128*16) + m*16
+          *reinterpret_cast<uint4*>(hs_gen + (c / 8) * (BM * 16) + row_in_tile * 16) = lo;
+          *reinterpret_cast<uint4*>(hs_gen + (c / 8 + 1) * (BM * 16) + row_in_tile * 16) = hi;
+          if (p.H != nullptr && nt == 0 && grow < p.M) {
+            uint4* hp = reinterpret_cast<uint4*>(p.H + grow * p.rp + c);
+            hp[0] = lo;
+            hp[1] = hi;
+          }
+        }
+        fence_proxy_async_smem();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(b.h_ready0 + 8 * a);
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(b.d1_full0 + 8 * a, u & 1, abort_flag, 32, p.status));
+      if (!ok) break;
+      tcgen05_fence_after();
+      if (p.Y != nullptr) {
+        for (int c = 0; c < p.BN; c += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(d1 + c, v);
+          tmem_ld_wait();
+          const int gcol = n0 + c;
+          if (grow < p.M && gcol < p.N) {
+            float f[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
+            }
+            __nv_bfloat16* yp = p.Y + grow * p.N + gcol;
+            const uint4 lo = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
+                                        pack_bf16(f[6], f[7]));
+            const uint4 hi = make_uint4(pack_bf16(f[8], f[9]), pack_bf16(f[10], f[11]), pack_bf16(f[12], f[13]),
+                                        pack_bf16(f[14], f[15]));
+            if (gcol + 8 <= p.N) reinterpret_cast<uint4*>(yp)[0] = lo;
+            if (gcol + 16 <= p.N) reinterpret_cast<uint4*>(yp)[1] = hi;
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b.acc_empty0 + 8 * a);
+    }
+  }
+
+  // ---------------- common exit ----------------
+  __syncwarp();
+  if (*abort_flag != 0) {
+    // give loads still in flight time to land before the CTA's shared memory is released
+    for (int k = 0; k < 200; ++k) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- operand packing -----------------------------------------------------------------------------
+// Turns the float32 LoRA factors into the two K-major bf16 operands of the kernel above, zero-padded
+// from r to rp rows/columns.
+//   forward  (mode 0): P = A^T [rp,K],  Q = B^T [N,rp]
+//   backward (mode 1): P = B   [rp,N],  Q = A   [K,rp]
+__global__ void pack_lora_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                 __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Q, int K, int N, int r,
+                                 int rp, int mode) {
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nP = static_cast<int64_t>(rp) * (mode == 0 ? K : N);
+  const int64_t nQ = static_cast<int64_t>(rp) * (mode == 0 ? N : K);
+  if (tid < nP) {
+    if (mode == 0) {  // P[j,k] = A[k,j]
+      const int j = static_cast<int>(tid / K), k = static_cast<int>(tid % K);
+      P[tid] = __float2bfloat16_rn(j < r ? A[static_cast<int64_t>(k) * r + j] : 0.0f);
+    } else {  // P[j,n] = B[j,n]
+      const int j = static_cast<int>(tid / N);
+      P[tid] = __float2bfloat16_rn(j < r ? B[tid] : 0.0f);
+    }
+  } else if (tid < nP + nQ) {
+    const int64_t q = tid - nP;
+    const int j = static_cast<int>(q % rp);
+    const int64_t row = q / rp;
+    if (mode == 0)  // Q[n,j] = B[j,n]
+      Q[q] = __float2bfloat16_rn(j < r ? B[static_cast<int64_t>(j) * N + row] : 0.0f);
+    else  // Q[k,j] = A[k,j]
+      Q[q] = __float2bfloat16_rn(j < r ? A[row * r + j] : 0.0f);
+  }
+}
+
+// ---- LoRA weight gradients -------------------------------------------------------------------------
+// part[split][c][j] = sum over the split's rows m of X[m,c] * H[m,j]    (X bf16 [M,C], H bf16 [M,rp])
+// Each thread owns two adjacent columns and 16 rank columns; rows of H are staged in shared memory
+// as float.  grid = (ceil(C/256), splits, rp/16).
+constexpr int kGradRows = 64;
+__global__ void __launch_bounds__(128)
+lora_grad_partial_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ H,
+                         float* __restrict__ part, int M, int C, int rp, int rows_per_split) {
+  __shared__ float hs[kGradRows][16];
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 2;
+  const int j0 = blockIdx.z * 16;
+  const int m_begin = blockIdx.y * rows_per_split;
+  const int m_end = min(M, m_begin + rows_per_split);
+  float acc0[16], acc1[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) { acc0[j] = 0.0f; acc1[j] = 0.0f; }
+  const bool live = c < C;  // C is even (checked on the host)
+  for (int mb = m_begin; mb < m_end; mb += kGradRows) {
+    const int nrows = min(kGradRows, m_end - mb);
+    __syncthreads();
+    for (int i = threadIdx.x; i < kGradRows * 16; i += 128) {
+      const int rr = i >> 4, jj = i & 15;
+      hs[rr][jj] = rr < nrows ? __bfloat162float(H[static_cast<int64_t>(mb + rr) * rp + j0 + jj]) : 0.0f;
+    }
+    __syncthreads();
+    if (live) {
+#pragma unroll 4
+      for (int rr = 0; rr < nrows; ++rr) {
+        const uint32_t xw = *reinterpret_cast<const uint32_t*>(X + static_cast<int64_t>(mb + rr) * C + c);
+        const float x0 = __uint_as_float(xw << 16), x1 = __uint_as_float(xw & 0xffff0000u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float h = hs[rr][j];
+          acc0[j] = fmaf(x0, h, acc0[j]);
+          acc1[j] = fmaf(x1, h, acc1[j]);
+        }
+      }
+    }
+  }
+  if (live) {
+    float* o = part + (static_cast<int64_t>(blockIdx.y) * C + c) * rp + j0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { o[j] = acc0[j]; o[rp + j] = acc1[j]; }
+  }
+}
+
+// out (+)= sum over splits, in split order.  transposed == 0: out[c*r + j] (dA [K,r]);
+// transposed == 1: out[j*C + c] (dB [r,N]).
+__global__ void lora_grad_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int splits, int C,
+                                        int r, int rp, int transposed, int accumulate) {
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (tid >= static_cast<int64_t>(C) * r) return;
+  int c, j;
+  if (transposed) { j = static_cast<int>(tid / C); c = static_cast<int>(tid % C); }
+  else { c = static_cast<int>(tid / r); j = static_cast<int>(tid % r); }
+  float s = 0.0f;
+  for (int sp = 0; sp < splits; ++sp) s += part[(static_cast<int64_t>(sp) * C + c) * rp + j];
+  out[tid] = accumulate ? out[tid] + s : s;
+}
+
+// ---- host side -----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_map(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int box_inner,
+             int box_outer, bool swizzle128, const char* what) {
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ds->encode_tiled)(
+      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MCB_ERR_ALIGN, "tensor map for %s rejected (CUresult %d): ptr=%p inner=%lld outer=%lld box=%dx%d", what,
+                static_cast<int>(r), ptr, (long long)inner, (long long)outer, box_inner, box_outer);
+  return MCB_OK;
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Tile width: the fewest n-tiles of at most `cap` columns, evened out, in multiples of 32.
+int pick_bn(int64_t N, int rp) {
+  const int cap = rp > 0 ? ((256 - rp) / 32) * 32 : 256;
+  const int64_t tiles = (N + cap - 1) / cap;
+  int bn = static_cast<int>(((N + tiles - 1) / tiles + 31) / 32 * 32);
+  if (bn > cap) bn = cap;
+  if (bn < 32) bn = 32;
+  return bn;
+}
+
+struct GemmCall {
+  const __nv_bfloat16* X = nullptr;   // [M,K]
+  const __nv_bfloat16* W = nullptr;   // [N,K] or null
+  const __nv_bfloat16* P = nullptr;   // [rp,K] or null
+  const __nv_bfloat16* Q = nullptr;   // [N,rp] or null
+  const __nv_bfloat16* bias = nullptr;
+  __nv_bfloat16* Y = nullptr;         // [M,N] or null
+  __nv_bfloat16* H = nullptr;         // [M,rp] or null
+  int64_t M = 0, N = 0, K = 0;
+  int rp = 0;
+  float scale = 1.0f;
+};
+
+int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
+  if (c.M > 0x7fffff00ll || c.N > 0x7fffff00ll || c.K > 0x7fffff00ll)
+    return fail(MCB_ERR_SHAPE, "bf16 GEMM: dimension exceeds 2^31");
+  if (c.K % 8 != 0 || c.N % 8 != 0)
+    return fail(MCB_ERR_ALIGN, "bf16 path needs in/out features that are multiples of 8 (got reduction %lld, output %lld)",
+                (long long)c.K, (long long)c.N);
+  if (!aligned16(c.X) || (c.W && !aligned16(c.W)) || (c.Y && !aligned16(c.Y)) || (c.H && !aligned16(c.H)))
+    return fail(MCB_ERR_ALIGN, "bf16 path needs 16-byte aligned matrices");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int>(c.M); p.N = static_cast<int>(c.N); p.K = static_cast<int>(c.K);
+  p.rp = c.rp;
+  p.has_w = c.W != nullptr ? 1 : 0;
+  p.BN = pick_bn(c.N, c.rp);
+  p.num_m_tiles = (p.M + BM - 1) / BM;
+  p.num_n_tiles = (p.N + p.BN - 1) / p.BN;
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  p.num_k_blocks = (p.K + BK - 1) / BK;
+  p.group_m = p.num_m_tiles < 16 ? p.num_m_tiles : 16;
+  p.scale = c.scale;
+  p.Y = c.Y; p.bias = c.bias; p.H = c.H; p.status = ds->status_word;
+  const uint32_t x_bytes = BM * BK * 2;
+  const uint32_t w_bytes = p.has_w ? p.BN * BK * 2 : 0;
+  const uint32_t p_bytes = p.rp * BK * 2;
+  p.w_off = x_bytes;
+  p.p_off = x_bytes + w_bytes;
+  p.stage_bytes = x_bytes + w_bytes + p_bytes;  // every part is a multiple of 1024
+  p.q_bytes = static_cast<uint32_t>(p.BN) * p.rp * 2;
+  p.hs_bytes = static_cast<uint32_t>(BM) * p.rp * 2;
+  const uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + 512;
+  int stages = static_cast<int>((kSmemBudget - fixed) / p.stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return fail(MCB_ERR_UNSUPPORTED, "bf16 GEMM: tile does not fit shared memory (BN=%d rp=%d)", p.BN, p.rp);
+  p.stages = stages;
+  p.q_off = stages * p.stage_bytes;
+  p.hs_off = p.q_off + 2 * p.q_bytes;
+  p.bar_off = p.hs_off + 2 * p.hs_bytes;
+
+  CUtensorMap tmX, tmW, tmP, tmQ;
+  if (int rc = make_map(ds, &tmX, c.X, c.K, c.M, BK, BM, true, "X")) return rc;
+  if (p.has_w) { if (int rc = make_map(ds, &tmW, c.W, c.K, c.N, BK, p.BN, true, "W")) return rc; }
+  else tmW = tmX;
+  if (p.rp > 0) {
+    if (int rc = make_map(ds, &tmP, c.P, c.K, p.rp, BK, p.rp, true, "P")) return rc;
+    if (int rc = make_map(ds, &tmQ, c.Q, p.rp, c.N, 8, p.BN, false, "Q")) return rc;
+  } else { tmP = tmX; tmQ = tmX; }
+  const int grid = p.num_tiles < ds->sm_count ? p.num_tiles : ds->sm_count;
+  lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, p);
+  MCB_CHECK_LAUNCH("lora_gemm_kernel");
+  return MCB_OK;
+}
+
+int grad_splits(int64_t M, int64_t C, int sm_count) {
+  const int64_t col_blocks = (C + 255) / 256;
+  int64_t s = (2 * static_cast<int64_t>(sm_count) + col_blocks - 1) / col_blocks;
+  const int64_t max_s = (M + kGradRows - 1) / kGradRows;
+  if (s > max_s) s = max_s;
+  if (s < 1) s = 1;
+  return static_cast<int>(s);
+}
+
+// out = X^T H through split partial sums.  `part` must hold splits*C*rp floats.
+int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* H, float* out, float* part, int64_t M, int64_t C, int r,
+                int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st) {
+  if (C % 2 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients need an even feature count (got %lld)", (long long)C);
+  const int splits = grad_splits(M, C, ds->sm_count);
+  int rows_per_split = static_cast<int>((M + splits - 1) / splits);
+  rows_per_split = (rows_per_split + kGradRows - 1) / kGradRows * kGradRows;
+  dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>(splits), static_cast<unsigned>(rp / 16));
+  lora_grad_partial_kernel<<<grid, 128, 0, st>>>(X, H, part, static_cast<int>(M), static_cast<int>(C), rp, rows_per_split);
+  MCB_CHECK_LAUNCH("lora_grad_partial");
+  const int64_t n = C * r;
+  lora_grad_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(part, out, splits, static_cast<int>(C), r,
+                                                                                   rp, transposed, accumulate);
+  MCB_CHECK_LAUNCH("lora_grad_reduce");
+  return MCB_OK;
+}
+
+struct Workspace {
+  __nv_bfloat16 *P, *Q, *H1, *H2;
+  float* part;
+  size_t total;
+};
+Workspace carve(void* ws, int64_t M, int64_t K, int64_t N, int64_t r) {
+  const int64_t rp = rank_padded(r);
+  const int64_t big = K > N ? K : N;
+  Workspace w;
+  size_t off = 0;
+  uint8_t* b = static_cast<uint8_t*>(ws);
+  auto take = [&](size_t bytes) { uint8_t* q = b ? b + off : nullptr; off += align_up(bytes, 1024); return q; };
+  w.P = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(rp) * big * 2));
+  w.Q = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(rp) * big * 2));
+  w.H1 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(M) * rp * 2));
+  w.H2 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(M) * rp * 2));
+  const size_t sk = static_cast<size_t>(grad_splits(M, K, 256)) * K;
+  const size_t sn = static_cast<size_t>(grad_splits(M, N, 256)) * N;
+  w.part = reinterpret_cast<float*>(take((sk > sn ? sk : sn) * rp * sizeof(float)));
+  w.total = off;
+  return w;
+}
+
+int pack(const LoraArgs& a, const Workspace& w, int mode) {
+  const int rp = static_cast<int>(rank_padded(a.r));
+  const int64_t n = static_cast<int64_t>(rp) * (a.K + a.N);
+  pack_lora_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, a.stream>>>(
+      a.A, a.B, w.P, w.Q, static_cast<int>(a.K), static_cast<int>(a.N), static_cast<int>(a.r), rp, mode);
+  MCB_CHECK_LAUNCH("pack_lora");
+  return MCB_OK;
+}
+
+int check_ws(const LoraArgs& a, const char* op) {
+  if (a.r == 0) return MCB_OK;
+  if (a.r > 64) return fail(MCB_ERR_UNSUPPORTED, "%s(bf16): rank %lld > 64", op, (long long)a.r);
+  if (!a.ws || a.ws_bytes < workspace_bytes(a.M, a.K, a.N, a.r))
+    return fail(MCB_ERR_WORKSPACE, "%s(bf16): workspace %zu < %zu bytes", op, a.ws_bytes,
+                workspace_bytes(a.M, a.K, a.N, a.r));
+  if ((reinterpret_cast<uintptr_t>(a.ws) & 1023u) != 0) return fail(MCB_ERR_ALIGN, "%s(bf16): workspace must be 1024-byte aligned", op);
+  return MCB_OK;
+}
+
+}  // namespace
+
+int init_kernels() {
+  cudaError_t e = cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(lora_gemm_kernel)");
+  return MCB_OK;
+}
+
+size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r) {
+  if (r <= 0) return 0;
+  return carve(nullptr, M, K, N, r).total;
+}
+
+int delta_fwd(const LoraArgs& a, const DeviceState* ds) {
+  if (int rc = check_ws(a, "lora_delta_fwd")) return rc;
+  Workspace w = carve(a.ws, a.M, a.K, a.N, a.r);
+  if (int rc = pack(a, w, 0)) return rc;
+  GemmCall c;
+  c.X = static_cast<const __nv_bfloat16*>(a.x);
+  c.P = w.P; c.Q = w.Q;
+  c.Y = static_cast<__nv_bfloat16*>(a.y);
+  c.M = a.M; c.N = a.N; c.K = a.K;
+  c.rp = static_cast<int>(rank_padded(a.r));
+  c.scale = a.scale;
+  return launch_gemm(c, ds, a.stream);
+}
+
+int linear_fwd(const LoraArgs& a, const DeviceState* ds) {
+  if (a.w_layout != MCB_W_OUT_IN)
+    return fail(MCB_ERR_UNSUPPORTED, "lora_linear_fwd(bf16) needs W as [out,in] (MCB_W_OUT_IN); transpose it once with mcb_transpose_2d");
+  if (int rc = check_ws(a, "lora_linear_fwd")) return rc;
+  GemmCall c;
+  c.X = static_cast<const __nv_bfloat16*>(a.x);
+  c.W = static_cast<const __nv_bfloat16*>(a.W);
+  c.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  c.Y = static_cast<__nv_bfloat16*>(a.y);
+  c.M = a.M; c.N = a.N; c.K = a.K;
+  if (a.r > 0) {
+    Workspace w = carve(a.ws, a.M, a.K, a.N, a.r);
+    if (int rc = pack(a, w, 0)) return rc;
+    c.P = w.P; c.Q = w.Q;
+    c.H = static_cast<__nv_bfloat16*>(a.h_save);
+    c.rp = static_cast<int>(rank_padded(a.r));
+    c.scale = a.scale;
+  }
+  return launch_gemm(c, ds, a.stream);
+}
+
+int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
+  if (a.dx != nullptr && a.w_layout != MCB_W_IN_OUT)
+    return fail(MCB_ERR_UNSUPPORTED, "lora_linear_bwd(bf16) needs W as [in,out] (MCB_W_IN_OUT); transpose it once with mcb_transpose_2d");
+  if (int rc = check_ws(a, "lora_linear_bwd")) return rc;
+  const int rp = static_cast<int>(rank_padded(a.r));
+  const bool want_grads = a.r > 0 && (a.dA != nullptr || a.dB != nullptr);
+  Workspace w;
+  memset(&w, 0, sizeof(w));
+  if (a.r > 0) {
+    w = carve(a.ws, a.M, a.K, a.N, a.r);
+    if (int rc = pack(a, w, 1)) return rc;
+  }
+  if (a.dx != nullptr || want_grads) {
+    // dx = dy W + (scale dy B^T) A^T ; the rank intermediate scale*dy*B^T lands in w.H1 for dA.
+    GemmCall c;
+    c.X = static_cast<const __nv_bfloat16*>(a.dy);
+    c.W = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.W) : nullptr;
+    c.Y = static_cast<__nv_bfloat16*>(a.dx);
+    c.M = a.M; c.N = a.K; c.K = a.N;
+    if (a.r > 0) {
+      c.P = w.P; c.Q = w.Q;
+      c.H = (a.dA != nullptr) ? w.H1 : nullptr;
+      c.rp = rp;
+      c.scale = a.scale;
+    }
+    if (c.W != nullptr || c.rp > 0) {
+      if (int rc = launch_gemm(c, ds, a.stream)) return rc;
+    }
+  }
+  if (!want_grads) return MCB_OK;
+  if (a.dA != nullptr) {
+    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.x), w.H1, a.dA, w.part, a.M, a.K, static_cast<int>(a.r), rp,
+                             0, a.accumulate, ds, a.stream))
+      return rc;
+  }
+  if (a.dB != nullptr) {
+    const __nv_bfloat16* hs = static_cast<const __nv_bfloat16*>(a.h_save);
+    if (hs == nullptr) {
+      // recompute scale * x A with the forward operands
+      LoraArgs f = a;
+      Workspace wf = w;
+      // P/Q of the backward are still needed by nothing after the GEMM above, so they can be repacked
+      if (int rc = pack(f, wf, 0)) return rc;
+      GemmCall c;
+      c.X = static_cast<const __nv_bfloat16*>(a.x);
+      c.P = wf.P; c.Q = wf.Q;
+      c.H = w.H2;
+      c.M = a.M; c.N = a.N; c.K = a.K;
+      c.rp = rp;
+      c.scale = a.scale;
+      if (int rc = launch_gemm(c, ds, a.stream)) return rc;
+      hs = w.H2;
+    }
+    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.dy), hs, a.dB, w.part, a.M, a.N, static_cast<int>(a.r), rp,
+                             1, a.accumulate, ds, a.stream))
+      return rc;
+  }
+  return MCB_OK;
+}
+
+}  // namespace bf16path
+
+int init_gemm_kernels() { return bf16path::init_kernels(); }
+
+}  // namespace mcb
