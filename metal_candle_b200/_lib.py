@@ -1,0 +1,90 @@
+"""ctypes binding of libmetal_candle_b200.so (the C ABI declared in include/mcb200.h).
+
+There is no fallback: if the library is missing, or it cannot bind a Blackwell GPU, every op raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmetal_candle_b200.so"
+
+MCB_F32, MCB_BF16 = 0, 1
+MCB_W_OUT_IN, MCB_W_IN_OUT = 0, 1
+
+
+class McbError(RuntimeError):
+    """A non-zero status from the C ABI; `.code` is the status, the message is mcb_last_error()."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[mcb status {code}] {msg}")
+        self.code = code
+
+
+class AdamWTensor(C.Structure):
+    _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("n", C.c_int64), ("t", C.c_int32), ("pad_", C.c_int32)]
+
+
+_vp, _i64, _i32, _f32, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); every symbol include/mcb200.h declares
+SIGNATURES = {
+    "mcb_init": (_i32, [_i32]),
+    "mcb_last_error": (C.c_char_p, []),
+    "mcb_version": (_i32, []),
+    "mcb_device_status": (_i32, [C.POINTER(C.c_int)]),
+    "mcb_lora_delta_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
+    "mcb_lora_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i32]),
+    "mcb_lora_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32,
+                                   _vp, _sz, _vp]),
+    "mcb_lora_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _f32,
+                                   _i32, _i32, _vp, _sz, _vp]),
+    "mcb_lora_rank_padded": (_i64, [_i64]),
+    "mcb_transpose_2d": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
+    "mcb_rmsnorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
+    "mcb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
+    "mcb_rmsnorm_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
+    "mcb_softmax_fwd": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
+    "mcb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "mcb_adamw_multi": (_i32, [C.POINTER(AdamWTensor), _i32, _f32, _f32, _f32, _f32, _f32, _f32, _vp]),
+}
+
+_lib = None
+_inited = set()
+
+
+def load() -> C.CDLL:
+    """Loads the shared library and declares the prototypes.  Needs no GPU."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise McbError(-100, f"{LIB_PATH} is not built; run `python -m metal_candle_b200.build` "
+                                 "(there is no CPU or PyTorch fallback)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise McbError(rc, load().mcb_last_error().decode("utf-8", "replace"))
+
+
+def init(device: int = 0) -> C.CDLL:
+    """Binds the library to a CUDA device (idempotent) and returns it."""
+    lib = load()
+    if device not in _inited:
+        check(lib.mcb_init(device))
+        _inited.add(device)
+    return lib
+
+
+def device_status() -> int:
+    out = C.c_int(0)
+    check(load().mcb_device_status(C.byref(out)))
+    return out.value

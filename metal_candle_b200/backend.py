@@ -1,0 +1,284 @@
+"""Custom-op entry points: the host-side mirror of the reference's `src/backend` for this path.
+
+Names follow the reference: the `CustomMetalOps` trait's three methods become the functions
+`lora_forward_fused`, `softmax_fused`, `rms_norm_fused` (src/backend/metal_ops.rs:33-171), and the op
+structs `FusedLoRAOp`, `FusedRMSNormOp`, `FusedSoftmaxOp` keep their constructors and validation
+(src/backend/custom_ops.rs:73-148,443-470,644-660).  Each call allocates its output through torch
+(the reference's ops allocate theirs through the device allocator, custom_ops.rs:395-397), enqueues
+the CUDA kernel on torch's current stream through the C ABI, and does not synchronise.
+
+torch is used for device memory and streams only; no arithmetic here runs in torch and nothing falls
+back to it: a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import MCB_BF16, MCB_F32, MCB_W_IN_OUT, MCB_W_OUT_IN, McbError
+
+
+class TrainingError(RuntimeError):
+    """Counterpart of `TrainingError::Failed { reason }` (src/error.rs:95-131)."""
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return MCB_F32
+    if t.dtype == torch.bfloat16:
+        return MCB_BF16
+    raise TrainingError(f"unsupported dtype {t.dtype}: the kernels take float32 or bfloat16")
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise TrainingError("tensor is not on a CUDA device (this library has no CPU path)")
+        if not t.is_contiguous():
+            raise TrainingError("tensor must be contiguous")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _lib_for(t: torch.Tensor):
+    return _lib.init(t.device.index if t.device.index is not None else torch.cuda.current_device())
+
+
+_ws_cache = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-device scratch buffer that only grows (1024-byte aligned, as the bf16 GEMM requires)."""
+    key = (device.type, device.index)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        assert buf.data_ptr() % 1024 == 0
+        _ws_cache[key] = buf
+    return buf
+
+
+# ---------------------------------------------------------------------------------------------
+# LoRA
+# ---------------------------------------------------------------------------------------------
+
+def _lora_shapes(x, lora_a, lora_b):
+    a_dims, b_dims = tuple(lora_a.shape), tuple(lora_b.shape)
+    if len(a_dims) != 2 or len(b_dims) != 2:
+        raise TrainingError(f"LoRA matrices must be 2D, got shapes {list(a_dims)} and {list(b_dims)}")
+    if a_dims[1] != b_dims[0]:
+        raise TrainingError(
+            f"Incompatible LoRA matrix dimensions: {a_dims[0]}×{a_dims[1]} and {b_dims[0]}×{b_dims[1]}")
+    if x.dim() == 0:
+        raise TrainingError("Input must have at least 1 dimension")
+    if x.shape[-1] != a_dims[0]:
+        raise TrainingError(f"Input feature dimension mismatch: expected {a_dims[0]}, got {x.shape[-1]}")
+    K, r = a_dims
+    N = b_dims[1]
+    M = x.numel() // K
+    return M, K, N, r
+
+
+class FusedLoRAOp:
+    """`out = scaling * (x @ A) @ B` in one kernel launch sequence; FusedLoRAOp::new's checks
+    (src/backend/custom_ops.rs:118-148)."""
+
+    def __init__(self, lora_a: torch.Tensor, lora_b: torch.Tensor, scaling: float):
+        a_dims, b_dims = tuple(lora_a.shape), tuple(lora_b.shape)
+        if len(a_dims) != 2 or len(b_dims) != 2:
+            raise TrainingError(f"LoRA matrices must be 2D, got shapes {list(a_dims)} and {list(b_dims)}")
+        if a_dims[1] != b_dims[0]:
+            raise TrainingError(
+                f"Incompatible LoRA matrix dimensions: {a_dims[0]}×{a_dims[1]} and {b_dims[0]}×{b_dims[1]}")
+        self.lora_a, self.lora_b, self.scaling = lora_a, lora_b, float(scaling)
+
+    def name(self) -> str:
+        return "fused-lora"
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return lora_forward_fused(x, self.lora_a, self.lora_b, self.scaling)
+
+
+def lora_forward_fused(x: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor, scaling: float) -> torch.Tensor:
+    """CustomMetalOps::lora_forward_fused (src/backend/metal_ops.rs:126-144).  A, B are float32."""
+    M, K, N, r = _lora_shapes(x, lora_a, lora_b)
+    _require_cuda(x, lora_a, lora_b)
+    if lora_a.dtype != torch.float32 or lora_b.dtype != torch.float32:
+        raise TrainingError("LoRA matrices must be float32")
+    lib = _lib_for(x)
+    dt = _dtype_code(x)
+    out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+    nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
+    ws = workspace(x.device, nws)
+    try:
+        _lib.check(lib.mcb_lora_delta_fwd(_ptr(x), _ptr(lora_a), _ptr(lora_b), _ptr(out), M, K, N, r, float(scaling),
+                                          dt, _ptr(ws), ws.numel(), _stream()))
+    except McbError as e:
+        raise TrainingError(f"Failed to apply fused LoRA op: {e}") from e
+    return out
+
+
+def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=True):
+    """`y = x W^T (+b) + scaling (x A) B` with W [out, in].  Returns (y, h_save or None)."""
+    K = x.shape[-1]
+    N = weight.shape[0]
+    if weight.dim() != 2 or weight.shape[1] != K:
+        raise TrainingError(f"weight must be [out, in={K}], got {list(weight.shape)}")
+    r = 0 if lora_a is None else lora_a.shape[1]
+    if r:
+        _lora_shapes(x, lora_a, lora_b)
+        if lora_b.shape[1] != N:
+            raise TrainingError(f"LoRA B must be [r, out={N}], got {list(lora_b.shape)}")
+    _require_cuda(x, weight, bias, lora_a, lora_b)
+    M = x.numel() // K
+    lib = _lib_for(x)
+    dt = _dtype_code(x)
+    y = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+    h = None
+    if r and save_hidden:
+        h = torch.empty(M, lib.mcb_lora_rank_padded(r), dtype=x.dtype, device=x.device)
+    nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
+    ws = workspace(x.device, nws)
+    _lib.check(lib.mcb_lora_linear_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(lora_a), _ptr(lora_b), _ptr(y), _ptr(h),
+                                       M, K, N, r, float(scaling), dt, MCB_W_OUT_IN, _ptr(ws), ws.numel(), _stream()))
+    return y, h
+
+
+def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, need_dx=True, grad_a=None,
+                         grad_b=None, accumulate=False, weight_layout=MCB_W_IN_OUT):
+    """Reverse of `lora_linear_forward`.  `weight_t` is the [in, out] copy of the frozen weight (for
+    float32 either layout works, say which with `weight_layout`).  Returns (dx, dA, dB)."""
+    K = x.shape[-1]
+    N = dy.shape[-1]
+    r = 0 if lora_a is None else lora_a.shape[1]
+    _require_cuda(x, weight_t, lora_a, lora_b, dy, h_save, grad_a, grad_b)
+    M = x.numel() // K
+    lib = _lib_for(x)
+    dt = _dtype_code(x)
+    dx = torch.empty_like(x) if need_dx else None
+    if r and grad_a is None:
+        grad_a = torch.empty(K, r, dtype=torch.float32, device=x.device)
+        grad_b = torch.empty(r, N, dtype=torch.float32, device=x.device)
+        accumulate = False
+    nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
+    ws = workspace(x.device, nws)
+    _lib.check(lib.mcb_lora_linear_bwd(_ptr(x), _ptr(weight_t), _ptr(lora_a), _ptr(lora_b), _ptr(dy), _ptr(h_save),
+                                       _ptr(dx), _ptr(grad_a), _ptr(grad_b), int(bool(accumulate)), M, K, N, r,
+                                       float(scaling), dt, weight_layout, _ptr(ws), ws.numel(), _stream()))
+    return dx, grad_a, grad_b
+
+
+def transpose_2d(src: torch.Tensor) -> torch.Tensor:
+    _require_cuda(src)
+    if src.dim() != 2:
+        raise TrainingError("transpose_2d takes a matrix")
+    lib = _lib_for(src)
+    dst = torch.empty(src.shape[1], src.shape[0], dtype=src.dtype, device=src.device)
+    _lib.check(lib.mcb_transpose_2d(_ptr(src), _ptr(dst), src.shape[0], src.shape[1], _dtype_code(src), _stream()))
+    return dst
+
+
+# ---------------------------------------------------------------------------------------------
+# RMSNorm
+# ---------------------------------------------------------------------------------------------
+
+class FusedRMSNormOp:
+    """FusedRMSNormOp::new (src/backend/custom_ops.rs:443-470): `x / sqrt(mean(x^2) + eps)`."""
+
+    def __init__(self, eps: float):
+        self.eps = float(eps)
+
+    def name(self) -> str:
+        return "fused-rms-norm"
+
+    def __call__(self, x):
+        return rms_norm_fused(x, self.eps)
+
+
+def _rows(x: torch.Tensor, what: str):
+    if x.dim() == 0:
+        raise TrainingError(f"Input tensor for {what} must have at least 1 dimension, got []")
+    D = x.shape[-1]
+    if D == 0 or x.numel() == 0:
+        raise TrainingError(f"{what}: empty tensor")
+    return x.numel() // D, D
+
+
+def rms_norm_fused(x: torch.Tensor, eps: float, weight: torch.Tensor | None = None, return_rstd: bool = False):
+    """CustomMetalOps::rms_norm_fused (src/backend/metal_ops.rs:160-170).  The reference's op accepts
+    1-3-D input (src/backend/custom_ops.rs:550-558); any rank is accepted here, rows = product of the
+    leading dims.  `weight` folds in the model layer's multiply (src/models/qwen.rs:314-325)."""
+    rows, D = _rows(x, "FusedRMSNormOp")
+    _require_cuda(x, weight)
+    if weight is not None and (weight.shape != (D,) or weight.dtype != x.dtype):
+        raise TrainingError(f"RMSNorm weight must be [{D}] of {x.dtype}")
+    lib = _lib_for(x)
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if return_rstd else None
+    try:
+        _lib.check(lib.mcb_rmsnorm_fwd(_ptr(x), _ptr(weight), _ptr(y), _ptr(rstd), rows, D, float(eps), _dtype_code(x),
+                                       _stream()))
+    except McbError as e:
+        raise TrainingError(f"Fused RMS Norm kernel execution failed: {e}") from e
+    return (y, rstd) if return_rstd else y
+
+
+def rms_norm_backward(x, weight, dy, eps, need_dw=True, grad_w=None, accumulate=False):
+    rows, D = _rows(x, "rms_norm_backward")
+    _require_cuda(x, weight, dy, grad_w)
+    lib = _lib_for(x)
+    dx = torch.empty_like(x)
+    if need_dw and grad_w is None:
+        grad_w = torch.empty(D, dtype=torch.float32, device=x.device)
+        accumulate = False
+    nws = lib.mcb_rmsnorm_bwd_workspace_bytes(rows, D) if need_dw else 0
+    ws = workspace(x.device, nws)
+    _lib.check(lib.mcb_rmsnorm_bwd(_ptr(x), _ptr(weight), _ptr(dy), _ptr(dx), _ptr(grad_w) if need_dw else None,
+                                   int(bool(accumulate)), rows, D, float(eps), _dtype_code(x), _ptr(ws), ws.numel(),
+                                   _stream()))
+    return dx, (grad_w if need_dw else None)
+
+
+# ---------------------------------------------------------------------------------------------
+# softmax
+# ---------------------------------------------------------------------------------------------
+
+class FusedSoftmaxOp:
+    """FusedSoftmaxOp::new (src/backend/custom_ops.rs:644-660): softmax over the last dimension."""
+
+    def name(self) -> str:
+        return "fused-softmax"
+
+    def __call__(self, x):
+        return softmax_fused(x)
+
+
+def softmax_fused(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """CustomMetalOps::softmax_fused (src/backend/metal_ops.rs:146-158).  Any rank (the reference's op
+    stops at 3-D, src/backend/custom_ops.rs:743-751, which makes the model's 4-D scores fall back)."""
+    rows, D = _rows(x, "FusedSoftmaxOp")
+    _require_cuda(x, out)
+    lib = _lib_for(x)
+    y = torch.empty_like(x) if out is None else out
+    try:
+        _lib.check(lib.mcb_softmax_fwd(_ptr(x), _ptr(y), rows, D, _dtype_code(x), _stream()))
+    except McbError as e:
+        raise TrainingError(f"Fused Softmax kernel execution failed: {e}") from e
+    return y
+
+
+def softmax_backward(y: torch.Tensor, dy: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    rows, D = _rows(y, "softmax_backward")
+    _require_cuda(y, dy, out)
+    lib = _lib_for(y)
+    dx = torch.empty_like(y) if out is None else out
+    _lib.check(lib.mcb_softmax_bwd(_ptr(y), _ptr(dy), _ptr(dx), rows, D, _dtype_code(y), _stream()))
+    return dx

@@ -25,6 +25,7 @@
 // the device status word, raises a CTA-wide abort flag, and all roles fall through to the common
 // exit where tensor memory is released.  No loads use cluster multicast.
 #include <cuda.h>
+#include <string.h>
 
 #include "lora_internal.cuh"
 

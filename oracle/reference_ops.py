@@ -248,10 +248,12 @@ def adamw_step(p, g, m, v, t, lr, beta1, beta2, eps, weight_decay, dtype=np.floa
     one_m_b2 = dtype(np.float32(1.0) - b2)
     m_new = m * dtype(b1) + g * one_m_b1
     v_new = v * dtype(b2) + (g * g) * one_m_b2
-    bc1 = dtype(np.float32(1.0) - powi_f32(b1, t))
-    bc2 = dtype(np.float32(1.0) - powi_f32(b2, t))
-    m_hat = m_new / bc1
-    v_hat = v_new / bc2
+    # candle evaluates `tensor / f64` as an affine by the reciprocal (third-party candle-core 0.9,
+    # not in the reference tree), so the bias corrections are multiplications by 1/(1-b^t).
+    inv_bc1 = dtype(1.0 / np.float64(np.float32(1.0) - powi_f32(b1, t)))
+    inv_bc2 = dtype(1.0 / np.float64(np.float32(1.0) - powi_f32(b2, t)))
+    m_hat = m_new * inv_bc1
+    v_hat = v_new * inv_bc2
     update = m_hat / (np.sqrt(v_hat) + dtype(np.float32(eps)))
     lr_update = update * dtype(np.float32(lr))
     wd_update = p * dtype(np.float32(weight_decay) * np.float32(lr))

@@ -1,0 +1,180 @@
+"""GPU parity of the fused LoRA linear (forward, backward) against the CPU oracle, through the C ABI.
+
+float32 validation path: max|gpu - oracle| / max|oracle| <= 1e-4 against the float64 oracle.
+bfloat16 production path: <= 2e-2 against the float64 oracle evaluated on the bf16-rounded inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import reference_ops as R
+from oracle import seeded as S
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+
+
+def dev_t(a, dtype, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev).to(dtype).contiguous()
+
+
+def back(t):
+    return t.detach().float().cpu().numpy()
+
+
+def rounded(c, dtype):
+    """Activations and the frozen weight live in `dtype`; A and B stay float32 masters, but the bf16 path
+    rounds them to bf16 when packing its operands, so the oracle sees the same values."""
+    if dtype == torch.float32:
+        return dict(c)
+    return {k: S.bf16_round(v) for k, v in c.items()}
+
+
+def run_case(dev, dtype, M, K, N, r, seed=11, with_bias=True, save_h=True):
+    from metal_candle_b200 import backend as B
+
+    scale = 2.0
+    c = S.lora_linear_case(seed, M, K, N, r)
+    c["bias"] = S.normal(seed, "bias", (N,), 0.0, 0.1)
+    o = rounded(c, dtype)
+    x, W, dy = dev_t(o["x"], dtype, dev), dev_t(o["W"], dtype, dev), dev_t(o["dy"], dtype, dev)
+    bias = dev_t(o["bias"], dtype, dev) if with_bias else None
+    A, Bm = dev_t(c["A"], torch.float32, dev), dev_t(c["B"], torch.float32, dev)
+    tol = TOL[dtype]
+
+    # forward
+    y, h = B.lora_linear_forward(x, W, bias, A, Bm, scale, save_hidden=save_h)
+    want_y, want_h = R.lora_linear_forward(o["x"], o["W"], o["bias"] if with_bias else None, o["A"], o["B"], scale)
+    assert R.max_abs_normalised(back(y), want_y) <= tol, "y"
+    if save_h:
+        assert R.max_abs_normalised(back(h)[:, :r], scale * want_h) <= tol, "h_save"
+
+    # delta only (the reference's FusedLoRAOp)
+    d = B.lora_forward_fused(x, A, Bm, scale)
+    want_d, _ = R.lora_forward(o["x"], o["A"], o["B"], scale)
+    assert R.max_abs_normalised(back(d), want_d) <= tol, "delta"
+
+    # backward
+    Wt = B.transpose_2d(W)
+    dx, dA, dB = B.lora_linear_backward(x, Wt, A, Bm, scale, dy, h_save=h)
+    wdx, wdA, wdB = R.lora_linear_backward(o["x"], o["W"], o["A"], o["B"], scale, o["dy"])
+    assert R.max_abs_normalised(back(dx), wdx) <= tol, "dx"
+    assert R.max_abs_normalised(back(dA), wdA) <= tol, "dA"
+    assert R.max_abs_normalised(back(dB), wdB) <= tol, "dB"
+    from metal_candle_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+# BASELINE config 1 (M = 4*128, 768 -> 768, r = 8) first, then Qwen2.5-0.5B projection shapes, ragged
+# sizes (M, N, K not multiples of the tiles), and the rank range of tests/custom_ops_correctness.rs.
+CASES = [
+    (512, 768, 768, 8),
+    (256, 896, 896, 8),
+    (256, 896, 128, 8),
+    (384, 896, 896, 16),
+    (128, 512, 512, 4),
+    (200, 264, 200, 8),
+    (130, 64, 72, 16),
+    (1000, 1024, 2048, 32),
+    (300, 896, 4864, 8),
+    (257, 2048, 896, 64),
+]
+
+
+@pytest.mark.parametrize("M,K,N,r", CASES)
+def test_lora_linear_f32(cuda_device, M, K, N, r):
+    run_case(cuda_device, torch.float32, M, K, N, r)
+
+
+@pytest.mark.parametrize("M,K,N,r", CASES)
+def test_lora_linear_bf16(cuda_device, M, K, N, r):
+    run_case(cuda_device, torch.bfloat16, M, K, N, r)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_lora_variants(cuda_device, dtype):
+    run_case(cuda_device, dtype, 256, 512, 512, 8, with_bias=False, save_h=False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_plain_linear_rank0(cuda_device, dtype):
+    """r = 0: the frozen projection alone (k_proj, o_proj, MLP, lm_head in the training step)."""
+    from metal_candle_b200 import backend as B
+
+    M, K, N = 300, 896, 1000 if dtype == torch.float32 else 1024
+    c = rounded(S.lora_linear_case(5, M, K, N, 1), dtype)
+    x, W, dy = (dev_t(c[k], dtype, cuda_device) for k in ("x", "W", "dy"))
+    y, h = B.lora_linear_forward(x, W, None, None, None, 1.0)
+    assert h is None
+    assert R.max_abs_normalised(back(y), R.linear(c["x"], c["W"])) <= TOL[dtype]
+    dx, dA, dB = B.lora_linear_backward(x, B.transpose_2d(W), None, None, 1.0, dy)
+    assert dA is None and dB is None
+    assert R.max_abs_normalised(back(dx), c["dy"].astype(np.float64) @ c["W"].astype(np.float64)) <= TOL[dtype]
+
+
+def test_lora_reference_fixed_inputs(cuda_device):
+    """The fixed inputs of tests/executor_direct.rs:339-376: x [[1..4],[5..8]], A 4x2, B 2x4, scale 0.5."""
+    from metal_candle_b200 import backend as B
+
+    x = torch.tensor([[1.0, 2, 3, 4], [5, 6, 7, 8]], device=cuda_device)
+    A = torch.tensor([[0.1, 0.2], [0.3, 0.4], [0.5, 0.6], [0.7, 0.8]], device=cuda_device)
+    Bm = torch.tensor([[1.0, 2, 3, 4], [5, 6, 7, 8]], device=cuda_device)
+    out = back(B.lora_forward_fused(x, A, Bm, 0.5))
+    want = 0.5 * (back(x) @ back(A)) @ back(Bm)
+    assert out.shape == (2, 4) and np.abs(out).min() > 0
+    assert np.allclose(out, want, rtol=1e-5)
+    assert np.allclose(out, R.lora_forward_msl(back(x), back(A), back(Bm), 0.5), rtol=1e-5)
+
+
+def test_lora_batched_shapes_and_zero_b(cuda_device):
+    """[2,64,512] r=8 as in tests/custom_ops_correctness.rs:16-85 (max-abs < 1e-4), 1-D and 2-D inputs
+    (custom_ops.rs:254-270), and B = 0 (the initial state, src/training/lora.rs:244) gives exactly 0."""
+    from metal_candle_b200 import backend as B
+    from metal_candle_b200.training import LoRAConfig, LoRALayer
+
+    g = torch.Generator(device=cuda_device).manual_seed(1)
+    layer = LoRALayer(512, 512, LoRAConfig(), cuda_device, generator=g)
+    x = torch.randn(2, 64, 512, device=cuda_device, generator=g)
+    assert layer.forward(x).shape == (2, 64, 512)
+    assert float(layer.forward(x).abs().max()) == 0.0
+    layer.lora_b.normal_(0, 0.02, generator=g)
+    got = back(layer.forward(x))
+    want, _ = R.lora_forward(back(x), back(layer.lora_a), back(layer.lora_b), 2.0)
+    assert np.abs(got - want).max() < 1e-4
+    assert layer.forward(x[0]).shape == (64, 512)
+    assert layer.forward(x[0, 0]).shape == (512,)
+    assert np.abs(back(layer.forward(x[0, 0])) - want[0, 0]).max() < 1e-4
+
+
+def test_lora_gradient_accumulation(cuda_device):
+    from metal_candle_b200 import backend as B
+
+    c = S.lora_linear_case(9, 256, 512, 384, 8)
+    for dtype in (torch.float32, torch.bfloat16):
+        x, W, dy = (dev_t(c[k], dtype, cuda_device) for k in ("x", "W", "dy"))
+        A, Bm = dev_t(c["A"], torch.float32, cuda_device), dev_t(c["B"], torch.float32, cuda_device)
+        Wt = B.transpose_2d(W)
+        _, dA, dB = B.lora_linear_backward(x, Wt, A, Bm, 2.0, dy)
+        ga, gb = dA.clone(), dB.clone()
+        B.lora_linear_backward(x, Wt, A, Bm, 2.0, dy, grad_a=ga, grad_b=gb, accumulate=True)
+        assert torch.allclose(ga, 2 * dA, rtol=1e-5, atol=1e-6) and torch.allclose(gb, 2 * dB, rtol=1e-5, atol=1e-6)
+
+
+def test_lora_rejects_bad_arguments(cuda_device):
+    from metal_candle_b200 import backend as B
+
+    dev = cuda_device
+    x = torch.zeros(4, 16, device=dev)
+    with pytest.raises(B.TrainingError, match="LoRA matrices must be 2D"):
+        B.lora_forward_fused(x, torch.zeros(16, device=dev), torch.zeros(2, 8, device=dev), 1.0)
+    with pytest.raises(B.TrainingError, match="Incompatible LoRA matrix dimensions"):
+        B.lora_forward_fused(x, torch.zeros(16, 2, device=dev), torch.zeros(3, 8, device=dev), 1.0)
+    with pytest.raises(B.TrainingError, match="Input feature dimension mismatch: expected 8, got 16"):
+        B.lora_forward_fused(x, torch.zeros(8, 2, device=dev), torch.zeros(2, 8, device=dev), 1.0)
+    with pytest.raises(B.TrainingError):
+        B.lora_forward_fused(x.cpu(), torch.zeros(16, 2), torch.zeros(2, 8), 1.0)
+    # bf16 path: feature counts must be multiples of 8 (TMA row pitch)
+    xb = torch.zeros(4, 20, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(B.TrainingError):
+        B.lora_forward_fused(xb, torch.zeros(20, 2, device=dev), torch.zeros(2, 8, device=dev), 1.0)
