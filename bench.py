@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Benchmarks of the B200 LoRA hot path.
+
+Headline (the line the driver reads):
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+        one LoRA training step (forward + backward + AdamW) on the Qwen2.5-0.5B-shaped decoder,
+        batch-data-parallel over N GPUs; prints ONE JSON line (tokens/s).
+
+Kernel micro-benchmarks (one JSON line per case; used for the roofline sweeps and for ncu captures):
+    python bench.py --micro lora    --M 32768 --K 896 --N 896 --r 16 [--dtype bf16|f32] [--pass fwd|bwd|both]
+    python bench.py --micro rmsnorm --rows 114688 --D 896  [--dtype bf16|f32]
+    python bench.py --micro softmax --rows 114688 --D 1024 [--dtype bf16|f32]
+    python bench.py --micro adamw   --n 67108864
+    python bench.py --sweep c2 | c3          the BASELINE row-kernel / LoRA-GEMM sweeps
+
+All inputs are synthetic (seeded torch generators on the device; shapes and value distributions of the
+benchmark configurations).  Kernel timings use CUDA events on the launching stream and rotate through
+enough input copies that the working set exceeds twice the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # under load = samples in the upper half of what was seen
+        busy = [s for s in sm if s >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _time_kernel(torch, fn, n_variants, iters, warmup):
+    """fn(i) launches the kernel on input set i % n_variants.  Returns (median_ms, min_ms)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for i, (a, b) in enumerate(evs):
+        a.record()
+        fn(warmup + i)
+        b.record()
+    torch.cuda.synchronize()
+    ts = [a.elapsed_time(b) for a, b in evs]
+    return statistics.median(ts), min(ts)
+
+
+def _variants(bytes_per_set: int) -> int:
+    return max(2, min(64, math.ceil(2.2 * L2_BYTES / max(1, bytes_per_set))))
+
+
+def micro_lora(torch, M, K, N, r, dtype, which, iters=20, warmup=5):
+    from metal_candle_b200 import backend as B
+
+    dev = torch.device("cuda", 0)
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    e = 2 if dtype == "bf16" else 4
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    nv = _variants((M * K + M * N) * e)
+    nv = min(nv, max(2, int(40e9 // max(1, (2 * M * K + 2 * M * N) * e))))
+    xs = [torch.randn(M, K, device=dev, generator=g).to(dt) for _ in range(nv)]
+    dys = [torch.randn(M, N, device=dev, generator=g).to(dt) for _ in range(nv)]
+    W = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).to(dt)
+    Wt = B.transpose_2d(W)
+    s = 1.0 / math.sqrt(K)
+    A = ((torch.rand(K, max(r, 1), device=dev, generator=g) * 2 - 1) * s) if r else None
+    Bm = (torch.randn(max(r, 1), N, device=dev, generator=g) * 0.02) if r else None
+    scale = 2.0
+    hs = [None] * nv
+    for i in range(nv):
+        _, hs[i] = B.lora_linear_forward(xs[i], W, None, A, Bm, scale)
+    dA = torch.zeros(K, r, device=dev) if r else None
+    dB = torch.zeros(r, N, device=dev) if r else None
+
+    def fwd(i):
+        B.lora_linear_forward(xs[i % nv], W, None, A, Bm, scale)
+
+    def bwd(i):
+        B.lora_linear_backward(xs[i % nv], Wt, A, Bm, scale, dys[i % nv], h_save=hs[i % nv], grad_a=dA, grad_b=dB)
+
+    def both(i):
+        fwd(i)
+        bwd(i)
+
+    fl_f = 2 * M * K * N + 2 * M * r * (K + N)
+    fl_b = 2 * M * K * N + 4 * M * r * (K + N)
+    by_f = e * (M * K + K * N + M * N) + e * r * (K + N)
+    by_b = e * (M * N + K * N + 2 * M * K) + 6 * r * (K + N)
+    fn, fl, by = {"fwd": (fwd, fl_f, by_f), "bwd": (bwd, fl_b, by_b), "both": (both, fl_f + fl_b, by_f + by_b)}[which]
+    med, mn = _time_kernel(torch, fn, nv, iters, warmup)
+    pk = measured_peaks()
+    tf = fl / med / 1e9
+    gbs = by / med / 1e6
+    ridge = pk["bf16_tflops"] * 1e3 / pk["hbm_gbs"]
+    bound = "tensor" if (dtype == "bf16" and fl / by >= ridge) else "hbm"
+    roof = ({"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+             "frac": tf / pk["bf16_tflops"]} if bound == "tensor" else
+            {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"]})
+    roof["traffic"] = None
+    roof["peak_source"] = pk["source"]
+    return {"metric": f"fused LoRA linear {which}", "value": tf, "unit": "TFLOP/s", "ms": med, "ms_min": mn,
+            "dtype": dtype, "config": {"workload": "lora_linear", "M": M, "K": K, "N": N, "r": r, "pass": which,
+                                       "input_sets": nv, "l2": "inputs rotated through >2x L2"},
+            "flop_per_byte": fl / by, "roofline": roof}
+
+
+def micro_rows(torch, op, rows, D, dtype, iters=20, warmup=5):
+    from metal_candle_b200 import backend as B
+
+    dev = torch.device("cuda", 0)
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    e = 2 if dtype == "bf16" else 4
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    nv = _variants(3 * rows * D * e)
+    nv = min(nv, max(2, int(30e9 // (4 * rows * D * e))))
+    out = []
+    if op == "rmsnorm":
+        xs = [torch.randn(rows, D, device=dev, generator=g).to(dt) for _ in range(nv)]
+        dys = [torch.randn(rows, D, device=dev, generator=g).to(dt) for _ in range(nv)]
+        w = (1 + 0.1 * torch.randn(D, device=dev, generator=g)).to(dt)
+        ybuf = torch.empty_like(xs[0])
+        dw = torch.empty(D, device=dev)
+        lib = B._lib_for(xs[0])
+        ws = B.workspace(dev, lib.mcb_rmsnorm_bwd_workspace_bytes(rows, D))
+        code = B._dtype_code(xs[0])
+        st = torch.cuda.current_stream().cuda_stream
+
+        def fwd(i):
+            lib.mcb_rmsnorm_fwd(xs[i % nv].data_ptr(), w.data_ptr(), ybuf.data_ptr(), None, rows, D, 1e-6, code, st)
+
+        def bwd(i):
+            lib.mcb_rmsnorm_bwd(xs[i % nv].data_ptr(), w.data_ptr(), dys[i % nv].data_ptr(), ybuf.data_ptr(),
+                                dw.data_ptr(), 0, rows, D, 1e-6, code, ws.data_ptr(), ws.numel(), st)
+
+        cases = [("rmsnorm fwd", fwd, 2 * rows * D * e + D * e), ("rmsnorm bwd", bwd, 3 * rows * D * e + D * e + 4 * D)]
+    else:
+        S = D
+        xs = []
+        for _ in range(nv):
+            x = (3.0 * torch.randn(rows, D, device=dev, generator=g))
+            if rows % S == 0:  # attention-score blocks: causal mask, -inf strictly above each diagonal
+                mask = torch.triu(torch.ones(S, S, device=dev, dtype=torch.bool), 1)
+                x.view(-1, S, S).masked_fill_(mask, float("-inf"))
+            xs.append(x.to(dt))
+        dys = [torch.randn(rows, D, device=dev, generator=g).to(dt) for _ in range(nv)]
+        ys = [B.softmax_fused(x) for x in xs]
+        buf = torch.empty_like(xs[0])
+
+        def fwd(i):
+            B.softmax_fused(xs[i % nv], out=buf)
+
+        def bwd(i):
+            B.softmax_backward(ys[i % nv], dys[i % nv], out=buf)
+
+        cases = [("softmax fwd", fwd, 2 * rows * D * e), ("softmax bwd", bwd, 3 * rows * D * e)]
+    pk = measured_peaks()
+    for name, fn, by in cases:
+        med, mn = _time_kernel(torch, fn, nv, iters, warmup)
+        gbs = by / med / 1e6
+        out.append({"metric": name, "value": gbs, "unit": "GB/s", "ms": med, "ms_min": mn, "dtype": dtype,
+                    "config": {"workload": op, "rows": rows, "D": D, "input_sets": nv,
+                               "l2": "inputs rotated through >2x L2"},
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                 "frac": gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"]}})
+    return out
+
+
+def micro_adamw(torch, n, n_tensors=1, iters=20, warmup=5):
+    from metal_candle_b200.training import AdamW, AdamWConfig
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    per = n // n_tensors
+    ps = [torch.randn(per, device=dev, generator=g) for _ in range(n_tensors)]
+    gs = [0.1 * torch.randn(per, device=dev, generator=g) for _ in range(n_tensors)]
+    opt = AdamW(AdamWConfig())
+
+    def step(i):
+        opt.step_vars(ps, gs)
+
+    med, mn = _time_kernel(torch, step, 1, iters, warmup)
+    by = 28 * per * n_tensors
+    gbs = by / med / 1e6
+    pk = measured_peaks()
+    return {"metric": "AdamW multi-tensor", "value": gbs, "unit": "GB/s", "ms": med, "ms_min": mn, "dtype": "f32",
+            "config": {"workload": "adamw", "elements": per * n_tensors, "tensors": n_tensors,
+                       "l2": "working set 16 B/element" + (" > L2" if 16 * n > L2_BYTES else " (fits L2: latency regime)")},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"]}}
+
+
+C3_SHAPES = [(896, 896), (896, 128), (2048, 2048), (4096, 4096), (4096, 14336)]
+
+
+def run_micro(args):
+    import torch
+
+    from metal_candle_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    _lib.init(0)
+    if args.sweep == "c2":
+        for dtype in ("bf16", "f32"):
+            for D in (896, 2048, 4096):
+                for rows in (4096, 16384, 114688, 262144, 1048576):
+                    if rows * D * (2 if dtype == "bf16" else 4) > 6e9:
+                        continue
+                    for r in micro_rows(torch, "rmsnorm", rows, D, dtype, args.iters, args.warmup_iters):
+                        print(json.dumps(r), flush=True)
+            for r in micro_rows(torch, "softmax", 8 * 14 * 1024, 1024, dtype, args.iters, args.warmup_iters):
+                print(json.dumps(r), flush=True)
+        return
+    if args.sweep == "c3":
+        for (K, N) in C3_SHAPES:
+            for M in (512, 4096, 32768, 131072):
+                for r in (8, 16, 64):
+                    if M * max(K, N) * 2 > 5e9:
+                        continue
+                    print(json.dumps(micro_lora(torch, M, K, N, r, "bf16", "both", args.iters, args.warmup_iters)),
+                          flush=True)
+        return
+    if args.micro == "lora":
+        print(json.dumps(micro_lora(torch, args.M, args.K, args.N, args.r, args.dtype, args.which, args.iters,
+                                    args.warmup_iters)), flush=True)
+    elif args.micro in ("rmsnorm", "softmax"):
+        for r in micro_rows(torch, args.micro, args.rows, args.D, args.dtype, args.iters, args.warmup_iters):
+            print(json.dumps(r), flush=True)
+    elif args.micro == "adamw":
+        print(json.dumps(micro_adamw(torch, args.n, args.tensors, args.iters, args.warmup_iters)), flush=True)
+    else:
+        raise SystemExit(f"unknown --micro {args.micro}")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c5", choices=["c4", "c5"])
+    ap.add_argument("--micro", default=None)
+    ap.add_argument("--sweep", default=None, choices=[None, "c2", "c3"])
+    ap.add_argument("--M", type=int, default=32768)
+    ap.add_argument("--K", type=int, default=896)
+    ap.add_argument("--N", type=int, default=896)
+    ap.add_argument("--r", type=int, default=16)
+    ap.add_argument("--rows", type=int, default=114688)
+    ap.add_argument("--D", type=int, default=1024)
+    ap.add_argument("--n", type=int, default=1 << 26)
+    ap.add_argument("--tensors", type=int, default=1)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup-iters", type=int, default=5)
+    args = ap.parse_args()
+    if args.micro or args.sweep:
+        return run_micro(args)
+    from metal_candle_b200 import step_bench  # the Qwen-shaped training-step benchmark
+
+    return step_bench.main(args)
+
+
+if __name__ == "__main__":
+    main()
