@@ -57,6 +57,13 @@ int mcb_version(void);
  * bounded wait that gave up.  Synchronises the device. */
 int mcb_device_status(int* status_out);
 
+/* Per-kernel timing for roofline reports.  While enabled, every launch of the tensor-core kernels is
+ * bracketed by CUDA events on its own stream and tagged with its algorithmic work; mcb_profile_summary
+ * synchronises the device, sums the finished records of one kind (0 = the fused LoRA GEMM, 1 = the LoRA
+ * weight-gradient kernel) and forgets them.  No counterpart in the reference. */
+int mcb_profile_enable(int on);
+int mcb_profile_summary(int kind, int64_t* launches, double* total_ms, double* total_flops, double* total_bytes);
+
 /* ---- fused LoRA -------------------------------------------------------------------------- */
 
 /* Replaces FusedLoRAOp / CustomMetalOps::lora_forward_fused (src/backend/custom_ops.rs:73-431,
@@ -77,7 +84,8 @@ size_t mcb_lora_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int 
  *   bias   [N] dtype, or null
  *   A,B    float32 [K,r], [r,N]; r may be 0 with A=B=null (plain frozen linear)
  *   y      [M,N] dtype
- *   h_save [M, mcb_lora_rank_padded(r)] dtype, or null: receives scale*(x A) for the backward. */
+ *   h_save [mcb_lora_rank_padded(r), mcb_lora_h_pitch(M)] dtype, or null: receives scale*(x A),
+ *          transposed (rank-major, token index contiguous), for the backward. */
 int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const float* A, const float* B,
                         void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale,
                         int dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream);
@@ -94,8 +102,10 @@ int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const floa
                         int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
                         void* workspace, size_t workspace_bytes, void* stream);
 
-/* Rank rounded up to the tensor-core K granule (16); the column count of h_save. */
+/* Rank rounded up to the tensor-core K granule (16): the row count of h_save. */
 int64_t mcb_lora_rank_padded(int64_t r);
+/* Row pitch of h_save in elements: the token count rounded up to 64. */
+int64_t mcb_lora_h_pitch(int64_t M);
 
 /* dst[cols,rows] = src[rows,cols]^T; makes the [K,N] copy of a frozen weight for the backward. */
 int mcb_transpose_2d(const void* src, void* dst, int64_t rows, int64_t cols, int dtype, void* stream);
@@ -126,6 +136,16 @@ int mcb_softmax_fwd(const void* x, void* y, int64_t rows, int64_t D, int dtype, 
 int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int dtype,
                     void* stream);
 
+/* Scaled scores with a causal mask, then softmax: row i belongs to query position i % seq and keeps
+ * columns c <= i % seq; y = softmax(scale * x) over the kept columns, 0 elsewhere.  Replaces the
+ * sequence divide-by-sqrt(d), broadcast_add(mask), softmax_stable in Attention::forward
+ * (src/models/transformer.rs:264-275); the reference builds no mask itself (its callers pass one). */
+int mcb_softmax_causal_fwd(const void* x, void* y, int64_t rows, int64_t D, int64_t seq, float scale, int dtype,
+                           void* stream);
+/* dx = scale * y * (dy - sum_j dy_j y_j): reverse of softmax(scale * x). */
+int mcb_softmax_scaled_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, float scale,
+                           int dtype, void* stream);
+
 /* ---- AdamW -------------------------------------------------------------------------------- */
 
 typedef struct {
@@ -145,6 +165,31 @@ typedef struct {
  * data-parallel step; 1 otherwise). */
 int mcb_adamw_multi(const mcb_adamw_tensor* tensors, int n_tensors, float lr, float beta1, float beta2,
                     float eps, float weight_decay, float grad_scale, void* stream);
+
+/* ---- element-wise frame of the Qwen-shaped training step ------------------------------------- */
+
+/* out[m,:] = table[ids[m],:]  (candle_nn::embedding, src/models/qwen.rs:189).  ids are int32. */
+int mcb_embedding_fwd(const int32_t* ids, const void* table, void* out, int64_t M, int64_t H, int64_t vocab,
+                      int dtype, void* stream);
+/* Rotary embedding (half-split, angle = position * theta^(-2i/d); src/models/transformer.rs:47-120)
+ * fused with the [B,S,H,d] -> [B,H,S,d] transpose of Attention::forward (transformer.rs:255-257).
+ * rotate = 0 only re-lays out (V).  inverse = 1 is the reverse pass: [B,H,S,d] -> [B,S,H,d] with the
+ * transposed rotation. */
+int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
+                      int rotate, int inverse, int dtype, void* stream);
+/* out = silu(gate) * up and its reverse (MLP::forward, src/models/transformer.rs:389-395). */
+int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
+int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup, int64_t n,
+                   int dtype, void* stream);
+/* out = a + b (the residual connections, src/models/qwen.rs:121,140). */
+int mcb_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
+/* Cross-entropy over logits [M,V] with targets int32 [M]; a target outside [0,V) (u32::MAX, the
+ * reference's ignore index, src/training/trainer.rs:385) is ignored.  Replaces cross_entropy_loss
+ * (src/training/loss.rs:58-147) and its autograd reverse: loss[0] = mean nll over kept rows,
+ * loss[1] = sum, count[0] = kept rows, nll [M] scratch; with write_grad the logits are overwritten by
+ * d loss / d logits. */
+int mcb_cross_entropy(void* logits, const int32_t* targets, float* nll, int32_t* count, float* loss,
+                      int64_t M, int64_t V, int write_grad, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

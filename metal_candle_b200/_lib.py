@@ -34,6 +34,9 @@ SIGNATURES = {
     "mcb_last_error": (C.c_char_p, []),
     "mcb_version": (_i32, []),
     "mcb_device_status": (_i32, [C.POINTER(C.c_int)]),
+    "mcb_profile_enable": (_i32, [_i32]),
+    "mcb_profile_summary": (_i32, [_i32, C.POINTER(C.c_int64), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                   C.POINTER(C.c_double)]),
     "mcb_lora_delta_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
     "mcb_lora_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i32]),
     "mcb_lora_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32,
@@ -41,12 +44,21 @@ SIGNATURES = {
     "mcb_lora_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _f32,
                                    _i32, _i32, _vp, _sz, _vp]),
     "mcb_lora_rank_padded": (_i64, [_i64]),
+    "mcb_lora_h_pitch": (_i64, [_i64]),
     "mcb_transpose_2d": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
     "mcb_rmsnorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
     "mcb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "mcb_rmsnorm_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
     "mcb_softmax_fwd": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
     "mcb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "mcb_softmax_causal_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "mcb_softmax_scaled_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
+    "mcb_embedding_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "mcb_rope_relayout": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _vp]),
+    "mcb_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "mcb_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp]),
+    "mcb_add": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "mcb_cross_entropy": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "mcb_adamw_multi": (_i32, [C.POINTER(AdamWTensor), _i32, _f32, _f32, _f32, _f32, _f32, _f32, _vp]),
 }
 
@@ -88,3 +100,14 @@ def device_status() -> int:
     out = C.c_int(0)
     check(load().mcb_device_status(C.byref(out)))
     return out.value
+
+
+def profile_enable(on: bool) -> None:
+    check(load().mcb_profile_enable(int(on)))
+
+
+def profile_summary(kind: int):
+    """(launches, total_ms, total_flops, total_bytes) of the finished records of `kind`; clears them."""
+    n, ms, fl, by = C.c_int64(0), C.c_double(0), C.c_double(0), C.c_double(0)
+    check(load().mcb_profile_summary(kind, C.byref(n), C.byref(ms), C.byref(fl), C.byref(by)))
+    return n.value, ms.value, fl.value, by.value

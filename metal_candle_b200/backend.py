@@ -127,7 +127,8 @@ def lora_forward_fused(x: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tens
 
 
 def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=True):
-    """`y = x W^T (+b) + scaling (x A) B` with W [out, in].  Returns (y, h_save or None)."""
+    """`y = x W^T (+b) + scaling (x A) B` with W [out, in].  Returns (y, h_save or None); h_save is
+    `scaling * (x A)` transposed, [rank padded to 16, tokens padded to 64]."""
     K = x.shape[-1]
     N = weight.shape[0]
     if weight.dim() != 2 or weight.shape[1] != K:
@@ -144,7 +145,7 @@ def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=Tr
     y = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
     h = None
     if r and save_hidden:
-        h = torch.empty(M, lib.mcb_lora_rank_padded(r), dtype=x.dtype, device=x.device)
+        h = torch.empty(lib.mcb_lora_rank_padded(r), lib.mcb_lora_h_pitch(M), dtype=x.dtype, device=x.device)
     nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
     ws = workspace(x.device, nws)
     _lib.check(lib.mcb_lora_linear_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(lora_a), _ptr(lora_b), _ptr(y), _ptr(h),
@@ -156,20 +157,22 @@ def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, 
                          grad_b=None, accumulate=False, weight_layout=MCB_W_IN_OUT):
     """Reverse of `lora_linear_forward`.  `weight_t` is the [in, out] copy of the frozen weight (for
     float32 either layout works, say which with `weight_layout`).  Returns (dx, dA, dB)."""
-    K = x.shape[-1]
     N = dy.shape[-1]
+    K = weight_t.shape[0] if weight_layout == MCB_W_IN_OUT else weight_t.shape[1]
     r = 0 if lora_a is None else lora_a.shape[1]
+    if r and x is None:
+        raise TrainingError("lora_linear_backward: the layer input x is needed for the LoRA gradients")
     _require_cuda(x, weight_t, lora_a, lora_b, dy, h_save, grad_a, grad_b)
-    M = x.numel() // K
-    lib = _lib_for(x)
-    dt = _dtype_code(x)
-    dx = torch.empty_like(x) if need_dx else None
+    M = dy.numel() // N
+    lib = _lib_for(dy)
+    dt = _dtype_code(dy)
+    dx = torch.empty(*dy.shape[:-1], K, dtype=dy.dtype, device=dy.device) if need_dx else None
     if r and grad_a is None:
-        grad_a = torch.empty(K, r, dtype=torch.float32, device=x.device)
-        grad_b = torch.empty(r, N, dtype=torch.float32, device=x.device)
+        grad_a = torch.empty(K, r, dtype=torch.float32, device=dy.device)
+        grad_b = torch.empty(r, N, dtype=torch.float32, device=dy.device)
         accumulate = False
     nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
-    ws = workspace(x.device, nws)
+    ws = workspace(dy.device, nws)
     _lib.check(lib.mcb_lora_linear_bwd(_ptr(x), _ptr(weight_t), _ptr(lora_a), _ptr(lora_b), _ptr(dy), _ptr(h_save),
                                        _ptr(dx), _ptr(grad_a), _ptr(grad_b), int(bool(accumulate)), M, K, N, r,
                                        float(scaling), dt, weight_layout, _ptr(ws), ws.numel(), _stream()))

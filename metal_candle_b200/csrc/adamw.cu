@@ -106,7 +106,9 @@ extern "C" int mcb_adamw_multi(const mcb_adamw_tensor* tensors, int n_tensors, f
   if (n_tensors == 0) return MCB_OK;
   if (!tensors) return fail(MCB_ERR_NULL, "adamw_multi: tensors is null");
   // The same ranges AdamWConfig::validate enforces (src/training/optimizer.rs:69-107).
-  if (!(lr > 0.0f)) return fail(MCB_ERR_SHAPE, "learning rate must be positive");
+  // AdamWConfig::validate wants lr > 0 at construction, but set_lr does not re-validate and a warm-up
+  // schedule starts at exactly 0 (src/training/scheduler.rs:152-160), so 0 is accepted here.
+  if (!(lr >= 0.0f)) return fail(MCB_ERR_SHAPE, "learning rate must be non-negative");
   if (!(beta1 >= 0.0f && beta1 < 1.0f)) return fail(MCB_ERR_SHAPE, "beta1 must be in [0, 1), got %g", beta1);
   if (!(beta2 >= 0.0f && beta2 < 1.0f)) return fail(MCB_ERR_SHAPE, "beta2 must be in [0, 1), got %g", beta2);
   if (!(eps > 0.0f)) return fail(MCB_ERR_SHAPE, "epsilon must be positive");

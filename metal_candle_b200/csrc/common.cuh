@@ -24,6 +24,13 @@ struct DeviceState {
 };
 DeviceState* current_device_state();  // null (and error set) when mcb_init was not called
 
+// Optional per-kernel timing (mcb_profile_enable): CUDA events recorded on the launching stream right
+// around one kernel launch, tagged with the launch's algorithmic work.
+enum ProfileKind { kProfGemm = 0, kProfGrad = 1, kProfKinds = 2 };
+bool profile_on();
+void profile_begin(int kind, double flops, double bytes, cudaStream_t st);
+void profile_end(cudaStream_t st);
+
 #define MCB_CHECK_CUDA(expr)                                   \
   do {                                                         \
     cudaError_t e_ = (expr);                                   \

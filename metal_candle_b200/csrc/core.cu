@@ -4,6 +4,8 @@
 #include <string.h>
 
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 
@@ -50,6 +52,41 @@ DeviceState* current_device_state() {
 }
 
 int init_gemm_kernels();  // umma_gemm.cu: raises dynamic shared-memory limits
+
+// ---- per-kernel timing -----------------------------------------------------------------------------
+namespace {
+struct ProfRecord {
+  cudaEvent_t a, b;
+  int kind;
+  double flops, bytes;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+std::vector<ProfRecord> g_prof_live;
+std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_prof_pool;
+}  // namespace
+
+bool profile_on() { return g_prof_on; }
+
+void profile_begin(int kind, double flops, double bytes, cudaStream_t st) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  ProfRecord r;
+  if (!g_prof_pool.empty()) {
+    r.a = g_prof_pool.back().first;
+    r.b = g_prof_pool.back().second;
+    g_prof_pool.pop_back();
+  } else {
+    if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+  }
+  r.kind = kind; r.flops = flops; r.bytes = bytes;
+  cudaEventRecord(r.a, st);
+  g_prof_live.push_back(r);
+}
+
+void profile_end(cudaStream_t st) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (!g_prof_live.empty()) cudaEventRecord(g_prof_live.back().b, st);
+}
 
 }  // namespace mcb
 
@@ -99,6 +136,31 @@ extern "C" int mcb_device_status(int* status_out) {
   MCB_CHECK_CUDA(cudaDeviceSynchronize());
   MCB_CHECK_CUDA(cudaMemcpy(status_out, ds->status_word, sizeof(int), cudaMemcpyDeviceToHost));
   if (*status_out != 0) MCB_CHECK_CUDA(cudaMemset(ds->status_word, 0, sizeof(int)));
+  return MCB_OK;
+}
+
+extern "C" int mcb_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof_on = on != 0;
+  return MCB_OK;
+}
+
+extern "C" int mcb_profile_summary(int kind, int64_t* launches, double* total_ms, double* total_flops, double* total_bytes) {
+  if (!launches || !total_ms || !total_flops || !total_bytes) return fail(MCB_ERR_NULL, "profile_summary: null output");
+  if (kind < 0 || kind >= kProfKinds) return fail(MCB_ERR_SHAPE, "profile_summary: kind %d", kind);
+  MCB_CHECK_CUDA(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  *launches = 0; *total_ms = 0; *total_flops = 0; *total_bytes = 0;
+  std::vector<ProfRecord> keep;
+  for (const ProfRecord& r : g_prof_live) {
+    if (r.kind != kind) { keep.push_back(r); continue; }
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+      *launches += 1; *total_ms += ms; *total_flops += r.flops; *total_bytes += r.bytes;
+    }
+    g_prof_pool.emplace_back(r.a, r.b);
+  }
+  g_prof_live.swap(keep);
   return MCB_OK;
 }
 

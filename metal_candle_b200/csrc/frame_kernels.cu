@@ -1,0 +1,348 @@
+// The element-wise "frame" of the Qwen-shaped training step around the LoRA hot path: embedding
+// gather, rotary embedding with the head-major re-layout attention wants, SwiGLU, residual add, and a
+// fused cross-entropy forward+backward.  All are HBM-bound streaming kernels; float32 or bfloat16
+// storage, float32 arithmetic.
+#include "common.cuh"
+
+namespace mcb {
+namespace {
+
+// ---- embedding (candle_nn::embedding, src/models/qwen.rs:189; gather of table rows) -----------------
+template <typename T>
+__global__ void embedding_fwd_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                     int64_t M, int H, int vocab) {
+  const int64_t row = blockIdx.x;
+  if (row >= M) return;
+  int32_t id = ids[row];
+  if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
+  const T* src = table + static_cast<int64_t>(id) * H;
+  T* dst = out + row * H;
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0 && (H * sizeof(T)) % 16 == 0) {
+    const int nv = H * sizeof(T) / 16;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// ---- rotary embedding + [B,S,H,d] -> [B,H,S,d] (src/models/transformer.rs:47-120,255-257) ----------------
+// Half-split rotation: (x1, x2) -> (x1 cos - x2 sin, x1 sin + x2 cos), angle = pos * theta^(-2i/d).
+// inverse != 0 applies the transposed rotation and the inverse layout change (the backward pass).
+// rotate == 0 only changes the layout (used for V).
+template <typename T>
+__global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int S, int H, int d,
+                                     float theta, int rotate, int inverse) {
+  // one thread per (b, s, h, i) with i in [0, d/2)
+  const int half = d / 2;
+  const int64_t total = static_cast<int64_t>(B) * S * H * half;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int i = static_cast<int>(idx % half);
+    int64_t t = idx / half;
+    const int h = static_cast<int>(t % H); t /= H;
+    const int s = static_cast<int>(t % S);
+    const int b = static_cast<int>(t / S);
+    const int64_t bshd = ((static_cast<int64_t>(b) * S + s) * H + h) * d;   // [B,S,H,d]
+    const int64_t bhsd = ((static_cast<int64_t>(b) * H + h) * S + s) * d;   // [B,H,S,d]
+    const int64_t in = inverse ? bhsd : bshd, out = inverse ? bshd : bhsd;
+    const float x1 = to_f32(src[in + i]), x2 = to_f32(src[in + half + i]);
+    float o1 = x1, o2 = x2;
+    if (rotate) {
+      // 1 / theta^(2i/d) as in the reference's table (float32 powf), angle = position * inv_freq
+      const float inv_freq = 1.0f / powf(theta, static_cast<float>(2 * i) / static_cast<float>(d));
+      float sn, cs;
+      sincosf(static_cast<float>(s) * inv_freq, &sn, &cs);
+      if (inverse) sn = -sn;
+      o1 = x1 * cs - x2 * sn;
+      o2 = x1 * sn + x2 * cs;
+    }
+    dst[out + i] = from_f32<T>(o1);
+    dst[out + half + i] = from_f32<T>(o2);
+  }
+}
+
+// ---- SwiGLU (src/models/transformer.rs:389-395) ---------------------------------------------------------
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t n) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  const int64_t nv = n / N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    V g, u, o;
+    g.raw = reinterpret_cast<const decltype(g.raw)*>(gate)[i];
+    u.raw = reinterpret_cast<const decltype(u.raw)*>(up)[i];
+    float gf[N], uf[N], of[N];
+    g.to_float(gf); u.to_float(uf);
+#pragma unroll
+    for (int j = 0; j < N; ++j) of[j] = gf[j] / (1.0f + __expf(-gf[j])) * uf[j];
+    o.from_float(of);
+    reinterpret_cast<decltype(o.raw)*>(out)[i] = o.raw;
+  }
+}
+
+// d_gate = d_out * up * sig(g) * (1 + g (1 - sig(g))),  d_up = d_out * silu(g).  In place on gate/up allowed.
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ dout,
+                                  T* __restrict__ dgate, T* __restrict__ dup, int64_t n) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  const int64_t nv = n / N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    V g, u, d, og, ou;
+    g.raw = reinterpret_cast<const decltype(g.raw)*>(gate)[i];
+    u.raw = reinterpret_cast<const decltype(u.raw)*>(up)[i];
+    d.raw = reinterpret_cast<const decltype(d.raw)*>(dout)[i];
+    float gf[N], uf[N], df[N], a[N], b[N];
+    g.to_float(gf); u.to_float(uf); d.to_float(df);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const float sg = 1.0f / (1.0f + __expf(-gf[j]));
+      a[j] = df[j] * uf[j] * sg * (1.0f + gf[j] * (1.0f - sg));
+      b[j] = df[j] * gf[j] * sg;
+    }
+    og.from_float(a); ou.from_float(b);
+    reinterpret_cast<decltype(og.raw)*>(dgate)[i] = og.raw;
+    reinterpret_cast<decltype(ou.raw)*>(dup)[i] = ou.raw;
+  }
+}
+
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  const int64_t nv = n / N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    V x, y, o;
+    x.raw = reinterpret_cast<const decltype(x.raw)*>(a)[i];
+    y.raw = reinterpret_cast<const decltype(y.raw)*>(b)[i];
+    float xf[N], yf[N];
+    x.to_float(xf); y.to_float(yf);
+#pragma unroll
+    for (int j = 0; j < N; ++j) xf[j] += yf[j];
+    o.from_float(xf);
+    reinterpret_cast<decltype(o.raw)*>(out)[i] = o.raw;
+  }
+}
+
+// ---- cross-entropy forward + backward (src/training/loss.rs:97-146) ----------------------------------------
+// One block per row of logits [M,V].  Sweep 1: online max / sum-exp (HBM read).  Sweep 2 (the row is in
+// L2 by now): overwrite the row with d loss / d logits = (softmax - onehot) * inv_count; ignored rows get
+// zeros.  nll[row] = logsumexp - logit[target] (0 for ignored rows); a second tiny kernel sums nll in
+// row order, so the loss is deterministic.
+__device__ __forceinline__ void online_combine(float& m, float& s, float m2, float s2) {
+  const float mm = fmaxf(m, m2);
+  if (mm == -INFINITY) { m = mm; s = 0.0f; return; }
+  s = s * __expf(m - mm) + s2 * __expf(m2 - mm);
+  m = mm;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+cross_entropy_kernel(T* __restrict__ logits, const int32_t* __restrict__ targets, float* __restrict__ nll,
+                     const int32_t* __restrict__ count_ptr, int64_t M, int V, int write_grad) {
+  __shared__ float sm[32], ss[32];
+  const int64_t row = blockIdx.x;
+  T* lr = logits + row * V;
+  const int32_t tgt = targets[row];
+  const bool ignored = tgt < 0 || tgt >= V;  // u32::MAX (src/training/trainer.rs:385) reads as -1
+  const float inv_count = 1.0f / static_cast<float>(max(1, *count_ptr));
+  if (ignored) {
+    if (threadIdx.x == 0) nll[row] = 0.0f;
+    if (write_grad)
+      for (int c = threadIdx.x; c < V; c += blockDim.x) lr[c] = from_f32<T>(0.0f);
+    return;
+  }
+  using VT = Vec16<T>;
+  constexpr int NV = VT::N;
+  const bool vec = (V % NV == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15u) == 0);
+  float m = -INFINITY, s = 0.0f;
+  if (vec) {
+    for (int c = threadIdx.x; c < V / NV; c += blockDim.x) {
+      VT t; t.raw = reinterpret_cast<const decltype(t.raw)*>(lr)[c];
+      float f[NV];
+      t.to_float(f);
+      float vm = f[0];
+#pragma unroll
+      for (int j = 1; j < NV; ++j) vm = fmaxf(vm, f[j]);
+      if (vm > m) { s *= __expf(m - vm); m = vm; }
+#pragma unroll
+      for (int j = 0; j < NV; ++j) s += __expf(f[j] - m);
+    }
+  } else {
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+      const float v = to_f32(lr[c]);
+      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    online_combine(m, s, m2, s2);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) { sm[warp] = m; ss[warp] = s; }
+  __syncthreads();
+  m = sm[0]; s = ss[0];
+  for (int w = 1; w < nw; ++w) online_combine(m, s, sm[w], ss[w]);
+  const float lse = m + logf(s);
+  if (threadIdx.x == 0) nll[row] = lse - to_f32(lr[tgt]);
+  if (write_grad) {
+    __syncthreads();  // thread 0 has read lr[tgt] before anyone overwrites it
+    if (vec) {
+      for (int c = threadIdx.x; c < V / NV; c += blockDim.x) {
+        VT t; t.raw = reinterpret_cast<const decltype(t.raw)*>(lr)[c];
+        float f[NV];
+        t.to_float(f);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          float p = __expf(f[j] - lse);
+          if (c * NV + j == tgt) p -= 1.0f;
+          f[j] = p * inv_count;
+        }
+        t.from_float(f);
+        reinterpret_cast<decltype(t.raw)*>(lr)[c] = t.raw;
+      }
+    } else {
+      for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float p = __expf(to_f32(lr[c]) - lse);
+        if (c == tgt) p -= 1.0f;
+        lr[c] = from_f32<T>(p * inv_count);
+      }
+    }
+  }
+}
+
+__global__ void count_valid_kernel(const int32_t* __restrict__ targets, int64_t M, int V, int32_t* __restrict__ count) {
+  __shared__ int red[32];
+  int c = 0;
+  for (int64_t i = threadIdx.x; i < M; i += blockDim.x) c += (targets[i] >= 0 && targets[i] < V) ? 1 : 0;
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+    *count = t;
+  }
+}
+
+// loss[0] = sum(nll) / count, loss[1] = sum(nll); serial tree in fixed order (one block).
+__global__ void reduce_nll_kernel(const float* __restrict__ nll, int64_t M, const int32_t* __restrict__ count,
+                                  float* __restrict__ loss) {
+  __shared__ double red[1024];
+  double acc = 0.0;
+  for (int64_t i = threadIdx.x; i < M; i += blockDim.x) acc += static_cast<double>(nll[i]);
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    loss[1] = static_cast<float>(red[0]);
+    loss[0] = static_cast<float>(red[0] / static_cast<double>(max(1, *count)));
+  }
+}
+
+int grid_for(int64_t work_items, int threads, int sm_count) {
+  int64_t g = (work_items + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(sm_count) * 16;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+}  // namespace mcb
+
+using namespace mcb;
+
+#define MCB_DTYPE_SWITCH(dtype, CALL)                                    \
+  if ((dtype) == MCB_F32) { using T = float; CALL; }                     \
+  else if ((dtype) == MCB_BF16) { using T = __nv_bfloat16; CALL; }       \
+  else return fail(MCB_ERR_UNSUPPORTED, "dtype %d", (dtype));
+
+extern "C" int mcb_embedding_fwd(const int32_t* ids, const void* table, void* out, int64_t M, int64_t H, int64_t vocab,
+                                 int dtype, void* stream) {
+  if (!ids || !table || !out) return fail(MCB_ERR_NULL, "embedding_fwd: null pointer");
+  if (M <= 0 || H <= 0 || vocab <= 0 || M > 0x7fffffff) return fail(MCB_ERR_SHAPE, "embedding_fwd: bad shape");
+  if (!current_device_state()) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MCB_DTYPE_SWITCH(dtype, (embedding_fwd_kernel<T><<<(unsigned)M, 128, 0, st>>>(ids, (const T*)table, (T*)out, M, (int)H, (int)vocab)));
+  MCB_CHECK_LAUNCH("embedding_fwd");
+  return MCB_OK;
+}
+
+extern "C" int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
+                                 int rotate, int inverse, int dtype, void* stream) {
+  if (!src || !dst) return fail(MCB_ERR_NULL, "rope_relayout: null pointer");
+  if (B <= 0 || S <= 0 || H <= 0 || d <= 0 || d % 2 != 0) return fail(MCB_ERR_SHAPE, "rope_relayout: bad shape (head_dim must be even)");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t total = B * S * H * (d / 2);
+  const int grid = grid_for(total, 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (rope_relayout_kernel<T><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse)));
+  MCB_CHECK_LAUNCH("rope_relayout");
+  return MCB_OK;
+}
+
+extern "C" int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream) {
+  if (!gate || !up || !out) return fail(MCB_ERR_NULL, "swiglu_fwd: null pointer");
+  if (n <= 0 || n % 8 != 0) return fail(MCB_ERR_SHAPE, "swiglu_fwd: element count must be a positive multiple of 8");
+  if (!aligned16(gate) || !aligned16(up) || !aligned16(out)) return fail(MCB_ERR_ALIGN, "swiglu_fwd: 16-byte alignment");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n / 4, 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (swiglu_fwd_kernel<T><<<grid, 256, 0, st>>>((const T*)gate, (const T*)up, (T*)out, n)));
+  MCB_CHECK_LAUNCH("swiglu_fwd");
+  return MCB_OK;
+}
+
+extern "C" int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup, int64_t n,
+                              int dtype, void* stream) {
+  if (!gate || !up || !dout || !dgate || !dup) return fail(MCB_ERR_NULL, "swiglu_bwd: null pointer");
+  if (n <= 0 || n % 8 != 0) return fail(MCB_ERR_SHAPE, "swiglu_bwd: element count must be a positive multiple of 8");
+  if (!aligned16(gate) || !aligned16(up) || !aligned16(dout) || !aligned16(dgate) || !aligned16(dup))
+    return fail(MCB_ERR_ALIGN, "swiglu_bwd: 16-byte alignment");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n / 4, 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (swiglu_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)gate, (const T*)up, (const T*)dout, (T*)dgate, (T*)dup, n)));
+  MCB_CHECK_LAUNCH("swiglu_bwd");
+  return MCB_OK;
+}
+
+extern "C" int mcb_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream) {
+  if (!a || !b || !out) return fail(MCB_ERR_NULL, "add: null pointer");
+  if (n <= 0 || n % 8 != 0) return fail(MCB_ERR_SHAPE, "add: element count must be a positive multiple of 8");
+  if (!aligned16(a) || !aligned16(b) || !aligned16(out)) return fail(MCB_ERR_ALIGN, "add: 16-byte alignment");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n / 4, 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (add_kernel<T><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)out, n)));
+  MCB_CHECK_LAUNCH("add");
+  return MCB_OK;
+}
+
+extern "C" int mcb_cross_entropy(void* logits, const int32_t* targets, float* nll, int32_t* count, float* loss,
+                                 int64_t M, int64_t V, int write_grad, int dtype, void* stream) {
+  if (!logits || !targets || !nll || !count || !loss) return fail(MCB_ERR_NULL, "cross_entropy: null pointer");
+  if (M <= 0 || V <= 0 || M > 0x7fffffff || V > 0x7fffffff) return fail(MCB_ERR_SHAPE, "cross_entropy: bad shape");
+  if (!current_device_state()) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  count_valid_kernel<<<1, 1024, 0, st>>>(targets, M, (int)V, count);
+  MCB_CHECK_LAUNCH("count_valid");
+  MCB_DTYPE_SWITCH(dtype, (cross_entropy_kernel<T><<<(unsigned)M, 512, 0, st>>>((T*)logits, targets, nll, count, M, (int)V, write_grad)));
+  MCB_CHECK_LAUNCH("cross_entropy");
+  reduce_nll_kernel<<<1, 1024, 0, st>>>(nll, M, count, loss);
+  MCB_CHECK_LAUNCH("reduce_nll");
+  return MCB_OK;
+}

@@ -27,6 +27,8 @@ int check_dims(const char* op, int64_t M, int64_t K, int64_t N, int64_t r, int d
 
 extern "C" int64_t mcb_lora_rank_padded(int64_t r) { return rank_padded(r); }
 
+extern "C" int64_t mcb_lora_h_pitch(int64_t M) { return M <= 0 ? 0 : h_pitch(M); }
+
 extern "C" size_t mcb_lora_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int dtype) {
   if (M <= 0 || K <= 0 || N <= 0 || r <= 0) return 0;
   return dtype == MCB_F32 ? f32path::workspace_bytes(M, K, N, r) : bf16path::workspace_bytes(M, K, N, r);

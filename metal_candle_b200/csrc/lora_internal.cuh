@@ -13,7 +13,7 @@ struct LoraArgs {
   const float* A = nullptr;    // [K,r] float32
   const float* B = nullptr;    // [r,N] float32
   void* y = nullptr;           // [M,N]
-  void* h_save = nullptr;      // [M,rp] scale*(x A), optional
+  void* h_save = nullptr;      // [rp, h_pitch(M)] scale*(x A) transposed, optional
   const void* dy = nullptr;    // [M,N]
   void* dx = nullptr;          // [M,K]
   float* dA = nullptr;         // [K,r]
@@ -28,6 +28,8 @@ struct LoraArgs {
 };
 
 inline int64_t rank_padded(int64_t r) { return r <= 0 ? 0 : ((r + 15) / 16) * 16; }
+// Row pitch (in elements) of the saved rank intermediate [rp, pitch]: tokens rounded up to 64.
+inline int64_t h_pitch(int64_t M) { return ((M + 63) / 64) * 64; }
 
 namespace f32path {
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);

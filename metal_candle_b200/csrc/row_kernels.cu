@@ -239,7 +239,7 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, float*
 // ---- softmax forward --------------------------------------------------------------------------
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(RowGeom<TPR>::THREADS)
-softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int D) {
+softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int D, int causal_seq, float scale) {
   using V = Vec16<T>;
   constexpr int N = V::N;
   constexpr int RPB = RowGeom<TPR>::RPB;
@@ -258,6 +258,15 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
       if (live && vi < nvec) {
         V t; t.raw = reinterpret_cast<const decltype(t.raw)*>(x + row * D)[vi];
         t.to_float(xv[i]);
+        if (causal_seq > 0) {
+          // scaled scores with an additive causal mask: column c of query position q is kept iff c <= q
+          const int q = static_cast<int>(row % causal_seq);
+#pragma unroll
+          for (int j = 0; j < N; ++j) xv[i][j] = (vi * N + j <= q) ? xv[i][j] * scale : -INFINITY;
+        } else if (scale != 1.0f) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) xv[i][j] *= scale;
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < N; ++j) xv[i][j] = -INFINITY;
@@ -299,7 +308,7 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(RowGeom<TPR>::THREADS)
 softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
-                   int64_t rows, int D) {
+                   int64_t rows, int D, float scale) {
   using V = Vec16<T>;
   constexpr int N = V::N;
   constexpr int RPB = RowGeom<TPR>::RPB;
@@ -336,7 +345,7 @@ softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
         if (vi < nvec) {
           float o[N];
 #pragma unroll
-          for (int j = 0; j < N; ++j) o[j] = yv[i][j] * (gv[i][j] - dot[0]);
+          for (int j = 0; j < N; ++j) o[j] = yv[i][j] * (gv[i][j] - dot[0]) * scale;
           V t; t.from_float(o);
           reinterpret_cast<decltype(t.raw)*>(dx + row * D)[vi] = t.raw;
         }
@@ -412,25 +421,27 @@ __global__ void rmsnorm_dw_wide_kernel(const T* x, const T* dy, const float* rin
 }
 
 template <typename T>
-__global__ void softmax_fwd_wide_kernel(const T* x, T* y, int64_t rows, int64_t D) {
+__global__ void softmax_fwd_wide_kernel(const T* x, T* y, int64_t rows, int64_t D, int causal_seq, float scale) {
   __shared__ float red[32];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* xr = x + row * D;
+    const int64_t q = causal_seq > 0 ? row % causal_seq : D;
+    auto val = [&](int64_t c) { return c <= q ? to_f32(xr[c]) * scale : -INFINITY; };
     float mx = -INFINITY;
-    for (int64_t c = threadIdx.x; c < D; c += blockDim.x) mx = fmaxf(mx, to_f32(xr[c]));
+    for (int64_t c = threadIdx.x; c < D; c += blockDim.x) mx = fmaxf(mx, val(c));
     mx = block_reduce(mx, true, red);
     const float m = (mx == -INFINITY) ? 0.0f : mx;
     float sum = 0.0f;
-    for (int64_t c = threadIdx.x; c < D; c += blockDim.x) sum += exp2f((to_f32(xr[c]) - m) * kLog2e);
+    for (int64_t c = threadIdx.x; c < D; c += blockDim.x) sum += exp2f((val(c) - m) * kLog2e);
     sum = block_reduce(sum, false, red);
     const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
     for (int64_t c = threadIdx.x; c < D; c += blockDim.x)
-      y[row * D + c] = from_f32<T>(exp2f((to_f32(xr[c]) - m) * kLog2e) * inv);
+      y[row * D + c] = from_f32<T>(exp2f((val(c) - m) * kLog2e) * inv);
   }
 }
 
 template <typename T>
-__global__ void softmax_bwd_wide_kernel(const T* y, const T* dy, T* dx, int64_t rows, int64_t D) {
+__global__ void softmax_bwd_wide_kernel(const T* y, const T* dy, T* dx, int64_t rows, int64_t D, float scale) {
   __shared__ float red[32];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     float dot = 0.0f;
@@ -438,7 +449,7 @@ __global__ void softmax_bwd_wide_kernel(const T* y, const T* dy, T* dx, int64_t 
       dot = fmaf(to_f32(y[row * D + c]), to_f32(dy[row * D + c]), dot);
     dot = block_reduce(dot, false, red);
     for (int64_t c = threadIdx.x; c < D; c += blockDim.x)
-      dx[row * D + c] = from_f32<T>(to_f32(y[row * D + c]) * (to_f32(dy[row * D + c]) - dot));
+      dx[row * D + c] = from_f32<T>(to_f32(y[row * D + c]) * (to_f32(dy[row * D + c]) - dot) * scale);
   }
 }
 
@@ -546,15 +557,16 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
 }
 
 template <typename T>
-int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, cudaStream_t st, const DeviceState* ds) {
+int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, int causal_seq, float scale, cudaStream_t st,
+                  const DeviceState* ds) {
   RowPlan p = plan_rows<T>(D, aligned16(x) && aligned16(y));
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);
-    softmax_fwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)y, rows, D);
+    softmax_fwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)y, rows, D, causal_seq, scale);
   } else {
 #define CALL(TPR, VPT)                                                                                \
   softmax_fwd_kernel<T, TPR, VPT><<<row_grid(rows, TPR, ds->sm_count, 8), RowGeom<TPR>::THREADS, 0, st>>>( \
-      (const T*)x, (T*)y, rows, (int)D)
+      (const T*)x, (T*)y, rows, (int)D, causal_seq, scale)
     MCB_ROW_DISPATCH(p, CALL)
 #undef CALL
   }
@@ -563,16 +575,16 @@ int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, cudaStream_t 
 }
 
 template <typename T>
-int softmax_bwd_t(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, cudaStream_t st,
+int softmax_bwd_t(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, float scale, cudaStream_t st,
                   const DeviceState* ds) {
   RowPlan p = plan_rows<T>(D, aligned16(y) && aligned16(dy) && aligned16(dx));
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);
-    softmax_bwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)y, (const T*)dy, (T*)dx, rows, D);
+    softmax_bwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)y, (const T*)dy, (T*)dx, rows, D, scale);
   } else {
 #define CALL(TPR, VPT)                                                                                \
   softmax_bwd_kernel<T, TPR, VPT><<<row_grid(rows, TPR, ds->sm_count, 8), RowGeom<TPR>::THREADS, 0, st>>>( \
-      (const T*)y, (const T*)dy, (T*)dx, rows, (int)D)
+      (const T*)y, (const T*)dy, (T*)dx, rows, (int)D, scale)
     MCB_ROW_DISPATCH(p, CALL)
 #undef CALL
   }
@@ -633,8 +645,21 @@ extern "C" int mcb_softmax_fwd(const void* x, void* y, int64_t rows, int64_t D, 
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == MCB_F32 ? softmax_fwd_t<float>(x, y, rows, D, st, ds)
-                          : softmax_fwd_t<__nv_bfloat16>(x, y, rows, D, st, ds);
+  return dtype == MCB_F32 ? softmax_fwd_t<float>(x, y, rows, D, 0, 1.0f, st, ds)
+                          : softmax_fwd_t<__nv_bfloat16>(x, y, rows, D, 0, 1.0f, st, ds);
+}
+
+extern "C" int mcb_softmax_causal_fwd(const void* x, void* y, int64_t rows, int64_t D, int64_t seq, float scale, int dtype,
+                                      void* stream) {
+  if (!x || !y) return fail(MCB_ERR_NULL, "softmax_causal_fwd: x or y is null");
+  if (int rc = check_rows("softmax_causal_fwd", rows, D, dtype)) return rc;
+  if (seq <= 0 || seq > 0x7fffffff || rows % seq != 0)
+    return fail(MCB_ERR_SHAPE, "softmax_causal_fwd: rows=%lld must be a multiple of seq=%lld", (long long)rows, (long long)seq);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == MCB_F32 ? softmax_fwd_t<float>(x, y, rows, D, (int)seq, scale, st, ds)
+                          : softmax_fwd_t<__nv_bfloat16>(x, y, rows, D, (int)seq, scale, st, ds);
 }
 
 extern "C" int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int dtype,
@@ -644,6 +669,17 @@ extern "C" int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t 
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, st, ds)
-                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, st, ds);
+  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, 1.0f, st, ds)
+                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, 1.0f, st, ds);
+}
+
+extern "C" int mcb_softmax_scaled_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, float scale,
+                                      int dtype, void* stream) {
+  if (!y || !dy || !dx) return fail(MCB_ERR_NULL, "softmax_scaled_bwd: y, dy or dx is null");
+  if (int rc = check_rows("softmax_scaled_bwd", rows, D, dtype)) return rc;
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, scale, st, ds)
+                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, scale, st, ds);
 }

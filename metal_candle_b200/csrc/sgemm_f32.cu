@@ -82,7 +82,7 @@ int sgemm(cudaStream_t st, const float* A, int64_t sam, int64_t sak, const float
 
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r) {
   (void)K; (void)N;
-  return 2 * static_cast<size_t>(M) * static_cast<size_t>(rank_padded(r)) * sizeof(float);
+  return (static_cast<size_t>(M) + static_cast<size_t>(h_pitch(M))) * static_cast<size_t>(rank_padded(r)) * sizeof(float);
 }
 
 int delta_fwd(const LoraArgs& a) {
@@ -97,26 +97,30 @@ int delta_fwd(const LoraArgs& a) {
 }
 
 int linear_fwd(const LoraArgs& a) {
-  const int64_t rp = rank_padded(a.r);
+  const int64_t pitch = h_pitch(a.M);
   const int64_t sbk = a.w_layout == MCB_W_OUT_IN ? 1 : a.N;
   const int64_t sbn = a.w_layout == MCB_W_OUT_IN ? a.K : 1;
   if (int rc = sgemm(a.stream, (const float*)a.x, a.K, 1, (const float*)a.W, sbk, sbn, (float*)a.y, a.N, a.M, a.N,
                      a.K, 1.0f, 0.0f, (const float*)a.bias))
     return rc;
   if (a.r == 0) return MCB_OK;
+  // hs = scale * (x A), kept transposed [rp, pitch] like the bf16 path's saved intermediate
   float* hs = static_cast<float*>(a.h_save);
   if (hs == nullptr) {
     if (a.ws_bytes < workspace_bytes(a.M, a.K, a.N, a.r) || !a.ws)
       return fail(MCB_ERR_WORKSPACE, "lora_linear_fwd(f32): workspace too small");
     hs = static_cast<float*>(a.ws);
   }
-  if (int rc = sgemm(a.stream, (const float*)a.x, a.K, 1, a.A, a.r, 1, hs, rp, a.M, a.r, a.K, a.scale, 0.0f, nullptr))
+  // hs[j, m] = scale * sum_k A[k, j] x[m, k]
+  if (int rc = sgemm(a.stream, a.A, 1, a.r, (const float*)a.x, 1, a.K, hs, pitch, a.r, a.M, a.K, a.scale, 0.0f, nullptr))
     return rc;
-  return sgemm(a.stream, hs, rp, 1, a.B, a.N, 1, (float*)a.y, a.N, a.M, a.N, a.r, 1.0f, 1.0f, nullptr);
+  // y[m, n] += sum_j hs[j, m] B[j, n]
+  return sgemm(a.stream, hs, 1, pitch, a.B, a.N, 1, (float*)a.y, a.N, a.M, a.N, a.r, 1.0f, 1.0f, nullptr);
 }
 
 int linear_bwd(const LoraArgs& a) {
   const int64_t rp = rank_padded(a.r);
+  const int64_t pitch = h_pitch(a.M);
   const float* dy = static_cast<const float*>(a.dy);
   // dy W : W(k_red = n, out = k)
   const int64_t sbk = a.w_layout == MCB_W_OUT_IN ? a.K : 1;
@@ -130,7 +134,7 @@ int linear_bwd(const LoraArgs& a) {
   if (a.ws_bytes < workspace_bytes(a.M, a.K, a.N, a.r) || !a.ws)
     return fail(MCB_ERR_WORKSPACE, "lora_linear_bwd(f32): workspace too small");
   float* dh = static_cast<float*>(a.ws);                  // scale * dy B^T   [M, rp]
-  float* hs_ws = dh + a.M * rp;                           // scale * x A      [M, rp] when not saved
+  float* hs_ws = dh + a.M * rp;                           // scale * x A      [rp, pitch] when not saved
   if (int rc = sgemm(a.stream, dy, a.N, 1, a.B, 1, a.N, dh, rp, a.M, a.r, a.N, a.scale, 0.0f, nullptr)) return rc;
   if (a.dx != nullptr) {
     if (int rc = sgemm(a.stream, dh, rp, 1, a.A, 1, a.r, (float*)a.dx, a.K, a.M, a.K, a.r, 1.0f, 1.0f, nullptr))
@@ -146,13 +150,13 @@ int linear_bwd(const LoraArgs& a) {
   if (a.dB != nullptr) {
     const float* hs = static_cast<const float*>(a.h_save);
     if (hs == nullptr) {
-      if (int rc = sgemm(a.stream, (const float*)a.x, a.K, 1, a.A, a.r, 1, hs_ws, rp, a.M, a.r, a.K, a.scale, 0.0f,
+      if (int rc = sgemm(a.stream, a.A, 1, a.r, (const float*)a.x, 1, a.K, hs_ws, pitch, a.r, a.M, a.K, a.scale, 0.0f,
                          nullptr))
         return rc;
       hs = hs_ws;
     }
-    // dB[j, n] = sum_m hs[m,j] dy[m,n]
-    if (int rc = sgemm(a.stream, hs, 1, rp, dy, a.N, 1, a.dB, a.N, a.r, a.N, a.M, 1.0f, beta, nullptr)) return rc;
+    // dB[j, n] = sum_m hs[j,m] dy[m,n]
+    if (int rc = sgemm(a.stream, hs, pitch, 1, dy, a.N, 1, a.dB, a.N, a.r, a.N, a.M, 1.0f, beta, nullptr)) return rc;
   }
   return MCB_OK;
 }

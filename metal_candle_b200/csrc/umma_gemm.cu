@@ -28,18 +28,24 @@
 #include <string.h>
 
 #include "lora_internal.cuh"
+#include "umma_ptx.cuh"
 
 namespace mcb {
 namespace bf16path {
+using namespace umma;
+
+int init_grad_kernel();
+size_t grad_partial_bytes(int64_t M, int64_t C, int rp);
+int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch, float* out, float* part, int64_t M,
+                int64_t C, int r, int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st);
+
 namespace {
 
-constexpr int BM = 128;
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kSmemBudget = 227 * 1024 - 1024;  // dynamic shared memory we ask for (minus alignment slack)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct GemmParams {
   int M, N, K;
@@ -48,111 +54,13 @@ struct GemmParams {
   float scale;
   __nv_bfloat16* Y;
   const __nv_bfloat16* bias;
-  __nv_bfloat16* H;
+  __nv_bfloat16* H;   // [rp, h_pitch]: scale * X P^T, transposed (token index contiguous), or null
+  int64_t h_pitch;
   int* status;
   uint32_t stage_bytes, w_off, p_off;        // within a stage
   uint32_t q_off, q_bytes, hs_off, hs_bytes; // from the aligned base
   uint32_t bar_off;
 };
-
-// ---- PTX wrappers ------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          int* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = code;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47).
-//   K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused (=1).
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
-  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
-         (1ull << 46) | (2ull << 61);
-}
-//   K-major, no swizzle: 8x16-byte core matrices; LBO = byte step between 16-byte K chunks,
-//   SBO = byte step between 8-row groups.
-__device__ __forceinline__ uint64_t desc_noswz(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo >> 4) << 16) |
-         (static_cast<uint64_t>(sbo >> 4) << 32) | (1ull << 46);
-}
-// Instruction descriptor for kind::f16: D=f32, A=B=bf16, both K-major, M=128, N=n.
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& mt, int& nt) {
   const int per_band = p.group_m * p.num_n_tiles;
@@ -338,9 +246,14 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           *reinterpret_cast<uint4*>(hs_gen + (c / 8) * (BM * 16) + row_in_tile * 16) = lo;
           *reinterpret_cast<uint4*>(hs_gen + (c / 8 + 1) * (BM * 16) + row_in_tile * 16) = hi;
           if (p.H != nullptr && nt == 0 && grow < p.M) {
-            uint4* hp = reinterpret_cast<uint4*>(p.H + grow * p.rp + c);
-            hp[0] = lo;
-            hp[1] = hi;
+            // transposed copy for the weight-gradient kernel: lanes hold consecutive tokens, so each of
+            // these 2-byte stores is a contiguous 64-byte run across the warp
+            __nv_bfloat16* hp = p.H + static_cast<int64_t>(c) * p.h_pitch + grow;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              hp[(2 * j) * p.h_pitch] = __ushort_as_bfloat16(static_cast<unsigned short>(w[j] & 0xffffu));
+              hp[(2 * j + 1) * p.h_pitch] = __ushort_as_bfloat16(static_cast<unsigned short>(w[j] >> 16));
+            }
           }
         }
         fence_proxy_async_smem();
@@ -426,66 +339,6 @@ __global__ void pack_lora_kernel(const float* __restrict__ A, const float* __res
   }
 }
 
-// ---- LoRA weight gradients -------------------------------------------------------------------------
-// part[split][c][j] = sum over the split's rows m of X[m,c] * H[m,j]    (X bf16 [M,C], H bf16 [M,rp])
-// Each thread owns two adjacent columns and 16 rank columns; rows of H are staged in shared memory
-// as float.  grid = (ceil(C/256), splits, rp/16).
-constexpr int kGradRows = 64;
-__global__ void __launch_bounds__(128)
-lora_grad_partial_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ H,
-                         float* __restrict__ part, int M, int C, int rp, int rows_per_split) {
-  __shared__ float hs[kGradRows][16];
-  const int c = (blockIdx.x * 128 + threadIdx.x) * 2;
-  const int j0 = blockIdx.z * 16;
-  const int m_begin = blockIdx.y * rows_per_split;
-  const int m_end = min(M, m_begin + rows_per_split);
-  float acc0[16], acc1[16];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) { acc0[j] = 0.0f; acc1[j] = 0.0f; }
-  const bool live = c < C;  // C is even (checked on the host)
-  for (int mb = m_begin; mb < m_end; mb += kGradRows) {
-    const int nrows = min(kGradRows, m_end - mb);
-    __syncthreads();
-    for (int i = threadIdx.x; i < kGradRows * 16; i += 128) {
-      const int rr = i >> 4, jj = i & 15;
-      hs[rr][jj] = rr < nrows ? __bfloat162float(H[static_cast<int64_t>(mb + rr) * rp + j0 + jj]) : 0.0f;
-    }
-    __syncthreads();
-    if (live) {
-#pragma unroll 4
-      for (int rr = 0; rr < nrows; ++rr) {
-        const uint32_t xw = *reinterpret_cast<const uint32_t*>(X + static_cast<int64_t>(mb + rr) * C + c);
-        const float x0 = __uint_as_float(xw << 16), x1 = __uint_as_float(xw & 0xffff0000u);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float h = hs[rr][j];
-          acc0[j] = fmaf(x0, h, acc0[j]);
-          acc1[j] = fmaf(x1, h, acc1[j]);
-        }
-      }
-    }
-  }
-  if (live) {
-    float* o = part + (static_cast<int64_t>(blockIdx.y) * C + c) * rp + j0;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { o[j] = acc0[j]; o[rp + j] = acc1[j]; }
-  }
-}
-
-// out (+)= sum over splits, in split order.  transposed == 0: out[c*r + j] (dA [K,r]);
-// transposed == 1: out[j*C + c] (dB [r,N]).
-__global__ void lora_grad_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int splits, int C,
-                                        int r, int rp, int transposed, int accumulate) {
-  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (tid >= static_cast<int64_t>(C) * r) return;
-  int c, j;
-  if (transposed) { j = static_cast<int>(tid / C); c = static_cast<int>(tid % C); }
-  else { c = static_cast<int>(tid / r); j = static_cast<int>(tid % r); }
-  float s = 0.0f;
-  for (int sp = 0; sp < splits; ++sp) s += part[(static_cast<int64_t>(sp) * C + c) * rp + j];
-  out[tid] = accumulate ? out[tid] + s : s;
-}
-
 // ---- host side -----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -526,9 +379,11 @@ struct GemmCall {
   const __nv_bfloat16* Q = nullptr;   // [N,rp] or null
   const __nv_bfloat16* bias = nullptr;
   __nv_bfloat16* Y = nullptr;         // [M,N] or null
-  __nv_bfloat16* H = nullptr;         // [M,rp] or null
+  __nv_bfloat16* H = nullptr;         // [rp,h_pitch] or null
+  int64_t h_pitch = 0;
   int64_t M = 0, N = 0, K = 0;
   int rp = 0;
+  int r_true = 0;  // unpadded rank, for the algorithmic flop count
   float scale = 1.0f;
 };
 
@@ -552,7 +407,7 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.num_k_blocks = (p.K + BK - 1) / BK;
   p.group_m = p.num_m_tiles < 16 ? p.num_m_tiles : 16;
   p.scale = c.scale;
-  p.Y = c.Y; p.bias = c.bias; p.H = c.H; p.status = ds->status_word;
+  p.Y = c.Y; p.bias = c.bias; p.H = c.H; p.h_pitch = c.h_pitch; p.status = ds->status_word;
   const uint32_t x_bytes = BM * BK * 2;
   const uint32_t w_bytes = p.has_w ? p.BN * BK * 2 : 0;
   const uint32_t p_bytes = p.rp * BK * 2;
@@ -579,34 +434,16 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     if (int rc = make_map(ds, &tmQ, c.Q, p.rp, c.N, 8, p.BN, false, "Q")) return rc;
   } else { tmP = tmX; tmQ = tmX; }
   const int grid = p.num_tiles < ds->sm_count ? p.num_tiles : ds->sm_count;
+  const bool prof = profile_on();
+  if (prof) {
+    const double m = static_cast<double>(c.M), n = static_cast<double>(c.N), k = static_cast<double>(c.K);
+    const double flops = (p.has_w ? 2.0 * m * n * k : 0.0) + 2.0 * m * c.r_true * (k + n);
+    const double bytes = 2.0 * (m * k + (p.has_w ? n * k : 0.0) + (c.Y ? m * n : 0.0)) + 2.0 * p.rp * (k + n);
+    profile_begin(kProfGemm, flops, bytes, st);
+  }
   lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, p);
+  if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm_kernel");
-  return MCB_OK;
-}
-
-int grad_splits(int64_t M, int64_t C, int sm_count) {
-  const int64_t col_blocks = (C + 255) / 256;
-  int64_t s = (2 * static_cast<int64_t>(sm_count) + col_blocks - 1) / col_blocks;
-  const int64_t max_s = (M + kGradRows - 1) / kGradRows;
-  if (s > max_s) s = max_s;
-  if (s < 1) s = 1;
-  return static_cast<int>(s);
-}
-
-// out = X^T H through split partial sums.  `part` must hold splits*C*rp floats.
-int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* H, float* out, float* part, int64_t M, int64_t C, int r,
-                int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st) {
-  if (C % 2 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients need an even feature count (got %lld)", (long long)C);
-  const int splits = grad_splits(M, C, ds->sm_count);
-  int rows_per_split = static_cast<int>((M + splits - 1) / splits);
-  rows_per_split = (rows_per_split + kGradRows - 1) / kGradRows * kGradRows;
-  dim3 grid(static_cast<unsigned>((C + 255) / 256), static_cast<unsigned>(splits), static_cast<unsigned>(rp / 16));
-  lora_grad_partial_kernel<<<grid, 128, 0, st>>>(X, H, part, static_cast<int>(M), static_cast<int>(C), rp, rows_per_split);
-  MCB_CHECK_LAUNCH("lora_grad_partial");
-  const int64_t n = C * r;
-  lora_grad_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(part, out, splits, static_cast<int>(C), r,
-                                                                                   rp, transposed, accumulate);
-  MCB_CHECK_LAUNCH("lora_grad_reduce");
   return MCB_OK;
 }
 
@@ -624,11 +461,10 @@ Workspace carve(void* ws, int64_t M, int64_t K, int64_t N, int64_t r) {
   auto take = [&](size_t bytes) { uint8_t* q = b ? b + off : nullptr; off += align_up(bytes, 1024); return q; };
   w.P = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(rp) * big * 2));
   w.Q = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(rp) * big * 2));
-  w.H1 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(M) * rp * 2));
-  w.H2 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(M) * rp * 2));
-  const size_t sk = static_cast<size_t>(grad_splits(M, K, 256)) * K;
-  const size_t sn = static_cast<size_t>(grad_splits(M, N, 256)) * N;
-  w.part = reinterpret_cast<float*>(take((sk > sn ? sk : sn) * rp * sizeof(float)));
+  w.H1 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(h_pitch(M)) * rp * 2));
+  w.H2 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(h_pitch(M)) * rp * 2));
+  const size_t pk = grad_partial_bytes(M, K, static_cast<int>(rp)), pn = grad_partial_bytes(M, N, static_cast<int>(rp));
+  w.part = reinterpret_cast<float*>(take(pk > pn ? pk : pn));
   w.total = off;
   return w;
 }
@@ -657,7 +493,7 @@ int check_ws(const LoraArgs& a, const char* op) {
 int init_kernels() {
   cudaError_t e = cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(lora_gemm_kernel)");
-  return MCB_OK;
+  return init_grad_kernel();
 }
 
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r) {
@@ -675,6 +511,7 @@ int delta_fwd(const LoraArgs& a, const DeviceState* ds) {
   c.Y = static_cast<__nv_bfloat16*>(a.y);
   c.M = a.M; c.N = a.N; c.K = a.K;
   c.rp = static_cast<int>(rank_padded(a.r));
+  c.r_true = static_cast<int>(a.r);
   c.scale = a.scale;
   return launch_gemm(c, ds, a.stream);
 }
@@ -694,7 +531,9 @@ int linear_fwd(const LoraArgs& a, const DeviceState* ds) {
     if (int rc = pack(a, w, 0)) return rc;
     c.P = w.P; c.Q = w.Q;
     c.H = static_cast<__nv_bfloat16*>(a.h_save);
+    c.h_pitch = h_pitch(a.M);
     c.rp = static_cast<int>(rank_padded(a.r));
+  c.r_true = static_cast<int>(a.r);
     c.scale = a.scale;
   }
   return launch_gemm(c, ds, a.stream);
@@ -722,7 +561,9 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
     if (a.r > 0) {
       c.P = w.P; c.Q = w.Q;
       c.H = (a.dA != nullptr) ? w.H1 : nullptr;
+      c.h_pitch = h_pitch(a.M);
       c.rp = rp;
+      c.r_true = static_cast<int>(a.r);
       c.scale = a.scale;
     }
     if (c.W != nullptr || c.rp > 0) {
@@ -731,8 +572,8 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
   }
   if (!want_grads) return MCB_OK;
   if (a.dA != nullptr) {
-    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.x), w.H1, a.dA, w.part, a.M, a.K, static_cast<int>(a.r), rp,
-                             0, a.accumulate, ds, a.stream))
+    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.x), w.H1, h_pitch(a.M), a.dA, w.part, a.M, a.K,
+                             static_cast<int>(a.r), rp, 0, a.accumulate, ds, a.stream))
       return rc;
   }
   if (a.dB != nullptr) {
@@ -747,14 +588,16 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
       c.X = static_cast<const __nv_bfloat16*>(a.x);
       c.P = wf.P; c.Q = wf.Q;
       c.H = w.H2;
+      c.h_pitch = h_pitch(a.M);
       c.M = a.M; c.N = a.N; c.K = a.K;
       c.rp = rp;
+      c.r_true = static_cast<int>(a.r);
       c.scale = a.scale;
       if (int rc = launch_gemm(c, ds, a.stream)) return rc;
       hs = w.H2;
     }
-    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.dy), hs, a.dB, w.part, a.M, a.N, static_cast<int>(a.r), rp,
-                             1, a.accumulate, ds, a.stream))
+    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.dy), hs, h_pitch(a.M), a.dB, w.part, a.M, a.N,
+                             static_cast<int>(a.r), rp, 1, a.accumulate, ds, a.stream))
       return rc;
   }
   return MCB_OK;

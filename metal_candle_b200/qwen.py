@@ -1,0 +1,331 @@
+"""Qwen2.5-shaped decoder with LoRA adapters and an explicit training step (forward, loss, backward).
+
+Mirrors the reference's model frame for this path -- `ModelConfig` (src/models/config.rs:25-76),
+`Qwen` / `QwenDecoderLayer` (src/models/qwen.rs:20-273), `Attention` / `MLP` / `RotaryEmbedding`
+(src/models/transformer.rs:27-396) -- with two deliberate differences: adapters are applied to the
+projections they name, on those projections' true inputs (the reference only consults o_proj and
+down_proj and feeds them the layer-norm output, src/models/qwen.rs:106-138), and K/V adapters are sized
+by the grouped-query width.  There is no autograd: the backward pass is written out and runs the
+library's own kernels; the frozen weights get no gradients.
+
+Everything with arithmetic in it is a kernel of libmetal_candle_b200 except the six batched attention
+contractions (Q K^T, P V and their reverses), which are plain library GEMMs (torch.bmm -> cuBLAS).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib, backend
+from .backend import TrainingError, _ptr, _stream
+from .training import LoRAAdapter, LoRALayer, TargetModule
+
+
+@dataclass
+class ModelConfig:
+    """The fields of src/models/config.rs:25-64 that the training path reads."""
+    vocab_size: int = 151936
+    hidden_size: int = 896
+    intermediate_size: int = 4864
+    num_hidden_layers: int = 24
+    num_attention_heads: int = 14
+    num_key_value_heads: int = 2
+    max_position_embeddings: int = 32768
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1_000_000.0
+
+    @staticmethod
+    def qwen25_05b() -> "ModelConfig":
+        return ModelConfig()
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def validate(self) -> None:
+        if self.hidden_size % self.num_attention_heads != 0:
+            raise TrainingError("hidden_size must be divisible by num_attention_heads")
+        if self.num_attention_heads % self.num_key_value_heads != 0:
+            raise TrainingError("num_attention_heads must be divisible by num_key_value_heads")
+        if self.head_dim % 2 != 0:
+            raise TrainingError("head_dim must be even")
+
+
+class _Linear:
+    """A frozen projection: W [out, in] (candle_nn::Linear's layout) plus its [in, out] copy for the
+    backward contraction, an optional bias, and an optional LoRA layer."""
+
+    def __init__(self, out_f: int, in_f: int, bias: bool, dtype, device, gen, std=0.02):
+        self.weight = (torch.randn(out_f, in_f, device=device, generator=gen) * std).to(dtype).contiguous()
+        self.weight_t = backend.transpose_2d(self.weight)
+        self.bias = torch.zeros(out_f, dtype=dtype, device=device) if bias else None
+        self.lora: Optional[LoRALayer] = None
+        self.in_f, self.out_f = in_f, out_f
+
+    def ab(self):
+        if self.lora is None:
+            return None, None, 1.0
+        return self.lora.lora_a, self.lora.lora_b, self.lora.config.scaling()
+
+
+class Qwen:
+    """Random-init weights N(0, 0.02^2) for embedding and projections, norm weights 1, biases 0."""
+
+    MODULES = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+    def __init__(self, config: ModelConfig, device, dtype=torch.bfloat16, seed: int = 0):
+        config.validate()
+        self.config = config
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise TrainingError("Qwen needs a CUDA device (this library has no CPU path)")
+        self.dtype = dtype
+        self.lib = _lib.init(self.device.index or 0)
+        self.dt = backend._dtype_code(torch.empty(0, dtype=dtype))
+        c = config
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        H, I, kv = c.hidden_size, c.intermediate_size, c.kv_size
+        self.embed_tokens = (torch.randn(c.vocab_size, H, device=self.device, generator=g) * 0.02).to(dtype)
+        self.layers: List[Dict[str, object]] = []
+        for _ in range(c.num_hidden_layers):
+            L = dict(
+                input_layernorm=torch.ones(H, dtype=dtype, device=self.device),
+                post_attention_layernorm=torch.ones(H, dtype=dtype, device=self.device),
+                q_proj=_Linear(H, H, True, dtype, self.device, g), k_proj=_Linear(kv, H, True, dtype, self.device, g),
+                v_proj=_Linear(kv, H, True, dtype, self.device, g), o_proj=_Linear(H, H, False, dtype, self.device, g),
+                gate_proj=_Linear(I, H, False, dtype, self.device, g), up_proj=_Linear(I, H, False, dtype, self.device, g),
+                down_proj=_Linear(H, I, False, dtype, self.device, g))
+            self.layers.append(L)
+        self.norm = torch.ones(H, dtype=dtype, device=self.device)
+        self.lm_head = _Linear(c.vocab_size, H, False, dtype, self.device, g)
+        self.lora_adapter: Optional[LoRAAdapter] = None
+        self._grad_flat: Optional[torch.Tensor] = None
+        self._grad_views: List[torch.Tensor] = []
+        self._grad_slices: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.layer_done_hook = None  # called as hook(layer_idx) when a layer's LoRA gradients are final
+
+    # -- adapter management (Qwen::apply_adapter / remove_adapter, src/models/qwen.rs:150-175) --
+    def apply_adapter(self, adapter: LoRAAdapter) -> None:
+        c = self.config
+        for key, layer in adapter.layers():
+            _, idx, module = key.split(".")
+            lin: _Linear = self.layers[int(idx)][module]
+            if (layer.in_features, layer.out_features) != (lin.in_f, lin.out_f):
+                raise TrainingError(f"adapter {key} is {layer.in_features}x{layer.out_features} but the projection is "
+                                    f"{lin.in_f}x{lin.out_f} (size K/V adapters with kv_size={c.kv_size})")
+            lin.lora = layer
+        self.lora_adapter = adapter
+        n = sum(l.lora_a.numel() + l.lora_b.numel() for _, l in adapter.layers())
+        self._grad_flat = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self._grad_views, self._grad_slices, off = [], {}, 0
+        self._layer_ranges: Dict[int, Tuple[int, int]] = {}
+        for key, l in adapter.layers():
+            idx = int(key.split(".")[1])
+            start = off
+            ga = self._grad_flat[off:off + l.lora_a.numel()].view_as(l.lora_a)
+            off += l.lora_a.numel()
+            gb = self._grad_flat[off:off + l.lora_b.numel()].view_as(l.lora_b)
+            off += l.lora_b.numel()
+            self._grad_views += [ga, gb]
+            self._grad_slices[key] = (ga, gb)
+            lo, hi = self._layer_ranges.get(idx, (start, start))
+            self._layer_ranges[idx] = (min(lo, start), off)
+
+    def remove_adapter(self) -> None:
+        for L in self.layers:
+            for m in self.MODULES:
+                L[m].lora = None
+        self.lora_adapter = None
+
+    def has_adapter(self) -> bool:
+        return self.lora_adapter is not None
+
+    def num_layers(self) -> int:
+        return self.config.num_hidden_layers
+
+    def grad_flat(self) -> torch.Tensor:
+        """All LoRA gradients as one float32 buffer (adapter order: layer, module, A then B)."""
+        return self._grad_flat
+
+    def grad_layer_range(self, layer_idx: int) -> Tuple[int, int]:
+        return self._layer_ranges[layer_idx]
+
+    # -- thin kernel wrappers --
+    def _norm(self, x, w):
+        return backend.rms_norm_fused(x, self.config.rms_norm_eps, weight=w)
+
+    def _lin(self, x, lin: _Linear, save: bool):
+        A, B, s = lin.ab()
+        return backend.lora_linear_forward(x, lin.weight, lin.bias, A, B, s, save_hidden=save and A is not None)
+
+    def _lin_bwd(self, x, lin: _Linear, dy, h_save, key: Optional[str], accumulate: bool):
+        A, B, s = lin.ab()
+        ga = gb = None
+        if A is not None:
+            ga, gb = self._grad_slices[key]
+        dx, _, _ = backend.lora_linear_backward(x, lin.weight_t, A, B, s, dy, h_save=h_save, grad_a=ga, grad_b=gb,
+                                                accumulate=accumulate)
+        return dx
+
+    def _rope(self, x, heads: int, B: int, S: int, rotate: bool, inverse: bool):
+        d = self.config.head_dim
+        out = torch.empty((B, heads, S, d) if not inverse else (B * S, heads * d), dtype=x.dtype, device=x.device)
+        _lib.check(self.lib.mcb_rope_relayout(_ptr(x), _ptr(out), B, S, heads, d, float(self.config.rope_theta),
+                                              int(rotate), int(inverse), self.dt, _stream()))
+        return out
+
+    def _add(self, a, b, out=None):
+        out = torch.empty_like(a) if out is None else out
+        _lib.check(self.lib.mcb_add(_ptr(a), _ptr(b), _ptr(out), a.numel(), self.dt, _stream()))
+        return out
+
+    def _embed(self, ids32: torch.Tensor) -> torch.Tensor:
+        M = ids32.numel()
+        out = torch.empty(M, self.config.hidden_size, dtype=self.dtype, device=self.device)
+        _lib.check(self.lib.mcb_embedding_fwd(_ptr(ids32), _ptr(self.embed_tokens), _ptr(out), M, self.config.hidden_size,
+                                              self.config.vocab_size, self.dt, _stream()))
+        return out
+
+    # -- attention core on [B,H,S,d] tensors; grouped-query heads are folded into the row dimension --
+    def _attention_fwd(self, Qr, Kr, Vr, B, S):
+        c = self.config
+        Hk, G, d = c.num_key_value_heads, c.num_attention_heads // c.num_key_value_heads, c.head_dim
+        scores = torch.bmm(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d).transpose(1, 2))  # [B*Hk, G*S, S]
+        rows = scores.numel() // S
+        _lib.check(self.lib.mcb_softmax_causal_fwd(_ptr(scores), _ptr(scores), rows, S, S, 1.0 / math.sqrt(d), self.dt,
+                                                   _stream()))
+        O = torch.bmm(scores, Vr.view(B * Hk, S, d))  # [B*Hk, G*S, d] == [B, Hq, S, d]
+        return scores, O
+
+    def _attention_bwd(self, Qr, Kr, Vr, P, dO, B, S):
+        c = self.config
+        Hk, G, d = c.num_key_value_heads, c.num_attention_heads // c.num_key_value_heads, c.head_dim
+        dO3 = dO.view(B * Hk, G * S, d)
+        dV = torch.bmm(P.transpose(1, 2), dO3)                       # [B*Hk, S, d], summed over the group
+        dP = torch.bmm(dO3, Vr.view(B * Hk, S, d).transpose(1, 2))   # [B*Hk, G*S, S]
+        rows = dP.numel() // S
+        _lib.check(self.lib.mcb_softmax_scaled_bwd(_ptr(P), _ptr(dP), _ptr(dP), rows, S, 1.0 / math.sqrt(d), self.dt,
+                                                   _stream()))
+        dQ = torch.bmm(dP, Kr.view(B * Hk, S, d))                    # [B*Hk, G*S, d]
+        dK = torch.bmm(dP.transpose(1, 2), Qr.view(B * Hk, G * S, d))  # [B*Hk, S, d]
+        return dQ, dK, dV
+
+    # -- forward --
+    def _layer_fwd(self, h, L, B, S, save: bool):
+        c = self.config
+        n1 = self._norm(h, L["input_layernorm"])
+        q, hq = self._lin(n1, L["q_proj"], save)
+        k, hk = self._lin(n1, L["k_proj"], save)
+        v, hv = self._lin(n1, L["v_proj"], save)
+        Qr = self._rope(q, c.num_attention_heads, B, S, True, False)
+        Kr = self._rope(k, c.num_key_value_heads, B, S, True, False)
+        Vr = self._rope(v, c.num_key_value_heads, B, S, False, False)
+        del q, k, v
+        P, O = self._attention_fwd(Qr, Kr, Vr, B, S)
+        o = self._rope(O, c.num_attention_heads, B, S, False, True)   # back to [M, hidden]
+        del O
+        a, ho = self._lin(o, L["o_proj"], save)
+        h2 = self._add(h, a)
+        del a
+        n2 = self._norm(h2, L["post_attention_layernorm"])
+        gt, hg = self._lin(n2, L["gate_proj"], save)
+        up, hu = self._lin(n2, L["up_proj"], save)
+        act = torch.empty_like(gt)
+        _lib.check(self.lib.mcb_swiglu_fwd(_ptr(gt), _ptr(up), _ptr(act), gt.numel(), self.dt, _stream()))
+        dn, hd = self._lin(act, L["down_proj"], save)
+        h3 = self._add(h2, dn)
+        if not save:
+            return h3, None
+        keep_n2 = L["gate_proj"].lora is not None or L["up_proj"].lora is not None
+        keep_act = L["down_proj"].lora is not None
+        saved = dict(h=h, n1=n1, Qr=Qr, Kr=Kr, Vr=Vr, P=P, o=o, h2=h2, n2=n2 if keep_n2 else None, gate=gt, up=up,
+                     act=act if keep_act else None, hq=hq, hk=hk, hv=hv, ho=ho, hg=hg, hu=hu, hd=hd)
+        return h3, saved
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Qwen::forward (src/models/qwen.rs:236-251) with a causal mask: logits [B, S, vocab]."""
+        B, S = input_ids.shape
+        h = self._embed(input_ids.to(torch.int32).contiguous().view(-1))
+        for L in self.layers:
+            h, _ = self._layer_fwd(h, L, B, S, save=False)
+        nf = self._norm(h, self.norm)
+        logits, _ = self._lin(nf, self.lm_head, False)
+        return logits.view(B, S, -1)
+
+    # -- forward + loss + backward --
+    def forward_backward(self, input_ids: torch.Tensor, target_ids: torch.Tensor, accumulate: bool = False):
+        """One pass of the training step's first three stages (src/training/trainer.rs:380-388): returns
+        (loss, grads) with loss a 1-element float32 CUDA tensor (mean next-token cross-entropy over
+        targets != u32::MAX) and grads the LoRA gradients in `TrainingStep.collect_trainable_vars` order.
+        With accumulate=True the gradients are added to what the buffers hold (micro-batching)."""
+        if self.lora_adapter is None:
+            raise TrainingError("forward_backward needs an adapter (apply_adapter)")
+        c = self.config
+        B, S = input_ids.shape
+        M = B * S
+        ids32 = input_ids.to(torch.int32).contiguous().view(-1)
+        tgt32 = target_ids.to(torch.int32).contiguous().view(-1)  # u32::MAX wraps to -1 = ignored
+        h = self._embed(ids32)
+        saved = []
+        for L in self.layers:
+            h, sv = self._layer_fwd(h, L, B, S, save=True)
+            saved.append(sv)
+        nf = self._norm(h, self.norm)
+        logits, _ = self._lin(nf, self.lm_head, False)
+        nll = torch.empty(M, dtype=torch.float32, device=self.device)
+        count = torch.empty(1, dtype=torch.int32, device=self.device)
+        loss = torch.empty(2, dtype=torch.float32, device=self.device)
+        _lib.check(self.lib.mcb_cross_entropy(_ptr(logits), _ptr(tgt32), _ptr(nll), _ptr(count), _ptr(loss), M,
+                                              c.vocab_size, 1, self.dt, _stream()))
+        self.last_count = count
+        # backward
+        dnf = self._lin_bwd(nf, self.lm_head, logits, None, None, False)
+        del logits
+        dh, _ = backend.rms_norm_backward(h, self.norm, dnf, c.rms_norm_eps, need_dw=False)
+        del dnf
+        for idx in range(len(self.layers) - 1, -1, -1):
+            dh = self._layer_bwd(dh, self.layers[idx], saved[idx], idx, B, S, accumulate)
+            saved[idx] = None
+            if self.layer_done_hook is not None:
+                self.layer_done_hook(idx)
+        return loss[:1], self._grad_views
+
+    def _layer_bwd(self, dh3, L, sv, idx, B, S, accumulate):
+        c = self.config
+        key = lambda m: f"layers.{idx}.{m}"
+        # MLP
+        dact = self._lin_bwd(sv["act"], L["down_proj"], dh3, sv["hd"], key("down_proj"), accumulate)
+        gt, up = sv["gate"], sv["up"]
+        _lib.check(self.lib.mcb_swiglu_bwd(_ptr(gt), _ptr(up), _ptr(dact), _ptr(gt), _ptr(up), gt.numel(), self.dt,
+                                           _stream()))  # in place: gate <- d gate, up <- d up
+        del dact
+        dn2 = self._lin_bwd(sv["n2"], L["gate_proj"], gt, sv["hg"], key("gate_proj"), accumulate)
+        dn2b = self._lin_bwd(sv["n2"], L["up_proj"], up, sv["hu"], key("up_proj"), accumulate)
+        self._add(dn2, dn2b, out=dn2)
+        del dn2b
+        dx2, _ = backend.rms_norm_backward(sv["h2"], L["post_attention_layernorm"], dn2, c.rms_norm_eps, need_dw=False)
+        dh2 = self._add(dh3, dx2, out=dx2)
+        # attention
+        do = self._lin_bwd(sv["o"], L["o_proj"], dh2, sv["ho"], key("o_proj"), accumulate)
+        dO = self._rope(do, c.num_attention_heads, B, S, False, False)
+        del do
+        dQ, dK, dV = self._attention_bwd(sv["Qr"], sv["Kr"], sv["Vr"], sv["P"], dO, B, S)
+        dq = self._rope(dQ, c.num_attention_heads, B, S, True, True)
+        dk = self._rope(dK, c.num_key_value_heads, B, S, True, True)
+        dv = self._rope(dV, c.num_key_value_heads, B, S, False, True)
+        del dQ, dK, dV, dO
+        n1 = sv["n1"]
+        dn1 = self._lin_bwd(n1, L["q_proj"], dq, sv["hq"], key("q_proj"), accumulate)
+        t = self._lin_bwd(n1, L["k_proj"], dk, sv["hk"], key("k_proj"), accumulate)
+        self._add(dn1, t, out=dn1)
+        t = self._lin_bwd(n1, L["v_proj"], dv, sv["hv"], key("v_proj"), accumulate)
+        self._add(dn1, t, out=dn1)
+        dx1, _ = backend.rms_norm_backward(sv["h"], L["input_layernorm"], dn1, c.rms_norm_eps, need_dw=False)
+        return self._add(dh2, dx1, out=dx1)

@@ -1,0 +1,65 @@
+"""CPU checks of the C-ABI boundary: the library loads without a GPU, exports every symbol that
+include/mcb200.h declares, and refuses to run without a CUDA device (no CPU fallback)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "mcb200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mcb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from metal_candle_b200 import _lib
+
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in mcb200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes prototype"
+    assert set(_lib.SIGNATURES) == set(names)
+    assert lib.mcb_version() >= 100
+
+
+def test_no_cpu_fallback():
+    import torch
+
+    from metal_candle_b200 import _lib, backend
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    lib = _lib.load()
+    assert lib.mcb_init(0) != 0
+    assert b"no CPU path" in lib.mcb_last_error() or b"CUDA" in lib.mcb_last_error()
+    # the ops reject host tensors instead of computing on the CPU
+    with pytest.raises(backend.TrainingError):
+        backend.softmax_fused(torch.zeros(2, 4))
+    with pytest.raises(backend.TrainingError):
+        backend.rms_norm_fused(torch.zeros(2, 4), 1e-5)
+    with pytest.raises(backend.TrainingError):
+        backend.lora_forward_fused(torch.zeros(2, 4), torch.zeros(4, 2), torch.zeros(2, 4), 1.0)
+
+
+def test_pure_host_helpers():
+    from metal_candle_b200 import _lib
+
+    lib = _lib.load()
+    assert [lib.mcb_lora_rank_padded(r) for r in (0, 1, 8, 16, 17, 64)] == [0, 16, 16, 16, 32, 64]
+    assert lib.mcb_lora_workspace_bytes(512, 768, 768, 8, _lib.MCB_F32) == 2 * 512 * 16 * 4
+    assert [lib.mcb_lora_h_pitch(m) for m in (1, 64, 65, 8192)] == [64, 64, 128, 8192]
+    assert lib.mcb_lora_workspace_bytes(512, 768, 768, 8, _lib.MCB_BF16) % 1024 == 0
+    assert lib.mcb_lora_workspace_bytes(512, 768, 768, 0, _lib.MCB_BF16) == 0
+    assert lib.mcb_rmsnorm_bwd_workspace_bytes(1000, 896) >= 296 * 896 * 4
+
+
+def test_product_never_imports_oracle():
+    for py in (ROOT / "metal_candle_b200").rglob("*.py"):
+        src = py.read_text()
+        assert "import oracle" not in src and "from oracle" not in src, py
