@@ -258,6 +258,81 @@ def micro_adamw(torch, n, n_tensors=1, iters=20, warmup=5):
                          "frac": gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"]}}
 
 
+# ---- CPU legs: the only code outside tests/ and smoke() that touches oracle/ ------------------------------
+def cpu_baseline(wl: dict, steps: int, warmup: int):
+    """The torch-CPU restatement of the reference's step (oracle/qwen_oracle.py, float32) timed on the host
+    cores on a bounded sample of the workload: ONE sequence of 512 tokens through the full 24-layer model."""
+    import numpy as np
+    import torch
+
+    from oracle import qwen_oracle as QO
+    from oracle import reference_ops as R
+
+    from metal_candle_b200.qwen import ModelConfig
+
+    cfg = ModelConfig.qwen25_05b()
+    S = 512
+    g = torch.Generator().manual_seed(0)
+    H, I, kv, V = cfg.hidden_size, cfg.intermediate_size, cfg.kv_size, cfg.vocab_size
+    w = {"embed_tokens": torch.randn(V, H, generator=g) * 0.02, "norm": torch.ones(H),
+         "lm_head": torch.randn(V, H, generator=g) * 0.02}
+    shapes = dict(q_proj=(H, H), k_proj=(kv, H), v_proj=(kv, H), o_proj=(H, H), gate_proj=(I, H), up_proj=(I, H),
+                  down_proj=(H, I))
+    lora = {}
+    for i in range(cfg.num_hidden_layers):
+        w[f"layers.{i}.input_layernorm"] = torch.ones(H)
+        w[f"layers.{i}.post_attention_layernorm"] = torch.ones(H)
+        for m, (o, n) in shapes.items():
+            w[f"layers.{i}.{m}.weight"] = torch.randn(o, n, generator=g) * 0.02
+            if m in ("q_proj", "k_proj", "v_proj"):
+                w[f"layers.{i}.{m}.bias"] = torch.zeros(o)
+            if m in wl["targets"]:
+                lora[f"layers.{i}.{m}"] = (torch.randn(n, wl["rank"], generator=g) * 0.03,
+                                           torch.zeros(wl["rank"], o))
+    orc = QO.QwenOracle(cfg, w, lora, wl["alpha"] / wl["rank"], dtype=torch.float32)
+    ids = torch.randint(0, V, (1, S), generator=g).numpy()
+    tg = np.concatenate([ids[:, 1:], np.full((1, 1), R.IGNORE_INDEX, dtype=np.int64)], 1)
+    opt = R.AdamWOracle(dtype=np.float32)
+
+    def step():
+        _, grads = orc.loss_and_grads(ids, tg)
+        for i, (p, gr) in enumerate(zip(orc.lora_params(), grads)):
+            new = opt.step(f"t{i}", p.detach().numpy(), gr)
+            with torch.no_grad():
+                p.copy_(torch.as_tensor(new))
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    return {"value": S * steps / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{steps} step(s) of 1 sequence x {S} tokens, full 24-layer model, float32, torch-CPU "
+                      "restatement of the reference's op sequence (the Rust reference cannot be built here)",
+            "ms_per_step": dt / steps * 1e3}
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU path (its torch-CPU restatement) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from metal_candle_b200.step_bench import WORKLOADS
+
+    wl = WORKLOADS[args.workload]
+    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    cb = cpu_baseline(wl, steps=steps, warmup=warmup)
+    line = {"impl": "reference", "metric": "LoRA fwd+bwd tokens/s, Qwen2.5-0.5B shape", "value": cb["value"],
+            "unit": "tokens/s", "n_gpus": max(1, args.gpus), "steps": steps, "warmup": warmup,
+            "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl["name"], "sample": cb["sample"]},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
 C3_SHAPES = [(896, 896), (896, 128), (2048, 2048), (4096, 4096), (4096, 14336)]
 
 
@@ -325,9 +400,11 @@ def main():
     args = ap.parse_args()
     if args.micro or args.sweep:
         return run_micro(args)
+    if args.impl == "reference":
+        return run_reference(args)
     from metal_candle_b200 import step_bench  # the Qwen-shaped training-step benchmark
 
-    return step_bench.main(args)
+    return step_bench.run_b200(args, ClockSampler, measured_peaks, cpu_baseline)
 
 
 if __name__ == "__main__":
