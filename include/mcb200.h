@@ -125,6 +125,22 @@ int mcb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, floa
                     int64_t rows, int64_t D, float eps, int dtype,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same reverse pass for callers that cannot allocate device memory at all -- for example a host
+ * runtime that has already handed every byte of the GPU to its own memory pool, or a service thread that
+ * must never hit the device-wide synchronisation an allocation implies -- and so can neither cudaMalloc a
+ * workspace nor size one in advance.  It has no counterpart in the reference.  The partial sums of dw go
+ * into a 2 MiB array compiled into the library (128 blocks x 4096 columns of float32), which every GPU
+ * that loads the library keeps until the process exits; the call itself runs no cudaMalloc/cudaFree and
+ * no allocating library routine.  Limits: D <= 4096, rows 16-byte aligned with D a multiple of 8 (bf16)
+ * or 4 (f32); anything larger is refused with MCB_ERR_SHAPE / MCB_ERR_ALIGN -- use mcb_rmsnorm_bwd then.
+ * The first call on each device looks up the array's device address (with that device current); make
+ * that first call before starting any stream capture.  All calls on a device share the one array, which
+ * keeps whatever the previous call left in it (each call overwrites the part it reads, nothing has to
+ * be cleared): two calls whose kernels overlap on the GPU -- different streams, or different host threads
+ * -- race on it, so serialise them. */
+int mcb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
+                            int64_t rows, int64_t D, float eps, int dtype, void* stream);
+
 /* ---- softmax ------------------------------------------------------------------------------ */
 
 /* Replaces FusedSoftmaxOp / softmax_fused (src/backend/custom_ops.rs:644-824, kernels.metal:187-261)

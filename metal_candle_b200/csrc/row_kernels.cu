@@ -683,3 +683,70 @@ extern "C" int mcb_softmax_scaled_bwd(const void* y, const void* dy, void* dx, i
   return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, scale, st, ds)
                           : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, scale, st, ds);
 }
+
+// ---- RMSNorm backward for callers that cannot allocate ------------------------------------------------
+// The per-block partial sums of dw live in this fixed device array instead of a caller workspace.  Every
+// GPU that loads the library holds these 2 MiB until the process exits.
+constexpr int kNoAllocMaxBlocks = 128;
+constexpr int kNoAllocMaxD = 4096;
+static __device__ __align__(256) float g_rmsnorm_dw_scratch[kNoAllocMaxBlocks * kNoAllocMaxD];
+
+namespace {
+// Device address of the array above, per device; filled on the first call on that device.
+float* g_noalloc_scratch_ptr[64] = {};
+
+template <typename T>
+int rmsnorm_bwd_noalloc_t(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
+                          int64_t rows, int64_t D, float eps, float* scratch, cudaStream_t st, const mcb::DeviceState* ds) {
+  using namespace mcb;
+  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && (w == nullptr || aligned16(w));
+  RowPlan p = plan_rows<T>(D, al);
+  if (p.tpr == 0)
+    return fail(MCB_ERR_ALIGN, "rmsnorm_bwd_noalloc: rows must be 16-byte aligned and D a multiple of %d", Vec16<T>::N);
+  int nblocks = bwd_blocks(rows, p.tpr, ds->sm_count);
+  if (nblocks > kNoAllocMaxBlocks) nblocks = kNoAllocMaxBlocks;
+  const int rpb = (p.tpr < 256 ? 256 : p.tpr) / p.tpr;
+  const size_t smem = (dw != nullptr && rpb > 1) ? static_cast<size_t>(rpb) * D * sizeof(float) : 0;
+#define CALL(TPR, VPT)                                                                     \
+  rmsnorm_bwd_kernel<T, TPR, VPT><<<nblocks, RowGeom<TPR>::THREADS, smem, st>>>(           \
+      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, dw ? scratch : nullptr, rows, (int)D, eps)
+  MCB_ROW_DISPATCH(p, CALL)
+#undef CALL
+  MCB_CHECK_LAUNCH("rmsnorm_bwd_noalloc");
+  if (dw != nullptr) {
+    // every block wrote its whole row of partials above, so nothing stale from an earlier call is read
+    colsum_partials_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(scratch, dw, nblocks, (int)D, accumulate);
+    MCB_CHECK_LAUNCH("rmsnorm_dw_reduce_noalloc");
+  }
+  return MCB_OK;
+}
+}  // namespace
+
+extern "C" int mcb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
+                                       int64_t rows, int64_t D, float eps, int dtype, void* stream) {
+  using namespace mcb;
+  if (!x || !dy || !dx) return fail(MCB_ERR_NULL, "rmsnorm_bwd_noalloc: x, dy or dx is null");
+  if (int rc = check_rows("rmsnorm_bwd_noalloc", rows, D, dtype)) return rc;
+  if (D > kNoAllocMaxD)
+    return fail(MCB_ERR_SHAPE, "rmsnorm_bwd_noalloc: D=%lld exceeds the built-in scratch limit of %d columns; "
+                "use mcb_rmsnorm_bwd with a caller workspace", (long long)D, kNoAllocMaxD);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  int dev = 0;
+  MCB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MCB_ERR_SHAPE, "rmsnorm_bwd_noalloc: device %d out of range", dev);
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    // First call on this device: ask the runtime where the array lives on the CURRENT device.  (The symbol's
+    // name in host code is only a handle; passing it to a kernel directly would not be a device address.)
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_rmsnorm_dw_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_rmsnorm_dw_scratch)");
+    if (ptr == nullptr) return fail(MCB_ERR_UNSUPPORTED, "rmsnorm_bwd_noalloc: scratch symbol has no device address");
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == MCB_F32
+             ? rmsnorm_bwd_noalloc_t<float>(x, w, dy, dx, dw, accumulate, rows, D, eps, scratch, st, ds)
+             : rmsnorm_bwd_noalloc_t<__nv_bfloat16>(x, w, dy, dx, dw, accumulate, rows, D, eps, scratch, st, ds);
+}
