@@ -110,6 +110,17 @@ int64_t mcb_lora_h_pitch(int64_t M);
 /* dst[cols,rows] = src[rows,cols]^T; makes the [K,N] copy of a frozen weight for the backward. */
 int mcb_transpose_2d(const void* src, void* dst, int64_t rows, int64_t cols, int dtype, void* stream);
 
+/* ---- lazy-graph primitives (Operation::{Matmul, Add, Mul, MulScalar}, src/graph/executor.rs:71-120) ---- */
+
+/* out[M,N] = a[M,K] b[K,N] (Tensor::broadcast_matmul with a 2-D right operand).  The bf16 path transposes b
+ * into `workspace` (mcb_matmul_workspace_bytes) and runs the tensor-core kernel. */
+size_t mcb_matmul_workspace_bytes(int64_t K, int64_t N, int dtype);
+int mcb_matmul(const void* a, const void* b, void* out, int64_t M, int64_t K, int64_t N, int dtype,
+               void* workspace, size_t workspace_bytes, void* stream);
+/* out = a * b element-wise; out = a * value. */
+int mcb_mul(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
+int mcb_mul_scalar(const void* a, void* out, int64_t n, float value, int dtype, void* stream);
+
 /* ---- RMSNorm ------------------------------------------------------------------------------ */
 
 /* Replaces FusedRMSNormOp / rms_norm_fused (src/backend/custom_ops.rs:443-632, kernels.metal:281-330)

@@ -46,6 +46,10 @@ SIGNATURES = {
     "mcb_lora_rank_padded": (_i64, [_i64]),
     "mcb_lora_h_pitch": (_i64, [_i64]),
     "mcb_transpose_2d": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
+    "mcb_matmul_workspace_bytes": (_sz, [_i64, _i64, _i32]),
+    "mcb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "mcb_mul": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "mcb_mul_scalar": (_i32, [_vp, _vp, _i64, _f32, _i32, _vp]),
     "mcb_rmsnorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
     "mcb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "mcb_rmsnorm_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),

@@ -56,12 +56,14 @@ _ws_cache = {}
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer that only grows (1024-byte aligned, as the bf16 GEMM requires)."""
+    """A per-device scratch buffer that only grows.  The returned view starts on a 1024-byte boundary (the
+    bf16 GEMM requires it; torch's allocator only promises 512)."""
     key = (device.type, device.index)
     buf = _ws_cache.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        assert buf.data_ptr() % 1024 == 0
+        raw = torch.empty(max(nbytes, 1 << 20) + 1024, dtype=torch.uint8, device=device)
+        off = (-raw.data_ptr()) % 1024
+        buf = raw[off:off + max(nbytes, 1 << 20)]
         _ws_cache[key] = buf
     return buf
 

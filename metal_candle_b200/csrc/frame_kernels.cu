@@ -128,6 +128,23 @@ __global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* 
   }
 }
 
+template <typename T>
+__global__ void add_scalar_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    out[i] = from_f32<T>(to_f32(a[i]) + to_f32(b[i]));
+}
+
+// out = a * b (mode 0) or out = a * scalar (mode 1): Operation::Mul / Operation::MulScalar of the lazy graph
+// (src/graph/executor.rs:97-120).
+template <typename T>
+__global__ void mul_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n, float scalar,
+                           int mode) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    out[i] = from_f32<T>(to_f32(a[i]) * (mode == 0 ? to_f32(b[i]) : scalar));
+}
+
 // ---- cross-entropy forward + backward (src/training/loss.rs:97-146) ----------------------------------------
 // One block per row of logits [M,V].  Sweep 1: online max / sum-exp (HBM read).  Sweep 2 (the row is in
 // L2 by now): overwrite the row with d loss / d logits = (softmax - onehot) * inv_count; ignored rows get
@@ -321,14 +338,41 @@ extern "C" int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout
 
 extern "C" int mcb_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream) {
   if (!a || !b || !out) return fail(MCB_ERR_NULL, "add: null pointer");
-  if (n <= 0 || n % 8 != 0) return fail(MCB_ERR_SHAPE, "add: element count must be a positive multiple of 8");
-  if (!aligned16(a) || !aligned16(b) || !aligned16(out)) return fail(MCB_ERR_ALIGN, "add: 16-byte alignment");
+  if (n <= 0) return fail(MCB_ERR_SHAPE, "add: element count must be positive");
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = grid_for(n / 4, 256, ds->sm_count);
-  MCB_DTYPE_SWITCH(dtype, (add_kernel<T><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)out, n)));
+  const int grid = grid_for(n / 4 + 1, 256, ds->sm_count);
+  if (n % 8 != 0 || !aligned16(a) || !aligned16(b) || !aligned16(out)) {
+    MCB_DTYPE_SWITCH(dtype, (add_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)out, n)));
+  } else {
+    MCB_DTYPE_SWITCH(dtype, (add_kernel<T><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)out, n)));
+  }
   MCB_CHECK_LAUNCH("add");
+  return MCB_OK;
+}
+
+extern "C" int mcb_mul(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream) {
+  if (!a || !b || !out) return fail(MCB_ERR_NULL, "mul: null pointer");
+  if (n <= 0) return fail(MCB_ERR_SHAPE, "mul: element count must be positive");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n, 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (mul_kernel<T><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)out, n, 0.0f, 0)));
+  MCB_CHECK_LAUNCH("mul");
+  return MCB_OK;
+}
+
+extern "C" int mcb_mul_scalar(const void* a, void* out, int64_t n, float value, int dtype, void* stream) {
+  if (!a || !out) return fail(MCB_ERR_NULL, "mul_scalar: null pointer");
+  if (n <= 0) return fail(MCB_ERR_SHAPE, "mul_scalar: element count must be positive");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n, 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (mul_kernel<T><<<grid, 256, 0, st>>>((const T*)a, (const T*)a, (T*)out, n, value, 1)));
+  MCB_CHECK_LAUNCH("mul_scalar");
   return MCB_OK;
 }
 

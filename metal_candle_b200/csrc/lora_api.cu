@@ -87,3 +87,25 @@ extern "C" int mcb_lora_linear_bwd(const void* x, const void* W, const float* A,
   a.stream = static_cast<cudaStream_t>(stream);
   return dtype == MCB_F32 ? f32path::linear_bwd(a) : bf16path::linear_bwd(a, ds);
 }
+
+extern "C" size_t mcb_matmul_workspace_bytes(int64_t K, int64_t N, int dtype) {
+  if (K <= 0 || N <= 0 || dtype != MCB_BF16) return 0;
+  return static_cast<size_t>(K) * static_cast<size_t>(N) * 2;
+}
+
+extern "C" int mcb_matmul(const void* a, const void* b, void* out, int64_t M, int64_t K, int64_t N, int dtype,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  if (!a || !b || !out) return fail(MCB_ERR_NULL, "matmul: null pointer");
+  if (M <= 0 || K <= 0 || N <= 0) return fail(MCB_ERR_SHAPE, "matmul: M=%lld K=%lld N=%lld must be positive", (long long)M, (long long)K, (long long)N);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MCB_F32)
+    return f32path::matmul(static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(out), M, K, N, st);
+  if (dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "matmul: dtype %d", dtype);
+  // tensor cores want both operands with the reduction index contiguous: transpose b into the workspace
+  if (!workspace || workspace_bytes < mcb_matmul_workspace_bytes(K, N, dtype))
+    return fail(MCB_ERR_WORKSPACE, "matmul(bf16): workspace %zu < %zu bytes", workspace_bytes, mcb_matmul_workspace_bytes(K, N, dtype));
+  if (int rc = mcb_transpose_2d(b, workspace, K, N, dtype, stream)) return rc;
+  return bf16path::matmul_nt(a, workspace, out, M, K, N, ds, st);
+}

@@ -36,6 +36,8 @@ size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a);
 int linear_fwd(const LoraArgs& a);
 int linear_bwd(const LoraArgs& a);
+// out[M,N] = a[M,K] b[K,N]
+int matmul(const float* a, const float* b, float* out, int64_t M, int64_t K, int64_t N, cudaStream_t st);
 }  // namespace f32path
 
 namespace bf16path {
@@ -43,6 +45,9 @@ size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_bwd(const LoraArgs& a, const DeviceState* ds);
+// out[M,N] = a[M,K] bt[N,K]^T (bt is b transposed, both operands K-major)
+int matmul_nt(const void* a, const void* bt, void* out, int64_t M, int64_t K, int64_t N, const DeviceState* ds,
+              cudaStream_t st);
 }  // namespace bf16path
 
 }  // namespace mcb

@@ -80,6 +80,10 @@ int sgemm(cudaStream_t st, const float* A, int64_t sam, int64_t sak, const float
 
 }  // namespace
 
+int matmul(const float* a, const float* b, float* out, int64_t M, int64_t K, int64_t N, cudaStream_t st) {
+  return sgemm(st, a, K, 1, b, N, 1, out, N, M, N, K, 1.0f, 0.0f, nullptr);
+}
+
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r) {
   (void)K; (void)N;
   return (static_cast<size_t>(M) + static_cast<size_t>(h_pitch(M))) * static_cast<size_t>(rank_padded(r)) * sizeof(float);

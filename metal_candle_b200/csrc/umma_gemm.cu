@@ -603,6 +603,16 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
   return MCB_OK;
 }
 
+int matmul_nt(const void* a, const void* bt, void* out, int64_t M, int64_t K, int64_t N, const DeviceState* ds,
+              cudaStream_t st) {
+  GemmCall c;
+  c.X = static_cast<const __nv_bfloat16*>(a);
+  c.W = static_cast<const __nv_bfloat16*>(bt);
+  c.Y = static_cast<__nv_bfloat16*>(out);
+  c.M = M; c.N = N; c.K = K;
+  return launch_gemm(c, ds, st);
+}
+
 }  // namespace bf16path
 
 int init_gemm_kernels() { return bf16path::init_kernels(); }

@@ -415,6 +415,41 @@ class StepMetrics:
     learning_rate: float
 
 
+IGNORE_INDEX = 0xFFFFFFFF  # u32::MAX, what TrainingStep passes (src/training/trainer.rs:385)
+
+
+def cross_entropy_loss(logits: torch.Tensor, targets: torch.Tensor, ignore_index: Optional[int] = None,
+                       return_grad: bool = False):
+    """cross_entropy_loss (src/training/loss.rs:58-147): mean over non-ignored tokens of
+    -log_softmax(logits)[target].  logits [batch, seq, vocab], targets [batch, seq] integer.  Returns a
+    1-element float32 CUDA tensor; with return_grad also d loss / d logits (the logits are left untouched)."""
+    ls, ts = tuple(logits.shape), tuple(targets.shape)
+    if len(ls) != 3:
+        raise InvalidConfig(f"logits must be 3D (batch, seq_len, vocab_size), got shape {list(ls)}")
+    if len(ts) != 2:
+        raise InvalidConfig(f"targets must be 2D (batch, seq_len), got shape {list(ts)}")
+    if ls[0] != ts[0] or ls[1] != ts[1]:
+        raise InvalidConfig(f"logits and targets batch/seq_len mismatch: logits {list(ls[:2])} vs targets {list(ts)}")
+    backend._require_cuda(logits.contiguous(), targets.contiguous())
+    M, V = ls[0] * ls[1], ls[2]
+    t = targets.contiguous().view(-1).to(torch.int64)
+    if ignore_index is not None:
+        t = torch.where(t == ignore_index, torch.full_like(t, -1), t)
+    if bool(((t >= V) | ((t < 0) & (t != -1))).any()):
+        raise TrainingError(f"target index out of range for vocab size {V}")
+    t32 = t.to(torch.int32)
+    work = logits.contiguous().clone() if return_grad else logits.contiguous()
+    lib = backend._lib_for(work)
+    nll = torch.empty(M, dtype=torch.float32, device=work.device)
+    count = torch.empty(1, dtype=torch.int32, device=work.device)
+    loss = torch.empty(2, dtype=torch.float32, device=work.device)
+    _lib.check(lib.mcb_cross_entropy(work.data_ptr(), t32.data_ptr(), nll.data_ptr(), count.data_ptr(), loss.data_ptr(),
+                                     M, V, int(return_grad), backend._dtype_code(work), backend._stream()))
+    if int(count.item()) == 0:
+        raise InvalidConfig("all tokens are ignored, cannot compute loss")
+    return (loss[:1], work) if return_grad else loss[:1]
+
+
 class TrainingStep:
     """One optimisation step: forward, loss, backward, AdamW (src/training/trainer.rs:297-442).
 
@@ -449,3 +484,54 @@ class TrainingStep:
 
     def reset(self) -> None:
         self._step = 0
+
+
+class Trainer:
+    """Trainer (src/training/trainer.rs:60-259): owns the adapter, the optimiser and the step counter; `train`
+    runs epochs x batches with the configured LR schedule and prints the reference's progress lines.
+    `forward_backward_fn` has the contract described at TrainingStep."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_layers: int, lora_config: LoRAAdapterConfig,
+                 training_config: TrainingConfig, device, kv_size: Optional[int] = None,
+                 generator: Optional[torch.Generator] = None):
+        self._lora_adapter = LoRAAdapter(hidden_size, intermediate_size, num_layers, lora_config, device,
+                                         kv_size=kv_size, generator=generator)
+        self.optimizer = AdamW(training_config.optimizer_config)
+        self.config = training_config
+        self.training_step = TrainingStep()
+        self._global_step = 0
+
+    def train(self, dataset, forward_backward_fn: Callable, verbose: bool = True) -> List[StepMetrics]:
+        import time
+
+        say = print if verbose else (lambda *a, **k: None)
+        all_metrics: List[StepMetrics] = []
+        say("\nStarting LoRA Training")
+        say(f"Epochs: {self.config.num_epochs}")
+        say(f"Batches per epoch: {len(dataset)}")
+        say(f"Total steps: {self.config.num_epochs * len(dataset)}")
+        say(f"LoRA trainable params: {self._lora_adapter.num_trainable_parameters()}")
+        t_start = time.perf_counter()
+        for epoch in range(self.config.num_epochs):
+            t_epoch, epoch_loss = time.perf_counter(), 0.0
+            say(f"Epoch {epoch + 1}/{self.config.num_epochs}")
+            for batch_idx, (input_ids, target_ids) in enumerate(dataset):
+                lr = self.config.lr_scheduler.get_lr(self._global_step)
+                m = self.training_step.execute(input_ids, target_ids, self._lora_adapter, self.optimizer, lr,
+                                               forward_backward_fn)
+                epoch_loss += m.loss
+                all_metrics.append(m)
+                self._global_step += 1
+                if (batch_idx + 1) % 10 == 0 or batch_idx + 1 == len(dataset):
+                    say(f"  Step {batch_idx + 1}/{len(dataset)} | Loss: {m.loss:.4f} | LR: {m.learning_rate:.6f}")
+            say(f"  Epoch {epoch + 1} complete | Avg Loss: {epoch_loss / max(1, len(dataset)):.4f} | "
+                f"Time: {time.perf_counter() - t_epoch:.2f}s")
+        say(f"Training Complete! Total time: {time.perf_counter() - t_start:.2f}s")
+        say(f"Final loss: {all_metrics[-1].loss if all_metrics else 0.0:.4f}")
+        return all_metrics
+
+    def lora_adapter(self) -> LoRAAdapter:
+        return self._lora_adapter
+
+    def global_step(self) -> int:
+        return self._global_step
