@@ -222,6 +222,22 @@ def micro_rows(torch, op, rows, D, dtype, iters=20, warmup=5):
             B.softmax_backward(ys[i % nv], dys[i % nv], out=buf)
 
         cases = [("softmax fwd", fwd, 2 * rows * D * e), ("softmax bwd", bwd, 3 * rows * D * e)]
+        if rows % S == 0:
+            # the attention form: scale + causal mask inside the kernel, masked columns never read.  Reported
+            # against the same dense byte count (masked elements count as traffic in the contract).
+            lib = B._lib_for(xs[0])
+            code = B._dtype_code(xs[0])
+            st = torch.cuda.current_stream().cuda_stream
+
+            def cfwd(i):
+                lib.mcb_softmax_causal_fwd(xs[i % nv].data_ptr(), buf.data_ptr(), rows, D, S, 0.125, code, st)
+
+            def cbwd(i):
+                lib.mcb_softmax_causal_bwd(ys[i % nv].data_ptr(), dys[i % nv].data_ptr(), buf.data_ptr(), rows, D, S,
+                                           0.125, code, st)
+
+            cases += [("softmax causal fwd (dense-equivalent bytes)", cfwd, 2 * rows * D * e),
+                      ("softmax causal bwd (dense-equivalent bytes)", cbwd, 3 * rows * D * e)]
     pk = measured_peaks()
     for name, fn, by in cases:
         med, mn = _time_kernel(torch, fn, nv, iters, warmup)

@@ -169,9 +169,10 @@ int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64
  * (src/models/transformer.rs:264-275); the reference builds no mask itself (its callers pass one). */
 int mcb_softmax_causal_fwd(const void* x, void* y, int64_t rows, int64_t D, int64_t seq, float scale, int dtype,
                            void* stream);
-/* dx = scale * y * (dy - sum_j dy_j y_j): reverse of softmax(scale * x). */
-int mcb_softmax_scaled_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, float scale,
-                           int dtype, void* stream);
+/* Reverse of the call above: dx = scale * y * (dy - sum_j dy_j y_j), with the masked columns (where y
+ * is 0) neither read nor computed: they get 0.  seq = 0 means "no mask, scale only". */
+int mcb_softmax_causal_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int64_t seq,
+                           float scale, int dtype, void* stream);
 
 /* ---- AdamW -------------------------------------------------------------------------------- */
 

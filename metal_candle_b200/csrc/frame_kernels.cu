@@ -33,7 +33,57 @@ __global__ void embedding_fwd_kernel(const int32_t* __restrict__ ids, const T* _
 template <typename T>
 __global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int S, int H, int d,
                                      float theta, int rotate, int inverse) {
-  // one thread per (b, s, h, i) with i in [0, d/2)
+  // One thread owns a 16-byte chunk of the first half of a head (and the matching chunk of the second
+  // half) at one (batch, position), computes its sines and cosines once, and walks over the heads.
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  const int half = d / 2;
+  const int chunks = half / N;  // host guarantees half % N == 0
+  const int64_t total = static_cast<int64_t>(B) * S * chunks;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % chunks);
+    const int64_t bs = idx / chunks;
+    const int s = static_cast<int>(bs % S);
+    const int b = static_cast<int>(bs / S);
+    float cs[N], sn[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      if (rotate) {
+        // 1 / theta^(2i/d) as in the reference's table (float32 powf), angle = position * inv_freq
+        const int i = c * N + j;
+        const float inv_freq = 1.0f / powf(theta, static_cast<float>(2 * i) / static_cast<float>(d));
+        sincosf(static_cast<float>(s) * inv_freq, &sn[j], &cs[j]);
+        if (inverse) sn[j] = -sn[j];
+      } else {
+        cs[j] = 1.0f; sn[j] = 0.0f;
+      }
+    }
+    for (int h = 0; h < H; ++h) {
+      const int64_t bshd = ((static_cast<int64_t>(b) * S + s) * H + h) * d;   // [B,S,H,d]
+      const int64_t bhsd = ((static_cast<int64_t>(b) * H + h) * S + s) * d;   // [B,H,S,d]
+      const int64_t in = inverse ? bhsd : bshd, out = inverse ? bshd : bhsd;
+      V a, bb;
+      a.raw = *reinterpret_cast<const decltype(a.raw)*>(src + in + c * N);
+      bb.raw = *reinterpret_cast<const decltype(bb.raw)*>(src + in + half + c * N);
+      float x1[N], x2[N], o1[N], o2[N];
+      a.to_float(x1); bb.to_float(x2);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        o1[j] = x1[j] * cs[j] - x2[j] * sn[j];
+        o2[j] = x1[j] * sn[j] + x2[j] * cs[j];
+      }
+      a.from_float(o1); bb.from_float(o2);
+      *reinterpret_cast<decltype(a.raw)*>(dst + out + c * N) = a.raw;
+      *reinterpret_cast<decltype(bb.raw)*>(dst + out + half + c * N) = bb.raw;
+    }
+  }
+}
+
+// Scalar variant for head sizes whose half is not a multiple of the vector width.
+template <typename T>
+__global__ void rope_relayout_scalar_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int S, int H, int d,
+                                            float theta, int rotate, int inverse) {
   const int half = d / 2;
   const int64_t total = static_cast<int64_t>(B) * S * H * half;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -43,13 +93,12 @@ __global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ 
     const int h = static_cast<int>(t % H); t /= H;
     const int s = static_cast<int>(t % S);
     const int b = static_cast<int>(t / S);
-    const int64_t bshd = ((static_cast<int64_t>(b) * S + s) * H + h) * d;   // [B,S,H,d]
-    const int64_t bhsd = ((static_cast<int64_t>(b) * H + h) * S + s) * d;   // [B,H,S,d]
+    const int64_t bshd = ((static_cast<int64_t>(b) * S + s) * H + h) * d;
+    const int64_t bhsd = ((static_cast<int64_t>(b) * H + h) * S + s) * d;
     const int64_t in = inverse ? bhsd : bshd, out = inverse ? bshd : bhsd;
     const float x1 = to_f32(src[in + i]), x2 = to_f32(src[in + half + i]);
     float o1 = x1, o2 = x2;
     if (rotate) {
-      // 1 / theta^(2i/d) as in the reference's table (float32 powf), angle = position * inv_freq
       const float inv_freq = 1.0f / powf(theta, static_cast<float>(2 * i) / static_cast<float>(d));
       float sn, cs;
       sincosf(static_cast<float>(s) * inv_freq, &sn, &cs);
@@ -301,9 +350,15 @@ extern "C" int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t 
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t total = B * S * H * (d / 2);
-  const int grid = grid_for(total, 256, ds->sm_count);
-  MCB_DTYPE_SWITCH(dtype, (rope_relayout_kernel<T><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse)));
+  const int64_t half = d / 2;
+  const int vec_n = dtype == MCB_F32 ? 4 : 8;
+  if (half % vec_n == 0 && aligned16(src) && aligned16(dst)) {
+    const int grid = grid_for(B * S * (half / vec_n), 128, ds->sm_count);
+    MCB_DTYPE_SWITCH(dtype, (rope_relayout_kernel<T><<<grid, 128, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse)));
+  } else {
+    const int grid = grid_for(B * S * H * half, 256, ds->sm_count);
+    MCB_DTYPE_SWITCH(dtype, (rope_relayout_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse)));
+  }
   MCB_CHECK_LAUNCH("rope_relayout");
   return MCB_OK;
 }

@@ -20,14 +20,16 @@ namespace {
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ---- group reductions ---------------------------------------------------------------------
-// All threads of the block call these the same number of times (the row loop is block-uniform).
+// A group of TPR threads owns a row.  Up to a warp: shuffles only.  Wider groups add one shared-memory
+// hop synchronised with a named barrier of their own (bar.sync id, TPR), so groups in a block do not
+// wait for each other; the two halves of `red_smem` alternate between consecutive reductions, which is
+// what makes a single barrier per reduction enough.
 template <int TPR, int NV, bool IS_MAX>
-__device__ __forceinline__ void group_reduce(float (&v)[NV], float* red_smem) {
-  constexpr int SUB = TPR < 32 ? TPR : 32;
+__device__ __forceinline__ void group_reduce(float (&v)[NV], float* red_smem, int& parity) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
 #pragma unroll
-    for (int o = SUB / 2; o > 0; o >>= 1) {
+    for (int o = 16; o > 0; o >>= 1) {
       float other = __shfl_xor_sync(0xffffffffu, v[i], o);
       v[i] = IS_MAX ? fmaxf(v[i], other) : v[i] + other;
     }
@@ -35,18 +37,20 @@ __device__ __forceinline__ void group_reduce(float (&v)[NV], float* red_smem) {
   if constexpr (TPR > 32) {
     constexpr int WPG = TPR / 32;  // warps per group
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int group_first_warp = (warp / WPG) * WPG;
-    __syncthreads();  // previous use of red_smem is over
+    const int group = warp / WPG, group_first_warp = group * WPG;
+    float* buf = red_smem + parity * (32 * NV);
+    parity ^= 1;
     if (lane == 0) {
 #pragma unroll
-      for (int i = 0; i < NV; ++i) red_smem[warp * NV + i] = v[i];
+      for (int i = 0; i < NV; ++i) buf[warp * NV + i] = v[i];
     }
-    __syncthreads();
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(TPR) : "memory");
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      float acc = red_smem[group_first_warp * NV + i];
+      float acc = buf[group_first_warp * NV + i];
+#pragma unroll
       for (int w = 1; w < WPG; ++w) {
-        float other = red_smem[(group_first_warp + w) * NV + i];
+        float other = buf[(group_first_warp + w) * NV + i];
         acc = IS_MAX ? fmaxf(acc, other) : acc + other;
       }
       v[i] = acc;
@@ -60,6 +64,17 @@ struct RowGeom {
   static constexpr int RPB = THREADS / TPR;  // rows per block per iteration
 };
 
+template <typename V>
+__device__ __forceinline__ V load_stream(const void* base, int64_t vec_index) {
+  V t;
+  t.raw = __ldcs(reinterpret_cast<const decltype(t.raw)*>(base) + vec_index);
+  return t;
+}
+template <typename V>
+__device__ __forceinline__ void store_stream(void* base, int64_t vec_index, const V& t) {
+  __stcs(reinterpret_cast<decltype(t.raw)*>(base) + vec_index, t.raw);
+}
+
 // ---- RMSNorm forward ------------------------------------------------------------------------
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(RowGeom<TPR>::THREADS)
@@ -68,7 +83,8 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
   using V = Vec16<T>;
   constexpr int N = V::N;
   constexpr int RPB = RowGeom<TPR>::RPB;
-  __shared__ float red[32];
+  __shared__ float red[64];
+  int parity = 0;
   const int tg = threadIdx.x % TPR, g = threadIdx.x / TPR;
   const int nvec = D / N;
   float wv[VPT][N];
@@ -94,8 +110,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
     for (int i = 0; i < VPT; ++i) {
       const int vi = tg + i * TPR;
       if (live && vi < nvec) {
-        V t; t.raw = reinterpret_cast<const decltype(t.raw)*>(x + row * D)[vi];
-        t.to_float(xv[i]);
+        load_stream<V>(x + row * D, vi).to_float(xv[i]);
       } else {
 #pragma unroll
         for (int j = 0; j < N; ++j) xv[i][j] = 0.0f;
@@ -103,7 +118,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
 #pragma unroll
       for (int j = 0; j < N; ++j) ss[0] = fmaf(xv[i][j], xv[i][j], ss[0]);
     }
-    group_reduce<TPR, 1, false>(ss, red);
+    group_reduce<TPR, 1, false>(ss, red, parity);
     const float rinv = 1.0f / sqrtf(ss[0] * inv_d + eps);
     if (live) {
       if (rstd != nullptr && tg == 0) rstd[row] = rinv;
@@ -115,7 +130,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
 #pragma unroll
           for (int j = 0; j < N; ++j) o[j] = xv[i][j] * rinv * wv[i][j];
           V t; t.from_float(o);
-          reinterpret_cast<decltype(t.raw)*>(y + row * D)[vi] = t.raw;
+          store_stream<V>(y + row * D, vi, t);
         }
       }
     }
@@ -123,19 +138,20 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
 }
 
 // ---- RMSNorm backward -----------------------------------------------------------------------
-// dx = rinv * (g - xh * mean(g*xh)), g = dy*w, xh = x*rinv;  dw_partial[block][c] = sum dy*xh.
-template <typename T, int TPR, int VPT>
+// dx = rinv * (g - xh * mean(g*xh)), g = dy*w, xh = x*rinv;  dw_partial[block][c] = sum dy*xh (NEED_DW).
+template <typename T, int TPR, int VPT, bool NEED_DW>
 __global__ void __launch_bounds__(RowGeom<TPR>::THREADS)
 rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
                    T* __restrict__ dx, float* __restrict__ dw_partial, int64_t rows, int D, float eps) {
   using V = Vec16<T>;
   constexpr int N = V::N;
   constexpr int RPB = RowGeom<TPR>::RPB;
-  __shared__ float red[64];
+  __shared__ float red[128];
   extern __shared__ float dw_smem[];  // [RPB][D] when RPB > 1 and dw is wanted
+  int parity = 0;
   const int tg = threadIdx.x % TPR, g = threadIdx.x / TPR;
   const int nvec = D / N;
-  float wv[VPT][N], dwa[VPT][N];
+  float wv[VPT][N], dwa[NEED_DW ? VPT : 1][N];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int vi = tg + i * TPR;
@@ -146,8 +162,10 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
 #pragma unroll
       for (int j = 0; j < N; ++j) wv[i][j] = 1.0f;
     }
+    if constexpr (NEED_DW) {
 #pragma unroll
-    for (int j = 0; j < N; ++j) dwa[i][j] = 0.0f;
+      for (int j = 0; j < N; ++j) dwa[i][j] = 0.0f;
+    }
   }
   const float inv_d = 1.0f / static_cast<float>(D);
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * RPB; row0 < rows;
@@ -160,11 +178,8 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
     for (int i = 0; i < VPT; ++i) {
       const int vi = tg + i * TPR;
       if (live && vi < nvec) {
-        V a, b;
-        a.raw = reinterpret_cast<const decltype(a.raw)*>(x + row * D)[vi];
-        b.raw = reinterpret_cast<const decltype(b.raw)*>(dy + row * D)[vi];
-        a.to_float(xv[i]);
-        b.to_float(gv[i]);
+        load_stream<V>(x + row * D, vi).to_float(xv[i]);
+        load_stream<V>(dy + row * D, vi).to_float(gv[i]);
       } else {
 #pragma unroll
         for (int j = 0; j < N; ++j) { xv[i][j] = 0.0f; gv[i][j] = 0.0f; }
@@ -175,7 +190,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
         acc[1] = fmaf(gv[i][j] * wv[i][j], xv[i][j], acc[1]);
       }
     }
-    group_reduce<TPR, 2, false>(acc, red);
+    group_reduce<TPR, 2, false>(acc, red, parity);
     const float rinv = 1.0f / sqrtf(acc[0] * inv_d + eps);
     const float c = acc[1] * rinv * inv_d;  // mean(g * xh)
     if (live) {
@@ -187,41 +202,42 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
 #pragma unroll
           for (int j = 0; j < N; ++j) {
             const float xh = xv[i][j] * rinv;
-            dwa[i][j] = fmaf(gv[i][j], xh, dwa[i][j]);
+            if constexpr (NEED_DW) dwa[i][j] = fmaf(gv[i][j], xh, dwa[i][j]);
             o[j] = rinv * (gv[i][j] * wv[i][j] - xh * c);
           }
           V t; t.from_float(o);
-          reinterpret_cast<decltype(t.raw)*>(dx + row * D)[vi] = t.raw;
+          store_stream<V>(dx + row * D, vi, t);
         }
       }
     }
   }
-  if (dw_partial == nullptr) return;
-  float* out = dw_partial + static_cast<int64_t>(blockIdx.x) * D;
-  if constexpr (RPB == 1) {
+  if constexpr (NEED_DW) {
+    float* out = dw_partial + static_cast<int64_t>(blockIdx.x) * D;
+    if constexpr (RPB == 1) {
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = tg + i * TPR;
-      if (vi < nvec) {
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = tg + i * TPR;
+        if (vi < nvec) {
 #pragma unroll
-        for (int j = 0; j < N; ++j) out[vi * N + j] = dwa[i][j];
+          for (int j = 0; j < N; ++j) out[vi * N + j] = dwa[i][j];
+        }
       }
-    }
-  } else {
+    } else {
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = tg + i * TPR;
-      if (vi < nvec) {
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = tg + i * TPR;
+        if (vi < nvec) {
 #pragma unroll
-        for (int j = 0; j < N; ++j) dw_smem[g * D + vi * N + j] = dwa[i][j];
+          for (int j = 0; j < N; ++j) dw_smem[g * D + vi * N + j] = dwa[i][j];
+        }
       }
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-      float s = 0.0f;
+      __syncthreads();
+      for (int cc = threadIdx.x; cc < D; cc += blockDim.x) {
+        float s = 0.0f;
 #pragma unroll
-      for (int gg = 0; gg < RPB; ++gg) s += dw_smem[gg * D + c];  // fixed order: deterministic
-      out[c] = s;
+        for (int gg = 0; gg < RPB; ++gg) s += dw_smem[gg * D + cc];  // fixed order: deterministic
+        out[cc] = s;
+      }
     }
   }
 }
@@ -237,30 +253,31 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, float*
 }
 
 // ---- softmax forward --------------------------------------------------------------------------
+// causal_seq > 0: row i is query position i % causal_seq; columns beyond it are masked and are not even
+// read (their output is 0), and the kept scores are multiplied by `scale` first.
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(RowGeom<TPR>::THREADS)
 softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int D, int causal_seq, float scale) {
   using V = Vec16<T>;
   constexpr int N = V::N;
   constexpr int RPB = RowGeom<TPR>::RPB;
-  __shared__ float red[32];
+  __shared__ float red[64];
+  int parity = 0;
   const int tg = threadIdx.x % TPR, g = threadIdx.x / TPR;
   const int nvec = D / N;
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * RPB; row0 < rows;
        row0 += static_cast<int64_t>(gridDim.x) * RPB) {
     const int64_t row = row0 + g;
     const bool live = row < rows;
+    const int q = causal_seq > 0 ? static_cast<int>(row % causal_seq) : D;  // last kept column
     float xv[VPT][N];
     float mx[1] = {-INFINITY};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = tg + i * TPR;
-      if (live && vi < nvec) {
-        V t; t.raw = reinterpret_cast<const decltype(t.raw)*>(x + row * D)[vi];
-        t.to_float(xv[i]);
+      if (live && vi < nvec && vi * N <= q) {
+        load_stream<V>(x + row * D, vi).to_float(xv[i]);
         if (causal_seq > 0) {
-          // scaled scores with an additive causal mask: column c of query position q is kept iff c <= q
-          const int q = static_cast<int>(row % causal_seq);
 #pragma unroll
           for (int j = 0; j < N; ++j) xv[i][j] = (vi * N + j <= q) ? xv[i][j] * scale : -INFINITY;
         } else if (scale != 1.0f) {
@@ -274,7 +291,7 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
 #pragma unroll
       for (int j = 0; j < N; ++j) mx[0] = fmaxf(mx[0], xv[i][j]);
     }
-    group_reduce<TPR, 1, true>(mx, red);
+    group_reduce<TPR, 1, true>(mx, red, parity);
     // A fully masked row has max = -inf; use 0 so that exp2(-inf) = 0 instead of NaN.
     const float m = (mx[0] == -INFINITY) ? 0.0f : mx[0];
     float sum[1] = {0.0f};
@@ -286,7 +303,7 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
         sum[0] += xv[i][j];
       }
     }
-    group_reduce<TPR, 1, false>(sum, red);
+    group_reduce<TPR, 1, false>(sum, red, parity);
     const float inv = sum[0] > 0.0f ? 1.0f / sum[0] : 0.0f;
     if (live) {
 #pragma unroll
@@ -297,7 +314,7 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
 #pragma unroll
           for (int j = 0; j < N; ++j) o[j] = xv[i][j] * inv;
           V t; t.from_float(o);
-          reinterpret_cast<decltype(t.raw)*>(y + row * D)[vi] = t.raw;
+          store_stream<V>(y + row * D, vi, t);
         }
       }
     }
@@ -305,31 +322,32 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
 }
 
 // ---- softmax backward -------------------------------------------------------------------------
+// dx = scale * y * (dy - sum_j dy_j y_j).  causal_seq > 0: y is known to be 0 beyond the query position,
+// so those vectors of y and dy are not read and dx gets zeros there.
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(RowGeom<TPR>::THREADS)
 softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
-                   int64_t rows, int D, float scale) {
+                   int64_t rows, int D, int causal_seq, float scale) {
   using V = Vec16<T>;
   constexpr int N = V::N;
   constexpr int RPB = RowGeom<TPR>::RPB;
-  __shared__ float red[32];
+  __shared__ float red[64];
+  int parity = 0;
   const int tg = threadIdx.x % TPR, g = threadIdx.x / TPR;
   const int nvec = D / N;
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * RPB; row0 < rows;
        row0 += static_cast<int64_t>(gridDim.x) * RPB) {
     const int64_t row = row0 + g;
     const bool live = row < rows;
+    const int q = causal_seq > 0 ? static_cast<int>(row % causal_seq) : D;
     float yv[VPT][N], gv[VPT][N];
     float dot[1] = {0.0f};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = tg + i * TPR;
-      if (live && vi < nvec) {
-        V a, b;
-        a.raw = reinterpret_cast<const decltype(a.raw)*>(y + row * D)[vi];
-        b.raw = reinterpret_cast<const decltype(b.raw)*>(dy + row * D)[vi];
-        a.to_float(yv[i]);
-        b.to_float(gv[i]);
+      if (live && vi < nvec && vi * N <= q) {
+        load_stream<V>(y + row * D, vi).to_float(yv[i]);
+        load_stream<V>(dy + row * D, vi).to_float(gv[i]);
       } else {
 #pragma unroll
         for (int j = 0; j < N; ++j) { yv[i][j] = 0.0f; gv[i][j] = 0.0f; }
@@ -337,7 +355,7 @@ softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
 #pragma unroll
       for (int j = 0; j < N; ++j) dot[0] = fmaf(yv[i][j], gv[i][j], dot[0]);
     }
-    group_reduce<TPR, 1, false>(dot, red);
+    group_reduce<TPR, 1, false>(dot, red, parity);
     if (live) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
@@ -347,7 +365,7 @@ softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
 #pragma unroll
           for (int j = 0; j < N; ++j) o[j] = yv[i][j] * (gv[i][j] - dot[0]) * scale;
           V t; t.from_float(o);
-          reinterpret_cast<decltype(t.raw)*>(dx + row * D)[vi] = t.raw;
+          store_stream<V>(dx + row * D, vi, t);
         }
       }
     }
@@ -458,7 +476,7 @@ struct RowPlan {
   int tpr = 0, vpt = 0;  // 0 = wide kernel
 };
 template <typename T>
-RowPlan plan_rows(int64_t D, bool all_aligned) {
+RowPlan plan_rows(int64_t D, bool all_aligned, bool /*light*/) {
   constexpr int N = Vec16<T>::N;
   RowPlan p;
   if (!all_aligned || D % N != 0 || D > 4096 * N) return p;
@@ -475,15 +493,15 @@ RowPlan plan_rows(int64_t D, bool all_aligned) {
 }
 
 #define MCB_ROW_DISPATCH(plan, CALL)                    \
-  switch ((plan).tpr * 8 + (plan).vpt) {                \
-    case 32 * 8 + 1: { CALL(32, 1); } break;            \
-    case 32 * 8 + 2: { CALL(32, 2); } break;            \
-    case 64 * 8 + 2: { CALL(64, 2); } break;            \
-    case 128 * 8 + 2: { CALL(128, 2); } break;          \
-    case 256 * 8 + 2: { CALL(256, 2); } break;          \
-    case 256 * 8 + 4: { CALL(256, 4); } break;          \
-    case 512 * 8 + 4: { CALL(512, 4); } break;          \
-    case 1024 * 8 + 4: { CALL(1024, 4); } break;        \
+  switch ((plan).tpr * 16 + (plan).vpt) {               \
+    case 32 * 16 + 1: { CALL(32, 1); } break;           \
+    case 32 * 16 + 2: { CALL(32, 2); } break;           \
+    case 64 * 16 + 2: { CALL(64, 2); } break;           \
+    case 128 * 16 + 2: { CALL(128, 2); } break;         \
+    case 256 * 16 + 2: { CALL(256, 2); } break;         \
+    case 256 * 16 + 4: { CALL(256, 4); } break;         \
+    case 512 * 16 + 4: { CALL(512, 4); } break;         \
+    case 1024 * 16 + 4: { CALL(1024, 4); } break;       \
     default: return fail(MCB_ERR_UNSUPPORTED, "row plan"); \
   }
 
@@ -499,7 +517,7 @@ template <typename T>
 int rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t rows, int64_t D, float eps,
                   cudaStream_t st, const DeviceState* ds) {
   const bool al = aligned16(x) && aligned16(y) && (w == nullptr || aligned16(w));
-  RowPlan p = plan_rows<T>(D, al);
+  RowPlan p = plan_rows<T>(D, al, false);
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);
     rmsnorm_fwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, rows, D, eps);
@@ -514,14 +532,27 @@ int rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t ro
   return MCB_OK;
 }
 
-int bwd_blocks(int64_t rows, int tpr, int sm_count) { return row_grid(rows, tpr, sm_count, 2); }
+// Blocks of the RMSNorm backward.  Without dw: as many as keep the SMs full.  With dw every block also writes
+// and later re-reads one float32 row of partial sums, so the count is capped to keep that below a few
+// per cent of the main traffic (and within the workspace, kMaxDwBlocks rows).
+constexpr int kMaxDwBlocks = 2048;
+int bwd_blocks(int64_t rows, int tpr, int sm_count, bool need_dw, int elem_bytes) {
+  int n = row_grid(rows, tpr, sm_count, 8);
+  if (need_dw) {
+    int64_t cap = rows * elem_bytes / 96;
+    if (cap < 2 * static_cast<int64_t>(sm_count)) cap = 2 * static_cast<int64_t>(sm_count);
+    if (n > cap) n = static_cast<int>(cap);
+    if (n > kMaxDwBlocks) n = kMaxDwBlocks;
+  }
+  return n < 1 ? 1 : n;
+}
 
 template <typename T>
 int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
                   int64_t rows, int64_t D, float eps, void* ws, size_t ws_bytes, cudaStream_t st,
                   const DeviceState* ds) {
   const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && (w == nullptr || aligned16(w));
-  RowPlan p = plan_rows<T>(D, al);
+  RowPlan p = plan_rows<T>(D, al, false);
   if (dw != nullptr && ws_bytes < mcb_rmsnorm_bwd_workspace_bytes(rows, D))
     return fail(MCB_ERR_WORKSPACE, "rmsnorm_bwd: workspace %zu < %zu bytes", ws_bytes,
                 mcb_rmsnorm_bwd_workspace_bytes(rows, D));
@@ -539,14 +570,22 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
     }
     return MCB_OK;
   }
-  const int nblocks = bwd_blocks(rows, p.tpr, ds->sm_count);
+  const int nblocks = bwd_blocks(rows, p.tpr, ds->sm_count, dw != nullptr, (int)sizeof(T));
   const int rpb = (p.tpr < 256 ? 256 : p.tpr) / p.tpr;
   const size_t smem = (dw != nullptr && rpb > 1) ? static_cast<size_t>(rpb) * D * sizeof(float) : 0;
-#define CALL(TPR, VPT)                                                                     \
-  rmsnorm_bwd_kernel<T, TPR, VPT><<<nblocks, RowGeom<TPR>::THREADS, smem, st>>>(           \
-      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, dw ? (float*)ws : nullptr, rows, (int)D, eps)
-  MCB_ROW_DISPATCH(p, CALL)
+  if (dw != nullptr) {
+#define CALL(TPR, VPT)                                                                           \
+  rmsnorm_bwd_kernel<T, TPR, VPT, true><<<nblocks, RowGeom<TPR>::THREADS, smem, st>>>(           \
+      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, (float*)ws, rows, (int)D, eps)
+    MCB_ROW_DISPATCH(p, CALL)
 #undef CALL
+  } else {
+#define CALL(TPR, VPT)                                                                           \
+  rmsnorm_bwd_kernel<T, TPR, VPT, false><<<nblocks, RowGeom<TPR>::THREADS, 0, st>>>(             \
+      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, nullptr, rows, (int)D, eps)
+    MCB_ROW_DISPATCH(p, CALL)
+#undef CALL
+  }
   MCB_CHECK_LAUNCH("rmsnorm_bwd");
   if (dw != nullptr) {
     colsum_partials_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>((const float*)ws, dw, nblocks, (int)D,
@@ -559,7 +598,7 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
 template <typename T>
 int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, int causal_seq, float scale, cudaStream_t st,
                   const DeviceState* ds) {
-  RowPlan p = plan_rows<T>(D, aligned16(x) && aligned16(y));
+  RowPlan p = plan_rows<T>(D, aligned16(x) && aligned16(y), true);
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);
     softmax_fwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)y, rows, D, causal_seq, scale);
@@ -575,16 +614,16 @@ int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, int causal_se
 }
 
 template <typename T>
-int softmax_bwd_t(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, float scale, cudaStream_t st,
+int softmax_bwd_t(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int causal_seq, float scale, cudaStream_t st,
                   const DeviceState* ds) {
-  RowPlan p = plan_rows<T>(D, aligned16(y) && aligned16(dy) && aligned16(dx));
+  RowPlan p = plan_rows<T>(D, aligned16(y) && aligned16(dy) && aligned16(dx), true);
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);
     softmax_bwd_wide_kernel<T><<<grid, 256, 0, st>>>((const T*)y, (const T*)dy, (T*)dx, rows, D, scale);
   } else {
 #define CALL(TPR, VPT)                                                                                \
   softmax_bwd_kernel<T, TPR, VPT><<<row_grid(rows, TPR, ds->sm_count, 8), RowGeom<TPR>::THREADS, 0, st>>>( \
-      (const T*)y, (const T*)dy, (T*)dx, rows, (int)D, scale)
+      (const T*)y, (const T*)dy, (T*)dx, rows, (int)D, causal_seq, scale)
     MCB_ROW_DISPATCH(p, CALL)
 #undef CALL
   }
@@ -617,9 +656,8 @@ extern "C" int mcb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
 
 extern "C" size_t mcb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t D) {
   if (rows <= 0 || D <= 0) return 0;
-  // Either per-block partial sums of dw (at most 2 blocks per SM on up to 256 SMs) or, for the wide
-  // kernel, one float per row.
-  size_t partials = static_cast<size_t>(512) * static_cast<size_t>(D) * sizeof(float);
+  // Either per-block partial sums of dw (at most kMaxDwBlocks rows) or, for the wide kernel, one float per row.
+  size_t partials = static_cast<size_t>(kMaxDwBlocks) * static_cast<size_t>(D) * sizeof(float);
   size_t per_row = static_cast<size_t>(rows) * sizeof(float);
   return partials > per_row ? partials : per_row;
 }
@@ -669,19 +707,21 @@ extern "C" int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t 
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, 1.0f, st, ds)
-                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, 1.0f, st, ds);
+  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, 0, 1.0f, st, ds)
+                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, 0, 1.0f, st, ds);
 }
 
-extern "C" int mcb_softmax_scaled_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, float scale,
-                                      int dtype, void* stream) {
-  if (!y || !dy || !dx) return fail(MCB_ERR_NULL, "softmax_scaled_bwd: y, dy or dx is null");
-  if (int rc = check_rows("softmax_scaled_bwd", rows, D, dtype)) return rc;
+extern "C" int mcb_softmax_causal_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int64_t seq,
+                                      float scale, int dtype, void* stream) {
+  if (!y || !dy || !dx) return fail(MCB_ERR_NULL, "softmax_causal_bwd: y, dy or dx is null");
+  if (int rc = check_rows("softmax_causal_bwd", rows, D, dtype)) return rc;
+  if (seq < 0 || seq > 0x7fffffff || (seq > 0 && rows % seq != 0))
+    return fail(MCB_ERR_SHAPE, "softmax_causal_bwd: rows=%lld must be a multiple of seq=%lld", (long long)rows, (long long)seq);
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, scale, st, ds)
-                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, scale, st, ds);
+  return dtype == MCB_F32 ? softmax_bwd_t<float>(y, dy, dx, rows, D, (int)seq, scale, st, ds)
+                          : softmax_bwd_t<__nv_bfloat16>(y, dy, dx, rows, D, (int)seq, scale, st, ds);
 }
 
 // ---- RMSNorm backward for callers that cannot allocate ------------------------------------------------
@@ -700,18 +740,26 @@ int rmsnorm_bwd_noalloc_t(const void* x, const void* w, const void* dy, void* dx
                           int64_t rows, int64_t D, float eps, float* scratch, cudaStream_t st, const mcb::DeviceState* ds) {
   using namespace mcb;
   const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && (w == nullptr || aligned16(w));
-  RowPlan p = plan_rows<T>(D, al);
+  RowPlan p = plan_rows<T>(D, al, false);
   if (p.tpr == 0)
     return fail(MCB_ERR_ALIGN, "rmsnorm_bwd_noalloc: rows must be 16-byte aligned and D a multiple of %d", Vec16<T>::N);
-  int nblocks = bwd_blocks(rows, p.tpr, ds->sm_count);
-  if (nblocks > kNoAllocMaxBlocks) nblocks = kNoAllocMaxBlocks;
+  int nblocks = bwd_blocks(rows, p.tpr, ds->sm_count, dw != nullptr, (int)sizeof(T));
+  if (dw != nullptr && nblocks > kNoAllocMaxBlocks) nblocks = kNoAllocMaxBlocks;
   const int rpb = (p.tpr < 256 ? 256 : p.tpr) / p.tpr;
   const size_t smem = (dw != nullptr && rpb > 1) ? static_cast<size_t>(rpb) * D * sizeof(float) : 0;
-#define CALL(TPR, VPT)                                                                     \
-  rmsnorm_bwd_kernel<T, TPR, VPT><<<nblocks, RowGeom<TPR>::THREADS, smem, st>>>(           \
-      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, dw ? scratch : nullptr, rows, (int)D, eps)
-  MCB_ROW_DISPATCH(p, CALL)
+  if (dw != nullptr) {
+#define CALL(TPR, VPT)                                                                           \
+  rmsnorm_bwd_kernel<T, TPR, VPT, true><<<nblocks, RowGeom<TPR>::THREADS, smem, st>>>(           \
+      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, scratch, rows, (int)D, eps)
+    MCB_ROW_DISPATCH(p, CALL)
 #undef CALL
+  } else {
+#define CALL(TPR, VPT)                                                                           \
+  rmsnorm_bwd_kernel<T, TPR, VPT, false><<<nblocks, RowGeom<TPR>::THREADS, 0, st>>>(             \
+      (const T*)x, (const T*)w, (const T*)dy, (T*)dx, nullptr, rows, (int)D, eps)
+    MCB_ROW_DISPATCH(p, CALL)
+#undef CALL
+  }
   MCB_CHECK_LAUNCH("rmsnorm_bwd_noalloc");
   if (dw != nullptr) {
     // every block wrote its whole row of partials above, so nothing stale from an earlier call is read

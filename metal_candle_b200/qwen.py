@@ -211,7 +211,7 @@ class Qwen:
         dV = torch.bmm(P.transpose(1, 2), dO3)                       # [B*Hk, S, d], summed over the group
         dP = torch.bmm(dO3, Vr.view(B * Hk, S, d).transpose(1, 2))   # [B*Hk, G*S, S]
         rows = dP.numel() // S
-        _lib.check(self.lib.mcb_softmax_scaled_bwd(_ptr(P), _ptr(dP), _ptr(dP), rows, S, 1.0 / math.sqrt(d), self.dt,
+        _lib.check(self.lib.mcb_softmax_causal_bwd(_ptr(P), _ptr(dP), _ptr(dP), rows, S, S, 1.0 / math.sqrt(d), self.dt,
                                                    _stream()))
         dQ = torch.bmm(dP, Kr.view(B * Hk, S, d))                    # [B*Hk, G*S, d]
         dK = torch.bmm(dP.transpose(1, 2), Qr.view(B * Hk, G * S, d))  # [B*Hk, S, d]
