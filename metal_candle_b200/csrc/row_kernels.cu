@@ -15,6 +15,13 @@
 #include "common.cuh"
 
 namespace mcb {
+namespace rowpipe {
+enum Op { kRmsFwd = 0, kRmsBwd = 1, kSmFwd = 2, kSmBwd = 3 };
+template <typename T>
+int try_launch(int op, const void* in0, const void* in1, const void* w, void* out, float* rstd, float* dw_part,
+               int* dw_blocks, int64_t rows, int64_t D, float eps, int causal_seq, float scale, const DeviceState* ds,
+               cudaStream_t st);
+}  // namespace rowpipe
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -516,6 +523,10 @@ int row_grid(int64_t rows, int tpr, int sm_count, int blocks_per_sm) {
 template <typename T>
 int rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t rows, int64_t D, float eps,
                   cudaStream_t st, const DeviceState* ds) {
+  {
+    const int rc = rowpipe::try_launch<T>(rowpipe::kRmsFwd, x, nullptr, w, y, rstd, nullptr, nullptr, rows, D, eps, 0, 1.0f, ds, st);
+    if (rc != 1) return rc;
+  }
   const bool al = aligned16(x) && aligned16(y) && (w == nullptr || aligned16(w));
   RowPlan p = plan_rows<T>(D, al, false);
   if (p.tpr == 0) {
@@ -551,6 +562,20 @@ template <typename T>
 int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
                   int64_t rows, int64_t D, float eps, void* ws, size_t ws_bytes, cudaStream_t st,
                   const DeviceState* ds) {
+  if (dw != nullptr && ws_bytes < mcb_rmsnorm_bwd_workspace_bytes(rows, D))
+    return fail(MCB_ERR_WORKSPACE, "rmsnorm_bwd: workspace %zu < %zu bytes", ws_bytes,
+                mcb_rmsnorm_bwd_workspace_bytes(rows, D));
+  if (dw != nullptr && ws == nullptr) return fail(MCB_ERR_WORKSPACE, "rmsnorm_bwd: workspace is null");
+  {
+    int blocks = 0;
+    const int rc = rowpipe::try_launch<T>(rowpipe::kRmsBwd, x, dy, w, dx, nullptr, dw ? (float*)ws : nullptr, &blocks, rows, D,
+                                          eps, 0, 1.0f, ds, st);
+    if (rc == MCB_OK && dw != nullptr) {
+      colsum_partials_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>((const float*)ws, dw, blocks, (int)D, accumulate);
+      MCB_CHECK_LAUNCH("rmsnorm_dw_reduce");
+    }
+    if (rc != 1) return rc;
+  }
   const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && (w == nullptr || aligned16(w));
   RowPlan p = plan_rows<T>(D, al, false);
   if (dw != nullptr && ws_bytes < mcb_rmsnorm_bwd_workspace_bytes(rows, D))
@@ -598,6 +623,11 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
 template <typename T>
 int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, int causal_seq, float scale, cudaStream_t st,
                   const DeviceState* ds) {
+  {
+    const int rc = rowpipe::try_launch<T>(rowpipe::kSmFwd, x, nullptr, nullptr, y, nullptr, nullptr, nullptr, rows, D, 0.0f,
+                                          causal_seq, scale, ds, st);
+    if (rc != 1) return rc;
+  }
   RowPlan p = plan_rows<T>(D, aligned16(x) && aligned16(y), true);
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);
@@ -616,6 +646,11 @@ int softmax_fwd_t(const void* x, void* y, int64_t rows, int64_t D, int causal_se
 template <typename T>
 int softmax_bwd_t(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int causal_seq, float scale, cudaStream_t st,
                   const DeviceState* ds) {
+  {
+    const int rc = rowpipe::try_launch<T>(rowpipe::kSmBwd, y, dy, nullptr, dx, nullptr, nullptr, nullptr, rows, D, 0.0f,
+                                          causal_seq, scale, ds, st);
+    if (rc != 1) return rc;
+  }
   RowPlan p = plan_rows<T>(D, aligned16(y) && aligned16(dy) && aligned16(dx), true);
   if (p.tpr == 0) {
     int grid = static_cast<int>(rows < ds->sm_count * 8 ? rows : ds->sm_count * 8);

@@ -1,0 +1,424 @@
+// RMSNorm / softmax row kernels fed by bulk asynchronous copies (cp.async.bulk + mbarrier).
+//
+// The register kernels of row_kernels.cu can only keep as many bytes in flight as their registers hold,
+// which on B200 is not enough to cover HBM latency at 6.5 TB/s.  Here the bytes in flight live in shared
+// memory instead: a producer thread streams tiles of W consecutive rows (one row per consumer warp) of
+// every input into a ring of stages with cp.async.bulk.shared.global (completion counted on an mbarrier),
+// W consumer warps each take one row of the tile out of shared memory (two passes: reduce, then write),
+// reduce with warp shuffles only, and store the result straight to global memory with 16-byte stores.
+// Two CTAs per SM with up to ~100 KB of stages each keep ~100-200 KB in flight per SM.
+//
+// Causal softmax rows are copied only up to the query position (rounded up to 16 bytes), so the masked
+// part of the scores is never read from HBM.
+//
+// Every mbarrier wait is bounded; on expiry the CTA records a code in the device status word and leaves.
+#include "common.cuh"
+#include "umma_ptx.cuh"
+
+namespace mcb {
+namespace rowpipe {
+using namespace umma;
+
+enum Op { kRmsFwd = 0, kRmsBwd = 1, kSmFwd = 2, kSmBwd = 3 };
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 100 * 1024;
+
+struct Params {
+  const void* in0;   // x (rms), x (softmax fwd), y (softmax bwd)
+  const void* in1;   // dy (backward ops) or null
+  const void* w;     // rmsnorm weight or null
+  void* out;         // y / dx
+  float* rstd;       // rms fwd, optional
+  float* dw_part;    // rms bwd with dw: [gridDim.x][D] partial sums
+  int64_t rows;
+  int D, nvec, row_bytes;
+  int stages, n_streams;
+  int causal_seq;
+  float eps, scale;
+  int* status;
+  uint32_t stage_bytes, bar_off;
+};
+
+// 2^x by the special-function unit (ex2.approx.ftz): x <= 0 here, -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// bytes of a causal row that are needed: columns 0..q, rounded up to 16 bytes
+__device__ __forceinline__ uint32_t causal_bytes(int q, int elem_bytes, int row_bytes) {
+  uint32_t b = (static_cast<uint32_t>(q + 1) * elem_bytes + 15u) & ~15u;
+  return b < static_cast<uint32_t>(row_bytes) ? b : static_cast<uint32_t>(row_bytes);
+}
+
+template <typename T, int OP, int W, int KMAX>  // KMAX > 0: rmsnorm backward with dw, KMAX vectors per lane
+__global__ void __launch_bounds__((W + 1) * 32)
+rowpipe_kernel(const Params p) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  constexpr bool kTwoIn = (OP == kRmsBwd || OP == kSmBwd);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + p.bar_off + 16 * kMaxStages);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, W); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+
+  const int64_t n_tiles = (p.rows + W - 1) / W;
+  const uint32_t stream_bytes = static_cast<uint32_t>(W) * p.row_bytes;
+
+  float dwa[KMAX > 0 ? KMAX : 1][N];
+  if constexpr (KMAX > 0) {
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k)
+#pragma unroll
+      for (int j = 0; j < N; ++j) dwa[k][j] = 0.0f;
+  }
+
+  if (warp == W) {
+    // ---------------- producer (one warp; lane 0 alone unless rows are copied one by one) ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 51, p.status);
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      const int64_t row0 = t * W;
+      const int nrows = static_cast<int>(p.rows - row0 < W ? p.rows - row0 : W);
+      const uint32_t fb = full0 + 8 * stage, sb = base + stage * p.stage_bytes;
+      const char* g0 = static_cast<const char*>(p.in0) + row0 * p.row_bytes;
+      const char* g1 = kTwoIn ? static_cast<const char*>(p.in1) + row0 * p.row_bytes : nullptr;
+      if (p.causal_seq > 0) {
+        // lane r copies row r of the tile, only up to its query position
+        const int q0 = static_cast<int>(row0 % p.causal_seq);  // one division per tile
+        int q = q0 + lane;
+        if (q >= p.causal_seq) q -= p.causal_seq;              // W <= causal_seq is checked on the host
+        const uint32_t b = lane < nrows ? causal_bytes(q, sizeof(T), p.row_bytes) : 0u;
+        uint32_t total = b;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (lane == 0) mbar_expect_tx(fb, total * (kTwoIn ? 2u : 1u));
+        __syncwarp();
+        if (lane < nrows) {
+          bulk_load(sb + lane * p.row_bytes, g0 + static_cast<int64_t>(lane) * p.row_bytes, b, fb);
+          if (kTwoIn) bulk_load(sb + stream_bytes + lane * p.row_bytes, g1 + static_cast<int64_t>(lane) * p.row_bytes, b, fb);
+        }
+      } else if (lane == 0) {
+        const uint32_t b = static_cast<uint32_t>(nrows) * p.row_bytes;
+        mbar_expect_tx(fb, b * (kTwoIn ? 2u : 1u));
+        bulk_load(sb, g0, b, fb);
+        if (kTwoIn) bulk_load(sb + stream_bytes, g1, b, fb);
+      }
+      if (++stage == p.stages) { stage = 0; phase ^= 1; }
+    }
+  } else {
+    // ---------------- consumers: warp `warp` owns row `warp` of every tile ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    const float inv_d = 1.0f / static_cast<float>(p.D);
+    const int nvec = p.nvec;
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+      if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, abort_flag, 52, p.status))) break;
+      const int64_t row = t * W + warp;
+      if (row < p.rows) {
+        const uint8_t* s0 = gen_base + stage * p.stage_bytes + warp * p.row_bytes;
+        const uint8_t* s1 = s0 + stream_bytes;
+        T* orow = static_cast<T*>(p.out) + row * p.D;
+        if constexpr (OP == kRmsFwd) {
+          float ss = 0.0f;
+#pragma unroll 4
+          for (int vi = lane; vi < nvec; vi += 32) {
+            V a; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            float f[N]; a.to_float(f);
+#pragma unroll
+            for (int j = 0; j < N; ++j) ss = fmaf(f[j], f[j], ss);
+          }
+          ss = warp_sum(ss);
+          const float rinv = 1.0f / sqrtf(ss * inv_d + p.eps);
+          if (p.rstd != nullptr && lane == 0) p.rstd[row] = rinv;
+#pragma unroll 4
+          for (int vi = lane; vi < nvec; vi += 32) {
+            V a; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            float f[N]; a.to_float(f);
+            if (p.w != nullptr) {
+              V wv; wv.raw = __ldg(reinterpret_cast<const decltype(wv.raw)*>(p.w) + vi);
+              float g[N]; wv.to_float(g);
+#pragma unroll
+              for (int j = 0; j < N; ++j) f[j] = f[j] * rinv * g[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < N; ++j) f[j] *= rinv;
+            }
+            a.from_float(f);
+            __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+          }
+        } else if constexpr (OP == kRmsBwd) {
+          float ss = 0.0f, gx = 0.0f;
+#pragma unroll 4
+          for (int vi = lane; vi < nvec; vi += 32) {
+            V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
+            float x[N], g[N]; a.to_float(x); b.to_float(g);
+            if (p.w != nullptr) {
+              V wv; wv.raw = __ldg(reinterpret_cast<const decltype(wv.raw)*>(p.w) + vi);
+              float ww[N]; wv.to_float(ww);
+#pragma unroll
+              for (int j = 0; j < N; ++j) g[j] *= ww[j];
+            }
+#pragma unroll
+            for (int j = 0; j < N; ++j) { ss = fmaf(x[j], x[j], ss); gx = fmaf(g[j], x[j], gx); }
+          }
+          ss = warp_sum(ss);
+          gx = warp_sum(gx);
+          const float rinv = 1.0f / sqrtf(ss * inv_d + p.eps);
+          const float c = gx * rinv * inv_d;
+          auto body = [&](int vi, float* dw_slot) {
+            V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
+            float x[N], g[N], o[N]; a.to_float(x); b.to_float(g);
+            float ww[N];
+            if (p.w != nullptr) {
+              V wv; wv.raw = __ldg(reinterpret_cast<const decltype(wv.raw)*>(p.w) + vi);
+              wv.to_float(ww);
+            } else {
+#pragma unroll
+              for (int j = 0; j < N; ++j) ww[j] = 1.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+              const float xh = x[j] * rinv;
+              if (dw_slot != nullptr) dw_slot[j] = fmaf(g[j], xh, dw_slot[j]);
+              o[j] = rinv * (g[j] * ww[j] - xh * c);
+            }
+            a.from_float(o);
+            __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+          };
+          if constexpr (KMAX > 0) {
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k) {
+              const int vi = lane + 32 * k;
+              if (vi < nvec) body(vi, dwa[k]);
+            }
+          } else {
+            for (int vi = lane; vi < nvec; vi += 32) body(vi, nullptr);
+          }
+        } else if constexpr (OP == kSmFwd) {
+          const int q = p.causal_seq > 0 ? static_cast<int>(row % p.causal_seq) : p.D;  // last kept column (one division per row per warp)
+          const int nv_keep = p.causal_seq > 0 ? min(nvec, q / N + 1) : nvec;
+          const float sc = p.scale * kLog2e;  // work in base-2 logits
+          // pass 1: row maximum (cheap), pass 2: sum of 2^(x - max) with independent partial sums
+          float m = -INFINITY;
+#pragma unroll 4
+          for (int vi = lane; vi < nv_keep; vi += 32) {
+            V a; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            float f[N]; a.to_float(f);
+#pragma unroll
+            for (int j = 0; j < N; ++j) m = fmaxf(m, (vi * N + j <= q) ? f[j] : -INFINITY);
+          }
+          m = warp_max(m) * sc;  // sc > 0: max commutes with the scaling
+          float s = 0.0f;
+          if (m != -INFINITY) {
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int vi = lane; vi < nv_keep; vi += 32) {
+              V a; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+              float f[N]; a.to_float(f);
+#pragma unroll
+              for (int j = 0; j < N; ++j)
+                part[j & 3] += (vi * N + j <= q) ? fast_exp2(fmaf(f[j], sc, -m)) : 0.0f;
+            }
+            s = (part[0] + part[1]) + (part[2] + part[3]);
+          }
+          s = warp_sum(s);
+          const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+          const float mref = (m == -INFINITY) ? 0.0f : m;
+#pragma unroll 4
+          for (int vi = lane; vi < nvec; vi += 32) {
+            float f[N];
+            if (vi < nv_keep) {
+              V a; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+              a.to_float(f);
+#pragma unroll
+              for (int j = 0; j < N; ++j) f[j] = (vi * N + j <= q) ? fast_exp2(fmaf(f[j], sc, -mref)) * inv : 0.0f;
+            } else {
+#pragma unroll
+              for (int j = 0; j < N; ++j) f[j] = 0.0f;
+            }
+            V a; a.from_float(f);
+            __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+          }
+        } else {  // kSmBwd
+          const int q = p.causal_seq > 0 ? static_cast<int>(row % p.causal_seq) : p.D;
+          const int nv_keep = p.causal_seq > 0 ? min(nvec, q / N + 1) : nvec;
+          float dot = 0.0f;
+#pragma unroll 4
+          for (int vi = lane; vi < nv_keep; vi += 32) {
+            V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
+            float y[N], g[N]; a.to_float(y); b.to_float(g);
+#pragma unroll
+            for (int j = 0; j < N; ++j) dot = fmaf((vi * N + j <= q) ? y[j] : 0.0f, g[j], dot);
+          }
+          dot = warp_sum(dot);
+#pragma unroll 4
+          for (int vi = lane; vi < nvec; vi += 32) {
+            float o[N];
+            if (vi < nv_keep) {
+              V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+              b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
+              float y[N], g[N]; a.to_float(y); b.to_float(g);
+#pragma unroll
+              for (int j = 0; j < N; ++j) o[j] = (vi * N + j <= q) ? y[j] * (g[j] - dot) * p.scale : 0.0f;
+            } else {
+#pragma unroll
+              for (int j = 0; j < N; ++j) o[j] = 0.0f;
+            }
+            V a; a.from_float(o);
+            __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+      if (++stage == p.stages) { stage = 0; phase ^= 1; }
+    }
+  }
+
+  if constexpr (KMAX > 0) {
+    // Sum the W warps' dw accumulators in warp order through shared memory (the stage ring is idle now:
+    // every load that was issued has been consumed), then write this CTA's partial row.
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(gen_base);
+    if (warp < W) {
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < p.nvec) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) red[warp * p.D + vi * N + j] = dwa[k][j];
+        }
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < p.D; c += blockDim.x) {
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) s += red[w * p.D + c];
+      p.dw_part[static_cast<int64_t>(blockIdx.x) * p.D + c] = s;
+    }
+  }
+  if (*abort_flag != 0) {
+    for (int k = 0; k < 200; ++k) __nanosleep(1000);
+  }
+}
+
+template <typename T, int OP, int W, int KMAX>
+int launch_one(const Params& p, int grid, size_t smem, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(rowpipe_kernel<T, OP, W, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBudget + 2048);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(rowpipe_kernel)");
+    attr_set[dev] = true;
+  }
+  rowpipe_kernel<T, OP, W, KMAX><<<grid, (W + 1) * 32, smem, st>>>(p);
+  MCB_CHECK_LAUNCH("rowpipe_kernel");
+  return MCB_OK;
+}
+
+template <typename T, int OP, int KMAX>
+int launch_w(int W, const Params& p, int grid, size_t smem, cudaStream_t st) {
+  switch (W) {
+    case 16: return launch_one<T, OP, 16, KMAX>(p, grid, smem, st);
+    case 8: return launch_one<T, OP, 8, KMAX>(p, grid, smem, st);
+    case 4: return launch_one<T, OP, 4, KMAX>(p, grid, smem, st);
+    case 2: return launch_one<T, OP, 2, KMAX>(p, grid, smem, st);
+  }
+  return fail(MCB_ERR_UNSUPPORTED, "rowpipe: W=%d", W);
+}
+
+// Returns MCB_OK when the pipelined kernel was launched, 1 when the shape does not fit it (the caller
+// then uses the register kernels), or an error.
+template <typename T>
+int try_launch(int op, const void* in0, const void* in1, const void* w, void* out, float* rstd, float* dw_part,
+               int* dw_blocks, int64_t rows, int64_t D, float eps, int causal_seq, float scale, const DeviceState* ds,
+               cudaStream_t st) {
+  constexpr int N = Vec16<T>::N;
+  if (D % N != 0 || D > (1 << 20)) return 1;
+  if (!aligned16(in0) || !aligned16(out) || (in1 && !aligned16(in1)) || (w && !aligned16(w))) return 1;
+  const int n_streams = (op == kRmsBwd || op == kSmBwd) ? 2 : 1;
+  const int64_t row_bytes = D * static_cast<int64_t>(sizeof(T));
+  int W = 0, stages = 0;
+  for (int cand : {16, 8, 4, 2}) {
+    const int64_t stage_bytes = cand * row_bytes * n_streams;
+    const int s = static_cast<int>(kSmemBudget / stage_bytes);
+    if (s >= 3) { W = cand; stages = s > kMaxStages ? kMaxStages : s; break; }
+  }
+  // One warp per row only pays while enough warps fit: forward ops (one input stream, more arithmetic per
+  // byte) want at least 8 rows per tile, backward ops at least 4; wider rows go to the register kernels.
+  if (W < (n_streams == 1 ? 8 : 4) || rows < 4 * W) return 1;
+  if (causal_seq > 0 && causal_seq < W) return 1;
+  const int nvec = static_cast<int>(D / N);
+  int kmax = 0;
+  if (dw_part != nullptr) {
+    const int need = (nvec + 31) / 32;
+    kmax = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : 0;
+    if (kmax == 0) return 1;
+    if (static_cast<int64_t>(W) * D * 4 > static_cast<int64_t>(stages) * W * row_bytes * n_streams) return 1;
+  }
+  Params p;
+  p.in0 = in0; p.in1 = in1; p.w = w; p.out = out; p.rstd = rstd; p.dw_part = dw_part;
+  p.rows = rows; p.D = static_cast<int>(D); p.nvec = nvec; p.row_bytes = static_cast<int>(row_bytes);
+  p.stages = stages; p.n_streams = n_streams; p.causal_seq = causal_seq; p.eps = eps; p.scale = scale;
+  p.status = ds->status_word;
+  p.stage_bytes = static_cast<uint32_t>(W * row_bytes * n_streams);
+  p.bar_off = (static_cast<uint32_t>(stages) * p.stage_bytes + 127u) & ~127u;
+  const size_t smem = p.bar_off + 16 * kMaxStages + 16 + 128;
+  const int64_t n_tiles = (rows + W - 1) / W;
+  int grid = 2 * ds->sm_count;
+  if (grid > n_tiles) grid = static_cast<int>(n_tiles);
+  if (dw_blocks) *dw_blocks = grid;
+#define MCB_RP(OPC, KM) return launch_w<T, OPC, KM>(W, p, grid, smem, st)
+  switch (op) {
+    case kRmsFwd: MCB_RP(kRmsFwd, 0);
+    case kSmFwd: MCB_RP(kSmFwd, 0);
+    case kSmBwd: MCB_RP(kSmBwd, 0);
+    case kRmsBwd:
+      switch (kmax) {
+        case 0: MCB_RP(kRmsBwd, 0);
+        case 1: MCB_RP(kRmsBwd, 1);
+        case 2: MCB_RP(kRmsBwd, 2);
+        case 4: MCB_RP(kRmsBwd, 4);
+        case 8: MCB_RP(kRmsBwd, 8);
+        case 16: MCB_RP(kRmsBwd, 16);
+      }
+  }
+#undef MCB_RP
+  return 1;
+}
+
+template int try_launch<float>(int, const void*, const void*, const void*, void*, float*, float*, int*, int64_t, int64_t,
+                               float, int, float, const DeviceState*, cudaStream_t);
+template int try_launch<__nv_bfloat16>(int, const void*, const void*, const void*, void*, float*, float*, int*, int64_t,
+                                       int64_t, float, int, float, const DeviceState*, cudaStream_t);
+
+}  // namespace rowpipe
+}  // namespace mcb

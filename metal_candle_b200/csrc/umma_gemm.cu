@@ -166,6 +166,10 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc_main = make_idesc(p.BN);
       const uint32_t idesc_rank = make_idesc(p.rp);
+      // The P tile lies directly behind the W tile in a stage (same 128B-swizzled K-major layout), and the rank
+      // accumulator directly behind the main one in tensor memory, so one MMA with N = BN + rp produces both
+      // and reads the X tile from shared memory once.
+      const uint32_t idesc_both = make_idesc(p.BN + p.rp);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -187,8 +191,8 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           for (int k4 = 0; k4 < BK / 16; ++k4) {
             const uint64_t ad = desc_sw128(sb + k4 * 32);
             const uint32_t acc = (kb | k4) != 0 ? 1u : 0u;
-            if (p.has_w) umma_bf16(d1, ad, desc_sw128(sb + p.w_off + k4 * 32), idesc_main, acc);
-            if (p.rp > 0) umma_bf16(d2, ad, desc_sw128(sb + p.p_off + k4 * 32), idesc_rank, acc);
+            if (p.has_w) umma_bf16(d1, ad, desc_sw128(sb + p.w_off + k4 * 32), p.rp > 0 ? idesc_both : idesc_main, acc);
+            else umma_bf16(d2, ad, desc_sw128(sb + p.p_off + k4 * 32), idesc_rank, acc);
           }
           umma_commit(b.empty0 + 8 * stage);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -265,27 +269,30 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       if (!ok) break;
       tcgen05_fence_after();
       if (p.Y != nullptr) {
-        for (int c = 0; c < p.BN; c += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(d1 + c, v);
+        // 32 accumulator columns per round: two tensor-memory loads in flight, then 64 contiguous bytes per
+        // thread (whole 32-byte sectors) to global memory.
+        for (int c = 0; c < p.BN; c += 32) {
+          uint32_t v0[16], v1[16];
+          tmem_ld_x16(d1 + c, v0);
+          tmem_ld_x16(d1 + c + 16, v1);
           tmem_ld_wait();
           const int gcol = n0 + c;
           if (grow < p.M && gcol < p.N) {
-            float f[16];
+            float f[32];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
             if (p.bias != nullptr) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
+              for (int j = 0; j < 32; ++j)
                 if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
             }
-            __nv_bfloat16* yp = p.Y + grow * p.N + gcol;
-            const uint4 lo = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
-                                        pack_bf16(f[6], f[7]));
-            const uint4 hi = make_uint4(pack_bf16(f[8], f[9]), pack_bf16(f[10], f[11]), pack_bf16(f[12], f[13]),
-                                        pack_bf16(f[14], f[15]));
-            if (gcol + 8 <= p.N) reinterpret_cast<uint4*>(yp)[0] = lo;
-            if (gcol + 16 <= p.N) reinterpret_cast<uint4*>(yp)[1] = hi;
+            uint4* yp = reinterpret_cast<uint4*>(p.Y + grow * p.N + gcol);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              if (gcol + 8 * q4 + 8 <= p.N)
+                yp[q4] = make_uint4(pack_bf16(f[8 * q4], f[8 * q4 + 1]), pack_bf16(f[8 * q4 + 2], f[8 * q4 + 3]),
+                                    pack_bf16(f[8 * q4 + 4], f[8 * q4 + 5]), pack_bf16(f[8 * q4 + 6], f[8 * q4 + 7]));
+            }
           }
         }
       }
