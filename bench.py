@@ -100,10 +100,36 @@ class ClockSampler:
 
 
 def _time_kernel(torch, fn, n_variants, iters, warmup):
-    """fn(i) launches the kernel on input set i % n_variants.  Returns (median_ms, min_ms)."""
+    """fn(i) launches the kernel(s) on input set i % n_variants.  The `iters` launches are captured into one
+    CUDA graph and the graph is replayed, so that what is timed (CUDA events on the replay stream) is the
+    device time of the kernels back to back and not the Python launch path.  Returns (median_ms, min_ms)
+    per iteration over five replays."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(iters):
+                    fn(warmup + i)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) / iters)
+        return statistics.median(ts), min(ts)
+    except Exception as e:  # capture refused: time launch by launch
+        sys.stderr.write(f"graph capture failed ({e!r}); timing individual launches\n")
+        torch.cuda.synchronize()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
     for i, (a, b) in enumerate(evs):
         a.record()
@@ -192,14 +218,14 @@ def micro_rows(torch, op, rows, D, dtype, iters=20, warmup=5):
         lib = B._lib_for(xs[0])
         ws = B.workspace(dev, lib.mcb_rmsnorm_bwd_workspace_bytes(rows, D))
         code = B._dtype_code(xs[0])
-        st = torch.cuda.current_stream().cuda_stream
+        cur = lambda: torch.cuda.current_stream().cuda_stream  # the capture stream while a graph is recorded
 
         def fwd(i):
-            lib.mcb_rmsnorm_fwd(xs[i % nv].data_ptr(), w.data_ptr(), ybuf.data_ptr(), None, rows, D, 1e-6, code, st)
+            lib.mcb_rmsnorm_fwd(xs[i % nv].data_ptr(), w.data_ptr(), ybuf.data_ptr(), None, rows, D, 1e-6, code, cur())
 
         def bwd(i):
             lib.mcb_rmsnorm_bwd(xs[i % nv].data_ptr(), w.data_ptr(), dys[i % nv].data_ptr(), ybuf.data_ptr(),
-                                dw.data_ptr(), 0, rows, D, 1e-6, code, ws.data_ptr(), ws.numel(), st)
+                                dw.data_ptr(), 0, rows, D, 1e-6, code, ws.data_ptr(), ws.numel(), cur())
 
         cases = [("rmsnorm fwd", fwd, 2 * rows * D * e + D * e), ("rmsnorm bwd", bwd, 3 * rows * D * e + D * e + 4 * D)]
     else:
@@ -227,14 +253,14 @@ def micro_rows(torch, op, rows, D, dtype, iters=20, warmup=5):
             # against the same dense byte count (masked elements count as traffic in the contract).
             lib = B._lib_for(xs[0])
             code = B._dtype_code(xs[0])
-            st = torch.cuda.current_stream().cuda_stream
+            cur = lambda: torch.cuda.current_stream().cuda_stream
 
             def cfwd(i):
-                lib.mcb_softmax_causal_fwd(xs[i % nv].data_ptr(), buf.data_ptr(), rows, D, S, 0.125, code, st)
+                lib.mcb_softmax_causal_fwd(xs[i % nv].data_ptr(), buf.data_ptr(), rows, D, S, 0.125, code, cur())
 
             def cbwd(i):
                 lib.mcb_softmax_causal_bwd(ys[i % nv].data_ptr(), dys[i % nv].data_ptr(), buf.data_ptr(), rows, D, S,
-                                           0.125, code, st)
+                                           0.125, code, cur())
 
             cases += [("softmax causal fwd (dense-equivalent bytes)", cfwd, 2 * rows * D * e),
                       ("softmax causal bwd (dense-equivalent bytes)", cbwd, 3 * rows * D * e)]

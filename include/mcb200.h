@@ -102,6 +102,18 @@ int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const floa
                         int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* The two calls above with one more operand fused into the epilogue: `residual` [M,N] is added to y (the
+ * residual connections around attention and MLP, src/models/qwen.rs:121,140), `dx_residual` [M,K] is added
+ * to dx (summing the input gradients of projections that share an input).  Null means none.  On the bf16
+ * path the operand may be the output buffer itself. */
+int mcb_lora_linear_fwd_ex(const void* x, const void* W, const void* bias, const float* A, const float* B,
+                           const void* residual, void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r,
+                           float scale, int dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream);
+int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                           const void* h_save, const void* dx_residual, void* dx, float* dA, float* dB, int accumulate,
+                           int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
 /* Rank rounded up to the tensor-core K granule (16): the row count of h_save. */
 int64_t mcb_lora_rank_padded(int64_t r);
 /* Row pitch of h_save in elements: the token count rounded up to 64. */

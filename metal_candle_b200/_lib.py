@@ -43,6 +43,10 @@ SIGNATURES = {
                                    _vp, _sz, _vp]),
     "mcb_lora_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _f32,
                                    _i32, _i32, _vp, _sz, _vp]),
+    "mcb_lora_linear_fwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32,
+                                      _vp, _sz, _vp]),
+    "mcb_lora_linear_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
+                                      _f32, _i32, _i32, _vp, _sz, _vp]),
     "mcb_lora_rank_padded": (_i64, [_i64]),
     "mcb_lora_h_pitch": (_i64, [_i64]),
     "mcb_transpose_2d": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),

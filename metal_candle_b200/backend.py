@@ -128,7 +128,7 @@ def lora_forward_fused(x: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tens
     return out
 
 
-def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=True):
+def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=True, residual=None):
     """`y = x W^T (+b) + scaling (x A) B` with W [out, in].  Returns (y, h_save or None); h_save is
     `scaling * (x A)` transposed, [rank padded to 16, tokens padded to 64]."""
     K = x.shape[-1]
@@ -140,7 +140,7 @@ def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=Tr
         _lora_shapes(x, lora_a, lora_b)
         if lora_b.shape[1] != N:
             raise TrainingError(f"LoRA B must be [r, out={N}], got {list(lora_b.shape)}")
-    _require_cuda(x, weight, bias, lora_a, lora_b)
+    _require_cuda(x, weight, bias, lora_a, lora_b, residual)
     M = x.numel() // K
     lib = _lib_for(x)
     dt = _dtype_code(x)
@@ -150,13 +150,14 @@ def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=Tr
         h = torch.empty(lib.mcb_lora_rank_padded(r), lib.mcb_lora_h_pitch(M), dtype=x.dtype, device=x.device)
     nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
     ws = workspace(x.device, nws)
-    _lib.check(lib.mcb_lora_linear_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(lora_a), _ptr(lora_b), _ptr(y), _ptr(h),
-                                       M, K, N, r, float(scaling), dt, MCB_W_OUT_IN, _ptr(ws), ws.numel(), _stream()))
+    _lib.check(lib.mcb_lora_linear_fwd_ex(_ptr(x), _ptr(weight), _ptr(bias), _ptr(lora_a), _ptr(lora_b), _ptr(residual),
+                                          _ptr(y), _ptr(h), M, K, N, r, float(scaling), dt, MCB_W_OUT_IN, _ptr(ws),
+                                          ws.numel(), _stream()))
     return y, h
 
 
 def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, need_dx=True, grad_a=None,
-                         grad_b=None, accumulate=False, weight_layout=MCB_W_IN_OUT):
+                         grad_b=None, accumulate=False, weight_layout=MCB_W_IN_OUT, dx_residual=None):
     """Reverse of `lora_linear_forward`.  `weight_t` is the [in, out] copy of the frozen weight (for
     float32 either layout works, say which with `weight_layout`).  Returns (dx, dA, dB)."""
     N = dy.shape[-1]
@@ -164,7 +165,7 @@ def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, 
     r = 0 if lora_a is None else lora_a.shape[1]
     if r and x is None:
         raise TrainingError("lora_linear_backward: the layer input x is needed for the LoRA gradients")
-    _require_cuda(x, weight_t, lora_a, lora_b, dy, h_save, grad_a, grad_b)
+    _require_cuda(x, weight_t, lora_a, lora_b, dy, h_save, grad_a, grad_b, dx_residual)
     M = dy.numel() // N
     lib = _lib_for(dy)
     dt = _dtype_code(dy)
@@ -175,8 +176,8 @@ def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, 
         accumulate = False
     nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
     ws = workspace(dy.device, nws)
-    _lib.check(lib.mcb_lora_linear_bwd(_ptr(x), _ptr(weight_t), _ptr(lora_a), _ptr(lora_b), _ptr(dy), _ptr(h_save),
-                                       _ptr(dx), _ptr(grad_a), _ptr(grad_b), int(bool(accumulate)), M, K, N, r,
+    _lib.check(lib.mcb_lora_linear_bwd_ex(_ptr(x), _ptr(weight_t), _ptr(lora_a), _ptr(lora_b), _ptr(dy), _ptr(h_save),
+                                       _ptr(dx_residual), _ptr(dx), _ptr(grad_a), _ptr(grad_b), int(bool(accumulate)), M, K, N, r,
                                        float(scaling), dt, weight_layout, _ptr(ws), ws.numel(), _stream()))
     return dx, grad_a, grad_b
 

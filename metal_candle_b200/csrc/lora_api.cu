@@ -49,8 +49,8 @@ extern "C" int mcb_lora_delta_fwd(const void* x, const float* A, const float* B,
   return dtype == MCB_F32 ? f32path::delta_fwd(a) : bf16path::delta_fwd(a, ds);
 }
 
-extern "C" int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const float* A, const float* B, void* y,
-                                   void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
+extern "C" int mcb_lora_linear_fwd_ex(const void* x, const void* W, const void* bias, const float* A, const float* B,
+                                      const void* residual, void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
                                    int w_layout, void* workspace, size_t workspace_bytes, void* stream) {
   if (!x || !W || !y) return fail(MCB_ERR_NULL, "lora_linear_fwd: x, W or y is null");
   if (r > 0 && (!A || !B)) return fail(MCB_ERR_NULL, "lora_linear_fwd: rank %lld but A or B is null", (long long)r);
@@ -59,15 +59,15 @@ extern "C" int mcb_lora_linear_fwd(const void* x, const void* W, const void* bia
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   LoraArgs a;
-  a.x = x; a.W = W; a.bias = bias; a.A = A; a.B = B; a.y = y; a.h_save = h_save;
+  a.x = x; a.W = W; a.bias = bias; a.A = A; a.B = B; a.y = y; a.h_save = h_save; a.residual = residual;
   a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = w_layout;
   a.ws = workspace; a.ws_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
   return dtype == MCB_F32 ? f32path::linear_fwd(a) : bf16path::linear_fwd(a, ds);
 }
 
-extern "C" int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const float* B, const void* dy,
-                                   const void* h_save, void* dx, float* dA, float* dB, int accumulate, int64_t M,
+extern "C" int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                                      const void* h_save, const void* dx_residual, void* dx, float* dA, float* dB, int accumulate, int64_t M,
                                    int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout, void* workspace,
                                    size_t workspace_bytes, void* stream) {
   if (!dy) return fail(MCB_ERR_NULL, "lora_linear_bwd: dy is null");
@@ -81,7 +81,7 @@ extern "C" int mcb_lora_linear_bwd(const void* x, const void* W, const float* A,
   if (!ds) return MCB_ERR_NOT_INIT;
   LoraArgs a;
   a.x = x; a.W = W; a.A = A; a.B = B; a.dy = dy; a.h_save = const_cast<void*>(h_save);
-  a.dx = dx; a.dA = dA; a.dB = dB; a.accumulate = accumulate;
+  a.dx = dx; a.dA = dA; a.dB = dB; a.accumulate = accumulate; a.residual = dx_residual;
   a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = w_layout;
   a.ws = workspace; a.ws_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
@@ -108,4 +108,19 @@ extern "C" int mcb_matmul(const void* a, const void* b, void* out, int64_t M, in
     return fail(MCB_ERR_WORKSPACE, "matmul(bf16): workspace %zu < %zu bytes", workspace_bytes, mcb_matmul_workspace_bytes(K, N, dtype));
   if (int rc = mcb_transpose_2d(b, workspace, K, N, dtype, stream)) return rc;
   return bf16path::matmul_nt(a, workspace, out, M, K, N, ds, st);
+}
+
+extern "C" int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const float* A, const float* B, void* y,
+                                   void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
+                                   int w_layout, void* workspace, size_t workspace_bytes, void* stream) {
+  return mcb_lora_linear_fwd_ex(x, W, bias, A, B, nullptr, y, h_save, M, K, N, r, scale, dtype, w_layout, workspace,
+                                workspace_bytes, stream);
+}
+
+extern "C" int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                                   const void* h_save, void* dx, float* dA, float* dB, int accumulate, int64_t M,
+                                   int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  return mcb_lora_linear_bwd_ex(x, W, A, B, dy, h_save, nullptr, dx, dA, dB, accumulate, M, K, N, r, scale, dtype, w_layout,
+                                workspace, workspace_bytes, stream);
 }

@@ -10,6 +10,7 @@ struct LoraArgs {
   const void* x = nullptr;     // [M,K]
   const void* W = nullptr;     // [N,K] or [K,N] per w_layout
   const void* bias = nullptr;  // [N] or null
+  const void* residual = nullptr;  // added to y (forward, [M,N]) or to dx (backward, [M,K]); may alias the output
   const float* A = nullptr;    // [K,r] float32
   const float* B = nullptr;    // [r,N] float32
   void* y = nullptr;           // [M,N]

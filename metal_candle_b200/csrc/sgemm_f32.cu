@@ -66,6 +66,22 @@ sgemm_strided_kernel(const float* __restrict__ A, int64_t sam, int64_t sak, cons
   }
 }
 
+__global__ void add_inplace_kernel(float* __restrict__ y, const float* __restrict__ r, int64_t n) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    y[i] += r[i];
+}
+
+int add_inplace(cudaStream_t st, float* y, const float* r, int64_t n) {
+  if (r == nullptr || n <= 0) return MCB_OK;
+  if (r == y) return fail(MCB_ERR_UNSUPPORTED, "f32 path: residual must not alias the output");
+  int64_t g = (n + 255) / 256;
+  if (g > 4096) g = 4096;
+  add_inplace_kernel<<<static_cast<unsigned>(g), 256, 0, st>>>(y, r, n);
+  MCB_CHECK_LAUNCH("add_inplace");
+  return MCB_OK;
+}
+
 int sgemm(cudaStream_t st, const float* A, int64_t sam, int64_t sak, const float* B, int64_t sbk, int64_t sbn,
           float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta, const float* bias) {
   if (M <= 0 || N <= 0) return MCB_OK;
@@ -107,6 +123,7 @@ int linear_fwd(const LoraArgs& a) {
   if (int rc = sgemm(a.stream, (const float*)a.x, a.K, 1, (const float*)a.W, sbk, sbn, (float*)a.y, a.N, a.M, a.N,
                      a.K, 1.0f, 0.0f, (const float*)a.bias))
     return rc;
+  if (int rc = add_inplace(a.stream, (float*)a.y, (const float*)a.residual, a.M * a.N)) return rc;
   if (a.r == 0) return MCB_OK;
   // hs = scale * (x A), kept transposed [rp, pitch] like the bf16 path's saved intermediate
   float* hs = static_cast<float*>(a.h_save);
@@ -133,6 +150,7 @@ int linear_bwd(const LoraArgs& a) {
     if (int rc = sgemm(a.stream, dy, a.N, 1, (const float*)a.W, sbk, sbn, (float*)a.dx, a.K, a.M, a.K, a.N, 1.0f, 0.0f,
                        nullptr))
       return rc;
+    if (int rc = add_inplace(a.stream, (float*)a.dx, (const float*)a.residual, a.M * a.K)) return rc;
   }
   if (a.r == 0) return MCB_OK;
   if (a.ws_bytes < workspace_bytes(a.M, a.K, a.N, a.r) || !a.ws)

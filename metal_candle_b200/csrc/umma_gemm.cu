@@ -54,6 +54,7 @@ struct GemmParams {
   float scale;
   __nv_bfloat16* Y;
   const __nv_bfloat16* bias;
+  const __nv_bfloat16* R;   // [M,N] added to the output (residual / gradient accumulation), or null
   __nv_bfloat16* H;   // [rp, h_pitch]: scale * X P^T, transposed (token index contiguous), or null
   int64_t h_pitch;
   int* status;
@@ -287,6 +288,21 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
             }
             uint4* yp = reinterpret_cast<uint4*>(p.Y + grow * p.N + gcol);
+            if (p.R != nullptr) {
+              const uint4* rp4 = reinterpret_cast<const uint4*>(p.R + grow * p.N + gcol);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                if (gcol + 8 * q4 + 8 <= p.N) {
+                  const uint4 rv = rp4[q4];
+                  const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                  for (int e2 = 0; e2 < 4; ++e2) {
+                    f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
+                    f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
+                  }
+                }
+              }
+            }
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
               if (gcol + 8 * q4 + 8 <= p.N)
@@ -385,6 +401,7 @@ struct GemmCall {
   const __nv_bfloat16* P = nullptr;   // [rp,K] or null
   const __nv_bfloat16* Q = nullptr;   // [N,rp] or null
   const __nv_bfloat16* bias = nullptr;
+  const __nv_bfloat16* R = nullptr;   // [M,N] or null
   __nv_bfloat16* Y = nullptr;         // [M,N] or null
   __nv_bfloat16* H = nullptr;         // [rp,h_pitch] or null
   int64_t h_pitch = 0;
@@ -400,7 +417,7 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   if (c.K % 8 != 0 || c.N % 8 != 0)
     return fail(MCB_ERR_ALIGN, "bf16 path needs in/out features that are multiples of 8 (got reduction %lld, output %lld)",
                 (long long)c.K, (long long)c.N);
-  if (!aligned16(c.X) || (c.W && !aligned16(c.W)) || (c.Y && !aligned16(c.Y)) || (c.H && !aligned16(c.H)))
+  if (!aligned16(c.X) || (c.W && !aligned16(c.W)) || (c.Y && !aligned16(c.Y)) || (c.H && !aligned16(c.H)) || (c.R && !aligned16(c.R)))
     return fail(MCB_ERR_ALIGN, "bf16 path needs 16-byte aligned matrices");
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -414,7 +431,7 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.num_k_blocks = (p.K + BK - 1) / BK;
   p.group_m = p.num_m_tiles < 16 ? p.num_m_tiles : 16;
   p.scale = c.scale;
-  p.Y = c.Y; p.bias = c.bias; p.H = c.H; p.h_pitch = c.h_pitch; p.status = ds->status_word;
+  p.Y = c.Y; p.bias = c.bias; p.R = c.R; p.H = c.H; p.h_pitch = c.h_pitch; p.status = ds->status_word;
   const uint32_t x_bytes = BM * BK * 2;
   const uint32_t w_bytes = p.has_w ? p.BN * BK * 2 : 0;
   const uint32_t p_bytes = p.rp * BK * 2;
@@ -531,6 +548,7 @@ int linear_fwd(const LoraArgs& a, const DeviceState* ds) {
   c.X = static_cast<const __nv_bfloat16*>(a.x);
   c.W = static_cast<const __nv_bfloat16*>(a.W);
   c.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  c.R = static_cast<const __nv_bfloat16*>(a.residual);
   c.Y = static_cast<__nv_bfloat16*>(a.y);
   c.M = a.M; c.N = a.N; c.K = a.K;
   if (a.r > 0) {
@@ -564,6 +582,7 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
     c.X = static_cast<const __nv_bfloat16*>(a.dy);
     c.W = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.W) : nullptr;
     c.Y = static_cast<__nv_bfloat16*>(a.dx);
+    c.R = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.residual) : nullptr;
     c.M = a.M; c.N = a.K; c.K = a.N;
     if (a.r > 0) {
       c.P = w.P; c.Q = w.Q;

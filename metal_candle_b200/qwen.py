@@ -161,17 +161,18 @@ class Qwen:
     def _norm(self, x, w):
         return backend.rms_norm_fused(x, self.config.rms_norm_eps, weight=w)
 
-    def _lin(self, x, lin: _Linear, save: bool):
+    def _lin(self, x, lin: _Linear, save: bool, residual=None):
         A, B, s = lin.ab()
-        return backend.lora_linear_forward(x, lin.weight, lin.bias, A, B, s, save_hidden=save and A is not None)
+        return backend.lora_linear_forward(x, lin.weight, lin.bias, A, B, s, save_hidden=save and A is not None,
+                                           residual=residual)
 
-    def _lin_bwd(self, x, lin: _Linear, dy, h_save, key: Optional[str], accumulate: bool):
+    def _lin_bwd(self, x, lin: _Linear, dy, h_save, key: Optional[str], accumulate: bool, dx_residual=None):
         A, B, s = lin.ab()
         ga = gb = None
         if A is not None:
             ga, gb = self._grad_slices[key]
         dx, _, _ = backend.lora_linear_backward(x, lin.weight_t, A, B, s, dy, h_save=h_save, grad_a=ga, grad_b=gb,
-                                                accumulate=accumulate)
+                                                accumulate=accumulate, dx_residual=dx_residual)
         return dx
 
     def _rope(self, x, heads: int, B: int, S: int, rotate: bool, inverse: bool):
@@ -231,16 +232,13 @@ class Qwen:
         P, O = self._attention_fwd(Qr, Kr, Vr, B, S)
         o = self._rope(O, c.num_attention_heads, B, S, False, True)   # back to [M, hidden]
         del O
-        a, ho = self._lin(o, L["o_proj"], save)
-        h2 = self._add(h, a)
-        del a
+        h2, ho = self._lin(o, L["o_proj"], save, residual=h)   # residual connection fused into the epilogue
         n2 = self._norm(h2, L["post_attention_layernorm"])
         gt, hg = self._lin(n2, L["gate_proj"], save)
         up, hu = self._lin(n2, L["up_proj"], save)
         act = torch.empty_like(gt)
         _lib.check(self.lib.mcb_swiglu_fwd(_ptr(gt), _ptr(up), _ptr(act), gt.numel(), self.dt, _stream()))
-        dn, hd = self._lin(act, L["down_proj"], save)
-        h3 = self._add(h2, dn)
+        h3, hd = self._lin(act, L["down_proj"], save, residual=h2)
         if not save:
             return h3, None
         keep_n2 = L["gate_proj"].lora is not None or L["up_proj"].lora is not None
@@ -307,9 +305,7 @@ class Qwen:
                                            _stream()))  # in place: gate <- d gate, up <- d up
         del dact
         dn2 = self._lin_bwd(sv["n2"], L["gate_proj"], gt, sv["hg"], key("gate_proj"), accumulate)
-        dn2b = self._lin_bwd(sv["n2"], L["up_proj"], up, sv["hu"], key("up_proj"), accumulate)
-        self._add(dn2, dn2b, out=dn2)
-        del dn2b
+        dn2 = self._lin_bwd(sv["n2"], L["up_proj"], up, sv["hu"], key("up_proj"), accumulate, dx_residual=dn2)
         dx2, _ = backend.rms_norm_backward(sv["h2"], L["post_attention_layernorm"], dn2, c.rms_norm_eps, need_dw=False)
         dh2 = self._add(dh3, dx2, out=dx2)
         # attention
@@ -323,9 +319,7 @@ class Qwen:
         del dQ, dK, dV, dO
         n1 = sv["n1"]
         dn1 = self._lin_bwd(n1, L["q_proj"], dq, sv["hq"], key("q_proj"), accumulate)
-        t = self._lin_bwd(n1, L["k_proj"], dk, sv["hk"], key("k_proj"), accumulate)
-        self._add(dn1, t, out=dn1)
-        t = self._lin_bwd(n1, L["v_proj"], dv, sv["hv"], key("v_proj"), accumulate)
-        self._add(dn1, t, out=dn1)
+        dn1 = self._lin_bwd(n1, L["k_proj"], dk, sv["hk"], key("k_proj"), accumulate, dx_residual=dn1)
+        dn1 = self._lin_bwd(n1, L["v_proj"], dv, sv["hv"], key("v_proj"), accumulate, dx_residual=dn1)
         dx1, _ = backend.rms_norm_backward(sv["h"], L["input_layernorm"], dn1, c.rms_norm_eps, need_dw=False)
         return self._add(dh2, dx1, out=dx1)

@@ -113,6 +113,28 @@ def test_plain_linear_rank0(cuda_device, dtype):
     assert R.max_abs_normalised(back(dx), c["dy"].astype(np.float64) @ c["W"].astype(np.float64)) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_lora_linear_fused_residuals(cuda_device, dtype):
+    """y = x W^T + s (x A) B + residual and dx = dy W + ... + dx_residual, the epilogue-fused adds that carry the
+    model's residual connections (src/models/qwen.rs:121,140) and the sum of input gradients."""
+    from metal_candle_b200 import backend as B
+
+    M, K, N, r, scale = 300, 896, 512, 8, 2.0
+    c = S.lora_linear_case(21, M, K, N, r)
+    c["res"] = S.normal(21, "res", (M, N))
+    c["dres"] = S.normal(21, "dres", (M, K))
+    o = rounded(c, dtype)
+    x, W, dy, res, dres = (dev_t(o[k], dtype, cuda_device) for k in ("x", "W", "dy", "res", "dres"))
+    A, Bm = dev_t(c["A"], torch.float32, cuda_device), dev_t(c["B"], torch.float32, cuda_device)
+    y, h = B.lora_linear_forward(x, W, None, A, Bm, scale, residual=res)
+    want_y, _ = R.lora_linear_forward(o["x"], o["W"], None, o["A"], o["B"], scale)
+    assert R.max_abs_normalised(back(y), want_y + o["res"]) <= TOL[dtype]
+    dx, dA, dB = B.lora_linear_backward(x, B.transpose_2d(W), A, Bm, scale, dy, h_save=h, dx_residual=dres)
+    wdx, wdA, wdB = R.lora_linear_backward(o["x"], o["W"], o["A"], o["B"], scale, o["dy"])
+    assert R.max_abs_normalised(back(dx), wdx + o["dres"]) <= TOL[dtype]
+    assert R.max_abs_normalised(back(dA), wdA) <= TOL[dtype] and R.max_abs_normalised(back(dB), wdB) <= TOL[dtype]
+
+
 def test_lora_reference_fixed_inputs(cuda_device):
     """The fixed inputs of tests/executor_direct.rs:339-376: x [[1..4],[5..8]], A 4x2, B 2x4, scale 0.5."""
     from metal_candle_b200 import backend as B
