@@ -34,6 +34,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 L2_BYTES = 126 * 1024 * 1024
+NO_GRAPH = False  # --no-graph: time launch by launch (what profiler captures use)
 
 
 def measured_peaks():
@@ -108,6 +109,8 @@ def _time_kernel(torch, fn, n_variants, iters, warmup):
         fn(i)
     torch.cuda.synchronize()
     try:
+        if NO_GRAPH:
+            raise RuntimeError("--no-graph")
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -128,7 +131,8 @@ def _time_kernel(torch, fn, n_variants, iters, warmup):
             ts.append(a.elapsed_time(b) / iters)
         return statistics.median(ts), min(ts)
     except Exception as e:  # capture refused: time launch by launch
-        sys.stderr.write(f"graph capture failed ({e!r}); timing individual launches\n")
+        if not NO_GRAPH:
+            sys.stderr.write(f"graph capture failed ({e!r}); timing individual launches\n")
         torch.cuda.synchronize()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
     for i, (a, b) in enumerate(evs):
@@ -439,7 +443,10 @@ def main():
     ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup-iters", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
+    global NO_GRAPH
+    NO_GRAPH = args.no_graph
     if args.micro or args.sweep:
         return run_micro(args)
     if args.impl == "reference":

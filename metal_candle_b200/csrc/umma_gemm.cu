@@ -175,6 +175,27 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       int i = 0;
+      // The rank update of a tile needs the epilogue warps to turn its rank accumulator into the bf16 operand
+      // first (a short wait: measured, deferring the update behind the next tile's main loop gains nothing).
+      int pend_a = -1;
+      uint32_t pend_u = 0;
+      auto finish_pending = [&]() -> bool {
+        const int pa = pend_a;
+        pend_a = -1;
+        if (!mbar_wait(b.h_ready0 + 8 * pa, pend_u & 1, abort_flag, 23, p.status)) return false;
+        if (!mbar_wait(b.q_full0 + 8 * pa, pend_u & 1, abort_flag, 24, p.status)) return false;
+        tcgen05_fence_after();
+        const uint32_t pd1 = tmem_base + pa * 256;
+        const uint32_t hs = base + p.hs_off + pa * p.hs_bytes;
+        const uint32_t qs = base + p.q_off + pa * p.q_bytes;
+        for (int kk = 0; kk < p.rp / 16; ++kk) {
+          const uint64_t hd = desc_noswz(hs + kk * 2 * (BM * 16), BM * 16, 128);
+          const uint64_t qd = desc_noswz(qs + kk * 2 * (p.BN * 16), p.BN * 16, 128);
+          umma_bf16(pd1, hd, qd, idesc_main, (p.has_w || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(b.d1_full0 + 8 * pa);
+        return true;
+      };
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++i) {
         const int a = i & 1;
         const uint32_t u = static_cast<uint32_t>(i >> 1);
@@ -201,20 +222,13 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (!ok) break;
         if (p.rp > 0) {
           umma_commit(b.d2_full0 + 8 * a);
-          ok = mbar_wait(b.h_ready0 + 8 * a, u & 1, abort_flag, 23, p.status);
+          pend_a = a;
+          pend_u = u;
+          ok = finish_pending();
           if (!ok) break;
-          ok = mbar_wait(b.q_full0 + 8 * a, u & 1, abort_flag, 24, p.status);
-          if (!ok) break;
-          tcgen05_fence_after();
-          const uint32_t hs = base + p.hs_off + a * p.hs_bytes;
-          const uint32_t qs = base + p.q_off + a * p.q_bytes;
-          for (int kk = 0; kk < p.rp / 16; ++kk) {
-            const uint64_t hd = desc_noswz(hs + kk * 2 * (BM * 16), BM * 16, 128);
-            const uint64_t qd = desc_noswz(qs + kk * 2 * (p.BN * 16), p.BN * 16, 128);
-            umma_bf16(d1, hd, qd, idesc_main, (p.has_w || kk > 0) ? 1u : 0u);
-          }
+        } else {
+          umma_commit(b.d1_full0 + 8 * a);
         }
-        umma_commit(b.d1_full0 + 8 * a);
       }
     }
   } else {
