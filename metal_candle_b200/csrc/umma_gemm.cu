@@ -35,6 +35,10 @@ namespace bf16path {
 using namespace umma;
 
 int init_grad_kernel();
+int init_gemm2_kernel();
+bool gemm2_eligible(int64_t M, int64_t N, int64_t K);
+int launch_gemm2(const __nv_bfloat16* X, const __nv_bfloat16* W, const __nv_bfloat16* bias, const __nv_bfloat16* R,
+                 __nv_bfloat16* Y, int64_t M, int64_t N, int64_t K, const DeviceState* ds, cudaStream_t st);
 size_t grad_partial_bytes(int64_t M, int64_t C, int rp);
 int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch, float* out, float* part, int64_t M,
                 int64_t C, int r, int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st);
@@ -433,6 +437,9 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
                 (long long)c.K, (long long)c.N);
   if (!aligned16(c.X) || (c.W && !aligned16(c.W)) || (c.Y && !aligned16(c.Y)) || (c.H && !aligned16(c.H)) || (c.R && !aligned16(c.R)))
     return fail(MCB_ERR_ALIGN, "bf16 path needs 16-byte aligned matrices");
+  // plain frozen linears of useful size run on CTA pairs (umma_gemm2.cu)
+  if (c.rp == 0 && c.W != nullptr && c.Y != nullptr && c.H == nullptr && gemm2_eligible(c.M, c.N, c.K))
+    return launch_gemm2(c.X, c.W, c.bias, c.R, c.Y, c.M, c.N, c.K, ds, st);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = static_cast<int>(c.M); p.N = static_cast<int>(c.N); p.K = static_cast<int>(c.K);
@@ -531,6 +538,7 @@ int check_ws(const LoraArgs& a, const char* op) {
 int init_kernels() {
   cudaError_t e = cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(lora_gemm_kernel)");
+  if (int rc = init_gemm2_kernel()) return rc;
   return init_grad_kernel();
 }
 
