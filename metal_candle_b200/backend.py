@@ -83,6 +83,9 @@ def _lora_shapes(x, lora_a, lora_b):
         raise TrainingError("Input must have at least 1 dimension")
     if x.shape[-1] != a_dims[0]:
         raise TrainingError(f"Input feature dimension mismatch: expected {a_dims[0]}, got {x.shape[-1]}")
+    if lora_a.dtype != torch.float32 or lora_b.dtype != torch.float32:
+        raise TrainingError(
+            f"LoRA matrices are float32 master copies (got {lora_a.dtype} and {lora_b.dtype}); the bf16 path rounds them itself")
     K, r = a_dims
     N = b_dims[1]
     M = x.numel() // K
@@ -113,8 +116,6 @@ def lora_forward_fused(x: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tens
     """CustomMetalOps::lora_forward_fused (src/backend/metal_ops.rs:126-144).  A, B are float32."""
     M, K, N, r = _lora_shapes(x, lora_a, lora_b)
     _require_cuda(x, lora_a, lora_b)
-    if lora_a.dtype != torch.float32 or lora_b.dtype != torch.float32:
-        raise TrainingError("LoRA matrices must be float32")
     lib = _lib_for(x)
     dt = _dtype_code(x)
     out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)

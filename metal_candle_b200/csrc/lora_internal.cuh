@@ -42,6 +42,22 @@ int matmul(const float* a, const float* b, float* out, int64_t M, int64_t K, int
 }  // namespace f32path
 
 namespace bf16path {
+// One call of the fused GEMM  Y = X W^T (+bias) (+R) + (scale X P^T) Q^T ; all operands bf16, K-major.
+struct GemmCall {
+  const __nv_bfloat16* X = nullptr;   // [M,K]
+  const __nv_bfloat16* W = nullptr;   // [N,K] or null
+  const __nv_bfloat16* P = nullptr;   // [rp,K] or null
+  const __nv_bfloat16* Q = nullptr;   // [N,rp] or null
+  const __nv_bfloat16* bias = nullptr;
+  const __nv_bfloat16* R = nullptr;   // [M,N] or null
+  __nv_bfloat16* Y = nullptr;         // [M,N] or null
+  __nv_bfloat16* H = nullptr;         // [rp,h_pitch] or null
+  int64_t h_pitch = 0;
+  int64_t M = 0, N = 0, K = 0;
+  int rp = 0;
+  int r_true = 0;  // unpadded rank, for the algorithmic flop count
+  float scale = 1.0f;
+};
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_fwd(const LoraArgs& a, const DeviceState* ds);

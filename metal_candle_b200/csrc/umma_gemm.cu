@@ -36,9 +36,8 @@ using namespace umma;
 
 int init_grad_kernel();
 int init_gemm2_kernel();
-bool gemm2_eligible(int64_t M, int64_t N, int64_t K);
-int launch_gemm2(const __nv_bfloat16* X, const __nv_bfloat16* W, const __nv_bfloat16* bias, const __nv_bfloat16* R,
-                 __nv_bfloat16* Y, int64_t M, int64_t N, int64_t K, const DeviceState* ds, cudaStream_t st);
+bool gemm2_eligible(const GemmCall& c);
+int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st);
 size_t grad_partial_bytes(int64_t M, int64_t C, int rp);
 int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch, float* out, float* part, int64_t M,
                 int64_t C, int r, int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st);
@@ -413,22 +412,6 @@ int pick_bn(int64_t N, int rp) {
   return bn;
 }
 
-struct GemmCall {
-  const __nv_bfloat16* X = nullptr;   // [M,K]
-  const __nv_bfloat16* W = nullptr;   // [N,K] or null
-  const __nv_bfloat16* P = nullptr;   // [rp,K] or null
-  const __nv_bfloat16* Q = nullptr;   // [N,rp] or null
-  const __nv_bfloat16* bias = nullptr;
-  const __nv_bfloat16* R = nullptr;   // [M,N] or null
-  __nv_bfloat16* Y = nullptr;         // [M,N] or null
-  __nv_bfloat16* H = nullptr;         // [rp,h_pitch] or null
-  int64_t h_pitch = 0;
-  int64_t M = 0, N = 0, K = 0;
-  int rp = 0;
-  int r_true = 0;  // unpadded rank, for the algorithmic flop count
-  float scale = 1.0f;
-};
-
 int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   if (c.M > 0x7fffff00ll || c.N > 0x7fffff00ll || c.K > 0x7fffff00ll)
     return fail(MCB_ERR_SHAPE, "bf16 GEMM: dimension exceeds 2^31");
@@ -437,9 +420,8 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
                 (long long)c.K, (long long)c.N);
   if (!aligned16(c.X) || (c.W && !aligned16(c.W)) || (c.Y && !aligned16(c.Y)) || (c.H && !aligned16(c.H)) || (c.R && !aligned16(c.R)))
     return fail(MCB_ERR_ALIGN, "bf16 path needs 16-byte aligned matrices");
-  // plain frozen linears of useful size run on CTA pairs (umma_gemm2.cu)
-  if (c.rp == 0 && c.W != nullptr && c.Y != nullptr && c.H == nullptr && gemm2_eligible(c.M, c.N, c.K))
-    return launch_gemm2(c.X, c.W, c.bias, c.R, c.Y, c.M, c.N, c.K, ds, st);
+  // linears of useful size (with or without the rank path) run on CTA pairs (umma_gemm2.cu)
+  if (gemm2_eligible(c)) return launch_gemm2(c, ds, st);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = static_cast<int>(c.M); p.N = static_cast<int>(c.N); p.K = static_cast<int>(c.K);

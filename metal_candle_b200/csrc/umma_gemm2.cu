@@ -1,4 +1,6 @@
-// Frozen linear  Y[M,N] = X[M,K] . W[N,K]^T (+ bias) (+ residual)  on CTA pairs (tcgen05 cta_group::2).
+// Linear with optional LoRA rank path
+//     Y[M,N] = X[M,K] . W[N,K]^T (+ bias) (+ residual) + (scale X P^T) Q^T
+// on CTA pairs (tcgen05 cta_group::2).
 //
 // The one-CTA kernel of umma_gemm.cu moves 48 KB from L2 per 128x256 tile and k-block and can hold only
 // four such stages, which leaves the tensor pipe waiting for loads about a third of the time.  Here two
@@ -7,11 +9,22 @@
 // reads both halves from both CTAs' shared memory, and each CTA finds its 128 x BN accumulator rows in
 // its own tensor memory.  Per SM and k-block that is 32 KB instead of 48 KB, and six stages fit.
 //
+// Rank path (rp > 0).  Each CTA puts its half of P (rp/2 rows) directly behind its half of W in a stage, so
+// the pair's B operand has BN + rp rows and one MMA fills the accumulator columns
+//     [ W half 0 : BN/2 | rank half 0 : rp/2 | W half 1 : BN/2 | rank half 1 : rp/2 ].
+// The epilogue warps of each CTA scale the rank columns of their own 128 rows, round them to bf16 into an
+// unswizzled K-major operand in their own shared memory (and store them transposed to H for the
+// weight-gradient kernel), and the leader then adds  H . Q^T  onto the two W halves with two more pair
+// MMAs per 16 rank columns, each CTA holding a quarter-tile of Q rows for either half.
+//
 // Synchronisation (no load uses cluster multicast):
 //   full[s]      in the LEADER: the leader's producer arms it for the bytes of BOTH CTAs; both producers'
 //                TMA loads (cp.async.bulk.tensor...cta_group::2) complete on it
 //   empty[s]     in each CTA: tcgen05.commit.cta_group::2 ... multicast::cluster from the leader's MMA thread
-//   acc_full[a]  in each CTA: same commit, after the last k-block of a tile
+//   d2_full[a]   in each CTA: same commit after the last k-block of a tile (rank columns complete)
+//   h_ready[a]   in the LEADER: 8 arrivals (epilogue warps of both CTAs) once the bf16 rank operand is in place
+//   q_full[a]    in the LEADER: the Q quarter-tiles of both CTAs have landed
+//   d1_full[a]   in each CTA: same commit, after the rank update (or the last k-block when rp == 0)
 //   acc_empty[a] in the LEADER: 8 arrivals, the 4 epilogue warps of each CTA (the peer's arrive remotely)
 // Every wait is bounded; both CTAs always meet at the cluster barrier before tensor memory is released.
 #include <cuda.h>
@@ -32,13 +45,17 @@ constexpr int kSmem2 = 227 * 1024 - 1024;
 
 struct Gemm2Params {
   int M, N, K;
-  int BN, stages;
+  int BN, stages, rp;
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;  // m tiles of 256 rows
+  float scale;
   __nv_bfloat16* Y;
   const __nv_bfloat16* bias;
   const __nv_bfloat16* R;
+  __nv_bfloat16* H;  // [rp, h_pitch]: scale * X P^T transposed, or null
+  int64_t h_pitch;
   int* status;
-  uint32_t stage_bytes, w_off, bar_off;
+  uint32_t stage_bytes, w_off, p_off, bar_off;
+  uint32_t q_off, q_bytes, hs_off, hs_bytes;  // per CTA and accumulator buffer; q_bytes covers both halves' quarter-tiles
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -89,6 +106,38 @@ __host__ __device__ constexpr uint32_t make_idesc2(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 }
 
+// NF accumulator columns of one output row: + bias, + residual, round to bf16, 16-byte stores.
+template <int NF>
+__device__ __forceinline__ void emit_cols(const Gemm2Params& p, float (&f)[NF], int64_t grow, int gcol) {
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < NF; ++j)
+      if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
+  }
+  uint4* yp = reinterpret_cast<uint4*>(p.Y + grow * p.N + gcol);
+  if (p.R != nullptr) {
+    const uint4* rp4 = reinterpret_cast<const uint4*>(p.R + grow * p.N + gcol);
+#pragma unroll
+    for (int q4 = 0; q4 < NF / 8; ++q4) {
+      if (gcol + 8 * q4 + 8 <= p.N) {
+        const uint4 rv = rp4[q4];
+        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+          f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
+          f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int q4 = 0; q4 < NF / 8; ++q4) {
+    if (gcol + 8 * q4 + 8 <= p.N)
+      yp[q4] = make_uint4(pack_bf16(f[8 * q4], f[8 * q4 + 1]), pack_bf16(f[8 * q4 + 2], f[8 * q4 + 3]),
+                          pack_bf16(f[8 * q4 + 4], f[8 * q4 + 5]), pack_bf16(f[8 * q4 + 6], f[8 * q4 + 7]));
+  }
+}
+
 __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& mt, int& nt) {
   const int per_band = p.group_m * p.num_n_tiles;
   const int band = t / per_band;
@@ -100,7 +149,8 @@ __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& m
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
-lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Gemm2Params p) {
+lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                  const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -110,16 +160,25 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
   const uint32_t full0 = base + p.bar_off;
   const uint32_t empty0 = full0 + 8 * kMaxStages2;
-  const uint32_t acc_full0 = empty0 + 8 * kMaxStages2;
-  const uint32_t acc_empty0 = acc_full0 + 16;
-  const uint32_t tmem_slot = acc_empty0 + 16;
+  const uint32_t d1_full0 = empty0 + 8 * kMaxStages2;
+  const uint32_t acc_empty0 = d1_full0 + 16;
+  const uint32_t d2_full0 = acc_empty0 + 16;
+  const uint32_t h_ready0 = d2_full0 + 16;
+  const uint32_t q_full0 = h_ready0 + 16;
+  const uint32_t tmem_slot = q_full0 + 16;
   const uint32_t abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 8); }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(d1_full0 + 8 * a, 1);
+      mbar_init(acc_empty0 + 8 * a, 8);
+      mbar_init(d2_full0 + 8 * a, 1);
+      mbar_init(h_ready0 + 8 * a, 8);
+      mbar_init(q_full0 + 8 * a, 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -134,7 +193,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   const int nkb = p.num_k_blocks;
-  const int half_n = p.BN / 2;
+  const int half_n = p.BN / 2, half_r = p.rp / 2, quarter_n = p.BN / 4;
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -142,11 +201,26 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; ok && t < p.num_tiles; t += npairs) {
+      int i = 0;
+      for (int t = pair; ok && t < p.num_tiles; t += npairs, ++i) {
         int mt, nt;
         tile_coords2(p, t, mt, nt);
         const int m0 = mt * 256 + static_cast<int>(rank) * 128;
         const int n0 = nt * p.BN + static_cast<int>(rank) * half_n;
+        if (p.rp > 0) {
+          // Q buffer a is free once the rank update of the tile before last has been read by the tensor pipe
+          const int a = i & 1;
+          if (i >= 2) ok = mbar_wait(d1_full0 + 8 * a, ((i - 2) >> 1) & 1, abort_flag, 60, p.status);
+          if (!ok) break;
+          const uint32_t qb = map_to_cta(q_full0 + 8 * a, 0);
+          if (rank == 0) mbar_expect_tx(q_full0 + 8 * a, 2 * p.q_bytes);
+          const uint32_t qs = base + p.q_off + a * p.q_bytes;
+          for (int h = 0; h < 2; ++h) {
+            const int rows0 = nt * p.BN + h * half_n + static_cast<int>(rank) * quarter_n;
+            for (int j = 0; j < p.rp / 8; ++j)
+              tma_load_2d_pair(qs + h * (p.q_bytes / 2) + j * quarter_n * 16, &tmQ, qb, j * 8, rows0);
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 61, p.status);
           if (!ok) break;
@@ -155,6 +229,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * p.stage_bytes);
           tma_load_2d_pair(sb, &tmX, fb, kb * BK2, m0);
           tma_load_2d_pair(sb + p.w_off, &tmW, fb, kb * BK2, n0);
+          if (p.rp > 0) tma_load_2d_pair(sb + p.p_off, &tmP, fb, kb * BK2, static_cast<int>(rank) * half_r);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -162,7 +237,8 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_idesc2(p.BN);
+      const uint32_t idesc = make_idesc2(p.BN + p.rp);
+      const uint32_t idesc_half = make_idesc2(half_n);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -186,7 +262,25 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma2_commit_both(acc_full0 + 8 * a);
+        if (p.rp > 0) {
+          umma2_commit_both(d2_full0 + 8 * a);
+          ok = mbar_wait(h_ready0 + 8 * a, u & 1, abort_flag, 65, p.status);
+          if (!ok) break;
+          ok = mbar_wait(q_full0 + 8 * a, u & 1, abort_flag, 66, p.status);
+          if (!ok) break;
+          asm volatile("fence.acq_rel.cluster;" ::: "memory");
+          tcgen05_fence_after();
+          const uint32_t hs = base + p.hs_off + a * p.hs_bytes;
+          const uint32_t qs = base + p.q_off + a * p.q_bytes;
+          for (int kk = 0; kk < p.rp / 16; ++kk) {
+            const uint64_t hd = desc_noswz(hs + kk * 2 * (128 * 16), 128 * 16, 128);
+            const uint64_t q0 = desc_noswz(qs + kk * 2 * (quarter_n * 16), quarter_n * 16, 128);
+            const uint64_t q1 = desc_noswz(qs + p.q_bytes / 2 + kk * 2 * (quarter_n * 16), quarter_n * 16, 128);
+            umma2_bf16(d, hd, q0, idesc_half, 1u);
+            umma2_bf16(d + half_n + half_r, hd, q1, idesc_half, 1u);
+          }
+        }
+        umma2_commit_both(d1_full0 + 8 * a);
       }
     }
   } else {
@@ -204,45 +298,71 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const uint32_t u = static_cast<uint32_t>(i >> 1);
       const int64_t grow = static_cast<int64_t>(m0) + row_in_tile;
       const uint32_t d = tmem_base + lane_addr + a * 256;
-      ok = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * a, u & 1, abort_flag, 64, p.status));
-      if (!ok) break;
-      tcgen05_fence_after();
-      for (int c = 0; c < p.BN; c += 32) {
-        uint32_t v0[16], v1[16];
-        tmem_ld_x16(d + c, v0);
-        tmem_ld_x16(d + c + 16, v1);
-        tmem_ld_wait();
-        const int gcol = n0 + c;
-        if (grow < p.M && gcol < p.N) {
-          float f[32];
+      if (p.rp > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(d2_full0 + 8 * a, u & 1, abort_flag, 67, p.status));
+        if (!ok) break;
+        tcgen05_fence_after();
+        uint8_t* hs_gen = gen_base + p.hs_off + a * p.hs_bytes;
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t tcol = d + (h == 0 ? half_n : p.BN + half_r);
+          for (int g = 0; g < half_r / 8; ++g) {
+            uint32_t v[8];
+            tmem_ld_x8(tcol + 8 * g, v);
+            tmem_ld_wait();
+            uint32_t w[4];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
-          if (p.bias != nullptr) {
+            for (int j = 0; j < 4; ++j)
+              w[j] = pack_bf16(__uint_as_float(v[2 * j]) * p.scale, __uint_as_float(v[2 * j + 1]) * p.scale);
+            // unswizzled K-major operand: 16-byte K chunk j of row m lives at j*(128*16) + m*16
+            const int chunk = h * (half_r / 8) + g;
+            *reinterpret_cast<uint4*>(hs_gen + chunk * (128 * 16) + row_in_tile * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (p.H != nullptr && nt == 0 && grow < p.M) {
+              __nv_bfloat16* hp = p.H + static_cast<int64_t>(chunk * 8) * p.h_pitch + grow;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
-          }
-          uint4* yp = reinterpret_cast<uint4*>(p.Y + grow * p.N + gcol);
-          if (p.R != nullptr) {
-            const uint4* rp4 = reinterpret_cast<const uint4*>(p.R + grow * p.N + gcol);
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              if (gcol + 8 * q4 + 8 <= p.N) {
-                const uint4 rv = rp4[q4];
-                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                for (int e2 = 0; e2 < 4; ++e2) {
-                  f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
-                  f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
-                }
+              for (int j = 0; j < 4; ++j) {
+                hp[(2 * j) * p.h_pitch] = __ushort_as_bfloat16(static_cast<unsigned short>(w[j] & 0xffffu));
+                hp[(2 * j + 1) * p.h_pitch] = __ushort_as_bfloat16(static_cast<unsigned short>(w[j] >> 16));
               }
             }
           }
+        }
+        fence_proxy_async_smem();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(h_ready0 + 8 * a);
+          else mbar_arrive_remote(h_ready0 + 8 * a, 0);
+        }
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(d1_full0 + 8 * a, u & 1, abort_flag, 64, p.status));
+      if (!ok) break;
+      tcgen05_fence_after();
+      // the W halves sit at columns [0, BN/2) and [BN/2 + rp/2, BN + rp/2) of the accumulator
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t tcol = d + (h == 0 ? 0 : half_n + half_r);
+        const int gcol0 = n0 + h * half_n;
+        int c = 0;
+        for (; c + 32 <= half_n; c += 32) {
+          uint32_t v0[16], v1[16];
+          tmem_ld_x16(tcol + c, v0);
+          tmem_ld_x16(tcol + c + 16, v1);
+          tmem_ld_wait();
+          if (grow < p.M && gcol0 + c < p.N) {
+            float f[32];
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            if (gcol + 8 * q4 + 8 <= p.N)
-              yp[q4] = make_uint4(pack_bf16(f[8 * q4], f[8 * q4 + 1]), pack_bf16(f[8 * q4 + 2], f[8 * q4 + 3]),
-                                  pack_bf16(f[8 * q4 + 4], f[8 * q4 + 5]), pack_bf16(f[8 * q4 + 6], f[8 * q4 + 7]));
+            for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
+            emit_cols<32>(p, f, grow, gcol0 + c);
+          }
+        }
+        if (c < half_n) {
+          uint32_t v0[16];
+          tmem_ld_x16(tcol + c, v0);
+          tmem_ld_wait();
+          if (grow < p.M && gcol0 + c < p.N) {
+            float f[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v0[j]);
+            emit_cols<16>(p, f, grow, gcol0 + c);
           }
         }
       }
@@ -273,16 +393,16 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-int make_map2(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int box_outer,
-              const char* what) {
+int make_map2(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int box_inner,
+              int box_outer, bool swizzle128, const char* what) {
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK2), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = reinterpret_cast<EncodeTiledFn2>(ds->encode_tiled)(
       map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MCB_ERR_ALIGN, "tensor map for %s rejected (CUresult %d)", what, static_cast<int>(r));
   return MCB_OK;
 }
@@ -295,18 +415,31 @@ int init_gemm2_kernel() {
   return MCB_OK;
 }
 
-// Whether the pair kernel takes this plain linear (everything else stays on the one-CTA kernel).
-bool gemm2_eligible(int64_t M, int64_t N, int64_t K) { return M >= 1024 && N >= 128 && K >= 64; }
+// Whether the pair kernel takes this call (everything else stays on the one-CTA kernel): a main product
+// with an output, large enough to fill CTA pairs; with a rank path, rank padded to a multiple of 16 and at
+// most 64 and a long enough reduction.
+bool gemm2_eligible(const GemmCall& c) {
+  if (c.W == nullptr || c.Y == nullptr || c.M < 1024 || c.N < 128 || c.K < 64) return false;
+  if (c.rp == 0) return true;
+  // The rank update costs a pair more per tile (its operand hand-over crosses the two CTAs) than it costs
+  // one CTA; measured, the pair wins once a tile's main loop is longer than about 1500 reduction elements
+  // (8192x4096x4096 r16: 1168 against 1039 TFLOP/s forward; 32768x896x896 r16: 817 against 894).
+  return c.rp % 16 == 0 && c.rp <= 64 && c.K >= 1536;
+}
 
-int launch_gemm2(const __nv_bfloat16* X, const __nv_bfloat16* W, const __nv_bfloat16* bias, const __nv_bfloat16* R,
-                 __nv_bfloat16* Y, int64_t M, int64_t N, int64_t K, const DeviceState* ds, cudaStream_t st) {
+int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
+  const int64_t M = c.M, N = c.N, K = c.K;
   Gemm2Params p;
   memset(&p, 0, sizeof(p));
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
-  // tile width: fewest n-tiles of at most 256 columns, evened out, multiple of 32 (so each half is a multiple of 16)
-  const int64_t tiles = (N + 255) / 256;
+  p.rp = c.rp;
+  p.scale = c.scale;
+  // tile width: fewest n-tiles that leave room for the rank columns in a 256-column accumulator, evened
+  // out, multiple of 32 (each half a multiple of 16, each quarter a multiple of 8)
+  const int cap = ((256 - c.rp) / 32) * 32;
+  const int64_t tiles = (N + cap - 1) / cap;
   int bn = static_cast<int>(((N + tiles - 1) / tiles + 31) / 32 * 32);
-  if (bn > 256) bn = 256;
+  if (bn > cap) bn = cap;
   if (bn < 32) bn = 32;
   p.BN = bn;
   p.num_m_tiles = static_cast<int>((M + 255) / 256);
@@ -314,22 +447,38 @@ int launch_gemm2(const __nv_bfloat16* X, const __nv_bfloat16* W, const __nv_bflo
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
   p.num_k_blocks = static_cast<int>((K + BK2 - 1) / BK2);
   p.group_m = p.num_m_tiles < 8 ? p.num_m_tiles : 8;
-  p.Y = Y; p.bias = bias; p.R = R; p.status = ds->status_word;
+  p.Y = c.Y; p.bias = c.bias; p.R = c.R; p.H = c.H; p.h_pitch = c.h_pitch; p.status = ds->status_word;
   const uint32_t x_bytes = 128 * BK2 * 2, w_bytes = static_cast<uint32_t>(bn / 2) * BK2 * 2;
+  const uint32_t p_bytes = static_cast<uint32_t>(c.rp / 2) * BK2 * 2;  // 8-row groups: a multiple of 1024
   p.w_off = x_bytes;
-  p.stage_bytes = x_bytes + w_bytes;
-  int stages = static_cast<int>((kSmem2 - 512) / p.stage_bytes);
+  p.p_off = x_bytes + w_bytes;
+  p.stage_bytes = x_bytes + w_bytes + p_bytes;
+  p.q_bytes = static_cast<uint32_t>(bn / 2) * c.rp * 2;
+  p.hs_bytes = 128u * c.rp * 2;
+  const uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + 512;
+  int stages = static_cast<int>((kSmem2 - fixed) / p.stage_bytes);
   if (stages > kMaxStages2) stages = kMaxStages2;
+  if (stages < 2) return fail(MCB_ERR_UNSUPPORTED, "pair GEMM: tile does not fit shared memory (BN=%d rp=%d)", bn, c.rp);
   p.stages = stages;
-  p.bar_off = stages * p.stage_bytes;
-  CUtensorMap tmX, tmW;
-  if (int rc = make_map2(ds, &tmX, X, K, M, 128, "X (pair)")) return rc;
-  if (int rc = make_map2(ds, &tmW, W, K, N, bn / 2, "W (pair)")) return rc;
+  p.q_off = stages * p.stage_bytes;
+  p.hs_off = p.q_off + 2 * p.q_bytes;
+  p.bar_off = p.hs_off + 2 * p.hs_bytes;
+  CUtensorMap tmX, tmW, tmP, tmQ;
+  if (int rc = make_map2(ds, &tmX, c.X, K, M, BK2, 128, true, "X (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmW, c.W, K, N, BK2, bn / 2, true, "W (pair)")) return rc;
+  if (c.rp > 0) {
+    if (int rc = make_map2(ds, &tmP, c.P, K, c.rp, BK2, c.rp / 2, true, "P (pair)")) return rc;
+    if (int rc = make_map2(ds, &tmQ, c.Q, c.rp, N, 8, bn / 4, false, "Q (pair)")) return rc;
+  } else { tmP = tmX; tmQ = tmX; }
   int pairs = ds->sm_count / 2;
   if (pairs > p.num_tiles) pairs = p.num_tiles;
   const bool prof = profile_on();
-  if (prof) profile_begin(kProfGemm, 2.0 * M * N * K, 2.0 * (static_cast<double>(M) * K + static_cast<double>(N) * K + static_cast<double>(M) * N), st);
-  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, p);
+  if (prof) {
+    const double m = static_cast<double>(M), n = static_cast<double>(N), k = static_cast<double>(K);
+    profile_begin(kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
+                  2.0 * (m * k + n * k + m * n) + 2.0 * c.rp * (k + n), st);
+  }
+  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm2_kernel");
   return MCB_OK;

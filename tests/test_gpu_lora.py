@@ -79,6 +79,11 @@ CASES = [
     (1000, 1024, 2048, 32),
     (300, 896, 4864, 8),
     (257, 2048, 896, 64),
+    # large enough for the CTA-pair kernel: rank path in both directions (reduction >= 1536 forward and
+    # backward), ragged tile edges; then the pair kernel without and the one-CTA kernel with the rank path
+    (1280, 1536, 1600, 16),
+    (1100, 1792, 1544, 64),
+    (1024, 896, 1024, 8),
 ]
 
 
@@ -97,12 +102,14 @@ def test_lora_variants(cuda_device, dtype):
     run_case(cuda_device, dtype, 256, 512, 512, 8, with_bias=False, save_h=False)
 
 
+@pytest.mark.parametrize("M", [300, 1300])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_plain_linear_rank0(cuda_device, dtype):
-    """r = 0: the frozen projection alone (k_proj, o_proj, MLP, lm_head in the training step)."""
+def test_plain_linear_rank0(cuda_device, dtype, M):
+    """r = 0: the frozen projection alone (k_proj, o_proj, MLP, lm_head in the training step); 1300 rows
+    reach the CTA-pair kernel."""
     from metal_candle_b200 import backend as B
 
-    M, K, N = 300, 896, 1000 if dtype == torch.float32 else 1024
+    K, N = 896, 1000 if dtype == torch.float32 else 1024
     c = rounded(S.lora_linear_case(5, M, K, N, 1), dtype)
     x, W, dy = (dev_t(c[k], dtype, cuda_device) for k in ("x", "W", "dy"))
     y, h = B.lora_linear_forward(x, W, None, None, None, 1.0)
@@ -113,13 +120,14 @@ def test_plain_linear_rank0(cuda_device, dtype):
     assert R.max_abs_normalised(back(dx), c["dy"].astype(np.float64) @ c["W"].astype(np.float64)) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("M,K,N,r", [(300, 896, 512, 8), (1100, 1792, 1600, 32)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_lora_linear_fused_residuals(cuda_device, dtype):
+def test_lora_linear_fused_residuals(cuda_device, dtype, M, K, N, r):
     """y = x W^T + s (x A) B + residual and dx = dy W + ... + dx_residual, the epilogue-fused adds that carry the
     model's residual connections (src/models/qwen.rs:121,140) and the sum of input gradients."""
     from metal_candle_b200 import backend as B
 
-    M, K, N, r, scale = 300, 896, 512, 8, 2.0
+    scale = 2.0
     c = S.lora_linear_case(21, M, K, N, r)
     c["res"] = S.normal(21, "res", (M, N))
     c["dres"] = S.normal(21, "dres", (M, K))
@@ -183,6 +191,33 @@ def test_lora_gradient_accumulation(cuda_device):
         assert torch.allclose(ga, 2 * dA, rtol=1e-5, atol=1e-6) and torch.allclose(gb, 2 * dB, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("M,K,N,r", [(1024, 64, 128, 16), (1500, 1024, 1000, 16), (2048, 1536, 896, 16),
+                                     (1100, 4864, 896, 32), (1024, 1600, 448, 64), (512, 64, 128, 16)])
+def test_bf16_kernels_exact_on_small_integers(cuda_device, M, K, N, r):
+    """Small-integer operands make every partial sum exact in fp32 and the rank intermediate exact in bf16,
+    so the tensor-core kernels (one CTA and CTA pair, with bias and fused residual) must match an fp32
+    matmul bit for bit after the final rounding, and the saved intermediate must be exact."""
+    from metal_candle_b200 import _lib, backend as B
+
+    g = torch.Generator(device="cpu").manual_seed(1000 * M + K + N + r)
+
+    def ints(shape, lo=-2, hi=3):
+        return torch.randint(lo, hi, shape, generator=g).float()
+
+    x, W, res, bias = ints((M, K)), ints((N, K)), ints((M, N)), ints((N,))
+    A = (torch.rand((K, r), generator=g) < 0.05).float() * ints((K, r), -1, 2)
+    Bm = ints((r, N), -1, 2)
+    dev = cuda_device
+    y, h = B.lora_linear_forward(x.to(dev).bfloat16(), W.to(dev).bfloat16(), bias.to(dev).bfloat16(), A.to(dev),
+                                 Bm.to(dev), 0.5, residual=res.to(dev).bfloat16())
+    hb = (0.5 * (x @ A)).bfloat16().float()
+    assert torch.equal(hb, 0.5 * (x @ A)), "test data: the intermediate must be exact in bf16"
+    want = x @ W.T + bias + res + hb @ Bm
+    assert torch.equal(h[:r, :M].float().T.cpu(), hb)
+    assert torch.equal(y.float().cpu(), want.bfloat16().float())
+    assert _lib.device_status() == 0
+
+
 def test_lora_rejects_bad_arguments(cuda_device):
     from metal_candle_b200 import backend as B
 
@@ -196,6 +231,9 @@ def test_lora_rejects_bad_arguments(cuda_device):
         B.lora_forward_fused(x, torch.zeros(8, 2, device=dev), torch.zeros(2, 8, device=dev), 1.0)
     with pytest.raises(B.TrainingError):
         B.lora_forward_fused(x.cpu(), torch.zeros(16, 2), torch.zeros(2, 8), 1.0)
+    with pytest.raises(B.TrainingError, match="float32 master copies"):
+        B.lora_forward_fused(x.bfloat16(), torch.zeros(16, 2, device=dev, dtype=torch.bfloat16),
+                             torch.zeros(2, 8, device=dev, dtype=torch.bfloat16), 1.0)
     # bf16 path: feature counts must be multiples of 8 (TMA row pitch)
     xb = torch.zeros(4, 20, device=dev, dtype=torch.bfloat16)
     with pytest.raises(B.TrainingError):
