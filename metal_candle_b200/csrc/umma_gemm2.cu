@@ -42,6 +42,8 @@ constexpr int BK2 = 64;
 constexpr int kThreads2 = 192;
 constexpr int kMaxStages2 = 8;
 constexpr int kSmem2 = 227 * 1024 - 1024;
+constexpr int kEpiBufs = 3;
+constexpr uint32_t kEpiBufBytes = 32 * 64;
 
 struct Gemm2Params {
   int M, N, K;
@@ -55,6 +57,7 @@ struct Gemm2Params {
   int64_t h_pitch;
   int* status;
   uint32_t stage_bytes, w_off, p_off, bar_off;
+  uint32_t epi_off;  // output staging: 4 epilogue warps x kEpiBufs buffers of 32 rows x 64 bytes
   uint32_t q_off, q_bytes, hs_off, hs_bytes;  // per CTA and accumulator buffer; q_bytes covers both halves' quarter-tiles
 };
 
@@ -106,36 +109,33 @@ __host__ __device__ constexpr uint32_t make_idesc2(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 }
 
-// NF accumulator columns of one output row: + bias, + residual, round to bf16, 16-byte stores.
-template <int NF>
-__device__ __forceinline__ void emit_cols(const Gemm2Params& p, float (&f)[NF], int64_t grow, int gcol) {
-  if (p.bias != nullptr) {
+// 32 accumulator columns of one output row: + bias, + residual (both only where the element exists), rounded to
+// bf16 and packed two per word.
+__device__ __forceinline__ void finish_cols(const Gemm2Params& p, float (&f)[32], int64_t grow, int gcol, uint32_t (&w)[16]) {
+  if (grow < p.M) {
+    if (p.bias != nullptr) {
 #pragma unroll
-    for (int j = 0; j < NF; ++j)
-      if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
-  }
-  uint4* yp = reinterpret_cast<uint4*>(p.Y + grow * p.N + gcol);
-  if (p.R != nullptr) {
-    const uint4* rp4 = reinterpret_cast<const uint4*>(p.R + grow * p.N + gcol);
+      for (int j = 0; j < 32; ++j)
+        if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
+    }
+    if (p.R != nullptr) {
+      const uint4* rp4 = reinterpret_cast<const uint4*>(p.R + grow * p.N + gcol);
 #pragma unroll
-    for (int q4 = 0; q4 < NF / 8; ++q4) {
-      if (gcol + 8 * q4 + 8 <= p.N) {
-        const uint4 rv = rp4[q4];
-        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+      for (int q4 = 0; q4 < 4; ++q4) {
+        if (gcol + 8 * q4 + 8 <= p.N) {
+          const uint4 rv = rp4[q4];
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
-        for (int e2 = 0; e2 < 4; ++e2) {
-          f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
-          f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
+          for (int e2 = 0; e2 < 4; ++e2) {
+            f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
+            f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
+          }
         }
       }
     }
   }
 #pragma unroll
-  for (int q4 = 0; q4 < NF / 8; ++q4) {
-    if (gcol + 8 * q4 + 8 <= p.N)
-      yp[q4] = make_uint4(pack_bf16(f[8 * q4], f[8 * q4 + 1]), pack_bf16(f[8 * q4 + 2], f[8 * q4 + 3]),
-                          pack_bf16(f[8 * q4 + 4], f[8 * q4 + 5]), pack_bf16(f[8 * q4 + 6], f[8 * q4 + 7]));
-  }
+  for (int j = 0; j < 16; ++j) w[j] = pack_bf16(f[2 * j], f[2 * j + 1]);
 }
 
 __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& mt, int& nt) {
@@ -150,7 +150,8 @@ __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& m
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                  const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const Gemm2Params p) {
+                  const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                  const __grid_constant__ CUtensorMap tmY, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -288,6 +289,8 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t epi_base = base + p.epi_off + static_cast<uint32_t>(quad) * (kEpiBufs * kEpiBufBytes);
+    int sbuf = 0;
     bool ok = true;
     int i = 0;
     for (int t = pair; ok && t < p.num_tiles; t += npairs, ++i) {
@@ -337,34 +340,36 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       ok = __all_sync(0xffffffffu, mbar_wait(d1_full0 + 8 * a, u & 1, abort_flag, 64, p.status));
       if (!ok) break;
       tcgen05_fence_after();
-      // the W halves sit at columns [0, BN/2) and [BN/2 + rp/2, BN + rp/2) of the accumulator
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t tcol = d + (h == 0 ? 0 : half_n + half_r);
-        const int gcol0 = n0 + h * half_n;
-        int c = 0;
-        for (; c + 32 <= half_n; c += 32) {
-          uint32_t v0[16], v1[16];
-          tmem_ld_x16(tcol + c, v0);
-          tmem_ld_x16(tcol + c + 16, v1);
-          tmem_ld_wait();
-          if (grow < p.M && gcol0 + c < p.N) {
-            float f[32];
+      // The W halves sit at columns [0, BN/2) and [BN/2 + rp/2, BN + rp/2) of the accumulator.  Output leaves in
+      // chunks of 32 columns: each thread rounds its row's 64 bytes into this warp's staging buffer (64-byte
+      // swizzle, conflict-free) and one tiled store per chunk writes 32 rows x 64 bytes, clipped at the edges.
+      for (int c = 0; c < p.BN; c += 32) {
+        const int gcol = n0 + c;
+        if (gcol >= p.N) break;
+        uint32_t v0[16], v1[16];
+        tmem_ld_x16(d + (c < half_n ? c : c + half_r), v0);
+        tmem_ld_x16(d + (c + 16 < half_n ? c + 16 : c + 16 + half_r), v1);
+        if (lane == 0) bulk_wait_group_read<kEpiBufs - 1>();  // the store that last used this buffer has read it
+        __syncwarp();
+        tmem_ld_wait();
+        float f[32];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
-            emit_cols<32>(p, f, grow, gcol0 + c);
-          }
-        }
-        if (c < half_n) {
-          uint32_t v0[16];
-          tmem_ld_x16(tcol + c, v0);
-          tmem_ld_wait();
-          if (grow < p.M && gcol0 + c < p.N) {
-            float f[16];
+        for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
+        uint32_t w[16];
+        finish_cols(p, f, grow, gcol, w);
+        const uint32_t buf = epi_base + static_cast<uint32_t>(sbuf) * kEpiBufBytes;
+        uint8_t* bg = gen_base + (buf - base) + lane * 64;
+        const int sw = (lane >> 1) & 3;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v0[j]);
-            emit_cols<16>(p, f, grow, gcol0 + c);
-          }
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(bg + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && m0 + quad * 32 < p.M) {
+          tma_store_2d(&tmY, buf, gcol, m0 + quad * 32);
+          bulk_commit_group();
         }
+        if (++sbuf == kEpiBufs) sbuf = 0;
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -373,6 +378,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         else mbar_arrive_remote(acc_empty0 + 8 * a, 0);
       }
     }
+    if (lane == 0) bulk_wait_group<0>();  // this warp's output stores are complete before the CTA may exit
   }
 
   // ---------------- common exit: both CTAs meet before either lets go of shared or tensor memory ----------------
@@ -394,14 +400,15 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int make_map2(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int box_inner,
-              int box_outer, bool swizzle128, const char* what) {
+              int box_outer, int swizzle_bytes, const char* what) {
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = reinterpret_cast<EncodeTiledFn2>(ds->encode_tiled)(
       map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_INTERLEAVE_NONE,
+      swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MCB_ERR_ALIGN, "tensor map for %s rejected (CUresult %d)", what, static_cast<int>(r));
   return MCB_OK;
@@ -455,20 +462,23 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.stage_bytes = x_bytes + w_bytes + p_bytes;
   p.q_bytes = static_cast<uint32_t>(bn / 2) * c.rp * 2;
   p.hs_bytes = 128u * c.rp * 2;
-  const uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + 512;
+  const uint32_t epi_bytes = 4 * kEpiBufs * kEpiBufBytes;
+  const uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + epi_bytes + 512;
   int stages = static_cast<int>((kSmem2 - fixed) / p.stage_bytes);
   if (stages > kMaxStages2) stages = kMaxStages2;
   if (stages < 2) return fail(MCB_ERR_UNSUPPORTED, "pair GEMM: tile does not fit shared memory (BN=%d rp=%d)", bn, c.rp);
   p.stages = stages;
   p.q_off = stages * p.stage_bytes;
   p.hs_off = p.q_off + 2 * p.q_bytes;
-  p.bar_off = p.hs_off + 2 * p.hs_bytes;
-  CUtensorMap tmX, tmW, tmP, tmQ;
-  if (int rc = make_map2(ds, &tmX, c.X, K, M, BK2, 128, true, "X (pair)")) return rc;
-  if (int rc = make_map2(ds, &tmW, c.W, K, N, BK2, bn / 2, true, "W (pair)")) return rc;
+  p.epi_off = p.hs_off + 2 * p.hs_bytes;  // a multiple of 1024, as the swizzled staging rows need
+  p.bar_off = p.epi_off + epi_bytes;
+  CUtensorMap tmX, tmW, tmP, tmQ, tmY;
+  if (int rc = make_map2(ds, &tmY, c.Y, N, M, 32, 32, 64, "Y (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmX, c.X, K, M, BK2, 128, 128, "X (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmW, c.W, K, N, BK2, bn / 2, 128, "W (pair)")) return rc;
   if (c.rp > 0) {
-    if (int rc = make_map2(ds, &tmP, c.P, K, c.rp, BK2, c.rp / 2, true, "P (pair)")) return rc;
-    if (int rc = make_map2(ds, &tmQ, c.Q, c.rp, N, 8, bn / 4, false, "Q (pair)")) return rc;
+    if (int rc = make_map2(ds, &tmP, c.P, K, c.rp, BK2, c.rp / 2, 128, "P (pair)")) return rc;
+    if (int rc = make_map2(ds, &tmQ, c.Q, c.rp, N, 8, bn / 4, 0, "Q (pair)")) return rc;
   } else { tmP = tmX; tmQ = tmX; }
   int pairs = ds->sm_count / 2;
   if (pairs > p.num_tiles) pairs = p.num_tiles;
@@ -478,7 +488,7 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     profile_begin(kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
                   2.0 * (m * k + n * k + m * n) + 2.0 * c.rp * (k + n), st);
   }
-  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, p);
+  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm2_kernel");
   return MCB_OK;
