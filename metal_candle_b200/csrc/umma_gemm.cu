@@ -63,6 +63,8 @@ struct GemmParams {
   int* status;
   uint32_t stage_bytes, w_off, p_off;        // within a stage
   uint32_t q_off, q_bytes, hs_off, hs_bytes; // from the aligned base
+  uint32_t epi_off;  // output staging (epi_bufs buffers per epilogue warp); epi_bufs == 0: direct stores
+  int epi_bufs;
   uint32_t bar_off;
 };
 
@@ -84,6 +86,7 @@ struct Bars {
 __global__ void __launch_bounds__(kThreads, 1)
 lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                  const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                 const __grid_constant__ CUtensorMap tmY,
                  const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -239,6 +242,8 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t epi_base = base + p.epi_off + static_cast<uint32_t>(quad * p.epi_bufs) * kEpiBufBytes;
+    int sbuf = 0;
     bool ok = true;
     int i = 0;
     for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++i) {
@@ -286,9 +291,36 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       ok = __all_sync(0xffffffffu, mbar_wait(b.d1_full0 + 8 * a, u & 1, abort_flag, 32, p.status));
       if (!ok) break;
       tcgen05_fence_after();
-      if (p.Y != nullptr) {
-        // 32 accumulator columns per round: two tensor-memory loads in flight, then 64 contiguous bytes per
-        // thread (whole 32-byte sectors) to global memory.
+      if (p.Y != nullptr && p.epi_bufs > 0) {
+        // Output leaves in chunks of 32 columns: each thread rounds its row's 64 bytes into this warp's staging
+        // buffer (64-byte swizzle, conflict-free) and one tiled store per chunk writes 32 rows x 64 bytes,
+        // clipped at the matrix edges.
+        for (int c = 0; c < p.BN; c += 32) {
+          const int gcol = n0 + c;
+          if (gcol >= p.N) break;
+          uint32_t v0[16], v1[16];
+          tmem_ld_x16(d1 + c, v0);
+          tmem_ld_x16(d1 + c + 16, v1);
+          if (lane == 0) bulk_wait_group_read_n(p.epi_bufs - 1);  // the store that last used this buffer has read it
+          __syncwarp();
+          tmem_ld_wait();
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
+          uint32_t w[16];
+          finish_cols(f, p.bias, p.R, grow, gcol, p.M, p.N, w);
+          const uint32_t buf = epi_base + static_cast<uint32_t>(sbuf) * kEpiBufBytes;
+          stage_row(gen_base + (buf - base), lane, w);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && m0 + quad * 32 < p.M) {
+            tma_store_2d(&tmY, buf, gcol, m0 + quad * 32);
+            bulk_commit_group();
+          }
+          if (++sbuf == p.epi_bufs) sbuf = 0;
+        }
+      } else if (p.Y != nullptr) {
+        // no room for staging: 64 contiguous bytes per thread straight to global memory
         for (int c = 0; c < p.BN; c += 32) {
           uint32_t v0[16], v1[16];
           tmem_ld_x16(d1 + c, v0);
@@ -333,6 +365,7 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(b.acc_empty0 + 8 * a);
     }
+    if (lane == 0) bulk_wait_group<0>();  // this warp's output stores are complete before the CTA may exit
   }
 
   // ---------------- common exit ----------------
@@ -385,14 +418,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int make_map(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int box_inner,
-             int box_outer, bool swizzle128, const char* what) {
+             int box_outer, int swizzle_bytes, const char* what) {
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = reinterpret_cast<EncodeTiledFn>(ds->encode_tiled)(
       map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_INTERLEAVE_NONE,
+      swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(MCB_ERR_ALIGN, "tensor map for %s rejected (CUresult %d): ptr=%p inner=%lld outer=%lld box=%dx%d", what,
@@ -443,22 +477,34 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.stage_bytes = x_bytes + w_bytes + p_bytes;  // every part is a multiple of 1024
   p.q_bytes = static_cast<uint32_t>(p.BN) * p.rp * 2;
   p.hs_bytes = static_cast<uint32_t>(BM) * p.rp * 2;
-  const uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + 512;
+  uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + 512;
   int stages = static_cast<int>((kSmemBudget - fixed) / p.stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
+  // output staging takes what the stage ring leaves over, never a stage
+  p.epi_bufs = 0;
+  if (c.Y != nullptr && stages >= 2) {
+    const uint32_t spare = kSmemBudget - fixed - static_cast<uint32_t>(stages) * p.stage_bytes;
+    p.epi_bufs = static_cast<int>(spare / (4 * kEpiBufBytes));
+    if (p.epi_bufs > kEpiBufsMax) p.epi_bufs = kEpiBufsMax;
+  }
+  const uint32_t epi_bytes = 4 * kEpiBufBytes * p.epi_bufs;
+  fixed += epi_bytes;
   if (stages < 2) return fail(MCB_ERR_UNSUPPORTED, "bf16 GEMM: tile does not fit shared memory (BN=%d rp=%d)", p.BN, p.rp);
   p.stages = stages;
   p.q_off = stages * p.stage_bytes;
   p.hs_off = p.q_off + 2 * p.q_bytes;
-  p.bar_off = p.hs_off + 2 * p.hs_bytes;
+  p.epi_off = p.hs_off + 2 * p.hs_bytes;  // a multiple of 1024
+  p.bar_off = p.epi_off + epi_bytes;
 
-  CUtensorMap tmX, tmW, tmP, tmQ;
-  if (int rc = make_map(ds, &tmX, c.X, c.K, c.M, BK, BM, true, "X")) return rc;
-  if (p.has_w) { if (int rc = make_map(ds, &tmW, c.W, c.K, c.N, BK, p.BN, true, "W")) return rc; }
+  CUtensorMap tmX, tmW, tmP, tmQ, tmY;
+  if (p.epi_bufs > 0) { if (int rc = make_map(ds, &tmY, c.Y, c.N, c.M, 32, 32, 64, "Y")) return rc; }
+  else tmY = CUtensorMap{};
+  if (int rc = make_map(ds, &tmX, c.X, c.K, c.M, BK, BM, 128, "X")) return rc;
+  if (p.has_w) { if (int rc = make_map(ds, &tmW, c.W, c.K, c.N, BK, p.BN, 128, "W")) return rc; }
   else tmW = tmX;
   if (p.rp > 0) {
-    if (int rc = make_map(ds, &tmP, c.P, c.K, p.rp, BK, p.rp, true, "P")) return rc;
-    if (int rc = make_map(ds, &tmQ, c.Q, p.rp, c.N, 8, p.BN, false, "Q")) return rc;
+    if (int rc = make_map(ds, &tmP, c.P, c.K, p.rp, BK, p.rp, 128, "P")) return rc;
+    if (int rc = make_map(ds, &tmQ, c.Q, p.rp, c.N, 8, p.BN, 0, "Q")) return rc;
   } else { tmP = tmX; tmQ = tmX; }
   const int grid = p.num_tiles < ds->sm_count ? p.num_tiles : ds->sm_count;
   const bool prof = profile_on();
@@ -468,7 +514,7 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     const double bytes = 2.0 * (m * k + (p.has_w ? n * k : 0.0) + (c.Y ? m * n : 0.0)) + 2.0 * p.rp * (k + n);
     profile_begin(kProfGemm, flops, bytes, st);
   }
-  lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, p);
+  lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm_kernel");
   return MCB_OK;

@@ -42,8 +42,7 @@ constexpr int BK2 = 64;
 constexpr int kThreads2 = 192;
 constexpr int kMaxStages2 = 8;
 constexpr int kSmem2 = 227 * 1024 - 1024;
-constexpr int kEpiBufs = 3;
-constexpr uint32_t kEpiBufBytes = 32 * 64;
+constexpr int kEpiBufs = kEpiBufsMax;
 
 struct Gemm2Params {
   int M, N, K;
@@ -107,35 +106,6 @@ __device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
 // kind::f16, D=f32, A=B=bf16 K-major, M=256 (the pair), N=n
 __host__ __device__ constexpr uint32_t make_idesc2(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
-}
-
-// 32 accumulator columns of one output row: + bias, + residual (both only where the element exists), rounded to
-// bf16 and packed two per word.
-__device__ __forceinline__ void finish_cols(const Gemm2Params& p, float (&f)[32], int64_t grow, int gcol, uint32_t (&w)[16]) {
-  if (grow < p.M) {
-    if (p.bias != nullptr) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (gcol + j < p.N) f[j] += __bfloat162float(p.bias[gcol + j]);
-    }
-    if (p.R != nullptr) {
-      const uint4* rp4 = reinterpret_cast<const uint4*>(p.R + grow * p.N + gcol);
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        if (gcol + 8 * q4 + 8 <= p.N) {
-          const uint4 rv = rp4[q4];
-          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-          for (int e2 = 0; e2 < 4; ++e2) {
-            f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
-            f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
-          }
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < 16; ++j) w[j] = pack_bf16(f[2 * j], f[2 * j + 1]);
 }
 
 __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& mt, int& nt) {
@@ -356,13 +326,9 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 16; ++j) { f[j] = __uint_as_float(v0[j]); f[16 + j] = __uint_as_float(v1[j]); }
         uint32_t w[16];
-        finish_cols(p, f, grow, gcol, w);
+        finish_cols(f, p.bias, p.R, grow, gcol, p.M, p.N, w);
         const uint32_t buf = epi_base + static_cast<uint32_t>(sbuf) * kEpiBufBytes;
-        uint8_t* bg = gen_base + (buf - base) + lane * 64;
-        const int sw = (lane >> 1) & 3;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(bg + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        stage_row(gen_base + (buf - base), lane, w);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && m0 + quad * 32 < p.M) {

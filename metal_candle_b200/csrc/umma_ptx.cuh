@@ -74,6 +74,12 @@ __device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.
 // at most N of this thread's store groups may still be incomplete
 template <int N>
 __device__ __forceinline__ void bulk_wait_group() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+// at most n (0..2) store groups may still be reading their source
+__device__ __forceinline__ void bulk_wait_group_read_n(int n) {
+  if (n >= 2) bulk_wait_group_read<2>();
+  else if (n == 1) bulk_wait_group_read<1>();
+  else bulk_wait_group_read<0>();
+}
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -128,6 +134,49 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Output staging of the GEMM epilogues: per epilogue warp, up to kEpiBufsMax buffers of 32 rows x 64 bytes
+// (32 bf16 columns), rows swizzled in 16-byte units as CU_TENSOR_MAP_SWIZZLE_64B expects.
+constexpr int kEpiBufsMax = 3;
+constexpr uint32_t kEpiBufBytes = 32 * 64;
+
+// 32 accumulator columns of output row `grow`: + bias, + residual (both only where the element exists),
+// rounded to bf16 and packed two per word.
+__device__ __forceinline__ void finish_cols(float (&f)[32], const __nv_bfloat16* bias, const __nv_bfloat16* R, int64_t grow,
+                                            int gcol, int M, int N, uint32_t (&w)[16]) {
+  if (grow < M) {
+    if (bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (gcol + j < N) f[j] += __bfloat162float(bias[gcol + j]);
+    }
+    if (R != nullptr) {
+      const uint4* rp4 = reinterpret_cast<const uint4*>(R + grow * N + gcol);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        if (gcol + 8 * q4 + 8 <= N) {
+          const uint4 rv = rp4[q4];
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int e2 = 0; e2 < 4; ++e2) {
+            f[8 * q4 + 2 * e2] += __uint_as_float(rw[e2] << 16);
+            f[8 * q4 + 2 * e2 + 1] += __uint_as_float(rw[e2] & 0xffff0000u);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) w[j] = pack_bf16(f[2 * j], f[2 * j + 1]);
+}
+// This lane's 64-byte row into a staging buffer (generic address of the buffer's first byte).
+__device__ __forceinline__ void stage_row(uint8_t* buf, int lane, const uint32_t (&w)[16]) {
+  uint8_t* bg = buf + lane * 64;
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(bg + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
 }
 
 
