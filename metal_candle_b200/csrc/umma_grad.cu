@@ -20,7 +20,8 @@ namespace {
 
 constexpr int kGradThreads = 192;
 constexpr int kGradBK = 64;       // tokens per stage
-constexpr int kGradStages = 6;
+constexpr int kGradMaxStages = 12;  // enough bytes in flight per SM to cover HBM latency under load
+constexpr int kGradSmemBudget = 216 * 1024;
 constexpr uint32_t kXBoxBytes = 64 * 64 * 2;  // one [64 tokens x 64 features] box
 
 struct GradParams {
@@ -29,6 +30,7 @@ struct GradParams {
   float* part;  // [splits][C][rp]
   int* status;
   uint32_t stage_bytes, bar_off;
+  int stages;
 };
 
 __global__ void __launch_bounds__(kGradThreads)
@@ -38,13 +40,13 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kGradStages, done_bar = empty0 + 8 * kGradStages;
+  const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kGradMaxStages, done_bar = empty0 + 8 * kGradMaxStages;
   const uint32_t tmem_slot = done_bar + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGradStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     mbar_init(done_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -75,7 +77,7 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         tma_load_2d(sb, &tmX, fb, c0, kb * kGradBK);
         tma_load_2d(sb + kXBoxBytes, &tmX, fb, c0 + 64, kb * kGradBK);
         tma_load_2d(sb + 2 * kXBoxBytes, &tmH, fb, kb * kGradBK, 0);
-        if (++stage == kGradStages) { stage = 0; phase ^= 1; }
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -98,7 +100,7 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           umma_bf16(tmem_base, ad, bd, idesc, (i | k4) != 0 ? 1u : 0u);
         }
         umma_commit(empty0 + 8 * stage);
-        if (++stage == kGradStages) { stage = 0; phase ^= 1; }
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
       if (ok) umma_commit(done_bar);
     }
@@ -169,7 +171,7 @@ int encode(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inn
   return MCB_OK;
 }
 
-constexpr int kGradSmem = kGradStages * (2 * 8192 + 64 * 128) + 1024 + 256;
+constexpr int kGradSmem = kGradSmemBudget + 1024 + 512;
 
 }  // namespace
 
@@ -179,11 +181,12 @@ int init_grad_kernel() {
   return MCB_OK;
 }
 
-// Token slices per feature tile: about one CTA per SM (measured: more, shorter CTAs lose to their set-up cost).
+// Token slices per feature tile: at most one CTA per SM, all resident at once (measured: more, shorter CTAs
+// lose to their set-up cost, and a second round of CTAs doubles the time).
 int grad_splits(int64_t M, int64_t C, int sm_count, int* kb_per_split) {
   const int64_t c_tiles = (C + BM - 1) / BM;
   const int64_t total_kb = (M + kGradBK - 1) / kGradBK;
-  int64_t target = (static_cast<int64_t>(sm_count) + c_tiles - 1) / c_tiles;
+  int64_t target = static_cast<int64_t>(sm_count) / c_tiles;
   if (target > total_kb) target = total_kb;
   if (target < 1) target = 1;
   const int64_t per = (total_kb + target - 1) / target;
@@ -207,7 +210,9 @@ int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch
   p.part = part;
   p.status = ds->status_word;
   p.stage_bytes = 2 * kXBoxBytes + static_cast<uint32_t>(rp) * 128;
-  p.bar_off = kGradStages * p.stage_bytes;
+  p.stages = static_cast<int>(kGradSmemBudget / p.stage_bytes);
+  if (p.stages > kGradMaxStages) p.stages = kGradMaxStages;
+  p.bar_off = p.stages * p.stage_bytes;
   CUtensorMap tmX, tmH;
   if (int rc = encode(ds, &tmX, X, C, M, C, 64, kGradBK, "grad X")) return rc;
   if (int rc = encode(ds, &tmH, Ht, M, rp, h_pitch, kGradBK, rp, "grad H")) return rc;
