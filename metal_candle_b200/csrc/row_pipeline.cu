@@ -4,8 +4,11 @@
 // which on B200 is not enough to cover HBM latency at 6.5 TB/s.  Here the bytes in flight live in shared
 // memory instead: a producer thread streams tiles of W consecutive rows (one row per consumer warp) of
 // every input into a ring of stages with cp.async.bulk.shared.global (completion counted on an mbarrier),
-// W consumer warps each take one row of the tile out of shared memory (two passes: reduce, then write),
-// reduce with warp shuffles only, and store the result straight to global memory with 16-byte stores.
+// W consumer warps each take one row of the tile out of shared memory, reduce with warp shuffles only, and
+// store the result straight to global memory with 16-byte stores.  The consumers are bound by instruction
+// issue, not by memory, so the forward kernels read a row from shared memory ONCE into registers (rows of up
+// to 256 vectors), do their arithmetic two lanes at a time (fma/mul/add .f32x2) and, for RMSNorm, take the
+// weight as float32 from a shared-memory copy made once per CTA; wider rows stream from shared memory twice.
 // Two CTAs per SM with up to ~100 KB of stages each keep ~100-200 KB in flight per SM.
 //
 // Causal softmax rows are copied only up to the query position (rounded up to 16 bytes), so the masked
@@ -39,6 +42,7 @@ struct Params {
   float eps, scale;
   int* status;
   uint32_t stage_bytes, bar_off;
+  uint32_t w_off;    // float32 copy of the rmsnorm weight (register-resident forward only), 0 = none
 };
 
 // 2^x by the special-function unit (ex2.approx.ftz): x <= 0 here, -inf gives 0.
@@ -53,14 +57,39 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+
+// ---- two-lane float32 arithmetic (fma.rn.f32x2 and friends) ----
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+// This lane's vectors lane, lane+32, ... of a row in shared memory, kept as they are (16 bytes each); vectors
+// at or beyond nv read as `fill`.
+template <typename T, int KMAX>
+__device__ __forceinline__ void load_row(const uint8_t* s0, int lane, int nv, Vec16<T> (&v)[KMAX], float fill) {
+  using V = Vec16<T>;
+  float ff[V::N];
+#pragma unroll
+  for (int j = 0; j < V::N; ++j) ff[j] = fill;
+  V fv;
+  fv.from_float(ff);
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nv) v[k].raw = reinterpret_cast<const decltype(fv.raw)*>(s0)[vi];
+    else v[k].raw = fv.raw;
+  }
+}
+
 // bytes of a causal row that are needed: columns 0..q, rounded up to 16 bytes
 __device__ __forceinline__ uint32_t causal_bytes(int q, int elem_bytes, int row_bytes) {
   uint32_t b = (static_cast<uint32_t>(q + 1) * elem_bytes + 15u) & ~15u;
   return b < static_cast<uint32_t>(row_bytes) ? b : static_cast<uint32_t>(row_bytes);
 }
 
-template <typename T, int OP, int W, int KMAX>  // KMAX > 0: rmsnorm backward with dw, KMAX vectors per lane
-__global__ void __launch_bounds__((W + 1) * 32)
+// KMAX > 0: a lane owns vectors lane, lane+32, ... (KMAX of them) of every row and keeps them in registers —
+// the row itself (forward ops) or the dw sums (rmsnorm backward with dw).  KMAX == 0: rows of any width,
+// streamed from shared memory twice.
+template <typename T, int OP, int W, int KMAX>
+__global__ void __launch_bounds__((W + 1) * 32, ((OP == kRmsFwd || OP == kSmFwd) && KMAX > 0 && (OP == kRmsFwd || KMAX * Vec16<T>::N <= 32 || W <= 8)) ? 2 : 1)
 rowpipe_kernel(const Params p) {
   using V = Vec16<T>;
   constexpr int N = V::N;
@@ -78,13 +107,22 @@ rowpipe_kernel(const Params p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
   }
+  const float* wsm = nullptr;
+  if constexpr (OP == kRmsFwd && KMAX > 0) {
+    if (p.w_off != 0) {
+      float* wd = reinterpret_cast<float*>(gen_base + p.w_off);
+      for (int c = threadIdx.x; c < p.D; c += blockDim.x) wd[c] = to_f32(static_cast<const T*>(p.w)[c]);
+      wsm = wd;
+    }
+  }
   __syncthreads();
 
   const int64_t n_tiles = (p.rows + W - 1) / W;
   const uint32_t stream_bytes = static_cast<uint32_t>(W) * p.row_bytes;
 
-  float dwa[KMAX > 0 ? KMAX : 1][N];
-  if constexpr (KMAX > 0) {
+  constexpr bool kDw = (OP == kRmsBwd && KMAX > 0);  // per-lane dw sums kept in registers
+  float dwa[kDw ? KMAX : 1][N];
+  if constexpr (kDw) {
 #pragma unroll
     for (int k = 0; k < KMAX; ++k)
 #pragma unroll
@@ -140,7 +178,43 @@ rowpipe_kernel(const Params p) {
         const uint8_t* s0 = gen_base + stage * p.stage_bytes + warp * p.row_bytes;
         const uint8_t* s1 = s0 + stream_bytes;
         T* orow = static_cast<T*>(p.out) + row * p.D;
-        if constexpr (OP == kRmsFwd) {
+        if constexpr (OP == kRmsFwd && KMAX > 0) {
+          V v[KMAX];
+          load_row<T, KMAX>(s0, lane, nvec, v, 0.0f);
+          float2 acc = f2(0.0f, 0.0f);
+#pragma unroll
+          for (int k = 0; k < KMAX; ++k) {
+            float f[N];
+            v[k].to_float(f);
+#pragma unroll
+            for (int j = 0; j < N; j += 2) acc = __ffma2_rn(f2(f[j], f[j + 1]), f2(f[j], f[j + 1]), acc);
+          }
+          const float ss = warp_sum(acc.x + acc.y);
+          const float rinv = 1.0f / sqrtf(ss * inv_d + p.eps);
+          if (p.rstd != nullptr && lane == 0) p.rstd[row] = rinv;
+          const float2 r2 = f2(rinv, rinv);
+#pragma unroll
+          for (int k = 0; k < KMAX; ++k) {
+            const int vi = lane + 32 * k;
+            if (vi < nvec) {
+              float f[N], o[N];
+              v[k].to_float(f);
+#pragma unroll
+              for (int j = 0; j < N; j += 4) {
+                float2 a = __fmul2_rn(f2(f[j], f[j + 1]), r2), b = __fmul2_rn(f2(f[j + 2], f[j + 3]), r2);
+                if (wsm != nullptr) {
+                  const float4 g = *reinterpret_cast<const float4*>(wsm + vi * N + j);
+                  a = __fmul2_rn(a, f2(g.x, g.y));
+                  b = __fmul2_rn(b, f2(g.z, g.w));
+                }
+                o[j] = a.x; o[j + 1] = a.y; o[j + 2] = b.x; o[j + 3] = b.y;
+              }
+              V a;
+              a.from_float(o);
+              __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+            }
+          }
+        } else if constexpr (OP == kRmsFwd) {
           float ss = 0.0f;
 #pragma unroll 4
           for (int vi = lane; vi < nvec; vi += 32) {
@@ -209,7 +283,7 @@ rowpipe_kernel(const Params p) {
             a.from_float(o);
             __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
           };
-          if constexpr (KMAX > 0) {
+          if constexpr (kDw) {
 #pragma unroll
             for (int k = 0; k < KMAX; ++k) {
               const int vi = lane + 32 * k;
@@ -217,6 +291,93 @@ rowpipe_kernel(const Params p) {
             }
           } else {
             for (int vi = lane; vi < nvec; vi += 32) body(vi, nullptr);
+          }
+        } else if constexpr (OP == kSmFwd && KMAX > 0) {
+          const bool causal = p.causal_seq > 0;
+          const int q = causal ? static_cast<int>(row % p.causal_seq) : p.D;  // last kept column
+          const int nv_keep = causal ? min(nvec, q / N + 1) : nvec;
+          const int vq = causal ? q / N : -1;  // only the vector that holds column q has masked elements behind it
+          const float sc = p.scale * kLog2e;   // work in base-2 logits
+          V v[KMAX];
+          load_row<T, KMAX>(s0, lane, nv_keep, v, -INFINITY);
+          float m = -INFINITY;
+#pragma unroll
+          for (int k = 0; k < KMAX; ++k) {
+            float f[N];
+            v[k].to_float(f);
+            if (lane + 32 * k == vq) {
+#pragma unroll
+              for (int j = 0; j < N; ++j)
+                if (vq * N + j > q) f[j] = -INFINITY;
+            }
+#pragma unroll
+            for (int j = 0; j < N; ++j) m = fmaxf(m, f[j]);
+          }
+          m = warp_max(m) * sc;  // sc > 0: max commutes with the scaling
+          // Up to 32 elements per lane keep their exponentials in registers; wider rows compute them twice
+          // (once for the sum, once for the output) rather than spill.
+          constexpr bool kKeep = KMAX * N <= 32;
+          float e[kKeep ? KMAX : 1][N];
+          float inv = 0.0f;
+          const float2 sc2 = f2(sc, sc), nm2 = f2(-m, -m);
+          auto exps = [&](int k, float (&o)[N]) {
+            float f[N];
+            v[k].to_float(f);
+            if (lane + 32 * k == vq) {
+#pragma unroll
+              for (int j = 0; j < N; ++j)
+                if (vq * N + j > q) f[j] = -INFINITY;
+            }
+#pragma unroll
+            for (int j = 0; j < N; j += 2) {
+              const float2 a = __ffma2_rn(f2(f[j], f[j + 1]), sc2, nm2);
+              o[j] = fast_exp2(a.x);
+              o[j + 1] = fast_exp2(a.y);
+            }
+          };
+          if (m != -INFINITY) {
+            float2 acc0 = f2(0.0f, 0.0f), acc1 = f2(0.0f, 0.0f);
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k) {
+              float t[N];
+              exps(k, t);
+#pragma unroll
+              for (int j = 0; j < N; j += 4) {
+                acc0 = __fadd2_rn(acc0, f2(t[j], t[j + 1]));
+                acc1 = __fadd2_rn(acc1, f2(t[j + 2], t[j + 3]));
+              }
+              if constexpr (kKeep) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) e[k][j] = t[j];
+              }
+            }
+            const float ssum = warp_sum((acc0.x + acc0.y) + (acc1.x + acc1.y));
+            inv = ssum > 0.0f ? 1.0f / ssum : 0.0f;
+          }
+          const float2 i2 = f2(inv, inv);
+#pragma unroll
+          for (int k = 0; k < KMAX; ++k) {
+            const int vi = lane + 32 * k;
+            if (vi < nvec) {
+              float t[N], o[N];
+              if (m == -INFINITY) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) t[j] = 0.0f;
+              } else if constexpr (kKeep) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) t[j] = e[k][j];
+              } else {
+                exps(k, t);
+              }
+#pragma unroll
+              for (int j = 0; j < N; j += 2) {
+                const float2 a = __fmul2_rn(f2(t[j], t[j + 1]), i2);
+                o[j] = a.x; o[j + 1] = a.y;
+              }
+              V a;
+              a.from_float(o);
+              __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+            }
           }
         } else if constexpr (OP == kSmFwd) {
           const int q = p.causal_seq > 0 ? static_cast<int>(row % p.causal_seq) : p.D;  // last kept column (one division per row per warp)
@@ -300,7 +461,7 @@ rowpipe_kernel(const Params p) {
     }
   }
 
-  if constexpr (KMAX > 0) {
+  if constexpr (kDw) {
     // Sum the W warps' dw accumulators in warp order through shared memory (the stage ring is idle now:
     // every load that was issued has been consumed), then write this CTA's partial row.
     __syncthreads();
@@ -335,7 +496,7 @@ int launch_one(const Params& p, int grid, size_t smem, cudaStream_t st) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(rowpipe_kernel<T, OP, W, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBudget + 2048);
+                                         kSmemBudget + 2048 + 8192 + 256);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(rowpipe_kernel)");
     attr_set[dev] = true;
   }
@@ -378,6 +539,16 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
   if (causal_seq > 0 && causal_seq < W) return 1;
   const int nvec = static_cast<int>(D / N);
   int kmax = 0;
+  if (op == kRmsFwd || op == kSmFwd) {
+    const int need = (nvec + 31) / 32;  // register-resident rows of up to 8 vectors per lane
+    kmax = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : 0;
+    if (kmax * N >= 32 && W > 8) {
+      // 32 or more elements per lane: eight rows per tile and two CTAs per SM keep the register file from spilling
+      W = 8;
+      const int sN = static_cast<int>(kSmemBudget / (W * row_bytes * n_streams));
+      stages = sN > kMaxStages ? kMaxStages : sN;
+    }
+  }
   if (dw_part != nullptr) {
     const int need = (nvec + 31) / 32;
     kmax = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : 0;
@@ -391,15 +562,36 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
   p.status = ds->status_word;
   p.stage_bytes = static_cast<uint32_t>(W * row_bytes * n_streams);
   p.bar_off = (static_cast<uint32_t>(stages) * p.stage_bytes + 127u) & ~127u;
-  const size_t smem = p.bar_off + 16 * kMaxStages + 16 + 128;
+  size_t smem = p.bar_off + 16 * kMaxStages + 16 + 128;
+  p.w_off = 0;
+  if (op == kRmsFwd && kmax > 0 && w != nullptr) {
+    p.w_off = static_cast<uint32_t>((smem + 15) & ~static_cast<size_t>(15));
+    smem = p.w_off + static_cast<size_t>(D) * 4 + 128;
+  }
   const int64_t n_tiles = (rows + W - 1) / W;
   int grid = 2 * ds->sm_count;
   if (grid > n_tiles) grid = static_cast<int>(n_tiles);
   if (dw_blocks) *dw_blocks = grid;
 #define MCB_RP(OPC, KM) return launch_w<T, OPC, KM>(W, p, grid, smem, st)
   switch (op) {
-    case kRmsFwd: MCB_RP(kRmsFwd, 0);
-    case kSmFwd: MCB_RP(kSmFwd, 0);
+    case kRmsFwd:
+      switch (kmax) {
+        case 0: MCB_RP(kRmsFwd, 0);
+        case 1: MCB_RP(kRmsFwd, 1);
+        case 2: MCB_RP(kRmsFwd, 2);
+        case 4: MCB_RP(kRmsFwd, 4);
+        case 8: MCB_RP(kRmsFwd, 8);
+      }
+      break;
+    case kSmFwd:
+      switch (kmax) {
+        case 0: MCB_RP(kSmFwd, 0);
+        case 1: MCB_RP(kSmFwd, 1);
+        case 2: MCB_RP(kSmFwd, 2);
+        case 4: MCB_RP(kSmFwd, 4);
+        case 8: MCB_RP(kSmFwd, 8);
+      }
+      break;
     case kSmBwd: MCB_RP(kSmBwd, 0);
     case kRmsBwd:
       switch (kmax) {
