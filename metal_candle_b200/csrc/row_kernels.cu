@@ -249,14 +249,26 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
   }
 }
 
-// dw[c] (+)= sum over blocks of dw_partial[b][c], in block order (deterministic).
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
-                                       int nblocks, int D, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+// dw[c] (+)= sum over blocks of dw_partial[b][c] (deterministic: fixed order).  A CTA owns 32 columns; its 8
+// warps each sum every 8th partial row (independent loads, unrolled), then warp 0 adds the 8 sums in warp order.
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nblocks, int D, int accumulate) {
+  __shared__ float red[8][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.0f;
-  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<int64_t>(b) * D + c];
-  dw[c] = accumulate ? dw[c] + s : s;
+  if (c < D) {
+#pragma unroll 8
+    for (int b = warp; b < nblocks; b += 8) s += partial[static_cast<int64_t>(b) * D + c];
+  }
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < D) {
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    dw[c] = accumulate ? dw[c] + t : t;
+  }
 }
 
 // ---- softmax forward --------------------------------------------------------------------------
@@ -571,7 +583,7 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
     const int rc = rowpipe::try_launch<T>(rowpipe::kRmsBwd, x, dy, w, dx, nullptr, dw ? (float*)ws : nullptr, &blocks, rows, D,
                                           eps, 0, 1.0f, ds, st);
     if (rc == MCB_OK && dw != nullptr) {
-      colsum_partials_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>((const float*)ws, dw, blocks, (int)D, accumulate);
+      colsum_partials_kernel<<<(unsigned)((D + 31) / 32), 256, 0, st>>>((const float*)ws, dw, blocks, (int)D, accumulate);
       MCB_CHECK_LAUNCH("rmsnorm_dw_reduce");
     }
     if (rc != 1) return rc;
@@ -613,7 +625,7 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
   }
   MCB_CHECK_LAUNCH("rmsnorm_bwd");
   if (dw != nullptr) {
-    colsum_partials_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>((const float*)ws, dw, nblocks, (int)D,
+    colsum_partials_kernel<<<(unsigned)((D + 31) / 32), 256, 0, st>>>((const float*)ws, dw, nblocks, (int)D,
                                                                         accumulate);
     MCB_CHECK_LAUNCH("rmsnorm_dw_reduce");
   }
@@ -798,7 +810,7 @@ int rmsnorm_bwd_noalloc_t(const void* x, const void* w, const void* dy, void* dx
   MCB_CHECK_LAUNCH("rmsnorm_bwd_noalloc");
   if (dw != nullptr) {
     // every block wrote its whole row of partials above, so nothing stale from an earlier call is read
-    colsum_partials_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(scratch, dw, nblocks, (int)D, accumulate);
+    colsum_partials_kernel<<<(unsigned)((D + 31) / 32), 256, 0, st>>>(scratch, dw, nblocks, (int)D, accumulate);
     MCB_CHECK_LAUNCH("rmsnorm_dw_reduce_noalloc");
   }
   return MCB_OK;

@@ -42,7 +42,7 @@ struct Params {
   float eps, scale;
   int* status;
   uint32_t stage_bytes, bar_off;
-  uint32_t w_off;    // float32 copy of the rmsnorm weight (register-resident forward only), 0 = none
+  uint32_t w_off;    // float32 copy of the rmsnorm weight in shared memory, 0 = none (no weight, or streamed forward)
 };
 
 // 2^x by the special-function unit (ex2.approx.ftz): x <= 0 here, -inf gives 0.
@@ -108,7 +108,7 @@ rowpipe_kernel(const Params p) {
     fence_proxy_async_smem();
   }
   const float* wsm = nullptr;
-  if constexpr (OP == kRmsFwd && KMAX > 0) {
+  if constexpr ((OP == kRmsFwd && KMAX > 0) || OP == kRmsBwd) {
     if (p.w_off != 0) {
       float* wd = reinterpret_cast<float*>(gen_base + p.w_off);
       for (int c = threadIdx.x; c < p.D; c += blockDim.x) wd[c] = to_f32(static_cast<const T*>(p.w)[c]);
@@ -243,42 +243,50 @@ rowpipe_kernel(const Params p) {
             __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
           }
         } else if constexpr (OP == kRmsBwd) {
-          float ss = 0.0f, gx = 0.0f;
+          // pass 1: sum x^2 and sum (dy*w)*x, two lanes of float32 at a time
+          float2 ss2 = f2(0.0f, 0.0f), gx2 = f2(0.0f, 0.0f);
 #pragma unroll 4
           for (int vi = lane; vi < nvec; vi += 32) {
             V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
             b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
             float x[N], g[N]; a.to_float(x); b.to_float(g);
-            if (p.w != nullptr) {
-              V wv; wv.raw = __ldg(reinterpret_cast<const decltype(wv.raw)*>(p.w) + vi);
-              float ww[N]; wv.to_float(ww);
 #pragma unroll
-              for (int j = 0; j < N; ++j) g[j] *= ww[j];
+            for (int j = 0; j < N; j += 4) {
+              float2 g0 = f2(g[j], g[j + 1]), g1 = f2(g[j + 2], g[j + 3]);
+              if (wsm != nullptr) {
+                const float4 ww = *reinterpret_cast<const float4*>(wsm + vi * N + j);
+                g0 = __fmul2_rn(g0, f2(ww.x, ww.y));
+                g1 = __fmul2_rn(g1, f2(ww.z, ww.w));
+              }
+              const float2 x0 = f2(x[j], x[j + 1]), x1 = f2(x[j + 2], x[j + 3]);
+              ss2 = __ffma2_rn(x0, x0, ss2);
+              ss2 = __ffma2_rn(x1, x1, ss2);
+              gx2 = __ffma2_rn(g0, x0, gx2);
+              gx2 = __ffma2_rn(g1, x1, gx2);
             }
-#pragma unroll
-            for (int j = 0; j < N; ++j) { ss = fmaf(x[j], x[j], ss); gx = fmaf(g[j], x[j], gx); }
           }
-          ss = warp_sum(ss);
-          gx = warp_sum(gx);
+          const float ss = warp_sum(ss2.x + ss2.y);
+          const float gx = warp_sum(gx2.x + gx2.y);
           const float rinv = 1.0f / sqrtf(ss * inv_d + p.eps);
           const float c = gx * rinv * inv_d;
+          const float2 r2 = f2(rinv, rinv), nc2 = f2(-c, -c);
+          // pass 2: dx = rinv * (dy*w - xhat*c), dw += dy*xhat
           auto body = [&](int vi, float* dw_slot) {
             V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
             b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
             float x[N], g[N], o[N]; a.to_float(x); b.to_float(g);
-            float ww[N];
-            if (p.w != nullptr) {
-              V wv; wv.raw = __ldg(reinterpret_cast<const decltype(wv.raw)*>(p.w) + vi);
-              wv.to_float(ww);
-            } else {
 #pragma unroll
-              for (int j = 0; j < N; ++j) ww[j] = 1.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < N; ++j) {
-              const float xh = x[j] * rinv;
-              if (dw_slot != nullptr) dw_slot[j] = fmaf(g[j], xh, dw_slot[j]);
-              o[j] = rinv * (g[j] * ww[j] - xh * c);
+            for (int j = 0; j < N; j += 2) {
+              const float2 gg = f2(g[j], g[j + 1]);
+              const float2 xh = __fmul2_rn(f2(x[j], x[j + 1]), r2);
+              if (dw_slot != nullptr) {
+                const float2 d = __ffma2_rn(gg, xh, f2(dw_slot[j], dw_slot[j + 1]));
+                dw_slot[j] = d.x; dw_slot[j + 1] = d.y;
+              }
+              float2 gw = gg;
+              if (wsm != nullptr) gw = __fmul2_rn(gg, *reinterpret_cast<const float2*>(wsm + vi * N + j));
+              const float2 u = __fmul2_rn(__ffma2_rn(xh, nc2, gw), r2);
+              o[j] = u.x; o[j + 1] = u.y;
             }
             a.from_float(o);
             __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
@@ -496,7 +504,7 @@ int launch_one(const Params& p, int grid, size_t smem, cudaStream_t st) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(rowpipe_kernel<T, OP, W, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBudget + 2048 + 8192 + 256);
+                                         (227 * 1024) / 2 - 1024);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(rowpipe_kernel)");
     attr_set[dev] = true;
   }
@@ -527,10 +535,16 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
   if (!aligned16(in0) || !aligned16(out) || (in1 && !aligned16(in1)) || (w && !aligned16(w))) return 1;
   const int n_streams = (op == kRmsBwd || op == kSmBwd) ? 2 : 1;
   const int64_t row_bytes = D * static_cast<int64_t>(sizeof(T));
+  // RMSNorm with a weight keeps a float32 copy of it in shared memory, taken out of the stage budget
+  const int64_t w_bytes = (w != nullptr && (op == kRmsFwd || op == kRmsBwd)) ? D * 4 : 0;
+  // two CTAs per SM: each may take half of the 227 KB less the 1 KB the system keeps per CTA
+  const int64_t per_cta = (227 * 1024) / 2 - 1024 - 1024;
+  const int64_t budget = w_bytes + kSmemBudget <= per_cta ? kSmemBudget : per_cta - w_bytes;
+  if (budget < kSmemBudget / 2) return 1;
   int W = 0, stages = 0;
   for (int cand : {16, 8, 4, 2}) {
     const int64_t stage_bytes = cand * row_bytes * n_streams;
-    const int s = static_cast<int>(kSmemBudget / stage_bytes);
+    const int s = static_cast<int>(budget / stage_bytes);
     if (s >= 3) { W = cand; stages = s > kMaxStages ? kMaxStages : s; break; }
   }
   // One warp per row only pays while enough warps fit: forward ops (one input stream, more arithmetic per
@@ -545,7 +559,7 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
     if (kmax * N >= 32 && W > 8) {
       // 32 or more elements per lane: eight rows per tile and two CTAs per SM keep the register file from spilling
       W = 8;
-      const int sN = static_cast<int>(kSmemBudget / (W * row_bytes * n_streams));
+      const int sN = static_cast<int>(budget / (W * row_bytes * n_streams));
       stages = sN > kMaxStages ? kMaxStages : sN;
     }
   }
@@ -564,7 +578,7 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
   p.bar_off = (static_cast<uint32_t>(stages) * p.stage_bytes + 127u) & ~127u;
   size_t smem = p.bar_off + 16 * kMaxStages + 16 + 128;
   p.w_off = 0;
-  if (op == kRmsFwd && kmax > 0 && w != nullptr) {
+  if (w != nullptr && ((op == kRmsFwd && kmax > 0) || op == kRmsBwd)) {
     p.w_off = static_cast<uint32_t>((smem + 15) & ~static_cast<size_t>(15));
     smem = p.w_off + static_cast<size_t>(D) * 4 + 128;
   }

@@ -147,6 +147,7 @@ __global__ void lora_grad_reduce_kernel(const float* __restrict__ part, float* _
   const int c = static_cast<int>(tid / rp), j = static_cast<int>(tid % rp);
   if (j >= r) return;
   float s = 0.0f;
+#pragma unroll 8
   for (int sp = 0; sp < splits; ++sp) s += part[static_cast<int64_t>(sp) * n + tid];
   const int64_t o = transposed ? static_cast<int64_t>(j) * C + c : static_cast<int64_t>(c) * r + j;
   out[o] = accumulate ? out[o] + s : s;
