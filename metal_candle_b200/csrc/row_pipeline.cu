@@ -85,11 +85,20 @@ __device__ __forceinline__ uint32_t causal_bytes(int q, int elem_bytes, int row_
   return b < static_cast<uint32_t>(row_bytes) ? b : static_cast<uint32_t>(row_bytes);
 }
 
+// Two CTAs per SM wherever the registers allow it without heavy spilling (a 9-warp CTA pair needs <= 96
+// registers per thread, a 17-warp pair <= 56); the wide register-resident forms run one CTA per SM.
+__host__ __device__ constexpr int rowpipe_min_blocks(int op, int w, int elems_per_lane) {
+  if (op == kRmsFwd) return elems_per_lane > 0 ? 2 : 1;
+  if (op == kSmFwd) return (elems_per_lane > 0 && (elems_per_lane <= 32 || w <= 8)) ? 2 : 1;
+  if (op == kRmsBwd) return (w <= 8 && elems_per_lane <= 32) ? 2 : 1;
+  return w <= 8 ? 2 : 1;
+}
+
 // KMAX > 0: a lane owns vectors lane, lane+32, ... (KMAX of them) of every row and keeps them in registers —
 // the row itself (forward ops) or the dw sums (rmsnorm backward with dw).  KMAX == 0: rows of any width,
 // streamed from shared memory twice.
 template <typename T, int OP, int W, int KMAX>
-__global__ void __launch_bounds__((W + 1) * 32, ((OP == kRmsFwd || OP == kSmFwd) && KMAX > 0 && (OP == kRmsFwd || KMAX * Vec16<T>::N <= 32 || W <= 8)) ? 2 : 1)
+__global__ void __launch_bounds__((W + 1) * 32, rowpipe_min_blocks(OP, W, KMAX * Vec16<T>::N))
 rowpipe_kernel(const Params p) {
   using V = Vec16<T>;
   constexpr int N = V::N;
@@ -506,6 +515,10 @@ int launch_one(const Params& p, int grid, size_t smem, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(rowpipe_kernel<T, OP, W, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (227 * 1024) / 2 - 1024);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(rowpipe_kernel)");
+    // ask for the largest shared-memory carve-out so that two CTAs of ~100 KB fit an SM
+    e = cudaFuncSetAttribute(rowpipe_kernel<T, OP, W, KMAX>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(rowpipe_kernel carve-out)");
     attr_set[dev] = true;
   }
   rowpipe_kernel<T, OP, W, KMAX><<<grid, (W + 1) * 32, smem, st>>>(p);
