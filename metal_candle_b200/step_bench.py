@@ -188,7 +188,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 4,
                     "d2h_bytes_per_step": 4},
             "gpu_launches": per_step_launches * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "lora_gemm_kernel (all projections of the step)",
+            "roofline": {"bound": "tensor", "kernel": "lora_gemm2_kernel + lora_gemm_kernel (all projections of the step)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
                          "launches": n_l, "kernel_ms_per_step": g_ms / args.steps,
