@@ -186,6 +186,18 @@ int mcb_softmax_causal_fwd(const void* x, void* y, int64_t rows, int64_t D, int6
 int mcb_softmax_causal_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int64_t seq,
                            float scale, int dtype, void* stream);
 
+/* ---- fused causal attention ----------------------------------------------------------------- */
+
+/* O = softmax(scale * Q K^T + causal mask) V for grouped-query attention without materialising the scores:
+ * Attention::forward computes matmul(q, k^T) / sqrt(d), adds the mask, applies softmax and multiplies by v as
+ * separate ops over a [B, H, S, S] tensor (src/models/transformer.rs:257-285).  nb = batch * kv_heads;
+ * q, o [nb, groups*seq, head_dim] (row g*seq + s = query head g of the group, position s); k [nb, seq,
+ * head_dim]; vt [nb, head_dim, seq] (V transposed); lse [nb, groups*seq] float32 (log-sum-exp of each row's
+ * scaled scores, kept for a backward pass; may be null).  Built for bf16, head_dim 64, seq a multiple of 128;
+ * other shapes return MCB_ERR_UNSUPPORTED (callers then use the unfused sequence above). */
+int mcb_attention_causal_fwd(const void* q, const void* k, const void* vt, void* o, float* lse, int64_t nb,
+                             int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype, void* stream);
+
 /* ---- AdamW -------------------------------------------------------------------------------- */
 
 typedef struct {

@@ -194,6 +194,31 @@ def transpose_2d(src: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------------
+# fused causal attention
+# ---------------------------------------------------------------------------------------------
+
+def attention_supported(q: torch.Tensor, seq: int) -> bool:
+    """Shapes the fused attention kernels are built for (others use the unfused sequence)."""
+    return q.dtype == torch.bfloat16 and q.shape[-1] == 64 and seq % 128 == 0
+
+
+def attention_causal_forward(q, k, v, groups: int, scale: float):
+    """Attention::forward's core (src/models/transformer.rs:257-285) in one kernel.  q [nb, groups*S, d]
+    (row g*S + s), k and v [nb, S, d].  Returns (o like q, lse [nb, groups*S] float32, vt [nb, d, S])."""
+    _require_cuda(q, k, v)
+    nb, S, d = k.shape
+    if q.shape != (nb, groups * S, d) or v.shape != k.shape:
+        raise TrainingError(f"attention: q {list(q.shape)}, k {list(k.shape)}, v {list(v.shape)} do not fit groups={groups}")
+    lib = _lib_for(q)
+    vt = v.transpose(1, 2).contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty(nb, groups * S, dtype=torch.float32, device=q.device)
+    _lib.check(lib.mcb_attention_causal_fwd(_ptr(q), _ptr(k), _ptr(vt), _ptr(o), _ptr(lse), nb, groups, S, d, float(scale),
+                                            _dtype_code(q), _stream()))
+    return o, lse, vt
+
+
+# ---------------------------------------------------------------------------------------------
 # RMSNorm
 # ---------------------------------------------------------------------------------------------
 

@@ -353,6 +353,39 @@ def cross_entropy_loss(logits, targets, ignore_index=IGNORE_INDEX, dtype=np.floa
 # ------------------------------------------------------------------------------------------
 
 
+def causal_gqa_attention(q, k, v, scale, dtype=np.float64):
+    """Attention::forward's core (src/models/transformer.rs:257-285): scores = q k^T * scale, an additive
+    causal mask (-inf above the diagonal, as the callers pass it), softmax over keys, times v; grouped-query
+    heads share a kv head (the reference repeats k and v, src/models/transformer.rs:246-255).
+    q [nb, G, S, d], k and v [nb, S, d] -> (o [nb, G, S, d], lse [nb, G, S], p [nb, G, S, S])."""
+    q, k, v = (np.asarray(t, dtype=dtype) for t in (q, k, v))
+    nb, G, S, d = q.shape
+    scores = np.einsum("ngsd,ntd->ngst", q, k) * dtype(scale)
+    mask = np.triu(np.ones((S, S), dtype=bool), 1)
+    scores = np.where(mask, -np.inf, scores)
+    m = scores.max(axis=-1, keepdims=True)
+    e = np.exp(scores - m)
+    l = e.sum(axis=-1, keepdims=True)
+    p = e / l
+    o = np.einsum("ngst,ntd->ngsd", p, v)
+    lse = (m + np.log(l))[..., 0]
+    return o, lse, p
+
+
+def causal_gqa_attention_backward(q, k, v, scale, do, dtype=np.float64):
+    """Gradients of `causal_gqa_attention` (the reference gets them from candle's autograd,
+    src/training/trainer.rs:388): dv = p^T do, dp = do v^T, ds = p * (dp - rowsum(dp * p)) * scale,
+    dq = ds k, dk = ds^T q, with dk and dv summed over the query heads of a group."""
+    q, k, v, do = (np.asarray(t, dtype=dtype) for t in (q, k, v, do))
+    _, _, p = causal_gqa_attention(q, k, v, scale, dtype)
+    dv = np.einsum("ngst,ngsd->ntd", p, do)
+    dp = np.einsum("ngsd,ntd->ngst", do, v)
+    ds = p * (dp - (dp * p).sum(axis=-1, keepdims=True)) * dtype(scale)
+    dq = np.einsum("ngst,ntd->ngsd", ds, k)
+    dk = np.einsum("ngst,ngsd->ntd", ds, q)
+    return dq, dk, dv
+
+
 def matmul(a, b, dtype=np.float64):
     """Operation::Matmul -> broadcast_matmul, src/graph/executor.rs:71-82."""
     return np.asarray(a, dtype=dtype) @ np.asarray(b, dtype=dtype)

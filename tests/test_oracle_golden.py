@@ -217,3 +217,34 @@ def test_seeded_generator_is_stable():
     # bf16 rounding agrees with torch's round-to-nearest-even
     x = S.normal(1, "b", (4096,)) * 100
     assert np.array_equal(S.bf16_round(x), torch.from_numpy(x).bfloat16().float().numpy())
+
+
+def test_oracle_attention_matches_torch_autograd():
+    """The attention restatement (forward and gradients) against torch-CPU autograd of the same op sequence
+    as Attention::forward (src/models/transformer.rs:257-285): matmul, scale, additive mask, softmax, matmul."""
+    import math
+
+    import torch
+
+    from oracle import reference_ops as R
+    from oracle import seeded as S
+
+    nb, G, seq, d = 2, 3, 16, 8
+    q = S.normal(3, "q", (nb, G, seq, d)).astype(np.float64)
+    k = S.normal(3, "k", (nb, seq, d)).astype(np.float64)
+    v = S.normal(3, "v", (nb, seq, d)).astype(np.float64)
+    do = S.normal(3, "do", (nb, G, seq, d)).astype(np.float64)
+    scale = 1.0 / math.sqrt(d)
+    tq, tk, tv = (torch.tensor(t, requires_grad=True) for t in (q, k, v))
+    scores = torch.matmul(tq, tk[:, None].transpose(-1, -2)) * scale
+    mask = torch.full((seq, seq), float("-inf"), dtype=torch.float64).triu(1)
+    p = torch.softmax(scores + mask, dim=-1)
+    o = torch.matmul(p, tv[:, None])
+    o.backward(torch.tensor(do))
+    wo, wlse, _ = R.causal_gqa_attention(q, k, v, scale)
+    assert np.allclose(wo, o.detach().numpy(), atol=1e-12)
+    assert np.allclose(wlse, torch.logsumexp(scores + mask, dim=-1).detach().numpy(), atol=1e-12)
+    dq, dk, dv = R.causal_gqa_attention_backward(q, k, v, scale, do)
+    assert np.allclose(dq, tq.grad.numpy(), atol=1e-12)
+    assert np.allclose(dk, tk.grad.numpy(), atol=1e-12)
+    assert np.allclose(dv, tv.grad.numpy(), atol=1e-12)
