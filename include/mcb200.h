@@ -191,12 +191,22 @@ int mcb_softmax_causal_bwd(const void* y, const void* dy, void* dx, int64_t rows
 /* O = softmax(scale * Q K^T + causal mask) V for grouped-query attention without materialising the scores:
  * Attention::forward computes matmul(q, k^T) / sqrt(d), adds the mask, applies softmax and multiplies by v as
  * separate ops over a [B, H, S, S] tensor (src/models/transformer.rs:257-285).  nb = batch * kv_heads;
- * q, o [nb, groups*seq, head_dim] (row g*seq + s = query head g of the group, position s); k [nb, seq,
- * head_dim]; vt [nb, head_dim, seq] (V transposed); lse [nb, groups*seq] float32 (log-sum-exp of each row's
- * scaled scores, kept for a backward pass; may be null).  Built for bf16, head_dim 64, seq a multiple of 128;
- * other shapes return MCB_ERR_UNSUPPORTED (callers then use the unfused sequence above). */
-int mcb_attention_causal_fwd(const void* q, const void* k, const void* vt, void* o, float* lse, int64_t nb,
-                             int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype, void* stream);
+ * q, o [nb, groups*seq, head_dim] (row g*seq + s = query head g of the group, position s); k, v [nb, seq,
+ * head_dim]; lse [nb, groups*seq] float32 (log-sum-exp of each row's scaled scores, which the backward needs;
+ * may be null for inference).  Built for bf16, head_dim 64, seq a multiple of 128; other shapes return
+ * MCB_ERR_UNSUPPORTED (callers then use the unfused sequence above).  The workspace (1024-byte aligned,
+ * mcb_attention_workspace_bytes) holds transposed copies of the small operands. */
+size_t mcb_attention_workspace_bytes(int64_t nb, int64_t groups, int64_t seq, int64_t head_dim);
+int mcb_attention_causal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
+                             int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
+                             void* workspace, size_t workspace_bytes, void* stream);
+/* Gradients of the call above (candle's autograd in the reference, src/training/trainer.rs:388): given o, lse
+ * from the forward and dout = dL/do, writes dq [like q], dk and dv [like k] (summed over the query heads of a
+ * group).  The probabilities are recomputed from q, k and lse; nothing of size seq x seq is stored. */
+int mcb_attention_causal_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                             const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
+                             int64_t seq, int64_t head_dim, float scale, int dtype, void* workspace,
+                             size_t workspace_bytes, void* stream);
 
 /* ---- AdamW -------------------------------------------------------------------------------- */
 

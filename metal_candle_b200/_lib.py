@@ -62,7 +62,10 @@ SIGNATURES = {
     "mcb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
     "mcb_softmax_causal_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
     "mcb_softmax_causal_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
-    "mcb_attention_causal_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "mcb_attention_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64]),
+    "mcb_attention_causal_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
+    "mcb_attention_causal_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32,
+                                        _vp, _sz, _vp]),
     "mcb_embedding_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "mcb_rope_relayout": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _vp]),
     "mcb_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),

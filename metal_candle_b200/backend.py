@@ -204,18 +204,31 @@ def attention_supported(q: torch.Tensor, seq: int) -> bool:
 
 def attention_causal_forward(q, k, v, groups: int, scale: float):
     """Attention::forward's core (src/models/transformer.rs:257-285) in one kernel.  q [nb, groups*S, d]
-    (row g*S + s), k and v [nb, S, d].  Returns (o like q, lse [nb, groups*S] float32, vt [nb, d, S])."""
+    (row g*S + s), k and v [nb, S, d].  Returns (o like q, lse [nb, groups*S] float32)."""
     _require_cuda(q, k, v)
     nb, S, d = k.shape
     if q.shape != (nb, groups * S, d) or v.shape != k.shape:
         raise TrainingError(f"attention: q {list(q.shape)}, k {list(k.shape)}, v {list(v.shape)} do not fit groups={groups}")
     lib = _lib_for(q)
-    vt = v.transpose(1, 2).contiguous()
     o = torch.empty_like(q)
     lse = torch.empty(nb, groups * S, dtype=torch.float32, device=q.device)
-    _lib.check(lib.mcb_attention_causal_fwd(_ptr(q), _ptr(k), _ptr(vt), _ptr(o), _ptr(lse), nb, groups, S, d, float(scale),
-                                            _dtype_code(q), _stream()))
-    return o, lse, vt
+    ws = workspace(q.device, lib.mcb_attention_workspace_bytes(nb, groups, S, d))
+    _lib.check(lib.mcb_attention_causal_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), nb, groups, S, d, float(scale),
+                                            _dtype_code(q), _ptr(ws), ws.numel(), _stream()))
+    return o, lse
+
+
+def attention_causal_backward(q, k, v, o, lse, dout, groups: int, scale: float):
+    """Gradients of `attention_causal_forward`: (dq like q, dk and dv like k, summed over the group)."""
+    _require_cuda(q, k, v, o, lse, dout)
+    nb, S, d = k.shape
+    lib = _lib_for(q)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws = workspace(q.device, lib.mcb_attention_workspace_bytes(nb, groups, S, d))
+    _lib.check(lib.mcb_attention_causal_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(dout), _ptr(lse), _ptr(dq), _ptr(dk),
+                                            _ptr(dv), nb, groups, S, d, float(scale), _dtype_code(q), _ptr(ws), ws.numel(),
+                                            _stream()))
+    return dq, dk, dv
 
 
 # ---------------------------------------------------------------------------------------------

@@ -12,6 +12,18 @@
 // warps 2-5 do the online softmax with one query row per thread: read S from tensor memory, rescale, write
 // P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout, and accumulate O in
 // registers.  Two CTAs per SM overlap one CTA's softmax with the other's MMAs.
+//
+// Backward: two kernels, each recomputes the probabilities from Q, K and the saved log-sum-exp, so that no
+// [S, S] tensor is ever stored and nothing is accumulated with atomics:
+//   dq kernel   one CTA per (128 queries, head), key blocks of 64, one query row per thread:
+//               S = Q K^T and dP = dO V^T into tensor memory, P = exp(scale*S - lse), dS = P (dP - delta) with
+//               delta = rowsum(dO * O), dS (bf16) through shared memory, dQ += dS K accumulated in tensor memory.
+//               It also writes delta and lse*log2(e) for the second kernel.
+//   dkv kernel  one CTA per (128 keys, kv head), steps of 64 queries over the heads of the group, one key row
+//               per thread: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T through shared memory, dV += P^T dO and
+//               dK += dS^T Q accumulated in tensor memory over all steps (which also sums over the group).
+// Every MMA operand is K-major; the transposed copies this needs (Vt, Kt, Qt, dOt: small [rows, 64] tensors) are
+// made by a tile-transpose kernel into the caller's workspace.
 // Every wait is bounded; on expiry the CTA records a code in the device status word and leaves.
 #include <cuda.h>
 #include <string.h>
@@ -262,6 +274,433 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// backward, part 1: dQ (and delta, lse2 for part 2)
+// ---------------------------------------------------------------------------------------------------------
+constexpr uint32_t kDqOffQ = 0;
+constexpr uint32_t kDqOffDO = kDqOffQ + kQBytes;
+constexpr uint32_t kDqOffStage = kDqOffDO + kQBytes;     // 2 stages of K, V, Kt tiles (8 KB each)
+constexpr uint32_t kDqStageBytes = 3 * kKBytes;
+constexpr uint32_t kDqOffDS = kDqOffStage + 2 * kDqStageBytes;
+constexpr uint32_t kDqOffBar = kDqOffDS + kPBytes;
+constexpr uint32_t kDqSmem = kDqOffBar + 256 + 1024;
+
+struct BwdParams {
+  int S, G;
+  float sc;     // scale * log2(e)
+  float scale;
+  const __nv_bfloat16* O;
+  const __nv_bfloat16* dO;
+  const float* lse;
+  float* delta;   // [nb, G*S]
+  float* lse2;    // [nb, G*S]: lse * log2(e)
+  __nv_bfloat16* dQ;
+  __nv_bfloat16* dK;
+  __nv_bfloat16* dV;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+               const __grid_constant__ CUtensorMap tmKt, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t q_full = base + kDqOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16, sdp_full = kv_empty0 + 16;
+  const uint32_t ds_ready = sdp_full + 8, dq_full = ds_ready + 8, tmem_slot = dq_full + 8, abort_addr = tmem_slot + 4;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 4);
+    mbar_init(dq_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
+
+  const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int g = blockIdx.y, nb = blockIdx.z;
+  const int nkb = 2 * qb + 2;
+  const int64_t qrow0 = (static_cast<int64_t>(nb) * p.G + g) * p.S + static_cast<int64_t>(qb) * kBQ;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * kQBytes);
+      tma_load_2d(base + kDqOffQ, &tmQ, q_full, 0, static_cast<int>(qrow0));
+      tma_load_2d(base + kDqOffDO, &tmdO, q_full, 0, static_cast<int>(qrow0));
+      for (int j = 0; j < nkb; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag, 81, p.status)) break;
+        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
+        mbar_expect_tx(kv_full0 + 8 * st, kDqStageBytes);
+        tma_load_2d(sb, &tmK, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
+        tma_load_2d(sb + kKBytes, &tmV, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
+        tma_load_2d(sb + 2 * kKBytes, &tmKt, kv_full0 + 8 * st, j * kBK, nb * kD);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(kBK);
+      auto issue_sdp = [&](int st) {
+        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
+#pragma unroll
+        for (int k4 = 0; k4 < kD / 16; ++k4)
+          umma_bf16(tS, desc_sw128(base + kDqOffQ + k4 * 32), desc_sw128(sb + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k4 = 0; k4 < kD / 16; ++k4)
+          umma_bf16(tDP, desc_sw128(base + kDqOffDO + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+        umma_commit(sdp_full);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, 82, p.status);
+      if (ok) ok = mbar_wait(kv_full0, 0, abort_flag, 83, p.status);
+      if (ok) {
+        tcgen05_fence_after();
+        issue_sdp(0);
+      }
+      for (int j = 0; ok && j < nkb; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(ds_ready, j & 1, abort_flag, 84, p.status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
+        // dQ += dS_j K_j   (A = dS [128 x 64 keys], B = Kt tile [64 d x 64 keys])
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 16; ++k4)
+          umma_bf16(tDQ, desc_sw128(base + kDqOffDS + k4 * 32), desc_sw128(sb + 2 * kKBytes + k4 * 32), idesc,
+                    (j | k4) != 0 ? 1u : 0u);
+        umma_commit(kv_empty0 + 8 * st);
+        if (j + 1 < nkb) {
+          const int s2 = (j + 1) & 1;
+          ok = mbar_wait(kv_full0 + 8 * s2, ((j + 1) >> 1) & 1, abort_flag, 85, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          issue_sdp(s2);
+        } else {
+          umma_commit(dq_full);
+        }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int qpos = qb * kBQ + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* dsrow = gen_base + kDqOffDS + row * 128;
+    const int sw = row & 7;
+    // delta = sum_d dO * O of this row, straight from global memory (once per CTA)
+    float delta = 0.0f;
+    {
+      const uint4* o4 = reinterpret_cast<const uint4*>(p.O + (qrow0 + row) * kD);
+      const uint4* d4 = reinterpret_cast<const uint4*>(p.dO + (qrow0 + row) * kD);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 a = o4[c], b = d4[c];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          delta = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(bw[e] << 16), delta);
+          delta = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(bw[e] & 0xffff0000u), delta);
+        }
+      }
+    }
+    const float lse2 = p.lse[qrow0 + row] * kLog2e;
+    p.delta[qrow0 + row] = delta;
+    p.lse2[qrow0 + row] = lse2;
+    bool ok = true;
+    for (int j = 0; j < nkb; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, j & 1, abort_flag, 86, p.status));
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int key0 = j * kBK;
+      const bool diag = key0 + kBK - 1 > qb * kBQ;
+#pragma unroll
+      for (int c = 0; c < kBK; c += 16) {
+        uint32_t vs[16], vd[16];
+        tmem_ld_x16(tS + lane_addr + c, vs);
+        tmem_ld_x16(tDP + lane_addr + c, vd);
+        tmem_ld_wait();
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          float p0 = ex2(fmaf(__uint_as_float(vs[e]), p.sc, -lse2));
+          float p1 = ex2(fmaf(__uint_as_float(vs[e + 1]), p.sc, -lse2));
+          if (diag) {
+            if (key0 + c + e > qpos) p0 = 0.0f;
+            if (key0 + c + e + 1 > qpos) p1 = 0.0f;
+          }
+          w[e >> 1] = pack_bf16(p0 * (__uint_as_float(vd[e]) - delta), p1 * (__uint_as_float(vd[e + 1]) - delta));
+        }
+        const int cc = c >> 3;
+        *reinterpret_cast<uint4*>(dsrow + ((cc ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(dsrow + (((cc + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(dq_full, 0, abort_flag, 87, p.status));
+    if (ok) {
+      tcgen05_fence_after();
+      __nv_bfloat16* orow = p.dQ + (qrow0 + row) * kD;
+#pragma unroll
+      for (int c = 0; c < kD; c += 16) {
+        uint32_t v[16];
+        tmem_ld_x16(tDQ + lane_addr + c, v);
+        tmem_ld_wait();
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2)
+          w[e >> 1] = pack_bf16(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale);
+        *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag != 0) {
+    for (int k = 0; k < 200; ++k) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// backward, part 2: dK, dV
+// ---------------------------------------------------------------------------------------------------------
+constexpr uint32_t kKvOffK = 0;                       // K block [128 keys x 64]
+constexpr uint32_t kKvOffV = kKvOffK + kQBytes;
+constexpr uint32_t kKvOffStage = kKvOffV + kQBytes;   // Q, dO, Qt, dOt tiles (8 KB each), then lse2 and delta (256 B each)
+constexpr uint32_t kKvStageBytes = 4 * kKBytes + 512;
+constexpr uint32_t kKvOffP = kKvOffStage + 4 * kKBytes + 1024;
+constexpr uint32_t kKvOffDS = kKvOffP + kPBytes;
+constexpr uint32_t kKvOffBar = kKvOffDS + kPBytes;
+constexpr uint32_t kKvSmem = kKvOffBar + 256 + 1024;
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t kv_full = base + kKvOffBar, ld_full = kv_full + 8, ld_empty = ld_full + 8, sdp_full = ld_empty + 8;
+  const uint32_t pds_ready = sdp_full + 8, out_full = pds_ready + 8, tmem_slot = out_full + 8, abort_addr = tmem_slot + 4;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(ld_full, 1);
+    mbar_init(ld_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 4);
+    mbar_init(out_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDV = tmem_base + 128, tDK = tmem_base + 192;
+
+  const int kb = blockIdx.x, nb = blockIdx.y;   // key block 0 has the most query steps and starts first
+  const int nq = p.S / kBK;                      // query steps of 64 per head
+  const int i0 = 2 * kb;                         // first query step that sees this key block
+  const int per_head = nq - i0;
+  const int nsteps = p.G * per_head;
+  const uint32_t sb = base + kKvOffStage;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * kQBytes);
+      tma_load_2d(base + kKvOffK, &tmK, kv_full, 0, nb * p.S + kb * kBQ);
+      tma_load_2d(base + kKvOffV, &tmV, kv_full, 0, nb * p.S + kb * kBQ);
+      for (int t = 0; t < nsteps; ++t) {
+        const int g = t / per_head, i = i0 + t % per_head;
+        if (!mbar_wait(ld_empty, (t & 1) ^ 1, abort_flag, 91, p.status)) break;
+        const int64_t qrow = (static_cast<int64_t>(nb) * p.G + g) * p.S + static_cast<int64_t>(i) * kBK;
+        const int trow = (nb * p.G + g) * kD;
+        mbar_expect_tx(ld_full, kKvStageBytes);
+        tma_load_2d(sb, &tmQ, ld_full, 0, static_cast<int>(qrow));
+        tma_load_2d(sb + kKBytes, &tmdO, ld_full, 0, static_cast<int>(qrow));
+        tma_load_2d(sb + 2 * kKBytes, &tmQt, ld_full, i * kBK, trow);
+        tma_load_2d(sb + 3 * kKBytes, &tmdOt, ld_full, i * kBK, trow);
+        bulk_load_1d(sb + 4 * kKBytes, p.lse2 + qrow, 256, ld_full);
+        bulk_load_1d(sb + 4 * kKBytes + 256, p.delta + qrow, 256, ld_full);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(kBK);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, 92, p.status);
+      for (int t = 0; ok && t < nsteps; ++t) {
+        ok = mbar_wait(ld_full, t & 1, abort_flag, 93, p.status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        // S^T = K Q^T, dP^T = V dO^T   (A = K / V block [128 keys x 64 d], B = Q / dO tile [64 queries x 64 d])
+#pragma unroll
+        for (int k4 = 0; k4 < kD / 16; ++k4)
+          umma_bf16(tS, desc_sw128(base + kKvOffK + k4 * 32), desc_sw128(sb + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k4 = 0; k4 < kD / 16; ++k4)
+          umma_bf16(tDP, desc_sw128(base + kKvOffV + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+        umma_commit(sdp_full);
+        ok = mbar_wait(pds_ready, t & 1, abort_flag, 94, p.status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        // dV += P^T dO, dK += dS^T Q   (A = P^T / dS^T [128 keys x 64 queries], B = dOt / Qt tile [64 d x 64 queries])
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 16; ++k4)
+          umma_bf16(tDV, desc_sw128(base + kKvOffP + k4 * 32), desc_sw128(sb + 3 * kKBytes + k4 * 32), idesc, (t | k4) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 16; ++k4)
+          umma_bf16(tDK, desc_sw128(base + kKvOffDS + k4 * 32), desc_sw128(sb + 2 * kKBytes + k4 * 32), idesc, (t | k4) != 0 ? 1u : 0u);
+        umma_commit(ld_empty);
+        if (t + 1 == nsteps) umma_commit(out_full);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int key = kb * kBQ + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* prow = gen_base + kKvOffP + row * 128;
+    uint8_t* dsrow = gen_base + kKvOffDS + row * 128;
+    const float* st_lse2 = reinterpret_cast<const float*>(gen_base + kKvOffStage + 4 * kKBytes);
+    const float* st_delta = st_lse2 + 64;
+    const int sw = row & 7;
+    bool ok = true;
+    for (int t = 0; t < nsteps; ++t) {
+      const int i = i0 + t % per_head;
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, t & 1, abort_flag, 95, p.status));
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int q0 = i * kBK;
+      const bool diag = q0 < (kb + 1) * kBQ;   // some query of this step lies before some key of the block
+#pragma unroll
+      for (int c = 0; c < kBK; c += 16) {
+        uint32_t vs[16], vd[16];
+        tmem_ld_x16(tS + lane_addr + c, vs);
+        tmem_ld_x16(tDP + lane_addr + c, vd);
+        float l2[16], dl[16];
+#pragma unroll
+        for (int e = 0; e < 16; e += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(st_lse2 + c + e);
+          const float4 b = *reinterpret_cast<const float4*>(st_delta + c + e);
+          l2[e] = a.x; l2[e + 1] = a.y; l2[e + 2] = a.z; l2[e + 3] = a.w;
+          dl[e] = b.x; dl[e + 1] = b.y; dl[e + 2] = b.z; dl[e + 3] = b.w;
+        }
+        tmem_ld_wait();
+        uint32_t wp[8], wd[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          float p0 = ex2(fmaf(__uint_as_float(vs[e]), p.sc, -l2[e]));
+          float p1 = ex2(fmaf(__uint_as_float(vs[e + 1]), p.sc, -l2[e + 1]));
+          if (diag) {
+            if (key > q0 + c + e) p0 = 0.0f;
+            if (key > q0 + c + e + 1) p1 = 0.0f;
+          }
+          wp[e >> 1] = pack_bf16(p0, p1);
+          wd[e >> 1] = pack_bf16(p0 * (__uint_as_float(vd[e]) - dl[e]), p1 * (__uint_as_float(vd[e + 1]) - dl[e + 1]));
+        }
+        const int cc = c >> 3;
+        *reinterpret_cast<uint4*>(prow + ((cc ^ sw) << 4)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+        *reinterpret_cast<uint4*>(prow + (((cc + 1) ^ sw) << 4)) = make_uint4(wp[4], wp[5], wp[6], wp[7]);
+        *reinterpret_cast<uint4*>(dsrow + ((cc ^ sw) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+        *reinterpret_cast<uint4*>(dsrow + (((cc + 1) ^ sw) << 4)) = make_uint4(wd[4], wd[5], wd[6], wd[7]);
+      }
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(out_full, 0, abort_flag, 96, p.status));
+    if (ok) {
+      tcgen05_fence_after();
+      const int64_t krow = static_cast<int64_t>(nb) * p.S + key;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* orow = (which == 0 ? p.dV : p.dK) + krow * kD;
+        const float f = which == 0 ? 1.0f : p.scale;
+#pragma unroll
+        for (int c = 0; c < kD; c += 16) {
+          uint32_t v[16];
+          tmem_ld_x16((which == 0 ? tDV : tDK) + lane_addr + c, v);
+          tmem_ld_wait();
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) w[e >> 1] = pack_bf16(__uint_as_float(v[e]) * f, __uint_as_float(v[e + 1]) * f);
+          *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag != 0) {
+    for (int k = 0; k < 200; ++k) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+// in [batch, rows, 64] -> out [batch, 64, rows]; rows a multiple of 64; one 64 x 64 tile per block of 256 threads
+__global__ void __launch_bounds__(256)
+transpose64_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int rows) {
+  __shared__ __nv_bfloat16 tile[64][66];
+  const int r0 = blockIdx.x * 64;
+  const int64_t b = blockIdx.y;
+  const __nv_bfloat16* src = in + (b * rows + r0) * 64;
+  __nv_bfloat16* dst = out + b * 64 * static_cast<int64_t>(rows) + r0;
+  for (int e = threadIdx.x; e < 64 * 64; e += 256) tile[e >> 6][e & 63] = src[e];
+  __syncthreads();
+  for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+    const int d = e >> 6, r = e & 63;
+    dst[static_cast<int64_t>(d) * rows + r] = tile[r][d];
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -296,23 +735,48 @@ int check_shape(const char* who, int64_t nb, int64_t groups, int64_t seq, int64_
 
 using namespace mcb;
 
-extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void* vt, void* o, float* lse, int64_t nb,
+namespace {
+inline size_t up1k(size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); }
+int set_attrs_once(const void* fn, uint32_t smem, bool* done) {
+  if (*done) return MCB_OK;
+  MCB_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  MCB_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  *done = true;
+  return MCB_OK;
+}
+}  // namespace
+
+extern "C" size_t mcb_attention_workspace_bytes(int64_t nb, int64_t groups, int64_t seq, int64_t head_dim) {
+  if (nb <= 0 || groups <= 0 || seq <= 0 || head_dim <= 0) return 0;
+  const size_t kv = static_cast<size_t>(nb) * seq * head_dim * 2, qq = kv * groups;
+  const size_t rows = static_cast<size_t>(nb) * groups * seq * 4;
+  // forward: Vt.  backward: Kt, Qt, dOt, delta, lse*log2(e).
+  return up1k(kv) + 2 * up1k(qq) + 2 * up1k(rows) + 1024;
+}
+
+extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
                                         int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
-                                        void* stream) {
+                                        void* workspace, size_t workspace_bytes, void* stream) {
   using namespace mcb::attn;
-  if (!q || !k || !vt || !o) return fail(MCB_ERR_NULL, "attention_causal_fwd: q, k, vt or o is null");
+  if (!q || !k || !v || !o) return fail(MCB_ERR_NULL, "attention_causal_fwd: q, k, v or o is null");
   if (int rc = check_shape("attention_causal_fwd", nb, groups, seq, head_dim, dtype)) return rc;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(vt) || !aligned16(o)) return fail(MCB_ERR_ALIGN, "attention_causal_fwd: 16-byte alignment");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(MCB_ERR_ALIGN, "attention_causal_fwd: 16-byte alignment");
+  if (!workspace || workspace_bytes < mcb_attention_workspace_bytes(nb, groups, seq, head_dim) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
+    return fail(MCB_ERR_WORKSPACE, "attention_causal_fwd: workspace of %zu bytes, 1024-byte aligned, needed",
+                mcb_attention_workspace_bytes(nb, groups, seq, head_dim));
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   static bool attr_set[64] = {};
   int dev = 0;
   MCB_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    MCB_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem));
-    MCB_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    attr_set[dev] = true;
-  }
+  if (dev < 0 || dev >= 64) return fail(MCB_ERR_SHAPE, "attention: device %d out of range", dev);
+  if (int rc = set_attrs_once(reinterpret_cast<const void*>(attn_fwd_kernel), kFwdSmem, &attr_set[dev])) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* vt = static_cast<__nv_bfloat16*>(workspace);
+  transpose64_kernel<<<dim3(static_cast<unsigned>(seq / 64), static_cast<unsigned>(nb)), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(v), vt, static_cast<int>(seq));
+  MCB_CHECK_LAUNCH("transpose64_kernel");
   CUtensorMap tmQ, tmK, tmVt;
   if (int rc = encode(ds, &tmQ, q, kD, nb * groups * seq, kBQ, "Q")) return rc;
   if (int rc = encode(ds, &tmK, k, kD, nb * seq, kBK, "K")) return rc;
@@ -322,8 +786,71 @@ extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void
   p.sc = scale * kLog2e;
   p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = ds->status_word;
   dim3 grid(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   attn_fwd_kernel<<<grid, kThreads, kFwdSmem, st>>>(tmQ, tmK, tmVt, p);
   MCB_CHECK_LAUNCH("attn_fwd_kernel");
+  return MCB_OK;
+}
+
+extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                        const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
+                                        int64_t seq, int64_t head_dim, float scale, int dtype, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  using namespace mcb::attn;
+  if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv)
+    return fail(MCB_ERR_NULL, "attention_causal_bwd: a required pointer is null");
+  if (int rc = check_shape("attention_causal_bwd", nb, groups, seq, head_dim, dtype)) return rc;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dout) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return fail(MCB_ERR_ALIGN, "attention_causal_bwd: 16-byte alignment");
+  if (!workspace || workspace_bytes < mcb_attention_workspace_bytes(nb, groups, seq, head_dim) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
+    return fail(MCB_ERR_WORKSPACE, "attention_causal_bwd: workspace of %zu bytes, 1024-byte aligned, needed",
+                mcb_attention_workspace_bytes(nb, groups, seq, head_dim));
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  static bool attr_dq[64] = {}, attr_kv[64] = {};
+  int dev = 0;
+  MCB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MCB_ERR_SHAPE, "attention: device %d out of range", dev);
+  if (int rc = set_attrs_once(reinterpret_cast<const void*>(attn_dq_kernel), kDqSmem, &attr_dq[dev])) return rc;
+  if (int rc = set_attrs_once(reinterpret_cast<const void*>(attn_dkv_kernel), kKvSmem, &attr_kv[dev])) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t kv = static_cast<size_t>(nb) * seq * kD * 2, qq = kv * groups, rows = static_cast<size_t>(nb) * groups * seq * 4;
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  __nv_bfloat16* kt = reinterpret_cast<__nv_bfloat16*>(w); w += up1k(kv);
+  __nv_bfloat16* qt = reinterpret_cast<__nv_bfloat16*>(w); w += up1k(qq);
+  __nv_bfloat16* dot = reinterpret_cast<__nv_bfloat16*>(w); w += up1k(qq);
+  float* delta = reinterpret_cast<float*>(w); w += up1k(rows);
+  float* lse2 = reinterpret_cast<float*>(w);
+  const unsigned sb64 = static_cast<unsigned>(seq / 64);
+  transpose64_kernel<<<dim3(sb64, static_cast<unsigned>(nb)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), kt, static_cast<int>(seq));
+  transpose64_kernel<<<dim3(sb64, static_cast<unsigned>(nb * groups)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(q), qt, static_cast<int>(seq));
+  transpose64_kernel<<<dim3(sb64, static_cast<unsigned>(nb * groups)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dout), dot, static_cast<int>(seq));
+  MCB_CHECK_LAUNCH("transpose64_kernel");
+  CUtensorMap tmQ128, tmdO128, tmK64, tmV64, tmKt, tmK128, tmV128, tmQ64, tmdO64, tmQt, tmdOt;
+  if (int rc = encode(ds, &tmQ128, q, kD, nb * groups * seq, kBQ, "Q")) return rc;
+  if (int rc = encode(ds, &tmdO128, dout, kD, nb * groups * seq, kBQ, "dO")) return rc;
+  if (int rc = encode(ds, &tmK64, k, kD, nb * seq, kBK, "K")) return rc;
+  if (int rc = encode(ds, &tmV64, v, kD, nb * seq, kBK, "V")) return rc;
+  if (int rc = encode(ds, &tmKt, kt, seq, nb * kD, kD, "Kt")) return rc;
+  if (int rc = encode(ds, &tmK128, k, kD, nb * seq, kBQ, "K block")) return rc;
+  if (int rc = encode(ds, &tmV128, v, kD, nb * seq, kBQ, "V block")) return rc;
+  if (int rc = encode(ds, &tmQ64, q, kD, nb * groups * seq, kBK, "Q step")) return rc;
+  if (int rc = encode(ds, &tmdO64, dout, kD, nb * groups * seq, kBK, "dO step")) return rc;
+  if (int rc = encode(ds, &tmQt, qt, seq, nb * groups * kD, kD, "Qt")) return rc;
+  if (int rc = encode(ds, &tmdOt, dot, seq, nb * groups * kD, kD, "dOt")) return rc;
+  BwdParams p;
+  p.S = static_cast<int>(seq); p.G = static_cast<int>(groups);
+  p.sc = scale * kLog2e; p.scale = scale;
+  p.O = static_cast<const __nv_bfloat16*>(o); p.dO = static_cast<const __nv_bfloat16*>(dout); p.lse = lse;
+  p.delta = delta; p.lse2 = lse2;
+  p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk); p.dV = static_cast<__nv_bfloat16*>(dv);
+  p.status = ds->status_word;
+  dim3 gq(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
+  attn_dq_kernel<<<gq, kThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, tmKt, p);
+  MCB_CHECK_LAUNCH("attn_dq_kernel");
+  dim3 gk(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(nb));
+  attn_dkv_kernel<<<gk, kThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, tmQt, tmdOt, p);
+  MCB_CHECK_LAUNCH("attn_dkv_kernel");
   return MCB_OK;
 }

@@ -34,11 +34,27 @@ def test_attention_forward(cuda_device, nb, G, seq):
     q, k, v, _ = _case(77, nb, G, seq)
     scale = 1.0 / math.sqrt(64)
     want_o, want_lse, _ = R.causal_gqa_attention(q, k, v, scale)
-    o, lse, _ = B.attention_causal_forward(_dev(q.reshape(nb, G * seq, 64), cuda_device), _dev(k, cuda_device),
-                                           _dev(v, cuda_device), G, scale)
+    o, lse = B.attention_causal_forward(_dev(q.reshape(nb, G * seq, 64), cuda_device), _dev(k, cuda_device),
+                                        _dev(v, cuda_device), G, scale)
     got = o.float().cpu().numpy().reshape(nb, G, seq, 64)
     assert R.max_abs_normalised(got, want_o) <= 2e-2
     assert np.abs(lse.cpu().numpy().reshape(nb, G, seq) - want_lse).max() <= 2e-2
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("nb,G,seq", [(1, 1, 128), (2, 2, 256), (3, 7, 384), (1, 3, 1024)])
+def test_attention_backward(cuda_device, nb, G, seq):
+    from metal_candle_b200 import _lib, backend as B
+
+    q, k, v, do = _case(78, nb, G, seq)
+    scale = 1.0 / math.sqrt(64)
+    wdq, wdk, wdv = R.causal_gqa_attention_backward(q, k, v, scale, do)
+    qd, kd, vd = _dev(q.reshape(nb, G * seq, 64), cuda_device), _dev(k, cuda_device), _dev(v, cuda_device)
+    o, lse = B.attention_causal_forward(qd, kd, vd, G, scale)
+    dq, dk, dv = B.attention_causal_backward(qd, kd, vd, o, lse, _dev(do.reshape(nb, G * seq, 64), cuda_device), G, scale)
+    assert R.max_abs_normalised(dq.float().cpu().numpy().reshape(nb, G, seq, 64), wdq) <= 2e-2, "dq"
+    assert R.max_abs_normalised(dk.float().cpu().numpy(), wdk) <= 2e-2, "dk"
+    assert R.max_abs_normalised(dv.float().cpu().numpy(), wdv) <= 2e-2, "dv"
     assert _lib.device_status() == 0
 
 
