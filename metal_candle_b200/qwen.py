@@ -9,7 +9,8 @@ by the grouped-query width.  There is no autograd: the backward pass is written 
 library's own kernels; the frozen weights get no gradients.
 
 Everything with arithmetic in it is a kernel of libmetal_candle_b200 except the six batched attention
-contractions (Q K^T, P V and their reverses), which are plain library GEMMs (torch.bmm -> cuBLAS).
+contractions (Q K^T, P V and their reverses): the fused attention kernels of csrc/flash_attn.cu where they apply
+(bf16, head_dim 64, sequence a multiple of 128), otherwise plain library GEMMs (torch.bmm -> cuBLAS).
 """
 from __future__ import annotations
 
@@ -196,19 +197,28 @@ class Qwen:
 
     # -- attention core on [B,H,S,d] tensors; grouped-query heads are folded into the row dimension --
     def _attention_fwd(self, Qr, Kr, Vr, B, S):
+        """Returns (P, O, lse): the fused kernel (bf16, head_dim 64, S a multiple of 128) keeps only the
+        log-sum-exp of each row; other shapes materialise the probabilities P as the reference does."""
         c = self.config
         Hk, G, d = c.num_key_value_heads, c.num_attention_heads // c.num_key_value_heads, c.head_dim
+        if backend.attention_supported(Qr, S):
+            O, lse = backend.attention_causal_forward(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d),
+                                                      Vr.view(B * Hk, S, d), G, 1.0 / math.sqrt(d))
+            return None, O, lse
         scores = torch.bmm(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d).transpose(1, 2))  # [B*Hk, G*S, S]
         rows = scores.numel() // S
         _lib.check(self.lib.mcb_softmax_causal_fwd(_ptr(scores), _ptr(scores), rows, S, S, 1.0 / math.sqrt(d), self.dt,
                                                    _stream()))
         O = torch.bmm(scores, Vr.view(B * Hk, S, d))  # [B*Hk, G*S, d] == [B, Hq, S, d]
-        return scores, O
+        return scores, O, None
 
-    def _attention_bwd(self, Qr, Kr, Vr, P, dO, B, S):
+    def _attention_bwd(self, Qr, Kr, Vr, P, O, lse, dO, B, S):
         c = self.config
         Hk, G, d = c.num_key_value_heads, c.num_attention_heads // c.num_key_value_heads, c.head_dim
         dO3 = dO.view(B * Hk, G * S, d)
+        if P is None:
+            return backend.attention_causal_backward(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d),
+                                                     Vr.view(B * Hk, S, d), O, lse, dO3, G, 1.0 / math.sqrt(d))
         dV = torch.bmm(P.transpose(1, 2), dO3)                       # [B*Hk, S, d], summed over the group
         dP = torch.bmm(dO3, Vr.view(B * Hk, S, d).transpose(1, 2))   # [B*Hk, G*S, S]
         rows = dP.numel() // S
@@ -229,9 +239,10 @@ class Qwen:
         Kr = self._rope(k, c.num_key_value_heads, B, S, True, False)
         Vr = self._rope(v, c.num_key_value_heads, B, S, False, False)
         del q, k, v
-        P, O = self._attention_fwd(Qr, Kr, Vr, B, S)
+        P, O, lse = self._attention_fwd(Qr, Kr, Vr, B, S)
         o = self._rope(O, c.num_attention_heads, B, S, False, True)   # back to [M, hidden]
-        del O
+        if not save or P is not None:
+            O = None   # only the fused backward needs the per-head output again
         h2, ho = self._lin(o, L["o_proj"], save, residual=h)   # residual connection fused into the epilogue
         n2 = self._norm(h2, L["post_attention_layernorm"])
         gt, hg = self._lin(n2, L["gate_proj"], save)
@@ -243,7 +254,7 @@ class Qwen:
             return h3, None
         keep_n2 = L["gate_proj"].lora is not None or L["up_proj"].lora is not None
         keep_act = L["down_proj"].lora is not None
-        saved = dict(h=h, n1=n1, Qr=Qr, Kr=Kr, Vr=Vr, P=P, o=o, h2=h2, n2=n2 if keep_n2 else None, gate=gt, up=up,
+        saved = dict(h=h, n1=n1, Qr=Qr, Kr=Kr, Vr=Vr, P=P, O=O, lse=lse, o=o, h2=h2, n2=n2 if keep_n2 else None, gate=gt, up=up,
                      act=act if keep_act else None, hq=hq, hk=hk, hv=hv, ho=ho, hg=hg, hu=hu, hd=hd)
         return h3, saved
 
@@ -312,7 +323,7 @@ class Qwen:
         do = self._lin_bwd(sv["o"], L["o_proj"], dh2, sv["ho"], key("o_proj"), accumulate)
         dO = self._rope(do, c.num_attention_heads, B, S, False, False)
         del do
-        dQ, dK, dV = self._attention_bwd(sv["Qr"], sv["Kr"], sv["Vr"], sv["P"], dO, B, S)
+        dQ, dK, dV = self._attention_bwd(sv["Qr"], sv["Kr"], sv["Vr"], sv["P"], sv["O"], sv["lse"], dO, B, S)
         dq = self._rope(dQ, c.num_attention_heads, B, S, True, True)
         dk = self._rope(dK, c.num_key_value_heads, B, S, True, True)
         dv = self._rope(dV, c.num_key_value_heads, B, S, False, True)

@@ -23,11 +23,20 @@ def tiny_config():
                        rms_norm_eps=1e-6, rope_theta=1.0e6)
 
 
-def build(dev, dtype, targets, rank=4, seed=3, b_std=0.05):
+def fused_attention_config():
+    """head_dim 64 and a sequence of 128: the shapes the fused attention kernels take."""
+    from metal_candle_b200.qwen import ModelConfig
+
+    return ModelConfig(vocab_size=320, hidden_size=256, intermediate_size=320, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                       rms_norm_eps=1e-6, rope_theta=1.0e6)
+
+
+def build(dev, dtype, targets, rank=4, seed=3, b_std=0.05, cfg=None):
     from metal_candle_b200.qwen import Qwen
     from metal_candle_b200.training import LoRAAdapter, LoRAAdapterConfig, TargetModule
 
-    cfg = tiny_config()
+    cfg = tiny_config() if cfg is None else cfg
     model = Qwen(cfg, dev, dtype=dtype, seed=seed)
     g = torch.Generator(device=dev).manual_seed(seed + 1)
     # non-trivial norm weights and biases so those code paths are exercised
@@ -100,6 +109,29 @@ def test_step_loss_and_gradients(cuda_device, dtype, tol):
     # logits of the inference path agree with the oracle's forward
     logits = model.forward(torch.from_numpy(ids).to(cuda_device)).float().cpu().numpy()
     assert R.max_abs_normalised(logits, orc.forward(ids).detach().numpy()) <= tol
+    from metal_candle_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("seq", [128, 256])
+def test_step_with_fused_attention(cuda_device, seq):
+    """bf16, head_dim 64, sequence a multiple of 128: the step runs the fused attention kernels (forward keeps
+    only the log-sum-exp, backward recomputes the probabilities).  Loss, logits and LoRA gradients against the
+    oracle, same bounds as the unfused chain."""
+    cfg, model, adapter = build(cuda_device, torch.bfloat16, all_targets(), cfg=fused_attention_config())
+    from metal_candle_b200 import backend as B
+    assert B.attention_supported(torch.empty(1, 1, cfg.head_dim, dtype=torch.bfloat16), seq)
+    ids, tg = batch(6, 2, seq, cfg.vocab_size)
+    loss, grads = model.forward_backward(torch.from_numpy(ids).to(cuda_device), torch.from_numpy(tg).to(cuda_device))
+    orc = oracle_of(cfg, model, adapter, True)
+    want_loss, want_grads = orc.loss_and_grads(ids, tg)
+    assert abs(float(loss) - want_loss) <= 2e-2 * abs(want_loss)
+    errs = [R.max_abs_normalised(g.cpu().numpy(), w) for g, w in zip(grads, want_grads)]
+    names = [f"{k}.{ab}" for k, _ in adapter.layers() for ab in "AB"]
+    worst = sorted(zip(errs, names), reverse=True)[:6]
+    assert worst[0][0] <= 4e-2, worst
+    logits = model.forward(torch.from_numpy(ids).to(cuda_device)).float().cpu().numpy()
+    assert R.max_abs_normalised(logits, orc.forward(ids).detach().numpy()) <= 2e-2
     from metal_candle_b200 import _lib
     assert _lib.device_status() == 0
 
