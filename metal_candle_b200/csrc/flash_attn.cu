@@ -10,8 +10,9 @@
 // Forward: one CTA per (128 queries, head); key blocks of 64.  Warp 0 streams K / Vt tiles by TMA into a
 // two-stage ring, warp 1 issues the tensor-core MMAs (S = Q K^T into tensor memory, then O_blk = P V),
 // warps 2-5 do the online softmax with one query row per thread: read S from tensor memory, rescale, write
-// P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout, and accumulate O in
-// registers.  Two CTAs per SM overlap one CTA's softmax with the other's MMAs.
+// P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout; O accumulates in tensor
+// memory and is rescaled there (tcgen05.ld / tcgen05.st) only when a row maximum has grown by more than
+// 2^8.  Three CTAs per SM overlap one CTA's softmax with the others' MMAs.
 //
 // Backward: two kernels, each recomputes the probabilities from Q, K and the saved log-sum-exp, so that no
 // [S, S] tensor is ever stored and nothing is accumulated with atomics:
@@ -73,7 +74,7 @@ __device__ __forceinline__ float lg2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmVt, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -145,7 +146,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
           umma_bf16(tO, desc_sw128(base + kOffP + k4 * 32), desc_sw128(base + kOffV + st * kKBytes + k4 * 32), idesc,
-                    k4 != 0 ? 1u : 0u);
+                    (j | k4) != 0 ? 1u : 0u);
         umma_commit(o_full);
         umma_commit(kv_empty0 + 8 * st);
         if (j + 1 < nkb) {
@@ -163,16 +164,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ---------------- online softmax, one query row per thread ----------------
+    // O accumulates in tensor memory (the P V product adds onto it).  The running maximum a row's exponentials
+    // are taken against is only raised when the true maximum has grown by more than 2^8 over it; then the
+    // warp rescales its 32 rows of O in tensor memory.  Between such events nothing but S is touched.
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const int qpos = qb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     uint8_t* prow = gen_base + kOffP + row * 128;
     const int sw = row & 7;
-    float m = -INFINITY, l = 0.0f;
-    float o[kD];
-#pragma unroll
-    for (int c = 0; c < kD; ++c) o[c] = 0.0f;
+    float m = -INFINITY, l = 0.0f;   // m: the maximum in use (base-2 logits)
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, 76, p.status));
@@ -182,35 +183,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool diag = key0 + kBK - 1 > qb * kBQ;  // some element of this block may lie above the diagonal
       // pass 1: row maximum of the raw scores
       float mx = -INFINITY;
+      if (!diag) {
 #pragma unroll
-      for (int c = 0; c < kBK; c += 16) {
-        uint32_t v[16];
-        tmem_ld_x16(tS + lane_addr + c, v);
-        tmem_ld_wait();
+        for (int c = 0; c < kBK; c += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(tS + lane_addr + c, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float s = __uint_as_float(v[e]);
-          mx = fmaxf(mx, (!diag || key0 + c + e <= qpos) ? s : -INFINITY);
+          for (int e = 0; e < 16; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kBK; c += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(tS + lane_addr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) mx = fmaxf(mx, key0 + c + e <= qpos ? __uint_as_float(v[e]) : -INFINITY);
         }
       }
-      const float m_new = fmaxf(m, mx * p.sc);  // key 0 is never masked, so m_new is finite from block 0 on
-      const float alpha = ex2(m - m_new);       // block 0: 2^(-inf) = 0
+      const float m_true = fmaxf(m, mx * p.sc);  // key 0 is never masked, so this is finite from block 0 on
+      const bool raise = m_true > m + 8.0f;       // block 0: m = -inf, always
       if (j > 0) {
+        // the previous P V product must have landed before O is rescaled or P overwritten
         ok = __all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1, abort_flag, 77, p.status));
         if (!ok) break;
         tcgen05_fence_after();
-#pragma unroll
-        for (int c = 0; c < kD; c += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(tO + lane_addr + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) o[c + e] = (o[c + e] + __uint_as_float(v[e])) * alpha;
-        }
       }
-      l *= alpha;
-      // pass 2: P = 2^(s*sc - m_new), row sum, bf16 into the swizzled operand buffer
-      float ls = 0.0f;
+      if (__any_sync(0xffffffffu, raise)) {
+        const float alpha = ex2(m - m_true);   // rows that did not ask get alpha <= 1 as well and move their maximum
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < kD; c += 16) {
+            uint32_t v[16];
+            tmem_ld_x16(tO + lane_addr + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+            tmem_st_x16(tO + lane_addr + c, v);
+          }
+          tmem_st_wait();
+        }
+        l *= alpha;
+        m = m_true;
+      }
+      // pass 2: P = 2^(s*sc - m), row sum, bf16 into the swizzled operand buffer
+      float ls0 = 0.0f, ls1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < kBK; c += 16) {
         uint32_t v[16];
@@ -219,23 +237,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t w[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(v[e]), p.sc, -m_new));
-          float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), p.sc, -m_new));
+          float p0 = ex2(fmaf(__uint_as_float(v[e]), p.sc, -m));
+          float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), p.sc, -m));
           if (diag) {
             if (key0 + c + e > qpos) p0 = 0.0f;
             if (key0 + c + e + 1 > qpos) p1 = 0.0f;
           }
-          // the sum uses the rounded values, the ones the P V product sees
-          const uint32_t pk = pack_bf16(p0, p1);
-          ls += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
-          w[e >> 1] = pk;
+          ls0 += p0;
+          ls1 += p1;
+          w[e >> 1] = pack_bf16(p0, p1);
         }
         const int cc = c >> 3;  // 16-byte chunk index of columns c .. c+7
         *reinterpret_cast<uint4*>(prow + (((cc) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(prow + (((cc + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
       }
-      l += ls;
-      m = m_new;
+      l += ls0 + ls1;
       tcgen05_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
@@ -254,7 +270,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t w[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2)
-          w[e >> 1] = pack_bf16((o[c + e] + __uint_as_float(v[e])) * inv, (o[c + e + 1] + __uint_as_float(v[e + 1])) * inv);
+          w[e >> 1] = pack_bf16(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
         *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
       }
