@@ -21,7 +21,7 @@
 //               delta = rowsum(dO * O), dS (bf16) through shared memory, dQ += dS K accumulated in tensor memory.
 //               It also writes delta and lse*log2(e) for the second kernel.
 //   dkv kernel  one CTA per (128 keys, kv head), steps of 64 queries over the heads of the group, one key row
-//               per thread: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T through shared memory, dV += P^T dO and
+//               per thread pair: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T through shared memory, dV += P^T dO and
 //               dK += dS^T Q accumulated in tensor memory over all steps (which also sums over the group).
 // Every MMA operand is K-major; the transposed copies this needs (Vt, Kt, Qt, dOt: small [rows, 64] tensors) are
 // made by a tile-transpose kernel into the caller's workspace.
@@ -506,13 +506,19 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 // ---------------------------------------------------------------------------------------------------------
 // backward, part 2: dK, dV
 // ---------------------------------------------------------------------------------------------------------
+// One CTA per SM: 2 control warps + 8 element-wise warps (two per tensor-memory lane quadrant, 32 of the 64 query
+// columns each; no row reductions are needed here because the log-sum-exp is known).  Loads are double-buffered,
+// S^T / dP^T are double-buffered in tensor memory and P^T / dS^T in shared memory, so the tensor core computes
+// the next step's S^T, dP^T while the element-wise warps work on the current one.
+constexpr int kKvThreads = 320;
 constexpr uint32_t kKvOffK = 0;                       // K block [128 keys x 64]
 constexpr uint32_t kKvOffV = kKvOffK + kQBytes;
-constexpr uint32_t kKvOffStage = kKvOffV + kQBytes;   // Q, dO, Qt, dOt tiles (8 KB each), then lse2 and delta (256 B each)
+constexpr uint32_t kKvOffStage = kKvOffV + kQBytes;   // per stage: Q, dO, Qt, dOt tiles (8 KB each), then lse2 and delta (256 B each)
 constexpr uint32_t kKvStageBytes = 4 * kKBytes + 512;
-constexpr uint32_t kKvOffP = kKvOffStage + 4 * kKBytes + 1024;
-constexpr uint32_t kKvOffDS = kKvOffP + kPBytes;
-constexpr uint32_t kKvOffBar = kKvOffDS + kPBytes;
+constexpr uint32_t kKvStageStride = 4 * kKBytes + 1024;
+constexpr uint32_t kKvOffP = kKvOffStage + 2 * kKvStageStride;   // two buffers of P^T, then two of dS^T
+constexpr uint32_t kKvOffDS = kKvOffP + 2 * kPBytes;
+constexpr uint32_t kKvOffBar = kKvOffDS + 2 * kPBytes;
 constexpr uint32_t kKvSmem = kKvOffBar + 256 + 1024;
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -520,7 +526,7 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kKvThreads, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                 const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                 const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const BwdParams p) {
@@ -529,38 +535,36 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t kv_full = base + kKvOffBar, ld_full = kv_full + 8, ld_empty = ld_full + 8, sdp_full = ld_empty + 8;
-  const uint32_t pds_ready = sdp_full + 8, out_full = pds_ready + 8, tmem_slot = out_full + 8, abort_addr = tmem_slot + 4;
+  const uint32_t kv_full = base + kKvOffBar, ld_full0 = kv_full + 8, ld_empty0 = ld_full0 + 16, sdp_full0 = ld_empty0 + 16;
+  const uint32_t pds_ready = sdp_full0 + 16, out_full = pds_ready + 8, tmem_slot = out_full + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(ld_full, 1);
-    mbar_init(ld_empty, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 4);
+    for (int s = 0; s < 2; ++s) { mbar_init(ld_full0 + 8 * s, 1); mbar_init(ld_empty0 + 8 * s, 1); mbar_init(sdp_full0 + 8 * s, 1); }
+    mbar_init(pds_ready, 8);
     mbar_init(out_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDV = tmem_base + 128, tDK = tmem_base + 192;
+  // columns: S^T buffers at 0 and 128, dP^T at 64 and 192, dV at 256, dK at 320
+  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 320;
 
-  const int kb = blockIdx.x, nb = blockIdx.y;   // key block 0 has the most query steps and starts first
+  const int kb = blockIdx.y, nb = blockIdx.x;   // all kv heads of key block 0 (the most query steps) start first
   const int nq = p.S / kBK;                      // query steps of 64 per head
   const int i0 = 2 * kb;                         // first query step that sees this key block
   const int per_head = nq - i0;
   const int nsteps = p.G * per_head;
-  const uint32_t sb = base + kKvOffStage;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -568,72 +572,97 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       tma_load_2d(base + kKvOffK, &tmK, kv_full, 0, nb * p.S + kb * kBQ);
       tma_load_2d(base + kKvOffV, &tmV, kv_full, 0, nb * p.S + kb * kBQ);
       for (int t = 0; t < nsteps; ++t) {
+        const int st = t & 1;
         const int g = t / per_head, i = i0 + t % per_head;
-        if (!mbar_wait(ld_empty, (t & 1) ^ 1, abort_flag, 91, p.status)) break;
+        if (!mbar_wait(ld_empty0 + 8 * st, ((t >> 1) & 1) ^ 1, abort_flag, 91, p.status)) break;
         const int64_t qrow = (static_cast<int64_t>(nb) * p.G + g) * p.S + static_cast<int64_t>(i) * kBK;
         const int trow = (nb * p.G + g) * kD;
-        mbar_expect_tx(ld_full, kKvStageBytes);
-        tma_load_2d(sb, &tmQ, ld_full, 0, static_cast<int>(qrow));
-        tma_load_2d(sb + kKBytes, &tmdO, ld_full, 0, static_cast<int>(qrow));
-        tma_load_2d(sb + 2 * kKBytes, &tmQt, ld_full, i * kBK, trow);
-        tma_load_2d(sb + 3 * kKBytes, &tmdOt, ld_full, i * kBK, trow);
-        bulk_load_1d(sb + 4 * kKBytes, p.lse2 + qrow, 256, ld_full);
-        bulk_load_1d(sb + 4 * kKBytes + 256, p.delta + qrow, 256, ld_full);
+        const uint32_t sb = base + kKvOffStage + st * kKvStageStride, fb = ld_full0 + 8 * st;
+        mbar_expect_tx(fb, kKvStageBytes);
+        tma_load_2d(sb, &tmQ, fb, 0, static_cast<int>(qrow));
+        tma_load_2d(sb + kKBytes, &tmdO, fb, 0, static_cast<int>(qrow));
+        tma_load_2d(sb + 2 * kKBytes, &tmQt, fb, i * kBK, trow);
+        tma_load_2d(sb + 3 * kKBytes, &tmdOt, fb, i * kBK, trow);
+        bulk_load_1d(sb + 4 * kKBytes, p.lse2 + qrow, 256, fb);
+        bulk_load_1d(sb + 4 * kKBytes + 256, p.delta + qrow, 256, fb);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, 92, p.status);
-      for (int t = 0; ok && t < nsteps; ++t) {
-        ok = mbar_wait(ld_full, t & 1, abort_flag, 93, p.status);
-        if (!ok) break;
-        tcgen05_fence_after();
-        // S^T = K Q^T, dP^T = V dO^T   (A = K / V block [128 keys x 64 d], B = Q / dO tile [64 queries x 64 d])
+      // S^T = K Q^T, dP^T = V dO^T of step t into tensor-memory buffer t & 1
+      auto issue_sdp = [&](int t) {
+        const int st = t & 1;
+        const uint32_t sb = base + kKvOffStage + st * kKvStageStride;
+        const uint32_t tS = tmem_base + st * 128, tDP = tS + 64;
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
           umma_bf16(tS, desc_sw128(base + kKvOffK + k4 * 32), desc_sw128(sb + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
           umma_bf16(tDP, desc_sw128(base + kKvOffV + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
-        umma_commit(sdp_full);
+        umma_commit(sdp_full0 + 8 * st);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, 92, p.status);
+      if (ok) ok = mbar_wait(ld_full0, 0, abort_flag, 93, p.status);
+      if (ok) {
+        tcgen05_fence_after();
+        issue_sdp(0);
+      }
+      for (int t = 0; ok && t < nsteps; ++t) {
+        const int st = t & 1;
+        if (t + 1 < nsteps) {
+          // buffer (t+1)&1 of tensor memory was last read by the element-wise warps of step t-1, whose
+          // pds_ready this thread has already waited for
+          ok = mbar_wait(ld_full0 + 8 * (st ^ 1), ((t + 1) >> 1) & 1, abort_flag, 93, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          issue_sdp(t + 1);
+        }
         ok = mbar_wait(pds_ready, t & 1, abort_flag, 94, p.status);
         if (!ok) break;
         tcgen05_fence_after();
+        const uint32_t sb = base + kKvOffStage + st * kKvStageStride;
         // dV += P^T dO, dK += dS^T Q   (A = P^T / dS^T [128 keys x 64 queries], B = dOt / Qt tile [64 d x 64 queries])
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDV, desc_sw128(base + kKvOffP + k4 * 32), desc_sw128(sb + 3 * kKBytes + k4 * 32), idesc, (t | k4) != 0 ? 1u : 0u);
+          umma_bf16(tDV, desc_sw128(base + kKvOffP + st * kPBytes + k4 * 32), desc_sw128(sb + 3 * kKBytes + k4 * 32), idesc,
+                    (t | k4) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDK, desc_sw128(base + kKvOffDS + k4 * 32), desc_sw128(sb + 2 * kKBytes + k4 * 32), idesc, (t | k4) != 0 ? 1u : 0u);
-        umma_commit(ld_empty);
+          umma_bf16(tDK, desc_sw128(base + kKvOffDS + st * kPBytes + k4 * 32), desc_sw128(sb + 2 * kKBytes + k4 * 32), idesc,
+                    (t | k4) != 0 ? 1u : 0u);
+        umma_commit(ld_empty0 + 8 * st);
         if (t + 1 == nsteps) umma_commit(out_full);
       }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3;            // tensor-memory lane quadrant of this warp
+    const int half = (warp - 2) >> 2;     // which 32 of the 64 query columns
     const int row = quad * 32 + lane;
     const int key = kb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* prow = gen_base + kKvOffP + row * 128;
-    uint8_t* dsrow = gen_base + kKvOffDS + row * 128;
-    const float* st_lse2 = reinterpret_cast<const float*>(gen_base + kKvOffStage + 4 * kKBytes);
-    const float* st_delta = st_lse2 + 64;
     const int sw = row & 7;
     bool ok = true;
     for (int t = 0; t < nsteps; ++t) {
+      const int st = t & 1;
       const int i = i0 + t % per_head;
-      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, t & 1, abort_flag, 95, p.status));
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full0 + 8 * st, (t >> 1) & 1, abort_flag, 95, p.status));
       if (!ok) break;
       tcgen05_fence_after();
+      const uint32_t tS = tmem_base + st * 128 + lane_addr, tDP = tS + 64;
+      uint8_t* prow = gen_base + kKvOffP + st * kPBytes + row * 128;
+      uint8_t* dsrow = gen_base + kKvOffDS + st * kPBytes + row * 128;
+      const float* st_lse2 = reinterpret_cast<const float*>(gen_base + kKvOffStage + st * kKvStageStride + 4 * kKBytes);
+      const float* st_delta = st_lse2 + 64;
       const int q0 = i * kBK;
       const bool diag = q0 < (kb + 1) * kBQ;   // some query of this step lies before some key of the block
 #pragma unroll
-      for (int c = 0; c < kBK; c += 16) {
+      for (int cb = 0; cb < 32; cb += 16) {
+        const int c = half * 32 + cb;
         uint32_t vs[16], vd[16];
-        tmem_ld_x16(tS + lane_addr + c, vs);
-        tmem_ld_x16(tDP + lane_addr + c, vd);
+        tmem_ld_x16(tS + c, vs);
+        tmem_ld_x16(tDP + c, vd);
         float l2[16], dl[16];
 #pragma unroll
         for (int e = 0; e < 16; e += 4) {
@@ -675,7 +704,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         __nv_bfloat16* orow = (which == 0 ? p.dV : p.dK) + krow * kD;
         const float f = which == 0 ? 1.0f : p.scale;
 #pragma unroll
-        for (int c = 0; c < kD; c += 16) {
+        for (int cb = 0; cb < 32; cb += 16) {
+          const int c = half * 32 + cb;
           uint32_t v[16];
           tmem_ld_x16((which == 0 ? tDV : tDK) + lane_addr + c, v);
           tmem_ld_wait();
@@ -697,7 +727,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -865,8 +895,8 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   dim3 gq(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
   attn_dq_kernel<<<gq, kThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, tmKt, p);
   MCB_CHECK_LAUNCH("attn_dq_kernel");
-  dim3 gk(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(nb));
-  attn_dkv_kernel<<<gk, kThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, tmQt, tmdOt, p);
+  dim3 gk(static_cast<unsigned>(nb), static_cast<unsigned>(seq / kBQ));
+  attn_dkv_kernel<<<gk, kKvThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, tmQt, tmdOt, p);
   MCB_CHECK_LAUNCH("attn_dkv_kernel");
   return MCB_OK;
 }
