@@ -195,7 +195,8 @@ int mcb_softmax_causal_bwd(const void* y, const void* dy, void* dx, int64_t rows
  * head_dim]; lse [nb, groups*seq] float32 (log-sum-exp of each row's scaled scores, which the backward needs;
  * may be null for inference).  Built for bf16, head_dim 64, seq a multiple of 128; other shapes return
  * MCB_ERR_UNSUPPORTED (callers then use the unfused sequence above).  The workspace (1024-byte aligned,
- * mcb_attention_workspace_bytes) holds transposed copies of the small operands. */
+ * mcb_attention_workspace_bytes) holds two float32 values per query row during the backward; the forward
+ * ignores it. */
 size_t mcb_attention_workspace_bytes(int64_t nb, int64_t groups, int64_t seq, int64_t head_dim);
 int mcb_attention_causal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
                              int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,

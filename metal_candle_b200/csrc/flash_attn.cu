@@ -4,10 +4,10 @@
 //
 // Layouts (bf16, head dimension 64, S a multiple of 128); nb = batch * kv_heads, G query heads per kv head:
 //   Q  [nb, G*S, 64]   row g*S + s is query head g, position s           O  the same
-//   K  [nb, S, 64]     Vt [nb, 64, S]  (V transposed, so that both MMA operands are K-major)
+//   K, V  [nb, S, 64]
 //   LSE [nb, G*S] float32: log-sum-exp of the scaled scores of a row (natural log), kept for the backward
 //
-// Forward: one CTA per (128 queries, head); key blocks of 64.  Warp 0 streams K / Vt tiles by TMA into a
+// Forward: one CTA per (128 queries, head); key blocks of 64.  Warp 0 streams K / V tiles by TMA into a
 // two-stage ring, warp 1 issues the tensor-core MMAs (S = Q K^T into tensor memory, then O_blk = P V),
 // warps 2-5 do the online softmax with one query row per thread: read S from tensor memory, rescale, write
 // P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout; O accumulates in tensor
@@ -23,8 +23,8 @@
 //   dkv kernel  one CTA per (128 keys, kv head), steps of 64 queries over the heads of the group, one key row
 //               per thread pair: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T through shared memory, dV += P^T dO and
 //               dK += dS^T Q accumulated in tensor memory over all steps (which also sums over the group).
-// Every MMA operand is K-major; the transposed copies this needs (Vt, Kt, Qt, dOt: small [rows, 64] tensors) are
-// made by a tile-transpose kernel into the caller's workspace.
+// Operands whose reduction index is the slow one in memory (V in P V, K in dS K, dO and Q in the dK / dV
+// products) are used as they lie, as N-major B operands (instruction-descriptor bit 16); nothing is transposed.
 // Every wait is bounded; on expiry the CTA records a code in the device status word and leaves.
 #include <cuda.h>
 #include <string.h>
@@ -122,7 +122,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag, 71, p.status)) break;
         mbar_expect_tx(kv_full0 + 8 * st, 2 * kKBytes);
         tma_load_2d(base + kOffK + st * kKBytes, &tmK, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
-        tma_load_2d(base + kOffV + st * kKBytes, &tmVt, kv_full0 + 8 * st, j * kBK, nb * kD);
+        tma_load_2d(base + kOffV + st * kKBytes, &tmVt, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
       }
     }
   } else if (warp == 1) {
@@ -142,11 +142,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = mbar_wait(p_ready, j & 1, abort_flag, 74, p.status);
         if (!ok) break;
         tcgen05_fence_after();
-        // O_blk = P_j V_j   (A = P [128 x 64 keys], B = Vt tile [64 d x 64 keys], both K-major)
+        // O += P_j V_j   (A = P [128 x 64 keys] K-major; B = the V tile as it lies, [64 keys x 64 d]: N-major,
+        // 16 keys further = two 8-row groups of 1024 bytes)
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tO, desc_sw128(base + kOffP + k4 * 32), desc_sw128(base + kOffV + st * kKBytes + k4 * 32), idesc,
-                    (j | k4) != 0 ? 1u : 0u);
+          umma_bf16(tO, desc_sw128(base + kOffP + k4 * 32), desc_sw128_mn(base + kOffV + st * kKBytes + k4 * 2048, kKBytes, 1024),
+                    idesc | (1u << 16), (j | k4) != 0 ? 1u : 0u);
         umma_commit(o_full);
         umma_commit(kv_empty0 + 8 * st);
         if (j + 1 < nkb) {
@@ -296,9 +297,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // ---------------------------------------------------------------------------------------------------------
 constexpr uint32_t kDqOffQ = 0;
 constexpr uint32_t kDqOffDO = kDqOffQ + kQBytes;
-constexpr uint32_t kDqOffStage = kDqOffDO + kQBytes;     // 2 stages of K, V, Kt tiles (8 KB each)
-constexpr uint32_t kDqStageBytes = 3 * kKBytes;
-constexpr uint32_t kDqOffDS = kDqOffStage + 2 * kDqStageBytes;
+constexpr int kDqStages = 3;
+constexpr uint32_t kDqOffStage = kDqOffDO + kQBytes;     // stages of a K and a V tile (8 KB each)
+constexpr uint32_t kDqStageBytes = 2 * kKBytes;
+constexpr uint32_t kDqOffDS = kDqOffStage + kDqStages * kDqStageBytes;
 constexpr uint32_t kDqOffBar = kDqOffDS + kPBytes;
 constexpr uint32_t kDqSmem = kDqOffBar + 256 + 1024;
 
@@ -319,21 +321,21 @@ struct BwdParams {
 
 __global__ void __launch_bounds__(kThreads, 2)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-               const __grid_constant__ CUtensorMap tmKt, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t q_full = base + kDqOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16, sdp_full = kv_empty0 + 16;
+  const uint32_t q_full = base + kDqOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * kDqStages;
+  const uint32_t sdp_full = kv_empty0 + 8 * kDqStages;
   const uint32_t ds_ready = sdp_full + 8, dq_full = ds_ready + 8, tmem_slot = dq_full + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+    for (int s = 0; s < kDqStages; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
     mbar_init(sdp_full, 1);
     mbar_init(ds_ready, 4);
     mbar_init(dq_full, 1);
@@ -362,13 +364,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tma_load_2d(base + kDqOffQ, &tmQ, q_full, 0, static_cast<int>(qrow0));
       tma_load_2d(base + kDqOffDO, &tmdO, q_full, 0, static_cast<int>(qrow0));
       for (int j = 0; j < nkb; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag, 81, p.status)) break;
+        const int st = j % kDqStages;
+        if (!mbar_wait(kv_empty0 + 8 * st, ((j / kDqStages) & 1) ^ 1, abort_flag, 81, p.status)) break;
         const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
         mbar_expect_tx(kv_full0 + 8 * st, kDqStageBytes);
         tma_load_2d(sb, &tmK, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
         tma_load_2d(sb + kKBytes, &tmV, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
-        tma_load_2d(sb + 2 * kKBytes, &tmKt, kv_full0 + 8 * st, j * kBK, nb * kD);
       }
     }
   } else if (warp == 1) {
@@ -391,20 +392,20 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         issue_sdp(0);
       }
       for (int j = 0; ok && j < nkb; ++j) {
-        const int st = j & 1;
+        const int st = j % kDqStages;
         ok = mbar_wait(ds_ready, j & 1, abort_flag, 84, p.status);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
-        // dQ += dS_j K_j   (A = dS [128 x 64 keys], B = Kt tile [64 d x 64 keys])
+        // dQ += dS_j K_j   (A = dS [128 x 64 keys] K-major; B = the K tile as it lies, [64 keys x 64 d]: N-major)
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDQ, desc_sw128(base + kDqOffDS + k4 * 32), desc_sw128(sb + 2 * kKBytes + k4 * 32), idesc,
-                    (j | k4) != 0 ? 1u : 0u);
+          umma_bf16(tDQ, desc_sw128(base + kDqOffDS + k4 * 32), desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024),
+                    idesc | (1u << 16), (j | k4) != 0 ? 1u : 0u);
         umma_commit(kv_empty0 + 8 * st);
         if (j + 1 < nkb) {
-          const int s2 = (j + 1) & 1;
-          ok = mbar_wait(kv_full0 + 8 * s2, ((j + 1) >> 1) & 1, abort_flag, 85, p.status);
+          const int s2 = (j + 1) % kDqStages;
+          ok = mbar_wait(kv_full0 + 8 * s2, ((j + 1) / kDqStages) & 1, abort_flag, 85, p.status);
           if (!ok) break;
           tcgen05_fence_after();
           issue_sdp(s2);
@@ -513,10 +514,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 constexpr int kKvThreads = 320;
 constexpr uint32_t kKvOffK = 0;                       // K block [128 keys x 64]
 constexpr uint32_t kKvOffV = kKvOffK + kQBytes;
-constexpr uint32_t kKvOffStage = kKvOffV + kQBytes;   // per stage: Q, dO, Qt, dOt tiles (8 KB each), then lse2 and delta (256 B each)
-constexpr uint32_t kKvStageBytes = 4 * kKBytes + 512;
-constexpr uint32_t kKvStageStride = 4 * kKBytes + 1024;
-constexpr uint32_t kKvOffP = kKvOffStage + 2 * kKvStageStride;   // two buffers of P^T, then two of dS^T
+constexpr int kKvStages = 4;
+constexpr uint32_t kKvOffStage = kKvOffV + kQBytes;   // per stage: Q and dO tiles (8 KB each), then lse2 and delta (256 B each)
+constexpr uint32_t kKvStageBytes = 2 * kKBytes + 512;
+constexpr uint32_t kKvStageStride = 2 * kKBytes + 1024;
+constexpr uint32_t kKvOffP = kKvOffStage + kKvStages * kKvStageStride;   // two buffers of P^T, then two of dS^T
 constexpr uint32_t kKvOffDS = kKvOffP + 2 * kPBytes;
 constexpr uint32_t kKvOffBar = kKvOffDS + 2 * kPBytes;
 constexpr uint32_t kKvSmem = kKvOffBar + 256 + 1024;
@@ -528,21 +530,22 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 
 __global__ void __launch_bounds__(kKvThreads, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-                const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const BwdParams p) {
+                const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t kv_full = base + kKvOffBar, ld_full0 = kv_full + 8, ld_empty0 = ld_full0 + 16, sdp_full0 = ld_empty0 + 16;
+  const uint32_t kv_full = base + kKvOffBar, ld_full0 = kv_full + 8, ld_empty0 = ld_full0 + 8 * kKvStages;
+  const uint32_t sdp_full0 = ld_empty0 + 8 * kKvStages;
   const uint32_t pds_ready = sdp_full0 + 16, out_full = pds_ready + 8, tmem_slot = out_full + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(ld_full0 + 8 * s, 1); mbar_init(ld_empty0 + 8 * s, 1); mbar_init(sdp_full0 + 8 * s, 1); }
+    for (int s = 0; s < kKvStages; ++s) { mbar_init(ld_full0 + 8 * s, 1); mbar_init(ld_empty0 + 8 * s, 1); }
+    for (int s = 0; s < 2; ++s) mbar_init(sdp_full0 + 8 * s, 1);
     mbar_init(pds_ready, 8);
     mbar_init(out_full, 1);
     *abort_flag = 0;
@@ -572,19 +575,16 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       tma_load_2d(base + kKvOffK, &tmK, kv_full, 0, nb * p.S + kb * kBQ);
       tma_load_2d(base + kKvOffV, &tmV, kv_full, 0, nb * p.S + kb * kBQ);
       for (int t = 0; t < nsteps; ++t) {
-        const int st = t & 1;
+        const int st = t % kKvStages;
         const int g = t / per_head, i = i0 + t % per_head;
-        if (!mbar_wait(ld_empty0 + 8 * st, ((t >> 1) & 1) ^ 1, abort_flag, 91, p.status)) break;
+        if (!mbar_wait(ld_empty0 + 8 * st, ((t / kKvStages) & 1) ^ 1, abort_flag, 91, p.status)) break;
         const int64_t qrow = (static_cast<int64_t>(nb) * p.G + g) * p.S + static_cast<int64_t>(i) * kBK;
-        const int trow = (nb * p.G + g) * kD;
         const uint32_t sb = base + kKvOffStage + st * kKvStageStride, fb = ld_full0 + 8 * st;
         mbar_expect_tx(fb, kKvStageBytes);
         tma_load_2d(sb, &tmQ, fb, 0, static_cast<int>(qrow));
         tma_load_2d(sb + kKBytes, &tmdO, fb, 0, static_cast<int>(qrow));
-        tma_load_2d(sb + 2 * kKBytes, &tmQt, fb, i * kBK, trow);
-        tma_load_2d(sb + 3 * kKBytes, &tmdOt, fb, i * kBK, trow);
-        bulk_load_1d(sb + 4 * kKBytes, p.lse2 + qrow, 256, fb);
-        bulk_load_1d(sb + 4 * kKBytes + 256, p.delta + qrow, 256, fb);
+        bulk_load_1d(sb + 2 * kKBytes, p.lse2 + qrow, 256, fb);
+        bulk_load_1d(sb + 2 * kKBytes + 256, p.delta + qrow, 256, fb);
       }
     }
   } else if (warp == 1) {
@@ -593,7 +593,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       // S^T = K Q^T, dP^T = V dO^T of step t into tensor-memory buffer t & 1
       auto issue_sdp = [&](int t) {
         const int st = t & 1;
-        const uint32_t sb = base + kKvOffStage + st * kKvStageStride;
+        const uint32_t sb = base + kKvOffStage + (t % kKvStages) * kKvStageStride;
         const uint32_t tS = tmem_base + st * 128, tDP = tS + 64;
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
@@ -614,7 +614,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         if (t + 1 < nsteps) {
           // buffer (t+1)&1 of tensor memory was last read by the element-wise warps of step t-1, whose
           // pds_ready this thread has already waited for
-          ok = mbar_wait(ld_full0 + 8 * (st ^ 1), ((t + 1) >> 1) & 1, abort_flag, 93, p.status);
+          ok = mbar_wait(ld_full0 + 8 * ((t + 1) % kKvStages), ((t + 1) / kKvStages) & 1, abort_flag, 93, p.status);
           if (!ok) break;
           tcgen05_fence_after();
           issue_sdp(t + 1);
@@ -622,17 +622,19 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         ok = mbar_wait(pds_ready, t & 1, abort_flag, 94, p.status);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t sb = base + kKvOffStage + st * kKvStageStride;
-        // dV += P^T dO, dK += dS^T Q   (A = P^T / dS^T [128 keys x 64 queries], B = dOt / Qt tile [64 d x 64 queries])
+        const int ls = t % kKvStages;
+        const uint32_t sb = base + kKvOffStage + ls * kKvStageStride;
+        // dV += P^T dO, dK += dS^T Q   (A = P^T / dS^T [128 keys x 64 queries] K-major; B = the dO / Q tile as it
+        // lies, [64 queries x 64 d]: N-major, 16 queries further = two 8-row groups of 1024 bytes)
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDV, desc_sw128(base + kKvOffP + st * kPBytes + k4 * 32), desc_sw128(sb + 3 * kKBytes + k4 * 32), idesc,
-                    (t | k4) != 0 ? 1u : 0u);
+          umma_bf16(tDV, desc_sw128(base + kKvOffP + st * kPBytes + k4 * 32), desc_sw128_mn(sb + kKBytes + k4 * 2048, kKBytes, 1024),
+                    idesc | (1u << 16), (t | k4) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDK, desc_sw128(base + kKvOffDS + st * kPBytes + k4 * 32), desc_sw128(sb + 2 * kKBytes + k4 * 32), idesc,
-                    (t | k4) != 0 ? 1u : 0u);
-        umma_commit(ld_empty0 + 8 * st);
+          umma_bf16(tDK, desc_sw128(base + kKvOffDS + st * kPBytes + k4 * 32), desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024),
+                    idesc | (1u << 16), (t | k4) != 0 ? 1u : 0u);
+        umma_commit(ld_empty0 + 8 * ls);
         if (t + 1 == nsteps) umma_commit(out_full);
       }
     }
@@ -653,7 +655,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       const uint32_t tS = tmem_base + st * 128 + lane_addr, tDP = tS + 64;
       uint8_t* prow = gen_base + kKvOffP + st * kPBytes + row * 128;
       uint8_t* dsrow = gen_base + kKvOffDS + st * kPBytes + row * 128;
-      const float* st_lse2 = reinterpret_cast<const float*>(gen_base + kKvOffStage + st * kKvStageStride + 4 * kKBytes);
+      const float* st_lse2 = reinterpret_cast<const float*>(gen_base + kKvOffStage + (t % kKvStages) * kKvStageStride + 2 * kKBytes);
       const float* st_delta = st_lse2 + 64;
       const int q0 = i * kBK;
       const bool diag = q0 < (kb + 1) * kBQ;   // some query of this step lies before some key of the block
@@ -731,22 +733,6 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   }
 }
 
-// in [batch, rows, 64] -> out [batch, 64, rows]; rows a multiple of 64; one 64 x 64 tile per block of 256 threads
-__global__ void __launch_bounds__(256)
-transpose64_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int rows) {
-  __shared__ __nv_bfloat16 tile[64][66];
-  const int r0 = blockIdx.x * 64;
-  const int64_t b = blockIdx.y;
-  const __nv_bfloat16* src = in + (b * rows + r0) * 64;
-  __nv_bfloat16* dst = out + b * 64 * static_cast<int64_t>(rows) + r0;
-  for (int e = threadIdx.x; e < 64 * 64; e += 256) tile[e >> 6][e & 63] = src[e];
-  __syncthreads();
-  for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-    const int d = e >> 6, r = e & 63;
-    dst[static_cast<int64_t>(d) * rows + r] = tile[r][d];
-  }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -794,10 +780,10 @@ int set_attrs_once(const void* fn, uint32_t smem, bool* done) {
 
 extern "C" size_t mcb_attention_workspace_bytes(int64_t nb, int64_t groups, int64_t seq, int64_t head_dim) {
   if (nb <= 0 || groups <= 0 || seq <= 0 || head_dim <= 0) return 0;
-  const size_t kv = static_cast<size_t>(nb) * seq * head_dim * 2, qq = kv * groups;
+  (void)head_dim;
   const size_t rows = static_cast<size_t>(nb) * groups * seq * 4;
-  // forward: Vt.  backward: Kt, Qt, dOt, delta, lse*log2(e).
-  return up1k(kv) + 2 * up1k(qq) + 2 * up1k(rows) + 1024;
+  // backward: delta = rowsum(dO * O) and lse * log2(e), one float32 per query row each; the forward needs none
+  return 2 * up1k(rows) + 1024;
 }
 
 extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
@@ -807,10 +793,7 @@ extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void
   if (!q || !k || !v || !o) return fail(MCB_ERR_NULL, "attention_causal_fwd: q, k, v or o is null");
   if (int rc = check_shape("attention_causal_fwd", nb, groups, seq, head_dim, dtype)) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(MCB_ERR_ALIGN, "attention_causal_fwd: 16-byte alignment");
-  if (!workspace || workspace_bytes < mcb_attention_workspace_bytes(nb, groups, seq, head_dim) ||
-      (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
-    return fail(MCB_ERR_WORKSPACE, "attention_causal_fwd: workspace of %zu bytes, 1024-byte aligned, needed",
-                mcb_attention_workspace_bytes(nb, groups, seq, head_dim));
+  (void)workspace; (void)workspace_bytes;  // the forward needs no scratch memory
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   static bool attr_set[64] = {};
@@ -819,14 +802,10 @@ extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void
   if (dev < 0 || dev >= 64) return fail(MCB_ERR_SHAPE, "attention: device %d out of range", dev);
   if (int rc = set_attrs_once(reinterpret_cast<const void*>(attn_fwd_kernel), kFwdSmem, &attr_set[dev])) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  __nv_bfloat16* vt = static_cast<__nv_bfloat16*>(workspace);
-  transpose64_kernel<<<dim3(static_cast<unsigned>(seq / 64), static_cast<unsigned>(nb)), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(v), vt, static_cast<int>(seq));
-  MCB_CHECK_LAUNCH("transpose64_kernel");
   CUtensorMap tmQ, tmK, tmVt;
   if (int rc = encode(ds, &tmQ, q, kD, nb * groups * seq, kBQ, "Q")) return rc;
   if (int rc = encode(ds, &tmK, k, kD, nb * seq, kBK, "K")) return rc;
-  if (int rc = encode(ds, &tmVt, vt, seq, nb * kD, kD, "Vt")) return rc;
+  if (int rc = encode(ds, &tmVt, v, kD, nb * seq, kBK, "V")) return rc;
   FwdParams p;
   p.S = static_cast<int>(seq); p.G = static_cast<int>(groups);
   p.sc = scale * kLog2e;
@@ -861,30 +840,19 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   if (int rc = set_attrs_once(reinterpret_cast<const void*>(attn_dq_kernel), kDqSmem, &attr_dq[dev])) return rc;
   if (int rc = set_attrs_once(reinterpret_cast<const void*>(attn_dkv_kernel), kKvSmem, &attr_kv[dev])) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t kv = static_cast<size_t>(nb) * seq * kD * 2, qq = kv * groups, rows = static_cast<size_t>(nb) * groups * seq * 4;
+  const size_t rows = static_cast<size_t>(nb) * groups * seq * 4;
   uint8_t* w = static_cast<uint8_t*>(workspace);
-  __nv_bfloat16* kt = reinterpret_cast<__nv_bfloat16*>(w); w += up1k(kv);
-  __nv_bfloat16* qt = reinterpret_cast<__nv_bfloat16*>(w); w += up1k(qq);
-  __nv_bfloat16* dot = reinterpret_cast<__nv_bfloat16*>(w); w += up1k(qq);
   float* delta = reinterpret_cast<float*>(w); w += up1k(rows);
   float* lse2 = reinterpret_cast<float*>(w);
-  const unsigned sb64 = static_cast<unsigned>(seq / 64);
-  transpose64_kernel<<<dim3(sb64, static_cast<unsigned>(nb)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), kt, static_cast<int>(seq));
-  transpose64_kernel<<<dim3(sb64, static_cast<unsigned>(nb * groups)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(q), qt, static_cast<int>(seq));
-  transpose64_kernel<<<dim3(sb64, static_cast<unsigned>(nb * groups)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dout), dot, static_cast<int>(seq));
-  MCB_CHECK_LAUNCH("transpose64_kernel");
-  CUtensorMap tmQ128, tmdO128, tmK64, tmV64, tmKt, tmK128, tmV128, tmQ64, tmdO64, tmQt, tmdOt;
+  CUtensorMap tmQ128, tmdO128, tmK64, tmV64, tmK128, tmV128, tmQ64, tmdO64;
   if (int rc = encode(ds, &tmQ128, q, kD, nb * groups * seq, kBQ, "Q")) return rc;
   if (int rc = encode(ds, &tmdO128, dout, kD, nb * groups * seq, kBQ, "dO")) return rc;
   if (int rc = encode(ds, &tmK64, k, kD, nb * seq, kBK, "K")) return rc;
   if (int rc = encode(ds, &tmV64, v, kD, nb * seq, kBK, "V")) return rc;
-  if (int rc = encode(ds, &tmKt, kt, seq, nb * kD, kD, "Kt")) return rc;
   if (int rc = encode(ds, &tmK128, k, kD, nb * seq, kBQ, "K block")) return rc;
   if (int rc = encode(ds, &tmV128, v, kD, nb * seq, kBQ, "V block")) return rc;
   if (int rc = encode(ds, &tmQ64, q, kD, nb * groups * seq, kBK, "Q step")) return rc;
   if (int rc = encode(ds, &tmdO64, dout, kD, nb * groups * seq, kBK, "dO step")) return rc;
-  if (int rc = encode(ds, &tmQt, qt, seq, nb * groups * kD, kD, "Qt")) return rc;
-  if (int rc = encode(ds, &tmdOt, dot, seq, nb * groups * kD, kD, "dOt")) return rc;
   BwdParams p;
   p.S = static_cast<int>(seq); p.G = static_cast<int>(groups);
   p.sc = scale * kLog2e; p.scale = scale;
@@ -893,10 +861,10 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk); p.dV = static_cast<__nv_bfloat16*>(dv);
   p.status = ds->status_word;
   dim3 gq(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
-  attn_dq_kernel<<<gq, kThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, tmKt, p);
+  attn_dq_kernel<<<gq, kThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, p);
   MCB_CHECK_LAUNCH("attn_dq_kernel");
   dim3 gk(static_cast<unsigned>(nb), static_cast<unsigned>(seq / kBQ));
-  attn_dkv_kernel<<<gk, kKvThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, tmQt, tmdOt, p);
+  attn_dkv_kernel<<<gk, kKvThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, p);
   MCB_CHECK_LAUNCH("attn_dkv_kernel");
   return MCB_OK;
 }
