@@ -16,7 +16,7 @@
 //
 // Backward: two kernels, each recomputes the probabilities from Q, K and the saved log-sum-exp, so that no
 // [S, S] tensor is ever stored and nothing is accumulated with atomics:
-//   dq kernel   one CTA per (128 queries, head), key blocks of 64, one query row per thread pair:
+//   dq kernel   one CTA per (128 queries, head), key blocks of 64, one query row per thread:
 //               S = Q K^T and dP = dO V^T into tensor memory, P = exp(scale*S - lse), dS = P (dP - delta) with
 //               delta = rowsum(dO * O), dS (bf16) through shared memory, dQ += dS K accumulated in tensor memory.
 //               It also writes delta and lse*log2(e) for the second kernel.
@@ -297,15 +297,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // ---------------------------------------------------------------------------------------------------------
 constexpr uint32_t kDqOffQ = 0;
 constexpr uint32_t kDqOffDO = kDqOffQ + kQBytes;
-// One CTA per SM: 2 control warps + 8 element-wise warps (two per tensor-memory lane quadrant, 32 of the 64 key
-// columns each).  K / V tiles in a four-stage ring, S / dP double-buffered in tensor memory and dS in shared
-// memory, so the tensor core computes the next block's S, dP while the element-wise warps work on this one.
-constexpr int kDqThreads = 320;
-constexpr int kDqStages = 4;
+constexpr int kDqStages = 3;
 constexpr uint32_t kDqOffStage = kDqOffDO + kQBytes;     // stages of a K and a V tile (8 KB each)
 constexpr uint32_t kDqStageBytes = 2 * kKBytes;
-constexpr uint32_t kDqOffDS = kDqOffStage + kDqStages * kDqStageBytes;   // two buffers
-constexpr uint32_t kDqOffBar = kDqOffDS + 2 * kPBytes;
+constexpr uint32_t kDqOffDS = kDqOffStage + kDqStages * kDqStageBytes;
+constexpr uint32_t kDqOffBar = kDqOffDS + kPBytes;
 constexpr uint32_t kDqSmem = kDqOffBar + 256 + 1024;
 
 struct BwdParams {
@@ -323,7 +319,7 @@ struct BwdParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(kDqThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -332,31 +328,30 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t q_full = base + kDqOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * kDqStages;
-  const uint32_t sdp_full0 = kv_empty0 + 8 * kDqStages;
-  // ds_ready has one barrier per buffer: an element-wise warp may run one block ahead of the slowest one
-  const uint32_t ds_ready0 = sdp_full0 + 16, dq_full = ds_ready0 + 16, tmem_slot = dq_full + 8, abort_addr = tmem_slot + 4;
+  const uint32_t sdp_full = kv_empty0 + 8 * kDqStages;
+  const uint32_t ds_ready = sdp_full + 8, dq_full = ds_ready + 8, tmem_slot = dq_full + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kDqStages; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(sdp_full0 + 8 * s, 1); mbar_init(ds_ready0 + 8 * s, 8); }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 4);
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  // columns: S buffers at 0 and 128, dP at 64 and 192, dQ at 256
-  const uint32_t tDQ = tmem_base + 256;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
 
   const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int g = blockIdx.y, nb = blockIdx.z;
@@ -380,17 +375,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);
-      // S = Q K^T, dP = dO V^T of block j into tensor-memory buffer j & 1
-      auto issue_sdp = [&](int j) {
-        const uint32_t sb = base + kDqOffStage + (j % kDqStages) * kDqStageBytes;
-        const uint32_t tS = tmem_base + (j & 1) * 128, tDP = tS + 64;
+      auto issue_sdp = [&](int st) {
+        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
           umma_bf16(tS, desc_sw128(base + kDqOffQ + k4 * 32), desc_sw128(sb + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
           umma_bf16(tDP, desc_sw128(base + kDqOffDO + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
-        umma_commit(sdp_full0 + 8 * (j & 1));
+        umma_commit(sdp_full);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, 82, p.status);
       if (ok) ok = mbar_wait(kv_full0, 0, abort_flag, 83, p.status);
@@ -399,34 +392,34 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         issue_sdp(0);
       }
       for (int j = 0; ok && j < nkb; ++j) {
-        if (j + 1 < nkb) {
-          // tensor-memory buffer (j+1)&1 was last read by the element-wise warps of block j-1, whose ds_ready
-          // this thread has already waited for
-          ok = mbar_wait(kv_full0 + 8 * ((j + 1) % kDqStages), ((j + 1) / kDqStages) & 1, abort_flag, 85, p.status);
-          if (!ok) break;
-          tcgen05_fence_after();
-          issue_sdp(j + 1);
-        }
-        ok = mbar_wait(ds_ready0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, 84, p.status);
+        const int st = j % kDqStages;
+        ok = mbar_wait(ds_ready, j & 1, abort_flag, 84, p.status);
         if (!ok) break;
         tcgen05_fence_after();
-        const int st = j % kDqStages;
         const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
         // dQ += dS_j K_j   (A = dS [128 x 64 keys] K-major; B = the K tile as it lies, [64 keys x 64 d]: N-major)
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDQ, desc_sw128(base + kDqOffDS + (j & 1) * kPBytes + k4 * 32), desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024),
+          umma_bf16(tDQ, desc_sw128(base + kDqOffDS + k4 * 32), desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024),
                     idesc | (1u << 16), (j | k4) != 0 ? 1u : 0u);
         umma_commit(kv_empty0 + 8 * st);
-        if (j + 1 == nkb) umma_commit(dq_full);
+        if (j + 1 < nkb) {
+          const int s2 = (j + 1) % kDqStages;
+          ok = mbar_wait(kv_full0 + 8 * s2, ((j + 1) / kDqStages) & 1, abort_flag, 85, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          issue_sdp(s2);
+        } else {
+          umma_commit(dq_full);
+        }
       }
     }
   } else {
-    const int quad = warp & 3;            // tensor-memory lane quadrant of this warp
-    const int half = (warp - 2) >> 2;     // which 32 of the 64 key columns
+    const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const int qpos = qb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* dsrow = gen_base + kDqOffDS + row * 128;
     const int sw = row & 7;
     // delta = sum_d dO * O of this row, straight from global memory (once per CTA)
     float delta = 0.0f;
@@ -445,25 +438,20 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
     }
     const float lse2 = p.lse[qrow0 + row] * kLog2e;
-    if (half == 0) {
-      p.delta[qrow0 + row] = delta;
-      p.lse2[qrow0 + row] = lse2;
-    }
+    p.delta[qrow0 + row] = delta;
+    p.lse2[qrow0 + row] = lse2;
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, 86, p.status));
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, j & 1, abort_flag, 86, p.status));
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t tS = tmem_base + (j & 1) * 128 + lane_addr, tDP = tS + 64;
-      uint8_t* dsrow = gen_base + kDqOffDS + (j & 1) * kPBytes + row * 128;
       const int key0 = j * kBK;
       const bool diag = key0 + kBK - 1 > qb * kBQ;
 #pragma unroll
-      for (int cb = 0; cb < 32; cb += 16) {
-        const int c = half * 32 + cb;
+      for (int c = 0; c < kBK; c += 16) {
         uint32_t vs[16], vd[16];
-        tmem_ld_x16(tS + c, vs);
-        tmem_ld_x16(tDP + c, vd);
+        tmem_ld_x16(tS + lane_addr + c, vs);
+        tmem_ld_x16(tDP + lane_addr + c, vd);
         tmem_ld_wait();
         uint32_t w[8];
 #pragma unroll
@@ -483,15 +471,14 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tcgen05_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready0 + 8 * (j & 1));
+      if (lane == 0) mbar_arrive(ds_ready);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(dq_full, 0, abort_flag, 87, p.status));
     if (ok) {
       tcgen05_fence_after();
       __nv_bfloat16* orow = p.dQ + (qrow0 + row) * kD;
 #pragma unroll
-      for (int cb = 0; cb < 32; cb += 16) {
-        const int c = half * 32 + cb;
+      for (int c = 0; c < kD; c += 16) {
         uint32_t v[16];
         tmem_ld_x16(tDQ + lane_addr + c, v);
         tmem_ld_wait();
@@ -513,7 +500,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
@@ -874,7 +861,7 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk); p.dV = static_cast<__nv_bfloat16*>(dv);
   p.status = ds->status_word;
   dim3 gq(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
-  attn_dq_kernel<<<gq, kDqThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, p);
+  attn_dq_kernel<<<gq, kThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, p);
   MCB_CHECK_LAUNCH("attn_dq_kernel");
   dim3 gk(static_cast<unsigned>(nb), static_cast<unsigned>(seq / kBQ));
   attn_dkv_kernel<<<gk, kKvThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, p);
