@@ -209,8 +209,12 @@ def _count_launches(cfg, wl) -> int:
     """Kernels of this library launched per training step (counted from the step's structure)."""
     L = cfg.num_hidden_layers
     n_lora = len(wl["targets"])
-    per_layer_fwd = 2 + 7 + n_lora + 3 + 1 + 1 + 1 + 2  # norms, GEMMs, packs, rope x3, softmax, relayout, swiglu, adds
-    per_layer_bwd = 7 + n_lora + 4 * n_lora + 1 + 2 + 4 + 1 + 3 + 4  # GEMMs, packs, grad+reduce, swiglu, norms, rope, softmax, adds
+    fused_attn = cfg.head_dim == 64 and wl["seq"] % 128 == 0   # else the scores are materialised (cuBLAS + row softmax)
+    # forward: 2 norms, 7 GEMMs, operand packs, 3 rope/relayout + 1 inverse relayout, attention (or softmax), swiglu
+    per_layer_fwd = 2 + 7 + n_lora + 4 + 1 + 1
+    # backward: 7 GEMMs, packs, dA/dB (gradient + reduce each), swiglu, 2 norms, 4 rope/relayout,
+    # attention (dq + dkv kernels, or one softmax), 2 residual-gradient adds
+    per_layer_bwd = 7 + n_lora + 4 * n_lora + 1 + 2 + 4 + (2 if fused_attn else 1) + 2
     tail = 1 + 1 + 1 + 3 + 1 + 1  # embed, norm, lm_head, CE x3, lm_head bwd, norm bwd
     adamw = math.ceil(2 * n_lora * L / 64)
     return L * (per_layer_fwd + per_layer_bwd) + tail + adamw
