@@ -8,6 +8,7 @@ Headline (the line the driver reads):
 
 Kernel micro-benchmarks (one JSON line per case; used for the roofline sweeps and for ncu captures):
     python bench.py --micro lora    --M 32768 --K 896 --N 896 --r 16 [--dtype bf16|f32] [--pass fwd|bwd|both]
+    python bench.py --micro attention --nb 32 --G 7 --S 2048 [--pass fwd|bwd|both]
     python bench.py --micro rmsnorm --rows 114688 --D 896  [--dtype bf16|f32]
     python bench.py --micro softmax --rows 114688 --D 1024 [--dtype bf16|f32]
     python bench.py --micro adamw   --n 67108864
@@ -201,6 +202,47 @@ def micro_lora(torch, M, K, N, r, dtype, which, iters=20, warmup=5):
             "dtype": dtype, "config": {"workload": "lora_linear", "M": M, "K": K, "N": N, "r": r, "pass": which,
                                        "input_sets": nv, "l2": "inputs rotated through >2x L2"},
             "flop_per_byte": fl / by, "roofline": roof}
+
+
+def micro_attention(torch, nb, G, S, which, iters=20, warmup=5):
+    """Fused causal grouped-query attention at one layer's shape (nb = batch * kv heads, G query heads per kv head,
+    head_dim 64, bf16).  FLOP counted over the causal half only: forward 4*nb*G*S*S*64/2, backward 2.5x that."""
+    from metal_candle_b200 import backend as B
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    d = 64
+    nv = _variants(4 * nb * G * S * d * 2)
+    nv = min(nv, 6)
+    mk = lambda *shape: torch.randn(*shape, device=dev, generator=g).to(torch.bfloat16)
+    qs = [mk(nb, G * S, d) for _ in range(nv)]
+    ks = [mk(nb, S, d) for _ in range(nv)]
+    vs = [mk(nb, S, d) for _ in range(nv)]
+    dos = [mk(nb, G * S, d) for _ in range(nv)]
+    scale = 1.0 / math.sqrt(d)
+    saved = [B.attention_causal_forward(qs[i], ks[i], vs[i], G, scale) for i in range(nv)]
+
+    def fwd(i):
+        B.attention_causal_forward(qs[i % nv], ks[i % nv], vs[i % nv], G, scale)
+
+    def bwd(i):
+        j = i % nv
+        B.attention_causal_backward(qs[j], ks[j], vs[j], saved[j][0], saved[j][1], dos[j], G, scale)
+
+    def both(i):
+        fwd(i)
+        bwd(i)
+
+    fl_f = 4.0 * nb * G * S * S * d / 2
+    fn, fl = {"fwd": (fwd, fl_f), "bwd": (bwd, 2.5 * fl_f), "both": (both, 3.5 * fl_f)}[which]
+    med, mn = _time_kernel(torch, fn, nv, iters, warmup)
+    pk = measured_peaks()
+    tf = fl / med / 1e9
+    return {"metric": f"fused causal attention {which}", "value": tf, "unit": "TFLOP/s", "ms": med, "ms_min": mn,
+            "dtype": "bf16", "config": {"workload": "causal_gqa_attention", "nb": nb, "G": G, "S": S, "head_dim": d,
+                                        "pass": which, "input_sets": nv},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / pk["bf16_tflops"], "traffic": None, "peak_source": pk["source"]}}
 
 
 def micro_rows(torch, op, rows, D, dtype, iters=20, warmup=5):
@@ -413,6 +455,9 @@ def run_micro(args):
     if args.micro == "lora":
         print(json.dumps(micro_lora(torch, args.M, args.K, args.N, args.r, args.dtype, args.which, args.iters,
                                     args.warmup_iters)), flush=True)
+    elif args.micro == "attention":
+        print(json.dumps(micro_attention(torch, args.nb, args.G, args.S, args.which, args.iters, args.warmup_iters)),
+              flush=True)
     elif args.micro in ("rmsnorm", "softmax"):
         for r in micro_rows(torch, args.micro, args.rows, args.D, args.dtype, args.iters, args.warmup_iters):
             print(json.dumps(r), flush=True)
@@ -435,6 +480,9 @@ def main():
     ap.add_argument("--K", type=int, default=896)
     ap.add_argument("--N", type=int, default=896)
     ap.add_argument("--r", type=int, default=16)
+    ap.add_argument("--nb", type=int, default=32)
+    ap.add_argument("--G", type=int, default=7)
+    ap.add_argument("--S", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=114688)
     ap.add_argument("--D", type=int, default=1024)
     ap.add_argument("--n", type=int, default=1 << 26)
