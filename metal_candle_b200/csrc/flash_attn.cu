@@ -12,7 +12,8 @@
 // warps 2-5 do the online softmax with one query row per thread: read S from tensor memory, rescale, write
 // P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout; O accumulates in tensor
 // memory and is rescaled there (tcgen05.ld / tcgen05.st) only when a row maximum has grown by more than
-// 2^8.  Three CTAs per SM overlap one CTA's softmax with the others' MMAs.
+// 2^8.  S is double-buffered in tensor memory, so the next block's Q K^T runs under this block's softmax;
+// two CTAs per SM.
 //
 // Backward: two kernels, each recomputes the probabilities from Q, K and the saved log-sum-exp, so that no
 // [S, S] tensor is ever stored and nothing is accumulated with atomics:
@@ -74,7 +75,7 @@ __device__ __forceinline__ float lg2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmVt, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -82,30 +83,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t q_full = base + kOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16, s_full = kv_empty0 + 16;
-  const uint32_t p_ready = s_full + 8, o_full = p_ready + 8, tmem_slot = o_full + 8, abort_addr = tmem_slot + 4;
+  // S is double-buffered in tensor memory (the next block's Q K^T runs under this block's softmax), with one
+  // s_full / p_ready barrier per buffer
+  const uint32_t q_full = base + kOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16, s_full0 = kv_empty0 + 16;
+  const uint32_t p_ready0 = s_full0 + 16, o_full = p_ready0 + 16, tmem_slot = o_full + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 4);
+    for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(p_ready0 + 8 * s, 4); }
     mbar_init(o_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(128u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const uint32_t tS = tmem_base, tO = tmem_base + 64;
+  const uint32_t tO = tmem_base + 128;  // S buffers at columns 0 and 64
 
   // heavy (late) query blocks first
   const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
@@ -128,18 +130,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);  // M = 128, N = 64 for both products
+      auto issue_s = [&](int j) {   // S_j = Q K_j^T into tensor-memory buffer j & 1
+        const uint32_t tS = tmem_base + (j & 1) * 64;
+#pragma unroll
+        for (int k4 = 0; k4 < kD / 16; ++k4)
+          umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + (j & 1) * kKBytes + k4 * 32), idesc,
+                    k4 != 0 ? 1u : 0u);
+        umma_commit(s_full0 + 8 * (j & 1));
+      };
       bool ok = mbar_wait(q_full, 0, abort_flag, 72, p.status);
       if (ok) ok = mbar_wait(kv_full0, 0, abort_flag, 73, p.status);
       if (ok) {
         tcgen05_fence_after();
-#pragma unroll
-        for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
-        umma_commit(s_full);
+        issue_s(0);
       }
       for (int j = 0; ok && j < nkb; ++j) {
         const int st = j & 1;
-        ok = mbar_wait(p_ready, j & 1, abort_flag, 74, p.status);
+        if (j + 1 < nkb) {
+          // buffer (j+1)&1 of S was last read by the softmax of block j-1, whose p_ready this thread has waited for
+          ok = mbar_wait(kv_full0 + 8 * (st ^ 1), ((j + 1) >> 1) & 1, abort_flag, 75, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          issue_s(j + 1);
+        }
+        ok = mbar_wait(p_ready0 + 8 * st, (j >> 1) & 1, abort_flag, 74, p.status);
         if (!ok) break;
         tcgen05_fence_after();
         // O += P_j V_j   (A = P [128 x 64 keys] K-major; B = the V tile as it lies, [64 keys x 64 d]: N-major,
@@ -150,17 +164,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     idesc | (1u << 16), (j | k4) != 0 ? 1u : 0u);
         umma_commit(o_full);
         umma_commit(kv_empty0 + 8 * st);
-        if (j + 1 < nkb) {
-          const int s2 = (j + 1) & 1;
-          ok = mbar_wait(kv_full0 + 8 * s2, ((j + 1) >> 1) & 1, abort_flag, 75, p.status);
-          if (!ok) break;
-          tcgen05_fence_after();
-#pragma unroll
-          for (int k4 = 0; k4 < kD / 16; ++k4)
-            umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + s2 * kKBytes + k4 * 32), idesc,
-                      k4 != 0 ? 1u : 0u);
-          umma_commit(s_full);
-        }
       }
     }
   } else {
@@ -177,9 +180,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m = -INFINITY, l = 0.0f;   // m: the maximum in use (base-2 logits)
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, 76, p.status));
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, 76, p.status));
       if (!ok) break;
       tcgen05_fence_after();
+      const uint32_t tS = tmem_base + (j & 1) * 64;
       const int key0 = j * kBK;
       const bool diag = key0 + kBK - 1 > qb * kBQ;  // some element of this block may lie above the diagonal
       // pass 1: row maximum of the raw scores
@@ -256,7 +260,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tcgen05_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(p_ready0 + 8 * (j & 1));
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, (nkb - 1) & 1, abort_flag, 78, p.status));
     if (ok) {
@@ -287,7 +291,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 

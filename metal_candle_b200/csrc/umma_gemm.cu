@@ -38,9 +38,11 @@ int init_grad_kernel();
 int init_gemm2_kernel();
 bool gemm2_eligible(const GemmCall& c);
 int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st);
-size_t grad_partial_bytes(int64_t M, int64_t C, int rp);
-int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch, float* out, float* part, int64_t M,
-                int64_t C, int r, int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st);
+size_t grad_partial_bytes(int64_t M, int64_t K, int64_t N, int rp);
+int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, float* out0, int transposed0,
+                 const __nv_bfloat16* X1, const __nv_bfloat16* Ht1, int64_t C1, float* out1, int transposed1,
+                 int64_t h_pitch, float* part, int64_t M, int r, int rp, int accumulate, const DeviceState* ds,
+                 cudaStream_t st);
 
 namespace {
 
@@ -536,8 +538,7 @@ Workspace carve(void* ws, int64_t M, int64_t K, int64_t N, int64_t r) {
   w.Q = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(rp) * big * 2));
   w.H1 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(h_pitch(M)) * rp * 2));
   w.H2 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(h_pitch(M)) * rp * 2));
-  const size_t pk = grad_partial_bytes(M, K, static_cast<int>(rp)), pn = grad_partial_bytes(M, N, static_cast<int>(rp));
-  w.part = reinterpret_cast<float*>(take(pk > pn ? pk : pn));
+  w.part = reinterpret_cast<float*>(take(grad_partial_bytes(M, K, N, static_cast<int>(rp))));
   w.total = off;
   return w;
 }
@@ -647,13 +648,9 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
     }
   }
   if (!want_grads) return MCB_OK;
-  if (a.dA != nullptr) {
-    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.x), w.H1, h_pitch(a.M), a.dA, w.part, a.M, a.K,
-                             static_cast<int>(a.r), rp, 0, a.accumulate, ds, a.stream))
-      return rc;
-  }
+  const __nv_bfloat16* hs = nullptr;
   if (a.dB != nullptr) {
-    const __nv_bfloat16* hs = static_cast<const __nv_bfloat16*>(a.h_save);
+    hs = static_cast<const __nv_bfloat16*>(a.h_save);
     if (hs == nullptr) {
       // recompute scale * x A with the forward operands
       LoraArgs f = a;
@@ -672,11 +669,18 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
       if (int rc = launch_gemm(c, ds, a.stream)) return rc;
       hs = w.H2;
     }
-    if (int rc = launch_grad(static_cast<const __nv_bfloat16*>(a.dy), hs, h_pitch(a.M), a.dB, w.part, a.M, a.N,
-                             static_cast<int>(a.r), rp, 1, a.accumulate, ds, a.stream))
-      return rc;
   }
-  return MCB_OK;
+  // dA = x^T (scale dy B^T) and dB = (scale x A)^T dy, both in one launch where both are asked for
+  const __nv_bfloat16* xa = static_cast<const __nv_bfloat16*>(a.x);
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(a.dy);
+  if (a.dA != nullptr && a.dB != nullptr)
+    return launch_grad2(xa, w.H1, a.K, a.dA, 0, xb, hs, a.N, a.dB, 1, h_pitch(a.M), w.part, a.M, static_cast<int>(a.r), rp,
+                        a.accumulate, ds, a.stream);
+  if (a.dA != nullptr)
+    return launch_grad2(xa, w.H1, a.K, a.dA, 0, nullptr, nullptr, 0, nullptr, 0, h_pitch(a.M), w.part, a.M,
+                        static_cast<int>(a.r), rp, a.accumulate, ds, a.stream);
+  return launch_grad2(xb, hs, a.N, a.dB, 1, nullptr, nullptr, 0, nullptr, 0, h_pitch(a.M), w.part, a.M, static_cast<int>(a.r), rp,
+                      a.accumulate, ds, a.stream);
 }
 
 int matmul_nt(const void* a, const void* bt, void* out, int64_t M, int64_t K, int64_t N, const DeviceState* ds,

@@ -3,13 +3,23 @@
 //   dA [K, r] = x^T  (scale * dy B^T)        X = x  [M,K],  H = the rank intermediate of the backward GEMM
 //   dB [r, N] = (scale * x A)^T dy           X = dy [M,N],  H = the rank intermediate saved by the forward
 //
-// Both operands are token-major in memory, i.e. the reduction index is the SLOW one.  X tiles are loaded
-// by TMA exactly as they lie ([64 tokens] x [64 features], 128-byte swizzle) and handed to tcgen05.mma as
-// an MN-major A operand; H arrives already transposed ([rp, tokens], written that way by the GEMM
-// epilogue) as a K-major B operand.  A CTA owns 128 features and one slice of the tokens, accumulates
-// [128 x rp] in tensor memory and writes one float32 partial; a second small kernel sums the partials
-// in slice order, so the result is deterministic.  The kernel is HBM-bound: it reads X once (2 bytes per
-// element) and issues one 128 x rp x 16 MMA per 4 KB of it.
+// Both operands are token-major in memory, i.e. the reduction index is the SLOW one.  X is handed to tcgen05.mma
+// as an MN-major A operand exactly as it lies; H arrives already transposed ([rp, tokens], written that way by
+// the GEMM epilogue) as a K-major B operand.  One launch serves both gradients of a LoRA linear.
+//
+// The kernel is HBM-bound (it reads X once, 2 bytes per element, and issues one 128 x rp x 16 MMA per 4 KB of
+// it), so what matters is how DRAM is read: a CTA owns a slice of the tokens and a GROUP of up to 1024 features
+// (all of them for the model's 896-wide projections) and streams whole token rows of its group - one
+// three-dimensional TMA copy per stage (features within a 64-wide atom, tokens, atoms), 16 or 32 tokens deep.
+// Every 128-feature tile of the group has its own [128 x rp] accumulator in tensor memory.  A CTA writes one
+// float32 partial; a second small kernel sums the partials in slice order, so the result is deterministic.
+//
+// Feature counts that are not a multiple of 64 cannot be seen as whole 64-feature atoms; they take the older
+// form further down (a CTA owns 128 features, [64 tokens] x [64 features] boxes, one problem per launch), which
+// reads 256-byte pieces of each row and reaches about half of the copy bandwidth.
+#include <cuda.h>
+#include <string.h>
+
 #include "lora_internal.cuh"
 #include "umma_ptx.cuh"
 
@@ -19,12 +29,237 @@ using namespace umma;
 namespace {
 
 constexpr int kGradThreads = 192;
-constexpr int kGradBK = 64;       // tokens per stage
-constexpr int kGradMaxStages = 12;  // enough bytes in flight per SM to cover HBM latency under load
-constexpr int kGradSmemBudget = 216 * 1024;
-constexpr uint32_t kXBoxBytes = 64 * 64 * 2;  // one [64 tokens x 64 features] box
+constexpr int kGradMaxStages = 8;
+constexpr int kGradGroup = 1024;               // features per CTA at most (8 tiles of 128)
+constexpr int kGradSmemBudget = 208 * 1024;
 
+struct GradProblem {
+  int C, groups, slices, tiles;   // features, feature groups, token slices, 128-feature tiles per group
+  int group_feats;                // features per group (a multiple of 128)
+  float* part;                    // [slices][C][rp]
+};
 struct GradParams {
+  int M, rp, T;                   // tokens, padded rank, tokens per stage (16 or 32)
+  int stages;
+  int n_cta0;                     // CTAs of problem 0 (the rest belong to problem 1)
+  GradProblem pr[2];
+  int* status;
+  uint32_t x_bytes[2], bar_off;   // X bytes per stage of each problem; H follows at x_bytes
+  uint32_t stage_stride;
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kGradThreads)
+lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmH0,
+                      const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmH1,
+                      const GradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kGradMaxStages, done_bar = empty0 + 8 * kGradMaxStages;
+  const uint32_t tmem_slot = done_bar + 8, abort_addr = tmem_slot + 4;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
+
+  // which problem, feature group and token slice this CTA has
+  const int which = static_cast<int>(blockIdx.x) >= p.n_cta0 ? 1 : 0;
+  const GradProblem& q = p.pr[which];
+  const int local = static_cast<int>(blockIdx.x) - (which ? p.n_cta0 : 0);
+  const int group = local % q.groups, slice = local / q.groups;
+  const CUtensorMap* tmX = which ? &tmX1 : &tmX0;
+  const CUtensorMap* tmH = which ? &tmH1 : &tmH0;
+  const int acc_cols = q.tiles * p.rp;
+  const uint32_t tmem_cols = acc_cols <= 32 ? 32u : acc_cols <= 64 ? 64u : acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(done_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // token steps of T tokens, split evenly over the slices
+  const int total_steps = (p.M + p.T - 1) / p.T;
+  const int per = (total_steps + q.slices - 1) / q.slices;
+  const int step_begin = slice * per;
+  const int step_end = min(total_steps, step_begin + per);
+  const int nsteps = max(0, step_end - step_begin);
+  const uint32_t xb = p.x_bytes[which];
+  const uint32_t atom_bytes = static_cast<uint32_t>(p.T) * 128;   // one 64-feature atom of a stage: T rows of 128 bytes
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int s = step_begin; s < step_end; ++s) {
+        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 41, p.status)) break;
+        const uint32_t fb = full0 + 8 * stage, sb = base + stage * p.stage_stride;
+        mbar_expect_tx(fb, xb + static_cast<uint32_t>(p.rp) * p.T * 2);
+        // X: [64 features][T tokens][atoms of the group]; in shared memory atom-major blocks of T rows x 128 bytes
+        tma_load_3d(sb, tmX, fb, 0, s * p.T, group * (q.group_feats / 64));
+        // H^T: K-major B operand, unswizzled 16-byte columns of 8 tokens each
+        for (int j = 0; j < p.T / 8; ++j) tma_load_2d(sb + xb + j * p.rp * 16, tmH, fb, s * p.T + j * 8, 0);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_a_mn(p.rp);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < nsteps; ++i) {
+        ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, 42, p.status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t sb = base + stage * p.stage_stride;
+        for (int k16 = 0; k16 < p.T / 16; ++k16) {
+          // B: 16 tokens further = two 16-byte columns of rp rows
+          const uint64_t bd = desc_noswz(sb + xb + k16 * 2 * (p.rp * 16), p.rp * 16, 128);
+          for (int f = 0; f < q.tiles; ++f) {
+            // A: tile f = atoms 2f, 2f+1 (LBO = one atom); 16 token rows further = two 8-row groups of 1024 bytes
+            const uint64_t ad = desc_sw128_mn(sb + (2 * f) * atom_bytes + k16 * 2048, atom_bytes, 1024);
+            umma_bf16(tmem_base + f * p.rp, ad, bd, idesc, (i | k16) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(empty0 + 8 * stage);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(done_bar);   // with no steps at all this completes at once
+    }
+  } else {
+    const int quad = warp & 3;
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(done_bar, 0, abort_flag, 43, p.status));
+    if (ok) {
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      for (int f = 0; f < q.tiles; ++f) {
+        const int c = group * q.group_feats + f * BM + quad * 32 + lane;
+        for (int j = 0; j < p.rp; j += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(taddr + f * p.rp + j, v);
+          tmem_ld_wait();
+          if (c < q.C) {
+            float4* o = reinterpret_cast<float4*>(q.part + (static_cast<int64_t>(slice) * q.C + c) * p.rp + j);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              // a slice without steps has accumulated nothing (its tensor memory is undefined): write zeros
+              o[e] = nsteps > 0 ? make_float4(__uint_as_float(v[4 * e]), __uint_as_float(v[4 * e + 1]),
+                                              __uint_as_float(v[4 * e + 2]), __uint_as_float(v[4 * e + 3]))
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (*abort_flag != 0) {
+    for (int k = 0; k < 200; ++k) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// out (+)= sum over slices, in slice order, for both problems in one launch.  One thread per (feature c, rank
+// column j < rp); reads are contiguous across the block.  transposed == 0 writes out[c*r + j] (dA [K,r]);
+// 1 writes out[j*C + c] (dB [r,N]).
+struct ReduceProblem {
+  const float* part;
+  float* out;
+  int slices, C, transposed;
+};
+__global__ void lora_grad_reduce_kernel(ReduceProblem a, ReduceProblem b, int r, int rp, int accumulate) {
+  int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t na = static_cast<int64_t>(a.C) * rp;
+  const bool second = tid >= na;
+  const ReduceProblem q = second ? b : a;
+  if (second) tid -= na;
+  const int64_t n = static_cast<int64_t>(q.C) * rp;
+  if (tid >= n) return;
+  const int c = static_cast<int>(tid / rp), j = static_cast<int>(tid % rp);
+  if (j >= r) return;
+  float s = 0.0f;
+#pragma unroll 8
+  for (int sp = 0; sp < q.slices; ++sp) s += q.part[static_cast<int64_t>(sp) * n + tid];
+  const int64_t o = q.transposed ? static_cast<int64_t>(j) * q.C + c : static_cast<int64_t>(c) * r + j;
+  q.out[o] = accumulate ? q.out[o] + s : s;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// X [M, C] (C a multiple of 64) seen as [64 features][M tokens][C/64 atoms]: box = 64 x T x atoms, 128-byte swizzle
+int encode_x(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t M, int64_t C, int T, int atoms) {
+  cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(C / 64)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 2, 128};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(T), static_cast<cuuint32_t>(atoms)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ds->encode_tiled)(
+      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MCB_ERR_ALIGN, "tensor map for grad X rejected (CUresult %d)", static_cast<int>(r));
+  return MCB_OK;
+}
+// H^T [rp, h_pitch]: box = 8 tokens x rp rows, no swizzle
+int encode_h(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t M, int64_t h_pitch, int rp) {
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(rp)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(h_pitch) * 2};
+  cuuint32_t box[2] = {8, static_cast<cuuint32_t>(rp)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ds->encode_tiled)(
+      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MCB_ERR_ALIGN, "tensor map for grad H rejected (CUresult %d)", static_cast<int>(r));
+  return MCB_OK;
+}
+
+constexpr int kGradSmem = kGradSmemBudget + 16 * kGradMaxStages + 64 + 1024;
+
+// feature groups of a problem: as few as keep a group within kGradGroup features and its accumulators within the
+// 512 tensor-memory columns; all groups equally wide (a multiple of 128), the last may hang over C (zero-filled)
+void plan_groups(int64_t C, int rp, GradProblem* q) {
+  int max_tiles = 512 / rp;
+  if (max_tiles > kGradGroup / 128) max_tiles = kGradGroup / 128;
+  const int tiles_total = static_cast<int>((C + 127) / 128);
+  q->groups = (tiles_total + max_tiles - 1) / max_tiles;
+  q->tiles = (tiles_total + q->groups - 1) / q->groups;
+  q->group_feats = q->tiles * 128;
+  q->C = static_cast<int>(C);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// older form, for feature counts that are not a multiple of 64: one problem per launch, a CTA owns 128 features
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kTileBK = 64;       // tokens per stage
+constexpr int kTileMaxStages = 12;  // enough bytes in flight per SM to cover HBM latency under load
+constexpr int kTileSmemBudget = 216 * 1024;
+constexpr uint32_t kTileBoxBytes = 64 * 64 * 2;  // one [64 tokens x 64 features] box
+
+struct TileParams {
   int M, C, rp;
   int total_kb, kb_per_split;
   float* part;  // [splits][C][rp]
@@ -34,13 +269,13 @@ struct GradParams {
 };
 
 __global__ void __launch_bounds__(kGradThreads)
-lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmH,
-                      const GradParams p) {
+lora_grad_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmH,
+                      const TileParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kGradMaxStages, done_bar = empty0 + 8 * kGradMaxStages;
+  const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kTileMaxStages, done_bar = empty0 + 8 * kTileMaxStages;
   const uint32_t tmem_slot = done_bar + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
@@ -74,9 +309,9 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 41, p.status)) break;
         const uint32_t fb = full0 + 8 * stage, sb = base + stage * p.stage_bytes;
         mbar_expect_tx(fb, p.stage_bytes);
-        tma_load_2d(sb, &tmX, fb, c0, kb * kGradBK);
-        tma_load_2d(sb + kXBoxBytes, &tmX, fb, c0 + 64, kb * kGradBK);
-        tma_load_2d(sb + 2 * kXBoxBytes, &tmH, fb, kb * kGradBK, 0);
+        tma_load_2d(sb, &tmX, fb, c0, kb * kTileBK);
+        tma_load_2d(sb + kTileBoxBytes, &tmX, fb, c0 + 64, kb * kTileBK);
+        tma_load_2d(sb + 2 * kTileBoxBytes, &tmH, fb, kb * kTileBK, 0);
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
     }
@@ -92,11 +327,11 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         tcgen05_fence_after();
         const uint32_t sb = base + stage * p.stage_bytes;
 #pragma unroll
-        for (int k4 = 0; k4 < kGradBK / 16; ++k4) {
+        for (int k4 = 0; k4 < kTileBK / 16; ++k4) {
           // A: 16 token rows further = 2 K-groups of 8 rows x 128 bytes; the second 64-feature atom is the
           // second box.  B: 16 tokens further along the contiguous dimension = 32 bytes.
-          const uint64_t ad = desc_sw128_mn(sb + k4 * 2048, kXBoxBytes, 1024);
-          const uint64_t bd = desc_sw128(sb + 2 * kXBoxBytes + k4 * 32);
+          const uint64_t ad = desc_sw128_mn(sb + k4 * 2048, kTileBoxBytes, 1024);
+          const uint64_t bd = desc_sw128(sb + 2 * kTileBoxBytes + k4 * 32);
           umma_bf16(tmem_base, ad, bd, idesc, (i | k4) != 0 ? 1u : 0u);
         }
         umma_commit(empty0 + 8 * stage);
@@ -139,7 +374,7 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 
 // out (+)= sum over splits, in split order.  One thread per (feature c, rank column j < rp); reads are
 // contiguous across the block.  transposed == 0 writes out[c*r + j] (dA [K,r]); 1 writes out[j*C + c] (dB [r,N]).
-__global__ void lora_grad_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int splits, int C,
+__global__ void lora_grad_tile_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int splits, int C,
                                         int r, int rp, int transposed, int accumulate) {
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t n = static_cast<int64_t>(C) * rp;
@@ -153,17 +388,17 @@ __global__ void lora_grad_reduce_kernel(const float* __restrict__ part, float* _
   out[o] = accumulate ? out[o] + s : s;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+typedef CUresult (*EncodeTiledFnT)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-int encode(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t pitch_elems,
+int encode_tile(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t pitch_elems,
            int box_inner, int box_outer, const char* what) {
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = reinterpret_cast<EncodeTiledFn>(ds->encode_tiled)(
+  CUresult r = reinterpret_cast<EncodeTiledFnT>(ds->encode_tiled)(
       map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -172,21 +407,14 @@ int encode(const DeviceState* ds, CUtensorMap* map, const void* ptr, int64_t inn
   return MCB_OK;
 }
 
-constexpr int kGradSmem = kGradSmemBudget + 1024 + 512;
+constexpr int kTileSmem = kTileSmemBudget + 1024 + 512;
 
-}  // namespace
-
-int init_grad_kernel() {
-  cudaError_t e = cudaFuncSetAttribute(lora_grad_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradSmem);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(lora_grad_umma_kernel)");
-  return MCB_OK;
-}
 
 // Token slices per feature tile: at most one CTA per SM, all resident at once (measured: more, shorter CTAs
 // lose to their set-up cost, and a second round of CTAs doubles the time).
-int grad_splits(int64_t M, int64_t C, int sm_count, int* kb_per_split) {
+int tile_splits(int64_t M, int64_t C, int sm_count, int* kb_per_split) {
   const int64_t c_tiles = (C + BM - 1) / BM;
-  const int64_t total_kb = (M + kGradBK - 1) / kGradBK;
+  const int64_t total_kb = (M + kTileBK - 1) / kTileBK;
   int64_t target = static_cast<int64_t>(sm_count) / c_tiles;
   if (target > total_kb) target = total_kb;
   if (target < 1) target = 1;
@@ -195,37 +423,139 @@ int grad_splits(int64_t M, int64_t C, int sm_count, int* kb_per_split) {
   return static_cast<int>((total_kb + per - 1) / per);
 }
 
-size_t grad_partial_bytes(int64_t M, int64_t C, int rp) {
-  return static_cast<size_t>(grad_splits(M, C, 256, nullptr)) * C * rp * sizeof(float);
-}
 
-// out = X^T H with H given transposed as Ht [rp, h_pitch] (token index contiguous).
-int launch_grad(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch, float* out, float* part, int64_t M,
+int launch_grad_tile(const __nv_bfloat16* X, const __nv_bfloat16* Ht, int64_t h_pitch, float* out, float* part, int64_t M,
                 int64_t C, int r, int rp, int transposed, int accumulate, const DeviceState* ds, cudaStream_t st) {
   if (C % 8 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients need a feature count that is a multiple of 8 (got %lld)", (long long)C);
   if (!aligned16(X) || !aligned16(Ht) || h_pitch % 8 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
-  GradParams p;
+  TileParams p;
   p.M = static_cast<int>(M); p.C = static_cast<int>(C); p.rp = rp;
-  p.total_kb = static_cast<int>((M + kGradBK - 1) / kGradBK);
-  const int splits = grad_splits(M, C, ds->sm_count, &p.kb_per_split);
+  p.total_kb = static_cast<int>((M + kTileBK - 1) / kTileBK);
+  const int splits = tile_splits(M, C, ds->sm_count, &p.kb_per_split);
   p.part = part;
   p.status = ds->status_word;
-  p.stage_bytes = 2 * kXBoxBytes + static_cast<uint32_t>(rp) * 128;
-  p.stages = static_cast<int>(kGradSmemBudget / p.stage_bytes);
-  if (p.stages > kGradMaxStages) p.stages = kGradMaxStages;
+  p.stage_bytes = 2 * kTileBoxBytes + static_cast<uint32_t>(rp) * 128;
+  p.stages = static_cast<int>(kTileSmemBudget / p.stage_bytes);
+  if (p.stages > kTileMaxStages) p.stages = kTileMaxStages;
   p.bar_off = p.stages * p.stage_bytes;
   CUtensorMap tmX, tmH;
-  if (int rc = encode(ds, &tmX, X, C, M, C, 64, kGradBK, "grad X")) return rc;
-  if (int rc = encode(ds, &tmH, Ht, M, rp, h_pitch, kGradBK, rp, "grad H")) return rc;
+  if (int rc = encode_tile(ds, &tmX, X, C, M, C, 64, kTileBK, "grad X")) return rc;
+  if (int rc = encode_tile(ds, &tmH, Ht, M, rp, h_pitch, kTileBK, rp, "grad H")) return rc;
   dim3 grid(static_cast<unsigned>((C + BM - 1) / BM), static_cast<unsigned>(splits));
   const bool prof = profile_on();
   if (prof) profile_begin(kProfGrad, 2.0 * M * C * r, 2.0 * M * C + 2.0 * M * rp, st);
-  lora_grad_umma_kernel<<<grid, kGradThreads, kGradSmem, st>>>(tmX, tmH, p);
+  lora_grad_tile_kernel<<<grid, kGradThreads, kTileSmem, st>>>(tmX, tmH, p);
+  if (prof) profile_end(st);
+  MCB_CHECK_LAUNCH("lora_grad_tile_kernel");
+  const int64_t n = C * rp;
+  lora_grad_tile_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(part, out, splits, static_cast<int>(C), r,
+                                                                                   rp, transposed, accumulate);
+  MCB_CHECK_LAUNCH("lora_grad_reduce");
+  return MCB_OK;
+}
+
+
+}  // namespace
+
+int init_grad_kernel() {
+  cudaError_t e = cudaFuncSetAttribute(lora_grad_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradSmem);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(lora_grad_umma_kernel)");
+  e = cudaFuncSetAttribute(lora_grad_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmem);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(lora_grad_tile_kernel)");
+  return MCB_OK;
+}
+
+// Partial sums of one launch: the CTAs of both problems together are at most the SM count (<= 256 assumed), each
+// writes at most kGradGroup x rp floats; the older form needs at most 256 slices of C x rp.
+size_t grad_partial_bytes(int64_t M, int64_t K, int64_t N, int rp) {
+  size_t b = static_cast<size_t>(256) * kGradGroup * rp * sizeof(float);
+  for (int64_t C : {K, N}) {
+    if (C % 64 != 0) {
+      const size_t t = static_cast<size_t>(tile_splits(M, C, 256, nullptr)) * C * rp * sizeof(float);
+      if (t > b) b = t;
+    }
+  }
+  return b;
+}
+
+// out_i = X_i^T H_i with H_i given transposed as Ht_i [rp, h_pitch] (token index contiguous), for one or two
+// problems over the same M tokens (X1 == nullptr: one problem).
+int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, float* out0, int transposed0,
+                 const __nv_bfloat16* X1, const __nv_bfloat16* Ht1, int64_t C1, float* out1, int transposed1,
+                 int64_t h_pitch, float* part, int64_t M, int r, int rp, int accumulate, const DeviceState* ds,
+                 cudaStream_t st) {
+  const int np = X1 != nullptr ? 2 : 1;
+  const __nv_bfloat16* Xs[2] = {X0, X1};
+  const __nv_bfloat16* Hs[2] = {Ht0, Ht1};
+  float* outs[2] = {out0, out1};
+  const int trs[2] = {transposed0, transposed1};
+  const int64_t Cs[2] = {C0, np == 2 ? C1 : 0};
+  bool ragged = false;
+  for (int i = 0; i < np; ++i) ragged = ragged || (Cs[i] % 64 != 0);
+  if (ragged) {
+    for (int i = 0; i < np; ++i)
+      if (int rc = launch_grad_tile(Xs[i], Hs[i], h_pitch, outs[i], part, M, Cs[i], r, rp, trs[i], accumulate, ds, st)) return rc;
+    return MCB_OK;
+  }
+  for (int i = 0; i < np; ++i)
+    if (!aligned16(Xs[i]) || !aligned16(Hs[i])) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
+  if (h_pitch % 8 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
+  GradParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int>(M); p.rp = rp;
+  p.status = ds->status_word;
+  for (int i = 0; i < np; ++i) plan_groups(Cs[i], rp, &p.pr[i]);
+  // tokens per stage: 32 when three stages of the widest group still fit, else 16
+  int widest = p.pr[0].group_feats;
+  if (np == 2 && p.pr[1].group_feats > widest) widest = p.pr[1].group_feats;
+  p.T = (3 * (32 * widest * 2 + rp * 32 * 2 + 1024) <= kGradSmemBudget) ? 32 : 16;
+  uint32_t stride = 0;
+  for (int i = 0; i < np; ++i) {
+    p.x_bytes[i] = static_cast<uint32_t>(p.T) * p.pr[i].group_feats * 2;
+    const uint32_t sbytes = p.x_bytes[i] + static_cast<uint32_t>(rp) * p.T * 2;
+    if (sbytes > stride) stride = sbytes;
+  }
+  p.stage_stride = (stride + 1023u) & ~1023u;
+  p.stages = static_cast<int>(kGradSmemBudget / p.stage_stride);
+  if (p.stages > kGradMaxStages) p.stages = kGradMaxStages;
+  if (p.stages < 2) return fail(MCB_ERR_UNSUPPORTED, "bf16 LoRA gradients: stage does not fit shared memory");
+  p.bar_off = p.stages * p.stage_stride;
+  // CTAs: shared between the problems in proportion to their bytes, whole token slices per feature group
+  const int total_steps = static_cast<int>((M + p.T - 1) / p.T);
+  const int sms = ds->sm_count;
+  const double wsum = static_cast<double>(Cs[0]) + static_cast<double>(Cs[1]);
+  int used = 0;
+  float* pp = part;
+  for (int i = 0; i < np; ++i) {
+    int share = np == 1 ? sms : static_cast<int>(sms * (static_cast<double>(Cs[i]) / wsum));
+    if (i == 1) share = sms - used;
+    int slices = share / p.pr[i].groups;
+    if (slices < 1) slices = 1;
+    if (slices > total_steps) slices = total_steps;
+    p.pr[i].slices = slices;
+    p.pr[i].part = pp;
+    pp += static_cast<size_t>(slices) * Cs[i] * rp;
+    const int n = slices * p.pr[i].groups;
+    if (i == 0) p.n_cta0 = n;
+    used += n;
+  }
+  if (static_cast<size_t>(pp - part) * sizeof(float) > static_cast<size_t>(256) * kGradGroup * rp * sizeof(float))
+    return fail(MCB_ERR_WORKSPACE, "bf16 LoRA gradients: partial sums exceed the workspace");
+  CUtensorMap tmX[2], tmH[2];
+  for (int i = 0; i < np; ++i) {
+    if (int rc = encode_x(ds, &tmX[i], Xs[i], M, Cs[i], p.T, p.pr[i].group_feats / 64)) return rc;
+    if (int rc = encode_h(ds, &tmH[i], Hs[i], M, h_pitch, rp)) return rc;
+  }
+  if (np == 1) { tmX[1] = tmX[0]; tmH[1] = tmH[0]; }
+  const bool prof = profile_on();
+  if (prof) profile_begin(kProfGrad, 2.0 * M * (Cs[0] + Cs[1]) * r, 2.0 * M * (Cs[0] + Cs[1]) + 2.0 * np * M * rp, st);
+  lora_grad_umma_kernel<<<used, kGradThreads, kGradSmem, st>>>(tmX[0], tmH[0], tmX[1], tmH[1], p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_grad_umma_kernel");
-  const int64_t n = C * rp;
-  lora_grad_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(part, out, splits, static_cast<int>(C), r,
-                                                                                   rp, transposed, accumulate);
+  ReduceProblem ra = {p.pr[0].part, out0, p.pr[0].slices, static_cast<int>(Cs[0]), transposed0};
+  ReduceProblem rb = {np == 2 ? p.pr[1].part : nullptr, out1, np == 2 ? p.pr[1].slices : 0, static_cast<int>(Cs[1]), transposed1};
+  const int64_t n = (Cs[0] + Cs[1]) * rp;
+  lora_grad_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(ra, rb, r, rp, accumulate);
   MCB_CHECK_LAUNCH("lora_grad_reduce");
   return MCB_OK;
 }
