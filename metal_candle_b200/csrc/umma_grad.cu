@@ -39,13 +39,14 @@ struct GradProblem {
   float* part;                    // [slices][C][rp]
 };
 struct GradParams {
-  int M, rp, T;                   // tokens, padded rank, tokens per stage (16 or 32)
-  int stages;
+  int M, rp;                      // tokens, padded rank
+  int T[2];                       // tokens per stage of each problem (a multiple of 16, at most 256)
+  int stages[2];                  // stage ring depth of each problem
   int n_cta0;                     // CTAs of problem 0 (the rest belong to problem 1)
   GradProblem pr[2];
   int* status;
   uint32_t x_bytes[2], bar_off;   // X bytes per stage of each problem; H follows at x_bytes
-  uint32_t stage_stride;
+  uint32_t stage_stride[2];
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
@@ -79,7 +80,7 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
   const uint32_t tmem_cols = acc_cols <= 32 ? 32u : acc_cols <= 64 ? 64u : acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int s = 0; s < kGradMaxStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     mbar_init(done_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -95,13 +96,16 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   // token steps of T tokens, split evenly over the slices
-  const int total_steps = (p.M + p.T - 1) / p.T;
+  const int T = p.T[which];
+  const int n_stages = p.stages[which];
+  const uint32_t stride = p.stage_stride[which];
+  const int total_steps = (p.M + T - 1) / T;
   const int per = (total_steps + q.slices - 1) / q.slices;
   const int step_begin = slice * per;
   const int step_end = min(total_steps, step_begin + per);
   const int nsteps = max(0, step_end - step_begin);
   const uint32_t xb = p.x_bytes[which];
-  const uint32_t atom_bytes = static_cast<uint32_t>(p.T) * 128;   // one 64-feature atom of a stage: T rows of 128 bytes
+  const uint32_t atom_bytes = static_cast<uint32_t>(T) * 128;   // one 64-feature atom of a stage: T rows of 128 bytes
 
   if (warp == 0) {
     if (lane == 0) {
@@ -109,13 +113,13 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
       uint32_t phase = 0;
       for (int s = step_begin; s < step_end; ++s) {
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 41, p.status)) break;
-        const uint32_t fb = full0 + 8 * stage, sb = base + stage * p.stage_stride;
-        mbar_expect_tx(fb, xb + static_cast<uint32_t>(p.rp) * p.T * 2);
+        const uint32_t fb = full0 + 8 * stage, sb = base + stage * stride;
+        mbar_expect_tx(fb, xb + static_cast<uint32_t>(p.rp) * T * 2);
         // X: [64 features][T tokens][atoms of the group]; in shared memory atom-major blocks of T rows x 128 bytes
-        tma_load_3d(sb, tmX, fb, 0, s * p.T, group * (q.group_feats / 64));
+        tma_load_3d(sb, tmX, fb, 0, s * T, group * (q.group_feats / 64));
         // H^T: K-major B operand, unswizzled 16-byte columns of 8 tokens each
-        for (int j = 0; j < p.T / 8; ++j) tma_load_2d(sb + xb + j * p.rp * 16, tmH, fb, s * p.T + j * 8, 0);
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        for (int j = 0; j < T / 8; ++j) tma_load_2d(sb + xb + j * p.rp * 16, tmH, fb, s * T + j * 8, 0);
+        if (++stage == n_stages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -128,8 +132,8 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
         ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, 42, p.status);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t sb = base + stage * p.stage_stride;
-        for (int k16 = 0; k16 < p.T / 16; ++k16) {
+        const uint32_t sb = base + stage * stride;
+        for (int k16 = 0; k16 < T / 16; ++k16) {
           // B: 16 tokens further = two 16-byte columns of rp rows
           const uint64_t bd = desc_noswz(sb + xb + k16 * 2 * (p.rp * 16), p.rp * 16, 128);
           for (int f = 0; f < q.tiles; ++f) {
@@ -139,7 +143,7 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
           }
         }
         umma_commit(empty0 + 8 * stage);
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        if (++stage == n_stages) { stage = 0; phase ^= 1; }
       }
       if (ok) umma_commit(done_bar);   // with no steps at all this completes at once
     }
@@ -505,23 +509,22 @@ int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, 
   p.M = static_cast<int>(M); p.rp = rp;
   p.status = ds->status_word;
   for (int i = 0; i < np; ++i) plan_groups(Cs[i], rp, &p.pr[i]);
-  // tokens per stage: 32 when three stages of the widest group still fit, else 16
-  int widest = p.pr[0].group_feats;
-  if (np == 2 && p.pr[1].group_feats > widest) widest = p.pr[1].group_feats;
-  p.T = (3 * (32 * widest * 2 + rp * 32 * 2 + 1024) <= kGradSmemBudget) ? 32 : 16;
-  uint32_t stride = 0;
+  // tokens per stage, per problem: as many (a multiple of 16, at most 256) as keep a stage near 48 KB, so that
+  // narrow problems have as many bytes in flight as wide ones
   for (int i = 0; i < np; ++i) {
-    p.x_bytes[i] = static_cast<uint32_t>(p.T) * p.pr[i].group_feats * 2;
-    const uint32_t sbytes = p.x_bytes[i] + static_cast<uint32_t>(rp) * p.T * 2;
-    if (sbytes > stride) stride = sbytes;
+    int T = (48 * 1024) / (p.pr[i].group_feats * 2) / 16 * 16;
+    if (T < 16) T = 16;
+    if (T > 256) T = 256;
+    p.T[i] = T;
+    p.x_bytes[i] = static_cast<uint32_t>(T) * p.pr[i].group_feats * 2;
+    const uint32_t sbytes = p.x_bytes[i] + static_cast<uint32_t>(rp) * T * 2;
+    p.stage_stride[i] = (sbytes + 1023u) & ~1023u;
+    p.stages[i] = static_cast<int>(kGradSmemBudget / p.stage_stride[i]);
+    if (p.stages[i] > kGradMaxStages) p.stages[i] = kGradMaxStages;
+    if (p.stages[i] < 2) return fail(MCB_ERR_UNSUPPORTED, "bf16 LoRA gradients: stage does not fit shared memory");
   }
-  p.stage_stride = (stride + 1023u) & ~1023u;
-  p.stages = static_cast<int>(kGradSmemBudget / p.stage_stride);
-  if (p.stages > kGradMaxStages) p.stages = kGradMaxStages;
-  if (p.stages < 2) return fail(MCB_ERR_UNSUPPORTED, "bf16 LoRA gradients: stage does not fit shared memory");
-  p.bar_off = p.stages * p.stage_stride;
+  p.bar_off = kGradSmemBudget;
   // CTAs: shared between the problems in proportion to their bytes, whole token slices per feature group
-  const int total_steps = static_cast<int>((M + p.T - 1) / p.T);
   const int sms = ds->sm_count;
   const double wsum = static_cast<double>(Cs[0]) + static_cast<double>(Cs[1]);
   int used = 0;
@@ -531,6 +534,7 @@ int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, 
     if (i == 1) share = sms - used;
     int slices = share / p.pr[i].groups;
     if (slices < 1) slices = 1;
+    const int total_steps = static_cast<int>((M + p.T[i] - 1) / p.T[i]);
     if (slices > total_steps) slices = total_steps;
     p.pr[i].slices = slices;
     p.pr[i].part = pp;
@@ -543,7 +547,7 @@ int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, 
     return fail(MCB_ERR_WORKSPACE, "bf16 LoRA gradients: partial sums exceed the workspace");
   CUtensorMap tmX[2], tmH[2];
   for (int i = 0; i < np; ++i) {
-    if (int rc = encode_x(ds, &tmX[i], Xs[i], M, Cs[i], p.T, p.pr[i].group_feats / 64)) return rc;
+    if (int rc = encode_x(ds, &tmX[i], Xs[i], M, Cs[i], p.T[i], p.pr[i].group_feats / 64)) return rc;
     if (int rc = encode_h(ds, &tmH[i], Hs[i], M, h_pitch, rp)) return rc;
   }
   if (np == 1) { tmX[1] = tmX[0]; tmH[1] = tmH[0]; }
