@@ -122,6 +122,14 @@ int64_t mcb_lora_h_pitch(int64_t M);
 /* dst[cols,rows] = src[rows,cols]^T; makes the [K,N] copy of a frozen weight for the backward. */
 int mcb_transpose_2d(const void* src, void* dst, int64_t rows, int64_t cols, int dtype, void* stream);
 
+/* The MLP's first half in one kernel: gate = x Wg^T, up = x Wu^T, act = silu(gate) * up  (MLP::forward,
+ * src/models/transformer.rs:389-395: two candle_nn::Linear calls, silu, mul).  w_gate_up is [2F, K]: the gate and up
+ * weights (each [F, K]) interleaved in blocks of 128 rows - gate rows 0..127, up rows 0..127, gate rows 128..255,
+ * ... - so that one output tile holds both projections of the same 128 features.  gate, up, act are [M, F]; gate
+ * and up are written too because the backward needs them.  bf16 only, F a multiple of 128, K of 8. */
+int mcb_linear_swiglu_fwd(const void* x, const void* w_gate_up, void* gate, void* up, void* act, int64_t M, int64_t K,
+                          int64_t F, int dtype, void* stream);
+
 /* ---- lazy-graph primitives (Operation::{Matmul, Add, Mul, MulScalar}, src/graph/executor.rs:71-120) ---- */
 
 /* out[M,N] = a[M,K] b[K,N] (Tensor::broadcast_matmul with a 2-D right operand).  The bf16 path transposes b

@@ -62,6 +62,7 @@ SIGNATURES = {
     "mcb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
     "mcb_softmax_causal_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
     "mcb_softmax_causal_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "mcb_linear_swiglu_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "mcb_attention_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64]),
     "mcb_attention_causal_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
     "mcb_attention_causal_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32,

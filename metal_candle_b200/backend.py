@@ -194,6 +194,33 @@ def transpose_2d(src: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------------
+# gate / up projections + SwiGLU in one kernel
+# ---------------------------------------------------------------------------------------------
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[2F, K] weight for `linear_swiglu_forward`: blocks of 128 gate rows alternate with the same 128 up rows."""
+    F, K = w_gate.shape
+    if w_up.shape != w_gate.shape or F % 128 != 0:
+        raise TrainingError(f"gate/up weights {list(w_gate.shape)} / {list(w_up.shape)}: equal shapes with a multiple of 128 rows")
+    return torch.stack([w_gate.view(F // 128, 128, K), w_up.view(F // 128, 128, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def linear_swiglu_forward(x: torch.Tensor, w_gate_up: torch.Tensor):
+    """MLP::forward's first half (src/models/transformer.rs:389-395): returns (gate, up, silu(gate) * up)."""
+    _require_cuda(x, w_gate_up)
+    K = x.shape[-1]
+    F = w_gate_up.shape[0] // 2
+    if w_gate_up.shape[1] != K:
+        raise TrainingError(f"interleaved gate/up weight must be [2F, {K}], got {list(w_gate_up.shape)}")
+    M = x.numel() // K
+    lib = _lib_for(x)
+    gate, up, act = (torch.empty(*x.shape[:-1], F, dtype=x.dtype, device=x.device) for _ in range(3))
+    _lib.check(lib.mcb_linear_swiglu_fwd(_ptr(x), _ptr(w_gate_up), _ptr(gate), _ptr(up), _ptr(act), M, K, F, _dtype_code(x),
+                                         _stream()))
+    return gate, up, act
+
+
+# ---------------------------------------------------------------------------------------------
 # fused causal attention
 # ---------------------------------------------------------------------------------------------
 

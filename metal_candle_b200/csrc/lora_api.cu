@@ -110,6 +110,20 @@ extern "C" int mcb_matmul(const void* a, const void* b, void* out, int64_t M, in
   return bf16path::matmul_nt(a, workspace, out, M, K, N, ds, st);
 }
 
+extern "C" int mcb_linear_swiglu_fwd(const void* x, const void* w_gate_up, void* gate, void* up, void* act, int64_t M,
+                                     int64_t K, int64_t F, int dtype, void* stream) {
+  if (!x || !w_gate_up || !gate || !up || !act) return fail(MCB_ERR_NULL, "linear_swiglu_fwd: null pointer");
+  if (M <= 0 || K <= 0 || F <= 0) return fail(MCB_ERR_SHAPE, "linear_swiglu_fwd: M=%lld K=%lld F=%lld must be positive", (long long)M, (long long)K, (long long)F);
+  if (dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "linear_swiglu_fwd: bfloat16 only (use two mcb_lora_linear_fwd calls and mcb_swiglu_fwd)");
+  if (!aligned16(x) || !aligned16(w_gate_up) || !aligned16(gate) || !aligned16(up) || !aligned16(act))
+    return fail(MCB_ERR_ALIGN, "linear_swiglu_fwd: 16-byte alignment");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  return bf16path::launch_gemm2_swiglu(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w_gate_up),
+                                       static_cast<__nv_bfloat16*>(gate), static_cast<__nv_bfloat16*>(up),
+                                       static_cast<__nv_bfloat16*>(act), M, K, F, ds, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const float* A, const float* B, void* y,
                                    void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
                                    int w_layout, void* workspace, size_t workspace_bytes, void* stream) {

@@ -65,6 +65,9 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds);
 // out[M,N] = a[M,K] bt[N,K]^T (bt is b transposed, both operands K-major)
 int matmul_nt(const void* a, const void* bt, void* out, int64_t M, int64_t K, int64_t N, const DeviceState* ds,
               cudaStream_t st);
+// gate, up [M,F] = x w_gu^T (w_gu: gate and up rows interleaved in blocks of 128), act = silu(gate) * up
+int launch_gemm2_swiglu(const __nv_bfloat16* X, const __nv_bfloat16* Wgu, __nv_bfloat16* G, __nv_bfloat16* U,
+                        __nv_bfloat16* Act, int64_t M, int64_t K, int64_t F, const DeviceState* ds, cudaStream_t st);
 }  // namespace bf16path
 
 }  // namespace mcb

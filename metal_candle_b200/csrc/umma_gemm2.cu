@@ -47,6 +47,7 @@ constexpr int kEpiBufs = kEpiBufsMax;
 struct Gemm2Params {
   int M, N, K;
   int BN, stages, rp;
+  int swiglu;   // 1: the tile is [128 gate columns | 128 up columns]; the epilogue also writes silu(gate) * up
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;  // m tiles of 256 rows
   float scale;
   __nv_bfloat16* Y;
@@ -121,7 +122,8 @@ __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& m
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                   const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                  const __grid_constant__ CUtensorMap tmY, const Gemm2Params p) {
+                  const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmU,
+                  const __grid_constant__ CUtensorMap tmAct, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -310,9 +312,52 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       ok = __all_sync(0xffffffffu, mbar_wait(d1_full0 + 8 * a, u & 1, abort_flag, 64, p.status));
       if (!ok) break;
       tcgen05_fence_after();
+      if (p.swiglu) {
+        // SwiGLU tile: accumulator columns [0, 128) are gate features nt*128.., columns [128, 256) the same
+        // features of up.  Per 32 features: gate, up and silu(gate)*up go out through three staging buffers.
+        const int F = p.N >> 1;
+        for (int c = 0; c < 128; c += 32) {
+          const int fcol = nt * 128 + c;
+          if (fcol >= F) break;
+          uint32_t g0[16], g1[16], u0[16], u1[16];
+          tmem_ld_x16(d + c, g0);
+          tmem_ld_x16(d + c + 16, g1);
+          tmem_ld_x16(d + 128 + c, u0);
+          tmem_ld_x16(d + 128 + c + 16, u1);
+          if (lane == 0) bulk_wait_group_read<0>();  // all three staging buffers have been read
+          __syncwarp();
+          tmem_ld_wait();
+          uint32_t wg[16], wu[16], wa[16];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const float ga = __uint_as_float(g0[j]), gb = __uint_as_float(g0[j + 1]);
+            const float ua = __uint_as_float(u0[j]), ub = __uint_as_float(u0[j + 1]);
+            wg[j >> 1] = pack_bf16(ga, gb);
+            wu[j >> 1] = pack_bf16(ua, ub);
+            wa[j >> 1] = pack_bf16(__fdividef(ga, 1.0f + __expf(-ga)) * ua, __fdividef(gb, 1.0f + __expf(-gb)) * ub);
+            const float gc = __uint_as_float(g1[j]), gd = __uint_as_float(g1[j + 1]);
+            const float uc = __uint_as_float(u1[j]), ud = __uint_as_float(u1[j + 1]);
+            wg[8 + (j >> 1)] = pack_bf16(gc, gd);
+            wu[8 + (j >> 1)] = pack_bf16(uc, ud);
+            wa[8 + (j >> 1)] = pack_bf16(__fdividef(gc, 1.0f + __expf(-gc)) * uc, __fdividef(gd, 1.0f + __expf(-gd)) * ud);
+          }
+          stage_row(gen_base + (epi_base - base), lane, wg);
+          stage_row(gen_base + (epi_base - base) + kEpiBufBytes, lane, wu);
+          stage_row(gen_base + (epi_base - base) + 2 * kEpiBufBytes, lane, wa);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && m0 + quad * 32 < p.M) {
+            tma_store_2d(&tmY, epi_base, fcol, m0 + quad * 32);
+            tma_store_2d(&tmU, epi_base + kEpiBufBytes, fcol, m0 + quad * 32);
+            tma_store_2d(&tmAct, epi_base + 2 * kEpiBufBytes, fcol, m0 + quad * 32);
+            bulk_commit_group();
+          }
+        }
+      } else
       // The W halves sit at columns [0, BN/2) and [BN/2 + rp/2, BN + rp/2) of the accumulator.  Output leaves in
       // chunks of 32 columns: each thread rounds its row's 64 bytes into this warp's staging buffer (64-byte
       // swizzle, conflict-free) and one tiled store per chunk writes 32 rows x 64 bytes, clipped at the edges.
+      {
       for (int c = 0; c < p.BN; c += 32) {
         const int gcol = n0 + c;
         if (gcol >= p.N) break;
@@ -336,6 +381,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           bulk_commit_group();
         }
         if (++sbuf == kEpiBufs) sbuf = 0;
+      }
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -454,7 +500,55 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     profile_begin(kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
                   2.0 * (m * k + n * k + m * n) + 2.0 * c.rp * (k + n), st);
   }
-  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, p);
+  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, tmY, tmY, p);
+  if (prof) profile_end(st);
+  MCB_CHECK_LAUNCH("lora_gemm2_kernel");
+  return MCB_OK;
+}
+
+// gate, up, act [M, F] = x [M, K] . w_gu^T with w_gu [2F, K] holding the gate and up weights interleaved in blocks
+// of 128 rows (gate rows f0..f0+127, then up rows f0..f0+127), and act = silu(gate) * up.
+int launch_gemm2_swiglu(const __nv_bfloat16* X, const __nv_bfloat16* Wgu, __nv_bfloat16* G, __nv_bfloat16* U,
+                        __nv_bfloat16* Act, int64_t M, int64_t K, int64_t F, const DeviceState* ds, cudaStream_t st) {
+  if (F % 128 != 0 || K % 8 != 0) return fail(MCB_ERR_ALIGN, "linear_swiglu: features %lld must be a multiple of 128, reduction %lld of 8", (long long)F, (long long)K);
+  if (M > 0x7fffff00ll || 2 * F > 0x7fffff00ll || K > 0x7fffff00ll) return fail(MCB_ERR_SHAPE, "linear_swiglu: dimension exceeds 2^31");
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int>(M); p.N = static_cast<int>(2 * F); p.K = static_cast<int>(K);
+  p.swiglu = 1;
+  p.BN = 256;
+  p.num_m_tiles = static_cast<int>((M + 255) / 256);
+  p.num_n_tiles = static_cast<int>(F / 128);
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  p.num_k_blocks = static_cast<int>((K + BK2 - 1) / BK2);
+  p.group_m = p.num_m_tiles < 8 ? p.num_m_tiles : 8;
+  p.Y = G; p.status = ds->status_word;
+  const uint32_t x_bytes = 128 * BK2 * 2, w_bytes = 128u * BK2 * 2;
+  p.w_off = x_bytes;
+  p.p_off = x_bytes + w_bytes;
+  p.stage_bytes = x_bytes + w_bytes;
+  const uint32_t epi_bytes = 4 * kEpiBufs * kEpiBufBytes;
+  int stages = static_cast<int>((kSmem2 - epi_bytes - 512) / p.stage_bytes);
+  if (stages > kMaxStages2) stages = kMaxStages2;
+  p.stages = stages;
+  p.q_off = stages * p.stage_bytes;
+  p.hs_off = p.q_off;
+  p.epi_off = p.hs_off;
+  p.bar_off = p.epi_off + epi_bytes;
+  CUtensorMap tmX, tmW, tmG, tmU, tmA;
+  if (int rc = make_map2(ds, &tmG, G, F, M, 32, 32, 64, "gate (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmU, U, F, M, 32, 32, 64, "up (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmA, Act, F, M, 32, 32, 64, "act (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmX, X, K, M, BK2, 128, 128, "X (pair)")) return rc;
+  if (int rc = make_map2(ds, &tmW, Wgu, K, 2 * F, BK2, 128, 128, "W gate/up (pair)")) return rc;
+  int pairs = ds->sm_count / 2;
+  if (pairs > p.num_tiles) pairs = p.num_tiles;
+  const bool prof = profile_on();
+  if (prof) {
+    const double m = static_cast<double>(M), n = static_cast<double>(2 * F), k = static_cast<double>(K);
+    profile_begin(kProfGemm, 2.0 * m * n * k, 2.0 * (m * k + n * k + 1.5 * m * n), st);
+  }
+  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmX, tmX, tmG, tmU, tmA, p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm2_kernel");
   return MCB_OK;

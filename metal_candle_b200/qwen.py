@@ -195,6 +195,20 @@ class Qwen:
                                               self.config.vocab_size, self.dt, _stream()))
         return out
 
+    def _gate_up_weight(self, L):
+        """The gate and up weights interleaved for `linear_swiglu_forward`, or None when that kernel does not
+        apply (an adapter on either projection, float32, or a width that is not a multiple of 128).  Cached per
+        layer and rebuilt when either weight tensor has been written to."""
+        g, u = L["gate_proj"], L["up_proj"]
+        if g.lora is not None or u.lora is not None or self.dtype != torch.bfloat16 or g.out_f % 128 != 0:
+            return None
+        ver = (g.weight._version, u.weight._version, g.weight.data_ptr(), u.weight.data_ptr())
+        cached = L.get("_gate_up")
+        if cached is None or cached[0] != ver:
+            cached = (ver, backend.interleave_gate_up(g.weight, u.weight))
+            L["_gate_up"] = cached
+        return cached[1]
+
     # -- attention core on [B,H,S,d] tensors; grouped-query heads are folded into the row dimension --
     def _attention_fwd(self, Qr, Kr, Vr, B, S):
         """Returns (P, O, lse): the fused kernel (bf16, head_dim 64, S a multiple of 128) keeps only the
@@ -245,10 +259,16 @@ class Qwen:
             O = None   # only the fused backward needs the per-head output again
         h2, ho = self._lin(o, L["o_proj"], save, residual=h)   # residual connection fused into the epilogue
         n2 = self._norm(h2, L["post_attention_layernorm"])
-        gt, hg = self._lin(n2, L["gate_proj"], save)
-        up, hu = self._lin(n2, L["up_proj"], save)
-        act = torch.empty_like(gt)
-        _lib.check(self.lib.mcb_swiglu_fwd(_ptr(gt), _ptr(up), _ptr(act), gt.numel(), self.dt, _stream()))
+        w_gu = self._gate_up_weight(L)
+        if w_gu is not None:
+            # gate and up projections and silu(gate) * up from one kernel (no adapters on either)
+            gt, up, act = backend.linear_swiglu_forward(n2, w_gu)
+            hg = hu = None
+        else:
+            gt, hg = self._lin(n2, L["gate_proj"], save)
+            up, hu = self._lin(n2, L["up_proj"], save)
+            act = torch.empty_like(gt)
+            _lib.check(self.lib.mcb_swiglu_fwd(_ptr(gt), _ptr(up), _ptr(act), gt.numel(), self.dt, _stream()))
         h3, hd = self._lin(act, L["down_proj"], save, residual=h2)
         if not save:
             return h3, None

@@ -210,8 +210,10 @@ def _count_launches(cfg, wl) -> int:
     L = cfg.num_hidden_layers
     n_lora = len(wl["targets"])
     fused_attn = cfg.head_dim == 64 and wl["seq"] % 128 == 0   # else the scores are materialised (cuBLAS + row softmax)
+    fused_mlp = (cfg.intermediate_size % 128 == 0 and "gate_proj" not in wl["targets"] and "up_proj" not in wl["targets"])
     # forward: 2 norms, 7 GEMMs, operand packs, 3 rope/relayout + 1 inverse relayout, attention (or softmax), swiglu
-    per_layer_fwd = 2 + 7 + n_lora + 4 + 1 + 1
+    # (gate, up and swiglu are one kernel when neither projection has an adapter)
+    per_layer_fwd = 2 + (5 if fused_mlp else 8) + n_lora + 4 + 1
     # backward: 7 GEMMs, packs, dA/dB (gradient + reduce each), swiglu, 2 norms, 4 rope/relayout,
     # attention (dq + dkv kernels, or one softmax), 2 residual-gradient adds
     per_layer_bwd = 7 + n_lora + 4 * n_lora + 1 + 2 + 4 + (2 if fused_attn else 1) + 2

@@ -356,7 +356,7 @@ def cross_entropy_loss(logits, targets, ignore_index=IGNORE_INDEX, dtype=np.floa
 def causal_gqa_attention(q, k, v, scale, dtype=np.float64):
     """Attention::forward's core (src/models/transformer.rs:257-285): scores = q k^T * scale, an additive
     causal mask (-inf above the diagonal, as the callers pass it), softmax over keys, times v; grouped-query
-    heads share a kv head (the reference repeats k and v, src/models/transformer.rs:246-255).
+    heads share a kv head (the reference repeats k and v, src/models/transformer.rs:260-261,295-310).
     q [nb, G, S, d], k and v [nb, S, d] -> (o [nb, G, S, d], lse [nb, G, S], p [nb, G, S, S])."""
     q, k, v = (np.asarray(t, dtype=dtype) for t in (q, k, v))
     nb, G, S, d = q.shape

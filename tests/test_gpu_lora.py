@@ -218,6 +218,24 @@ def test_bf16_kernels_exact_on_small_integers(cuda_device, M, K, N, r):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("M,K,F", [(300, 896, 256), (1300, 896, 4864), (2048, 256, 128)])
+def test_linear_swiglu_forward(cuda_device, M, K, F):
+    """gate = x Wg^T, up = x Wu^T, act = silu(gate) * up from one kernel, against the unfused restatement."""
+    from metal_candle_b200 import _lib, backend as B
+
+    x = S.bf16_round(S.normal(31, "x", (M, K)))
+    wg = S.bf16_round(S.normal(31, "wg", (F, K)) / np.sqrt(K))
+    wu = S.bf16_round(S.normal(31, "wu", (F, K)) / np.sqrt(K))
+    xd, wgd, wud = (dev_t(a, torch.bfloat16, cuda_device) for a in (x, wg, wu))
+    gate, up, act = B.linear_swiglu_forward(xd, B.interleave_gate_up(wgd, wud))
+    want_g, want_u = R.linear(x, wg), R.linear(x, wu)
+    want_a = want_g / (1.0 + np.exp(-want_g)) * want_u
+    assert R.max_abs_normalised(back(gate), want_g) <= 2e-2
+    assert R.max_abs_normalised(back(up), want_u) <= 2e-2
+    assert R.max_abs_normalised(back(act), want_a) <= 2e-2
+    assert _lib.device_status() == 0
+
+
 def test_lora_rejects_bad_arguments(cuda_device):
     from metal_candle_b200 import backend as B
 

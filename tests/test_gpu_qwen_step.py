@@ -24,10 +24,11 @@ def tiny_config():
 
 
 def fused_attention_config():
-    """head_dim 64 and a sequence of 128: the shapes the fused attention kernels take."""
+    """head_dim 64 and a sequence of 128: the shapes the fused attention kernels take; an MLP width that is a
+    multiple of 128, so that steps without gate/up adapters also take the fused gate/up/SwiGLU kernel."""
     from metal_candle_b200.qwen import ModelConfig
 
-    return ModelConfig(vocab_size=320, hidden_size=256, intermediate_size=320, num_hidden_layers=2,
+    return ModelConfig(vocab_size=320, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
                        rms_norm_eps=1e-6, rope_theta=1.0e6)
 
@@ -156,6 +157,27 @@ def test_fifty_step_loss_curve(cuda_device, dtype, tol):
     assert stepper.step() == 50 and opt.step_count == 50 * 2 * 2 * cfg.num_hidden_layers
     assert np.abs(got - want).max() / np.abs(want).max() <= tol, (got[:5], want[:5])
     assert want[-1] < want[0]  # it trains
+
+
+def test_loss_curve_with_fused_attention(cuda_device):
+    """The 50-step curve once more on the shapes that take the fused attention kernels (bf16, head_dim 64,
+    128 positions): q_proj/v_proj adapters, B = 0 at step 0, AdamW with WarmupCosine(5, 50)."""
+    from metal_candle_b200.training import AdamW, AdamWConfig, LRScheduler, TargetModule, TrainingStep
+
+    cfg, model, adapter = build(cuda_device, torch.bfloat16, [TargetModule.QProj, TargetModule.VProj], b_std=0.0,
+                                cfg=fused_attention_config())
+    orc = oracle_of(cfg, model, adapter, False)
+    sched = LRScheduler.warmup_cosine(5, 50, 1e-3, 1e-5)
+    batches = [batch(200 + s, 2, 128, cfg.vocab_size) for s in range(50)]
+    want = QO.train(orc, batches, sched.get_lr)
+    opt, stepper, got = AdamW(AdamWConfig()), TrainingStep(), []
+    for s, (ids, tg) in enumerate(batches):
+        m = stepper.execute(torch.from_numpy(ids).to(cuda_device), torch.from_numpy(tg).to(cuda_device), adapter, opt,
+                            sched.get_lr(s), model.forward_backward)
+        got.append(m.loss)
+    got, want = np.array(got), np.array(want)
+    assert np.abs(got - want).max() / np.abs(want).max() <= 2e-2, (got[:5], want[:5])
+    assert want[-1] < want[0]
 
 
 def test_gradient_accumulation_matches_one_big_batch(cuda_device):
