@@ -38,6 +38,7 @@ struct Params {
   int64_t rows;
   int D, nvec, row_bytes;
   int stages, n_streams;
+  int wpr;           // consumer warps per row (1; 2 or 4 for the rmsnorm backward of wide rows)
   int causal_seq;
   float eps, scale;
   int* status;
@@ -109,6 +110,7 @@ rowpipe_kernel(const Params p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = base + p.bar_off, empty0 = full0 + 8 * kMaxStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + p.bar_off + 16 * kMaxStages);
+  __shared__ float2 xch[16][4];   // per row of a tile: the partial sums of the warps that share it
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, W); }
@@ -126,8 +128,9 @@ rowpipe_kernel(const Params p) {
   }
   __syncthreads();
 
-  const int64_t n_tiles = (p.rows + W - 1) / W;
-  const uint32_t stream_bytes = static_cast<uint32_t>(W) * p.row_bytes;
+  const int R = W / p.wpr;   // rows per tile
+  const int64_t n_tiles = (p.rows + R - 1) / R;
+  const uint32_t stream_bytes = static_cast<uint32_t>(R) * p.row_bytes;
 
   constexpr bool kDw = (OP == kRmsBwd && KMAX > 0);  // per-lane dw sums kept in registers
   float dwa[kDw ? KMAX : 1][N];
@@ -146,8 +149,8 @@ rowpipe_kernel(const Params p) {
       bool ok = true;
       if (lane == 0) ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 51, p.status);
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      const int64_t row0 = t * W;
-      const int nrows = static_cast<int>(p.rows - row0 < W ? p.rows - row0 : W);
+      const int64_t row0 = t * R;
+      const int nrows = static_cast<int>(p.rows - row0 < R ? p.rows - row0 : R);
       const uint32_t fb = full0 + 8 * stage, sb = base + stage * p.stage_bytes;
       const char* g0 = static_cast<const char*>(p.in0) + row0 * p.row_bytes;
       const char* g1 = kTwoIn ? static_cast<const char*>(p.in1) + row0 * p.row_bytes : nullptr;
@@ -182,9 +185,10 @@ rowpipe_kernel(const Params p) {
     const int nvec = p.nvec;
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
       if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, abort_flag, 52, p.status))) break;
-      const int64_t row = t * W + warp;
+      const int rit = warp / p.wpr, seg = warp - rit * p.wpr;   // row of the tile, segment of the row
+      const int64_t row = t * R + rit;
       if (row < p.rows) {
-        const uint8_t* s0 = gen_base + stage * p.stage_bytes + warp * p.row_bytes;
+        const uint8_t* s0 = gen_base + stage * p.stage_bytes + rit * p.row_bytes;
         const uint8_t* s1 = s0 + stream_bytes;
         T* orow = static_cast<T*>(p.out) + row * p.D;
         if constexpr (OP == kRmsFwd && KMAX > 0) {
@@ -253,9 +257,11 @@ rowpipe_kernel(const Params p) {
           }
         } else if constexpr (OP == kRmsBwd) {
           // pass 1: sum x^2 and sum (dy*w)*x, two lanes of float32 at a time
+          // (a row may be shared by p.wpr warps, each with a contiguous segment of its vectors)
+          const int vseg = nvec / p.wpr, v_begin = seg * vseg, v_end = v_begin + vseg;
           float2 ss2 = f2(0.0f, 0.0f), gx2 = f2(0.0f, 0.0f);
 #pragma unroll 4
-          for (int vi = lane; vi < nvec; vi += 32) {
+          for (int vi = v_begin + lane; vi < v_end; vi += 32) {
             V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
             b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
             float x[N], g[N]; a.to_float(x); b.to_float(g);
@@ -274,8 +280,16 @@ rowpipe_kernel(const Params p) {
               gx2 = __ffma2_rn(g1, x1, gx2);
             }
           }
-          const float ss = warp_sum(ss2.x + ss2.y);
-          const float gx = warp_sum(gx2.x + gx2.y);
+          float ss = warp_sum(ss2.x + ss2.y);
+          float gx = warp_sum(gx2.x + gx2.y);
+          if (p.wpr > 1) {
+            // the row's warps exchange their sums through shared memory and add them in segment order
+            if (lane == 0) xch[rit][seg] = f2(ss, gx);
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rit), "r"(p.wpr * 32) : "memory");
+            ss = 0.0f; gx = 0.0f;
+            for (int q2 = 0; q2 < p.wpr; ++q2) { ss += xch[rit][q2].x; gx += xch[rit][q2].y; }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rit), "r"(p.wpr * 32) : "memory");
+          }
           const float rinv = 1.0f / sqrtf(ss * inv_d + p.eps);
           const float c = gx * rinv * inv_d;
           const float2 r2 = f2(rinv, rinv), nc2 = f2(-c, -c);
@@ -303,11 +317,11 @@ rowpipe_kernel(const Params p) {
           if constexpr (kDw) {
 #pragma unroll
             for (int k = 0; k < KMAX; ++k) {
-              const int vi = lane + 32 * k;
-              if (vi < nvec) body(vi, dwa[k]);
+              const int vi = v_begin + lane + 32 * k;
+              if (vi < v_end) body(vi, dwa[k]);
             }
           } else {
-            for (int vi = lane; vi < nvec; vi += 32) body(vi, nullptr);
+            for (int vi = v_begin + lane; vi < v_end; vi += 32) body(vi, nullptr);
           }
         } else if constexpr (OP == kSmFwd && KMAX > 0) {
           const bool causal = p.causal_seq > 0;
@@ -484,20 +498,21 @@ rowpipe_kernel(const Params p) {
     __syncthreads();
     float* red = reinterpret_cast<float*>(gen_base);
     if (warp < W) {
+      const int rit = warp / p.wpr, seg = warp - rit * p.wpr;
+      const int vseg = p.nvec / p.wpr, v_begin = seg * vseg, v_end = v_begin + vseg;
 #pragma unroll
       for (int k = 0; k < KMAX; ++k) {
-        const int vi = lane + 32 * k;
-        if (vi < p.nvec) {
+        const int vi = v_begin + lane + 32 * k;
+        if (vi < v_end) {
 #pragma unroll
-          for (int j = 0; j < N; ++j) red[warp * p.D + vi * N + j] = dwa[k][j];
+          for (int j = 0; j < N; ++j) red[rit * p.D + vi * N + j] = dwa[k][j];
         }
       }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < p.D; c += blockDim.x) {
       float s = 0.0f;
-#pragma unroll
-      for (int w = 0; w < W; ++w) s += red[w * p.D + c];
+      for (int w = 0; w < R; ++w) s += red[w * p.D + c];
       p.dw_part[static_cast<int64_t>(blockIdx.x) * p.D + c] = s;
     }
   }
@@ -560,11 +575,24 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
     const int s = static_cast<int>(budget / stage_bytes);
     if (s >= 3) { W = cand; stages = s > kMaxStages ? kMaxStages : s; break; }
   }
+  if (W == 0 && op == kRmsBwd && budget / (2 * row_bytes * n_streams) >= 2) {
+    // very wide rows: two rows per stage, two stages, four warps per row (below)
+    W = 2;
+    stages = 2;
+  }
   // One warp per row only pays while enough warps fit: forward ops (one input stream, more arithmetic per
   // byte) want at least 8 rows per tile, backward ops at least 4; wider rows go to the register kernels.
-  if (W < (n_streams == 1 ? 8 : 4) || rows < 4 * W) return 1;
-  if (causal_seq > 0 && causal_seq < W) return 1;
   const int nvec = static_cast<int>(D / N);
+  // The RMSNorm backward of very wide rows (only 2 rows fit a stage) gives every row 4 warps, each with a
+  // contiguous segment of the row; the warps of a row exchange their two sums through shared memory.
+  // (Measured: at 4 rows per stage, 2 warps per row are slower than one.)
+  int wpr = 1, R = W;   // warps per row, rows per tile
+  if (op == kRmsBwd && W == 2 && nvec % 4 == 0) {
+    wpr = 4;
+    W = 8;
+  }
+  if (W < (n_streams == 1 ? 8 : 4) || rows < 4 * R) return 1;
+  if (causal_seq > 0 && causal_seq < W) return 1;
   int kmax = 0;
   if (op == kRmsFwd || op == kSmFwd) {
     const int need = (nvec + 31) / 32;  // register-resident rows of up to 8 vectors per lane
@@ -576,18 +604,19 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
       stages = sN > kMaxStages ? kMaxStages : sN;
     }
   }
+  if (op != kRmsBwd) R = W;
   if (dw_part != nullptr) {
-    const int need = (nvec + 31) / 32;
+    const int need = (nvec / wpr + 31) / 32;
     kmax = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : 0;
     if (kmax == 0) return 1;
-    if (static_cast<int64_t>(W) * D * 4 > static_cast<int64_t>(stages) * W * row_bytes * n_streams) return 1;
+    if (static_cast<int64_t>(R) * D * 4 > static_cast<int64_t>(stages) * R * row_bytes * n_streams) return 1;
   }
   Params p;
   p.in0 = in0; p.in1 = in1; p.w = w; p.out = out; p.rstd = rstd; p.dw_part = dw_part;
   p.rows = rows; p.D = static_cast<int>(D); p.nvec = nvec; p.row_bytes = static_cast<int>(row_bytes);
-  p.stages = stages; p.n_streams = n_streams; p.causal_seq = causal_seq; p.eps = eps; p.scale = scale;
+  p.stages = stages; p.n_streams = n_streams; p.wpr = wpr; p.causal_seq = causal_seq; p.eps = eps; p.scale = scale;
   p.status = ds->status_word;
-  p.stage_bytes = static_cast<uint32_t>(W * row_bytes * n_streams);
+  p.stage_bytes = static_cast<uint32_t>(R * row_bytes * n_streams);
   p.bar_off = (static_cast<uint32_t>(stages) * p.stage_bytes + 127u) & ~127u;
   size_t smem = p.bar_off + 16 * kMaxStages + 16 + 128;
   p.w_off = 0;
@@ -595,7 +624,7 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
     p.w_off = static_cast<uint32_t>((smem + 15) & ~static_cast<size_t>(15));
     smem = p.w_off + static_cast<size_t>(D) * 4 + 128;
   }
-  const int64_t n_tiles = (rows + W - 1) / W;
+  const int64_t n_tiles = (rows + R - 1) / R;
   int grid = 2 * ds->sm_count;
   if (grid > n_tiles) grid = static_cast<int>(n_tiles);
   if (dw_blocks) *dw_blocks = grid;
