@@ -185,29 +185,38 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
   }
 }
 
-// out (+)= sum over slices, in slice order, for both problems in one launch.  One thread per (feature c, rank
-// column j < rp); reads are contiguous across the block.  transposed == 0 writes out[c*r + j] (dA [K,r]);
+// out (+)= sum over slices (fixed order: deterministic), for both problems in one launch.  A CTA owns 32
+// consecutive (feature, rank column) pairs of one problem; its 8 warps each sum every 8th slice (independent,
+// coalesced loads), then warp 0 adds the 8 sums in warp order.  transposed == 0 writes out[c*r + j] (dA [K,r]);
 // 1 writes out[j*C + c] (dB [r,N]).
 struct ReduceProblem {
   const float* part;
   float* out;
   int slices, C, transposed;
 };
-__global__ void lora_grad_reduce_kernel(ReduceProblem a, ReduceProblem b, int r, int rp, int accumulate) {
-  int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t na = static_cast<int64_t>(a.C) * rp;
-  const bool second = tid >= na;
+__global__ void __launch_bounds__(256)
+lora_grad_reduce_kernel(ReduceProblem a, ReduceProblem b, int blocks_a, int r, int rp, int accumulate) {
+  __shared__ float red[8][32];
+  const bool second = static_cast<int>(blockIdx.x) >= blocks_a;
   const ReduceProblem q = second ? b : a;
-  if (second) tid -= na;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n = static_cast<int64_t>(q.C) * rp;
-  if (tid >= n) return;
-  const int c = static_cast<int>(tid / rp), j = static_cast<int>(tid % rp);
-  if (j >= r) return;
+  const int64_t e = (static_cast<int64_t>(blockIdx.x) - (second ? blocks_a : 0)) * 32 + lane;   // index into [C][rp]
   float s = 0.0f;
-#pragma unroll 8
-  for (int sp = 0; sp < q.slices; ++sp) s += q.part[static_cast<int64_t>(sp) * n + tid];
+  if (e < n) {
+#pragma unroll 4
+    for (int sp = warp; sp < q.slices; sp += 8) s += q.part[static_cast<int64_t>(sp) * n + e];
+  }
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp != 0 || e >= n) return;
+  float t = 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) t += red[w][lane];
+  const int c = static_cast<int>(e / rp), j = static_cast<int>(e % rp);
+  if (j >= r) return;
   const int64_t o = q.transposed ? static_cast<int64_t>(j) * q.C + c : static_cast<int64_t>(c) * r + j;
-  q.out[o] = accumulate ? q.out[o] + s : s;
+  q.out[o] = accumulate ? q.out[o] + t : t;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -558,8 +567,8 @@ int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, 
   MCB_CHECK_LAUNCH("lora_grad_umma_kernel");
   ReduceProblem ra = {p.pr[0].part, out0, p.pr[0].slices, static_cast<int>(Cs[0]), transposed0};
   ReduceProblem rb = {np == 2 ? p.pr[1].part : nullptr, out1, np == 2 ? p.pr[1].slices : 0, static_cast<int>(Cs[1]), transposed1};
-  const int64_t n = (Cs[0] + Cs[1]) * rp;
-  lora_grad_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(ra, rb, r, rp, accumulate);
+  const int blocks_a = static_cast<int>((Cs[0] * rp + 31) / 32), blocks_b = static_cast<int>((Cs[1] * rp + 31) / 32);
+  lora_grad_reduce_kernel<<<static_cast<unsigned>(blocks_a + blocks_b), 256, 0, st>>>(ra, rb, blocks_a, r, rp, accumulate);
   MCB_CHECK_LAUNCH("lora_grad_reduce");
   return MCB_OK;
 }

@@ -216,7 +216,8 @@ def _count_launches(cfg, wl) -> int:
     per_layer_fwd = 2 + (5 if fused_mlp else 8) + n_lora + 4 + 1
     # backward: 7 GEMMs, packs, dA/dB (gradient + reduce each), swiglu, 2 norms, 4 rope/relayout,
     # attention (dq + dkv kernels, or one softmax), 2 residual-gradient adds
-    per_layer_bwd = 7 + n_lora + 4 * n_lora + 1 + 2 + 4 + (2 if fused_attn else 1) + 2
+    # (dA and dB of an adapter come from one gradient launch plus one partial-sum launch)
+    per_layer_bwd = 7 + n_lora + 2 * n_lora + 1 + 2 + 4 + (2 if fused_attn else 1) + 2
     tail = 1 + 1 + 1 + 3 + 1 + 1  # embed, norm, lm_head, CE x3, lm_head bwd, norm bwd
     adamw = math.ceil(2 * n_lora * L / 64)
     return L * (per_layer_fwd + per_layer_bwd) + tail + adamw
