@@ -9,7 +9,7 @@
 //
 // Forward: one CTA per (128 queries, head); key blocks of 64.  Warp 0 streams K / V tiles by TMA into a
 // two-stage ring, warp 1 issues the tensor-core MMAs (S = Q K^T into tensor memory, then O_blk = P V),
-// warps 2-5 do the online softmax with one query row per thread: read S from tensor memory, rescale, write
+// warps 2-5 do the online softmax with one query row per thread: read S from tensor memory (once), rescale, write
 // P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout; O accumulates in tensor
 // memory and is rescaled there (tcgen05.ld / tcgen05.st) only when a row maximum has grown by more than
 // 2^8.  S is double-buffered in tensor memory, so the next block's Q K^T runs under this block's softmax;
@@ -186,27 +186,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t tS = tmem_base + (j & 1) * 64;
       const int key0 = j * kBK;
       const bool diag = key0 + kBK - 1 > qb * kBQ;  // some element of this block may lie above the diagonal
-      // pass 1: row maximum of the raw scores
-      float mx = -INFINITY;
-      if (!diag) {
+      // the row's 64 scores of this block, read from tensor memory once (four loads in flight, one wait)
+      uint32_t sv[4][16];
 #pragma unroll
-        for (int c = 0; c < kBK; c += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(tS + lane_addr + c, v);
-          tmem_ld_wait();
+      for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tS + lane_addr + 16 * c4, sv[c4]);
+      tmem_ld_wait();
+      if (diag) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        }
-      } else {
+        for (int c4 = 0; c4 < 4; ++c4)
 #pragma unroll
-        for (int c = 0; c < kBK; c += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(tS + lane_addr + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) mx = fmaxf(mx, key0 + c + e <= qpos ? __uint_as_float(v[e]) : -INFINITY);
-        }
+          for (int e = 0; e < 16; ++e)
+            if (key0 + 16 * c4 + e > qpos) sv[c4][e] = 0xff800000u;   // -inf
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[0][e]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[1][e]));
+        mx2 = fmaxf(mx2, __uint_as_float(sv[2][e]));
+        mx3 = fmaxf(mx3, __uint_as_float(sv[3][e]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_true = fmaxf(m, mx * p.sc);  // key 0 is never masked, so this is finite from block 0 on
       const bool raise = m_true > m + 8.0f;       // block 0: m = -inf, always
       if (j > 0) {
@@ -232,27 +232,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l *= alpha;
         m = m_true;
       }
-      // pass 2: P = 2^(s*sc - m), row sum, bf16 into the swizzled operand buffer
+      // P = 2^(s*sc - m) (masked scores are -inf and give 0), row sum, bf16 into the swizzled operand buffer
       float ls0 = 0.0f, ls1 = 0.0f;
 #pragma unroll
-      for (int c = 0; c < kBK; c += 16) {
-        uint32_t v[16];
-        tmem_ld_x16(tS + lane_addr + c, v);
-        tmem_ld_wait();
+      for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t w[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(v[e]), p.sc, -m));
-          float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), p.sc, -m));
-          if (diag) {
-            if (key0 + c + e > qpos) p0 = 0.0f;
-            if (key0 + c + e + 1 > qpos) p1 = 0.0f;
-          }
+          const float p0 = ex2(fmaf(__uint_as_float(sv[c4][e]), p.sc, -m));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[c4][e + 1]), p.sc, -m));
           ls0 += p0;
           ls1 += p1;
           w[e >> 1] = pack_bf16(p0, p1);
         }
-        const int cc = c >> 3;  // 16-byte chunk index of columns c .. c+7
+        const int cc = c4 * 2;  // 16-byte chunk index of columns 16*c4 .. 16*c4+7
         *reinterpret_cast<uint4*>(prow + (((cc) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(prow + (((cc + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
       }
