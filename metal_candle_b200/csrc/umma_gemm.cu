@@ -184,7 +184,10 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       bool ok = true;
       int i = 0;
       // The rank update of a tile needs the epilogue warps to turn its rank accumulator into the bf16 operand
-      // first (a short wait: measured, deferring the update behind the next tile's main loop gains nothing).
+      // first (about a microsecond: barrier, tensor-memory load, conversion, barrier).  Instead of waiting, this
+      // thread goes on with the next tile's main loop in the other accumulator buffer and polls between
+      // k-blocks; the update is issued as soon as its operands are there.  (Deferring it behind the WHOLE next
+      // main loop gains nothing: the accumulator then stays occupied for an epilogue longer.)
       int pend_a = -1;
       uint32_t pend_u = 0;
       auto finish_pending = [&]() -> bool {
@@ -226,18 +229,26 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           }
           umma_commit(b.empty0 + 8 * stage);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (pend_a >= 0 && mbar_try_wait(b.h_ready0 + 8 * pend_a, pend_u & 1) &&
+              mbar_try_wait(b.q_full0 + 8 * pend_a, pend_u & 1)) {
+            ok = finish_pending();   // both operands are there: does not wait
+            if (!ok) break;
+          }
         }
         if (!ok) break;
         if (p.rp > 0) {
           umma_commit(b.d2_full0 + 8 * a);
+          if (pend_a >= 0) {         // the previous tile's update has still not been issued: wait for it now
+            ok = finish_pending();
+            if (!ok) break;
+          }
           pend_a = a;
           pend_u = u;
-          ok = finish_pending();
-          if (!ok) break;
         } else {
           umma_commit(b.d1_full0 + 8 * a);
         }
       }
+      if (ok && pend_a >= 0) ok = finish_pending();
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------

@@ -216,6 +216,31 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       int i = 0;
+      // The rank update of a tile waits for the epilogue warps of both CTAs to turn the rank accumulator into the
+      // bf16 operand.  Meanwhile this thread goes on with the next tile's main loop in the other accumulator
+      // buffer and polls between k-blocks; the update is issued as soon as its operands are there.
+      int pend_a = -1;
+      uint32_t pend_u = 0;
+      auto finish_pending = [&]() -> bool {
+        const int pa = pend_a;
+        pend_a = -1;
+        if (!mbar_wait(h_ready0 + 8 * pa, pend_u & 1, abort_flag, 65, p.status)) return false;
+        if (!mbar_wait(q_full0 + 8 * pa, pend_u & 1, abort_flag, 66, p.status)) return false;
+        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+        tcgen05_fence_after();
+        const uint32_t pd = tmem_base + pa * 256;
+        const uint32_t hs = base + p.hs_off + pa * p.hs_bytes;
+        const uint32_t qs = base + p.q_off + pa * p.q_bytes;
+        for (int kk = 0; kk < p.rp / 16; ++kk) {
+          const uint64_t hd = desc_noswz(hs + kk * 2 * (128 * 16), 128 * 16, 128);
+          const uint64_t q0 = desc_noswz(qs + kk * 2 * (quarter_n * 16), quarter_n * 16, 128);
+          const uint64_t q1 = desc_noswz(qs + p.q_bytes / 2 + kk * 2 * (quarter_n * 16), quarter_n * 16, 128);
+          umma2_bf16(pd, hd, q0, idesc_half, 1u);
+          umma2_bf16(pd + half_n + half_r, hd, q1, idesc_half, 1u);
+        }
+        umma2_commit_both(d1_full0 + 8 * pa);
+        return true;
+      };
       for (int t = pair; ok && t < p.num_tiles; t += npairs, ++i) {
         const int a = i & 1;
         const uint32_t u = static_cast<uint32_t>(i >> 1);
@@ -233,28 +258,26 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             umma2_bf16(d, desc_sw128(sb + k4 * 32), desc_sw128(sb + p.w_off + k4 * 32), idesc, (kb | k4) != 0 ? 1u : 0u);
           umma2_commit_both(empty0 + 8 * stage);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (pend_a >= 0 && mbar_try_wait(h_ready0 + 8 * pend_a, pend_u & 1) &&
+              mbar_try_wait(q_full0 + 8 * pend_a, pend_u & 1)) {
+            ok = finish_pending();   // both operands are there: does not wait
+            if (!ok) break;
+          }
         }
         if (!ok) break;
         if (p.rp > 0) {
           umma2_commit_both(d2_full0 + 8 * a);
-          ok = mbar_wait(h_ready0 + 8 * a, u & 1, abort_flag, 65, p.status);
-          if (!ok) break;
-          ok = mbar_wait(q_full0 + 8 * a, u & 1, abort_flag, 66, p.status);
-          if (!ok) break;
-          asm volatile("fence.acq_rel.cluster;" ::: "memory");
-          tcgen05_fence_after();
-          const uint32_t hs = base + p.hs_off + a * p.hs_bytes;
-          const uint32_t qs = base + p.q_off + a * p.q_bytes;
-          for (int kk = 0; kk < p.rp / 16; ++kk) {
-            const uint64_t hd = desc_noswz(hs + kk * 2 * (128 * 16), 128 * 16, 128);
-            const uint64_t q0 = desc_noswz(qs + kk * 2 * (quarter_n * 16), quarter_n * 16, 128);
-            const uint64_t q1 = desc_noswz(qs + p.q_bytes / 2 + kk * 2 * (quarter_n * 16), quarter_n * 16, 128);
-            umma2_bf16(d, hd, q0, idesc_half, 1u);
-            umma2_bf16(d + half_n + half_r, hd, q1, idesc_half, 1u);
+          if (pend_a >= 0) {         // the previous tile's update has still not been issued: wait for it now
+            ok = finish_pending();
+            if (!ok) break;
           }
+          pend_a = a;
+          pend_u = u;
+        } else {
+          umma2_commit_both(d1_full0 + 8 * a);
         }
-        umma2_commit_both(d1_full0 + 8 * a);
       }
+      if (ok && pend_a >= 0) ok = finish_pending();
     }
   } else {
     // ---------------- epilogue (warps 2..5, both CTAs): own 128 rows of the pair's tile ----------------
@@ -440,9 +463,10 @@ int init_gemm2_kernel() {
 bool gemm2_eligible(const GemmCall& c) {
   if (c.W == nullptr || c.Y == nullptr || c.M < 1024 || c.N < 128 || c.K < 64) return false;
   if (c.rp == 0) return true;
-  // The rank update costs a pair more per tile (its operand hand-over crosses the two CTAs) than it costs
-  // one CTA; measured, the pair wins once a tile's main loop is longer than about 1500 reduction elements
-  // (8192x4096x4096 r16: 1168 against 1039 TFLOP/s forward; 32768x896x896 r16: 817 against 894).
+  // Short reductions stay on the one-CTA kernel.  Alone, the pair is a little ahead even there once the rank
+  // update is issued between the next tile's k-blocks (32768x896x896 r16 forward 953 against 922 TFLOP/s), but
+  // inside the training step, with its k/v projections of 128 outputs and its backward calls, the one-CTA kernel
+  // measured 1-2 % faster per step on the same box (116.1-118.5 against 118.4-119.5 ms).
   return c.rp % 16 == 0 && c.rp <= 64 && c.K >= 1536;
 }
 
