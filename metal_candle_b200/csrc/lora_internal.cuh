@@ -42,6 +42,7 @@ int matmul(const float* a, const float* b, float* out, int64_t M, int64_t K, int
 }  // namespace f32path
 
 namespace bf16path {
+struct GradRequest;
 // One call of the fused GEMM  Y = X W^T (+bias) (+R) + (scale X P^T) Q^T ; all operands bf16, K-major.
 struct GemmCall {
   const __nv_bfloat16* X = nullptr;   // [M,K]
@@ -57,6 +58,9 @@ struct GemmCall {
   int rp = 0;
   int r_true = 0;  // unpadded rank, for the algorithmic flop count
   float scale = 1.0f;
+  // Weight-gradient problems to run as a tail phase of the same launch (one-CTA kernel only), or null.  Problem 0
+  // reads the H this call writes.
+  const GradRequest* grads = nullptr;
 };
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a, const DeviceState* ds);

@@ -21,12 +21,17 @@
 // Two accumulator buffers (256 columns each: BN main + rp rank columns) let the epilogue of tile i
 // overlap the main loop of tile i+1.
 //
+// In the backward the same launch can go on to the LoRA weight gradients: once a CTA has no tiles left it
+// takes a token slice of dA = x^T H or dB = h^T dy (the tail phase, grad_phase.cuh), waiting per 128-token tile
+// for the H rows that the n-tile-0 CTAs of this launch publish.
+//
 // Every wait on an mbarrier is bounded (about two seconds); a wait that runs out records a code in
 // the device status word, raises a CTA-wide abort flag, and all roles fall through to the common
 // exit where tensor memory is released.  No loads use cluster multicast.
 #include <cuda.h>
 #include <string.h>
 
+#include "grad_phase.cuh"
 #include "lora_internal.cuh"
 #include "umma_ptx.cuh"
 
@@ -62,6 +67,7 @@ struct GemmParams {
   const __nv_bfloat16* R;   // [M,N] added to the output (residual / gradient accumulation), or null
   __nv_bfloat16* H;   // [rp, h_pitch]: scale * X P^T, transposed (token index contiguous), or null
   int64_t h_pitch;
+  int* h_flags;       // per m-tile count of epilogue warps that have stored their H rows (tail phase), or null
   int* status;
   uint32_t stage_bytes, w_off, p_off;        // within a stage
   uint32_t q_off, q_bytes, hs_off, hs_bytes; // from the aligned base
@@ -89,7 +95,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                  const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                  const __grid_constant__ CUtensorMap tmY,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmGX0, const __grid_constant__ CUtensorMap tmGH0,
+                 const __grid_constant__ CUtensorMap tmGX1, const __grid_constant__ CUtensorMap tmGH1,
+                 const GemmParams p, const GradParams g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -298,8 +306,17 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
         fence_proxy_async_smem();
         tcgen05_fence_before();
+        if (p.h_flags != nullptr && nt == 0) {
+          // the tail phase of other CTAs reads these rows of H with TMA copies: publish them
+          __threadfence();
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         __syncwarp();
-        if (lane == 0) mbar_arrive(b.h_ready0 + 8 * a);
+        if (lane == 0) {
+          mbar_arrive(b.h_ready0 + 8 * a);
+          if (p.h_flags != nullptr && nt == 0)
+            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.h_flags + mt) : "memory");
+        }
       }
       ok = __all_sync(0xffffffffu, mbar_wait(b.d1_full0 + 8 * a, u & 1, abort_flag, 32, p.status));
       if (!ok) break;
@@ -389,6 +406,34 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   }
   tcgen05_fence_before();
   __syncthreads();
+  // ---------------- tail phase: the LoRA weight gradients of the same linear ----------------
+  // Every role is through with the tiles: the stage ring, the staging buffers and tensor memory are free.  The
+  // CTA now takes a token slice of dA = x^T H or dB = h^T dy (grad_phase.cuh) with a fresh set of barriers behind
+  // the ones used so far.  H rows written by other CTAs of this launch are awaited per 128-token tile.
+  if (g.n_cta > 0 && *abort_flag == 0) {
+    GradShared sh;
+    sh.base = base;
+    sh.full0 = base + p.bar_off + 256;
+    sh.empty0 = sh.full0 + 8 * kGradMaxStages;
+    sh.done_bar = sh.empty0 + 8 * kGradMaxStages;
+    sh.tmem_base = tmem_base;
+    sh.abort_flag = abort_flag;
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kGradMaxStages; ++s) { mbar_init(sh.full0 + 8 * s, 1); mbar_init(sh.empty0 + 8 * s, 1); }
+      mbar_init(sh.done_bar, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      fence_proxy_async_smem();
+    }
+    __syncthreads();
+    tcgen05_fence_after();
+    if (static_cast<int>(blockIdx.x) < g.n_cta) grad_roles(g, &tmGX0, &tmGH0, &tmGX1, &tmGH1, sh, static_cast<int>(blockIdx.x));
+    __syncwarp();
+    if (*abort_flag != 0) {
+      for (int k = 0; k < 200; ++k) __nanosleep(1000);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+  }
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -400,10 +445,13 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 // from r to rp rows/columns.
 //   forward  (mode 0): P = A^T [rp,K],  Q = B^T [N,rp]
 //   backward (mode 1): P = B   [rp,N],  Q = A   [K,rp]
+// and zeroes `n_flags` counters.
 __global__ void pack_lora_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                  __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Q, int K, int N, int r,
-                                 int rp, int mode) {
+                                 int rp, int mode, int* __restrict__ flags, int n_flags) {
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // the per-tile counters of the backward kernel's tail phase start from zero in every call
+  for (int64_t i = tid; i < n_flags; i += static_cast<int64_t>(gridDim.x) * blockDim.x) flags[i] = 0;
   const int64_t nP = static_cast<int64_t>(rp) * (mode == 0 ? K : N);
   const int64_t nQ = static_cast<int64_t>(rp) * (mode == 0 ? N : K);
   if (tid < nP) {
@@ -520,22 +568,50 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     if (int rc = make_map(ds, &tmQ, c.Q, p.rp, c.N, 8, p.BN, 0, "Q")) return rc;
   } else { tmP = tmX; tmQ = tmX; }
   const int grid = p.num_tiles < ds->sm_count ? p.num_tiles : ds->sm_count;
+  // the weight gradients as a tail phase: the same CTAs, the stage ring re-cut for token rows
+  GradPlan tail;
+  memset(&tail.p, 0, sizeof(tail.p));
+  bool tail_on = c.grads != nullptr;
+  if (tail_on) {
+    const uint32_t budget = p.bar_off < static_cast<uint32_t>(kGradSmemBudget) ? p.bar_off : static_cast<uint32_t>(kGradSmemBudget);
+    if (int rc = plan_grad2(*c.grads, c.M, c.rp, grid, budget, ds, &tail)) return rc;
+    // a grid of a single CTA cannot hold both problems: the gradients then take their own launch below
+    if (tail.p.n_cta > grid) tail_on = false;
+  }
+  if (tail_on) {
+    p.h_flags = c.grads->h_flags;
+  } else {
+    memset(&tail.p, 0, sizeof(tail.p));
+    tail.tmX[0] = tail.tmX[1] = tail.tmH[0] = tail.tmH[1] = tmX;
+  }
   const bool prof = profile_on();
   if (prof) {
     const double m = static_cast<double>(c.M), n = static_cast<double>(c.N), k = static_cast<double>(c.K);
-    const double flops = (p.has_w ? 2.0 * m * n * k : 0.0) + 2.0 * m * c.r_true * (k + n);
-    const double bytes = 2.0 * (m * k + (p.has_w ? n * k : 0.0) + (c.Y ? m * n : 0.0)) + 2.0 * p.rp * (k + n);
+    double flops = (p.has_w ? 2.0 * m * n * k : 0.0) + 2.0 * m * c.r_true * (k + n);
+    double bytes = 2.0 * (m * k + (p.has_w ? n * k : 0.0) + (c.Y ? m * n : 0.0)) + 2.0 * p.rp * (k + n);
+    if (tail_on) {
+      flops += 2.0 * m * (c.grads->C[0] + c.grads->C[1]) * c.r_true;
+      bytes += 2.0 * m * (c.grads->C[0] + c.grads->C[1]) + 4.0 * m * c.rp;
+    }
     profile_begin(kProfGemm, flops, bytes, st);
   }
-  lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, p);
+  lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, tail.tmX[0], tail.tmH[0], tail.tmX[1],
+                                                                tail.tmH[1], p, tail.p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm_kernel");
+  if (tail_on) return launch_grad_reduce(tail, st);
+  if (c.grads != nullptr) {
+    const GradRequest& q = *c.grads;
+    return launch_grad2(q.X[0], q.Ht[0], q.C[0], q.out[0], q.transposed[0], q.X[1], q.Ht[1], q.C[1], q.out[1], q.transposed[1],
+                        q.h_pitch, q.part, c.M, q.r, c.rp, q.accumulate, ds, st);
+  }
   return MCB_OK;
 }
 
 struct Workspace {
   __nv_bfloat16 *P, *Q, *H1, *H2;
   float* part;
+  int* flags;   // one counter per 128-token tile
   size_t total;
 };
 Workspace carve(void* ws, int64_t M, int64_t K, int64_t N, int64_t r) {
@@ -550,6 +626,7 @@ Workspace carve(void* ws, int64_t M, int64_t K, int64_t N, int64_t r) {
   w.H1 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(h_pitch(M)) * rp * 2));
   w.H2 = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(h_pitch(M)) * rp * 2));
   w.part = reinterpret_cast<float*>(take(grad_partial_bytes(M, K, N, static_cast<int>(rp))));
+  w.flags = reinterpret_cast<int*>(take(static_cast<size_t>((M + BM - 1) / BM) * sizeof(int)));
   w.total = off;
   return w;
 }
@@ -558,7 +635,8 @@ int pack(const LoraArgs& a, const Workspace& w, int mode) {
   const int rp = static_cast<int>(rank_padded(a.r));
   const int64_t n = static_cast<int64_t>(rp) * (a.K + a.N);
   pack_lora_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, a.stream>>>(
-      a.A, a.B, w.P, w.Q, static_cast<int>(a.K), static_cast<int>(a.N), static_cast<int>(a.r), rp, mode);
+      a.A, a.B, w.P, w.Q, static_cast<int>(a.K), static_cast<int>(a.N), static_cast<int>(a.r), rp, mode,
+      mode == 1 ? w.flags : nullptr, mode == 1 ? static_cast<int>((a.M + BM - 1) / BM) : 0);
   MCB_CHECK_LAUNCH("pack_lora");
   return MCB_OK;
 }
@@ -638,6 +716,10 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
     w = carve(a.ws, a.M, a.K, a.N, a.r);
     if (int rc = pack(a, w, 1)) return rc;
   }
+  // Both gradients asked for, the forward's rank intermediate at hand and shapes of one feature group each: dA and
+  // dB are accumulated by the CTAs of the dx kernel themselves, as its tail phase (one launch instead of two).
+  GradRequest rq;
+  bool fused_grads = false;
   if (a.dx != nullptr || want_grads) {
     // dx = dy W + (scale dy B^T) A^T ; the rank intermediate scale*dy*B^T lands in w.H1 for dA.
     GemmCall c;
@@ -654,11 +736,21 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
       c.r_true = static_cast<int>(a.r);
       c.scale = a.scale;
     }
+    if (a.dA != nullptr && a.dB != nullptr && a.h_save != nullptr && !gemm2_eligible(c) &&
+        grad_tail_possible(a.K, a.N, rp)) {
+      rq.X[0] = static_cast<const __nv_bfloat16*>(a.x);  rq.Ht[0] = w.H1; rq.C[0] = a.K; rq.out[0] = a.dA; rq.transposed[0] = 0;
+      rq.X[1] = static_cast<const __nv_bfloat16*>(a.dy); rq.Ht[1] = static_cast<const __nv_bfloat16*>(a.h_save);
+      rq.C[1] = a.N; rq.out[1] = a.dB; rq.transposed[1] = 1;
+      rq.h_pitch = h_pitch(a.M); rq.part = w.part; rq.r = static_cast<int>(a.r); rq.accumulate = a.accumulate;
+      rq.h_flags = w.flags;
+      c.grads = &rq;
+      fused_grads = true;
+    }
     if (c.W != nullptr || c.rp > 0) {
       if (int rc = launch_gemm(c, ds, a.stream)) return rc;
     }
   }
-  if (!want_grads) return MCB_OK;
+  if (!want_grads || fused_grads) return MCB_OK;
   const __nv_bfloat16* hs = nullptr;
   if (a.dB != nullptr) {
     hs = static_cast<const __nv_bfloat16*>(a.h_save);

@@ -20,6 +20,7 @@
 #include <cuda.h>
 #include <string.h>
 
+#include "grad_phase.cuh"
 #include "lora_internal.cuh"
 #include "umma_ptx.cuh"
 
@@ -29,32 +30,6 @@ using namespace umma;
 namespace {
 
 constexpr int kGradThreads = 192;
-constexpr int kGradMaxStages = 8;
-constexpr int kGradGroup = 1024;               // features per CTA at most (8 tiles of 128)
-constexpr int kGradSmemBudget = 208 * 1024;
-
-struct GradProblem {
-  int C, groups, slices, tiles;   // features, feature groups, token slices, 128-feature tiles per group
-  int group_feats;                // features per group (a multiple of 128)
-  float* part;                    // [slices][C][rp]
-};
-struct GradParams {
-  int M, rp;                      // tokens, padded rank
-  int T[2];                       // tokens per stage of each problem (a multiple of 16, at most 256)
-  int stages[2];                  // stage ring depth of each problem
-  int n_cta0;                     // CTAs of problem 0 (the rest belong to problem 1)
-  GradProblem pr[2];
-  int* status;
-  uint32_t x_bytes[2], bar_off;   // X bytes per stage of each problem; H follows at x_bytes
-  uint32_t stage_stride[2];
-};
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
 
 __global__ void __launch_bounds__(kGradThreads)
 lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmH0,
@@ -69,14 +44,8 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
-  // which problem, feature group and token slice this CTA has
-  const int which = static_cast<int>(blockIdx.x) >= p.n_cta0 ? 1 : 0;
-  const GradProblem& q = p.pr[which];
-  const int local = static_cast<int>(blockIdx.x) - (which ? p.n_cta0 : 0);
-  const int group = local % q.groups, slice = local / q.groups;
-  const CUtensorMap* tmX = which ? &tmX1 : &tmX0;
-  const CUtensorMap* tmH = which ? &tmH1 : &tmH0;
-  const int acc_cols = q.tiles * p.rp;
+  // tensor-memory columns for this CTA's problem: one [128 x rp] accumulator per 128-feature tile of a group
+  const int acc_cols = p.pr[static_cast<int>(blockIdx.x) >= p.n_cta0 ? 1 : 0].tiles * p.rp;
   const uint32_t tmem_cols = acc_cols <= 32 ? 32u : acc_cols <= 64 ? 64u : acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
 
   if (threadIdx.x == 0) {
@@ -95,84 +64,10 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  // token steps of T tokens, split evenly over the slices
-  const int T = p.T[which];
-  const int n_stages = p.stages[which];
-  const uint32_t stride = p.stage_stride[which];
-  const int total_steps = (p.M + T - 1) / T;
-  const int per = (total_steps + q.slices - 1) / q.slices;
-  const int step_begin = slice * per;
-  const int step_end = min(total_steps, step_begin + per);
-  const int nsteps = max(0, step_end - step_begin);
-  const uint32_t xb = p.x_bytes[which];
-  const uint32_t atom_bytes = static_cast<uint32_t>(T) * 128;   // one 64-feature atom of a stage: T rows of 128 bytes
-
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int s = step_begin; s < step_end; ++s) {
-        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, 41, p.status)) break;
-        const uint32_t fb = full0 + 8 * stage, sb = base + stage * stride;
-        mbar_expect_tx(fb, xb + static_cast<uint32_t>(p.rp) * T * 2);
-        // X: [64 features][T tokens][atoms of the group]; in shared memory atom-major blocks of T rows x 128 bytes
-        tma_load_3d(sb, tmX, fb, 0, s * T, group * (q.group_feats / 64));
-        // H^T: K-major B operand, unswizzled 16-byte columns of 8 tokens each
-        for (int j = 0; j < T / 8; ++j) tma_load_2d(sb + xb + j * p.rp * 16, tmH, fb, s * T + j * 8, 0);
-        if (++stage == n_stages) { stage = 0; phase ^= 1; }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_a_mn(p.rp);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int i = 0; i < nsteps; ++i) {
-        ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, 42, p.status);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t sb = base + stage * stride;
-        for (int k16 = 0; k16 < T / 16; ++k16) {
-          // B: 16 tokens further = two 16-byte columns of rp rows
-          const uint64_t bd = desc_noswz(sb + xb + k16 * 2 * (p.rp * 16), p.rp * 16, 128);
-          for (int f = 0; f < q.tiles; ++f) {
-            // A: tile f = atoms 2f, 2f+1 (LBO = one atom); 16 token rows further = two 8-row groups of 1024 bytes
-            const uint64_t ad = desc_sw128_mn(sb + (2 * f) * atom_bytes + k16 * 2048, atom_bytes, 1024);
-            umma_bf16(tmem_base + f * p.rp, ad, bd, idesc, (i | k16) != 0 ? 1u : 0u);
-          }
-        }
-        umma_commit(empty0 + 8 * stage);
-        if (++stage == n_stages) { stage = 0; phase ^= 1; }
-      }
-      if (ok) umma_commit(done_bar);   // with no steps at all this completes at once
-    }
-  } else {
-    const int quad = warp & 3;
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(done_bar, 0, abort_flag, 43, p.status));
-    if (ok) {
-      tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-      for (int f = 0; f < q.tiles; ++f) {
-        const int c = group * q.group_feats + f * BM + quad * 32 + lane;
-        for (int j = 0; j < p.rp; j += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(taddr + f * p.rp + j, v);
-          tmem_ld_wait();
-          if (c < q.C) {
-            float4* o = reinterpret_cast<float4*>(q.part + (static_cast<int64_t>(slice) * q.C + c) * p.rp + j);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              // a slice without steps has accumulated nothing (its tensor memory is undefined): write zeros
-              o[e] = nsteps > 0 ? make_float4(__uint_as_float(v[4 * e]), __uint_as_float(v[4 * e + 1]),
-                                              __uint_as_float(v[4 * e + 2]), __uint_as_float(v[4 * e + 3]))
-                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-          }
-        }
-      }
-    }
-  }
+  GradShared sh;
+  sh.base = base; sh.full0 = full0; sh.empty0 = empty0; sh.done_bar = done_bar; sh.tmem_base = tmem_base;
+  sh.abort_flag = abort_flag;
+  grad_roles(p, &tmX0, &tmH0, &tmX1, &tmH1, sh, static_cast<int>(blockIdx.x));
   __syncwarp();
   if (*abort_flag != 0) {
     for (int k = 0; k < 200; ++k) __nanosleep(1000);
@@ -491,33 +386,31 @@ size_t grad_partial_bytes(int64_t M, int64_t K, int64_t N, int rp) {
   return b;
 }
 
-// out_i = X_i^T H_i with H_i given transposed as Ht_i [rp, h_pitch] (token index contiguous), for one or two
-// problems over the same M tokens (X1 == nullptr: one problem).
-int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, float* out0, int transposed0,
-                 const __nv_bfloat16* X1, const __nv_bfloat16* Ht1, int64_t C1, float* out1, int transposed1,
-                 int64_t h_pitch, float* part, int64_t M, int r, int rp, int accumulate, const DeviceState* ds,
-                 cudaStream_t st) {
-  const int np = X1 != nullptr ? 2 : 1;
-  const __nv_bfloat16* Xs[2] = {X0, X1};
-  const __nv_bfloat16* Hs[2] = {Ht0, Ht1};
-  float* outs[2] = {out0, out1};
-  const int trs[2] = {transposed0, transposed1};
-  const int64_t Cs[2] = {C0, np == 2 ? C1 : 0};
-  bool ragged = false;
-  for (int i = 0; i < np; ++i) ragged = ragged || (Cs[i] % 64 != 0);
-  if (ragged) {
-    for (int i = 0; i < np; ++i)
-      if (int rc = launch_grad_tile(Xs[i], Hs[i], h_pitch, outs[i], part, M, Cs[i], r, rp, trs[i], accumulate, ds, st)) return rc;
-    return MCB_OK;
+bool grad_tail_possible(int64_t C0, int64_t C1, int rp) {
+  for (int64_t C : {C0, C1}) {
+    if (C <= 0 || C % 64 != 0) return false;
+    GradProblem q;
+    plan_groups(C, rp, &q);
+    if (q.groups != 1) return false;
   }
+  return true;
+}
+
+int plan_grad2(const GradRequest& rq, int64_t M, int rp, int max_ctas, uint32_t smem_budget, const DeviceState* ds,
+               GradPlan* plan) {
+  const int np = rq.X[1] != nullptr ? 2 : 1;
+  plan->np = np;
+  plan->rq = rq;
   for (int i = 0; i < np; ++i)
-    if (!aligned16(Xs[i]) || !aligned16(Hs[i])) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
-  if (h_pitch % 8 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
-  GradParams p;
+    if (!aligned16(rq.X[i]) || !aligned16(rq.Ht[i]) || rq.C[i] % 64 != 0)
+      return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
+  if (rq.h_pitch % 8 != 0) return fail(MCB_ERR_ALIGN, "bf16 LoRA gradients: operand alignment");
+  GradParams& p = plan->p;
   memset(&p, 0, sizeof(p));
   p.M = static_cast<int>(M); p.rp = rp;
   p.status = ds->status_word;
-  for (int i = 0; i < np; ++i) plan_groups(Cs[i], rp, &p.pr[i]);
+  p.h_flags = rq.h_flags;
+  for (int i = 0; i < np; ++i) plan_groups(rq.C[i], rp, &p.pr[i]);
   // tokens per stage, per problem: as many (a multiple of 16, at most 256) as keep a stage near 48 KB, so that
   // narrow problems have as many bytes in flight as wide ones
   for (int i = 0; i < np; ++i) {
@@ -528,49 +421,84 @@ int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, 
     p.x_bytes[i] = static_cast<uint32_t>(T) * p.pr[i].group_feats * 2;
     const uint32_t sbytes = p.x_bytes[i] + static_cast<uint32_t>(rp) * T * 2;
     p.stage_stride[i] = (sbytes + 1023u) & ~1023u;
-    p.stages[i] = static_cast<int>(kGradSmemBudget / p.stage_stride[i]);
+    p.stages[i] = static_cast<int>(smem_budget / p.stage_stride[i]);
     if (p.stages[i] > kGradMaxStages) p.stages[i] = kGradMaxStages;
     if (p.stages[i] < 2) return fail(MCB_ERR_UNSUPPORTED, "bf16 LoRA gradients: stage does not fit shared memory");
   }
   p.bar_off = kGradSmemBudget;
   // CTAs: shared between the problems in proportion to their bytes, whole token slices per feature group
-  const int sms = ds->sm_count;
-  const double wsum = static_cast<double>(Cs[0]) + static_cast<double>(Cs[1]);
+  const double wsum = static_cast<double>(rq.C[0]) + static_cast<double>(np == 2 ? rq.C[1] : 0);
   int used = 0;
-  float* pp = part;
+  float* pp = rq.part;
   for (int i = 0; i < np; ++i) {
-    int share = np == 1 ? sms : static_cast<int>(sms * (static_cast<double>(Cs[i]) / wsum));
-    if (i == 1) share = sms - used;
+    int share = np == 1 ? max_ctas : static_cast<int>(max_ctas * (static_cast<double>(rq.C[i]) / wsum));
+    if (i == 1) share = max_ctas - used;
     int slices = share / p.pr[i].groups;
     if (slices < 1) slices = 1;
     const int total_steps = static_cast<int>((M + p.T[i] - 1) / p.T[i]);
     if (slices > total_steps) slices = total_steps;
     p.pr[i].slices = slices;
     p.pr[i].part = pp;
-    pp += static_cast<size_t>(slices) * Cs[i] * rp;
+    pp += static_cast<size_t>(slices) * rq.C[i] * rp;
     const int n = slices * p.pr[i].groups;
     if (i == 0) p.n_cta0 = n;
     used += n;
   }
-  if (static_cast<size_t>(pp - part) * sizeof(float) > static_cast<size_t>(256) * kGradGroup * rp * sizeof(float))
+  p.n_cta = used;
+  if (static_cast<size_t>(pp - rq.part) * sizeof(float) > static_cast<size_t>(256) * kGradGroup * rp * sizeof(float))
     return fail(MCB_ERR_WORKSPACE, "bf16 LoRA gradients: partial sums exceed the workspace");
-  CUtensorMap tmX[2], tmH[2];
   for (int i = 0; i < np; ++i) {
-    if (int rc = encode_x(ds, &tmX[i], Xs[i], M, Cs[i], p.T[i], p.pr[i].group_feats / 64)) return rc;
-    if (int rc = encode_h(ds, &tmH[i], Hs[i], M, h_pitch, rp)) return rc;
+    if (int rc = encode_x(ds, &plan->tmX[i], rq.X[i], M, rq.C[i], p.T[i], p.pr[i].group_feats / 64)) return rc;
+    if (int rc = encode_h(ds, &plan->tmH[i], rq.Ht[i], M, rq.h_pitch, rp)) return rc;
   }
-  if (np == 1) { tmX[1] = tmX[0]; tmH[1] = tmH[0]; }
-  const bool prof = profile_on();
-  if (prof) profile_begin(kProfGrad, 2.0 * M * (Cs[0] + Cs[1]) * r, 2.0 * M * (Cs[0] + Cs[1]) + 2.0 * np * M * rp, st);
-  lora_grad_umma_kernel<<<used, kGradThreads, kGradSmem, st>>>(tmX[0], tmH[0], tmX[1], tmH[1], p);
-  if (prof) profile_end(st);
-  MCB_CHECK_LAUNCH("lora_grad_umma_kernel");
-  ReduceProblem ra = {p.pr[0].part, out0, p.pr[0].slices, static_cast<int>(Cs[0]), transposed0};
-  ReduceProblem rb = {np == 2 ? p.pr[1].part : nullptr, out1, np == 2 ? p.pr[1].slices : 0, static_cast<int>(Cs[1]), transposed1};
-  const int blocks_a = static_cast<int>((Cs[0] * rp + 31) / 32), blocks_b = static_cast<int>((Cs[1] * rp + 31) / 32);
-  lora_grad_reduce_kernel<<<static_cast<unsigned>(blocks_a + blocks_b), 256, 0, st>>>(ra, rb, blocks_a, r, rp, accumulate);
+  if (np == 1) { plan->tmX[1] = plan->tmX[0]; plan->tmH[1] = plan->tmH[0]; }
+  return MCB_OK;
+}
+
+int launch_grad_reduce(const GradPlan& plan, cudaStream_t st) {
+  const GradParams& p = plan.p;
+  const GradRequest& rq = plan.rq;
+  const bool two = plan.np == 2;
+  ReduceProblem ra = {p.pr[0].part, rq.out[0], p.pr[0].slices, static_cast<int>(rq.C[0]), rq.transposed[0]};
+  ReduceProblem rb = {two ? p.pr[1].part : nullptr, rq.out[1], two ? p.pr[1].slices : 0, two ? static_cast<int>(rq.C[1]) : 0,
+                      rq.transposed[1]};
+  const int blocks_a = static_cast<int>((rq.C[0] * p.rp + 31) / 32);
+  const int blocks_b = two ? static_cast<int>((rq.C[1] * p.rp + 31) / 32) : 0;
+  lora_grad_reduce_kernel<<<static_cast<unsigned>(blocks_a + blocks_b), 256, 0, st>>>(ra, rb, blocks_a, rq.r, p.rp, rq.accumulate);
   MCB_CHECK_LAUNCH("lora_grad_reduce");
   return MCB_OK;
+}
+
+// out_i = X_i^T H_i with H_i given transposed as Ht_i [rp, h_pitch] (token index contiguous), for one or two
+// problems over the same M tokens (X1 == nullptr: one problem).
+int launch_grad2(const __nv_bfloat16* X0, const __nv_bfloat16* Ht0, int64_t C0, float* out0, int transposed0,
+                 const __nv_bfloat16* X1, const __nv_bfloat16* Ht1, int64_t C1, float* out1, int transposed1,
+                 int64_t h_pitch, float* part, int64_t M, int r, int rp, int accumulate, const DeviceState* ds,
+                 cudaStream_t st) {
+  const int np = X1 != nullptr ? 2 : 1;
+  GradRequest rq;
+  rq.X[0] = X0; rq.X[1] = X1;
+  rq.Ht[0] = Ht0; rq.Ht[1] = Ht1;
+  rq.C[0] = C0; rq.C[1] = np == 2 ? C1 : 0;
+  rq.out[0] = out0; rq.out[1] = out1;
+  rq.transposed[0] = transposed0; rq.transposed[1] = transposed1;
+  rq.h_pitch = h_pitch; rq.part = part; rq.r = r; rq.accumulate = accumulate;
+  bool ragged = false;
+  for (int i = 0; i < np; ++i) ragged = ragged || (rq.C[i] % 64 != 0);
+  if (ragged) {
+    for (int i = 0; i < np; ++i)
+      if (int rc = launch_grad_tile(rq.X[i], rq.Ht[i], h_pitch, rq.out[i], part, M, rq.C[i], r, rp, rq.transposed[i], accumulate, ds, st))
+        return rc;
+    return MCB_OK;
+  }
+  GradPlan plan;
+  if (int rc = plan_grad2(rq, M, rp, ds->sm_count, kGradSmemBudget, ds, &plan)) return rc;
+  const bool prof = profile_on();
+  if (prof) profile_begin(kProfGrad, 2.0 * M * (rq.C[0] + rq.C[1]) * r, 2.0 * M * (rq.C[0] + rq.C[1]) + 2.0 * np * M * rp, st);
+  lora_grad_umma_kernel<<<plan.p.n_cta, kGradThreads, kGradSmem, st>>>(plan.tmX[0], plan.tmH[0], plan.tmX[1], plan.tmH[1], plan.p);
+  if (prof) profile_end(st);
+  MCB_CHECK_LAUNCH("lora_grad_umma_kernel");
+  return launch_grad_reduce(plan, st);
 }
 
 }  // namespace bf16path

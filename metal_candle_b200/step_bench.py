@@ -188,7 +188,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 4,
                     "d2h_bytes_per_step": 4},
             "gpu_launches": per_step_launches * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "lora_gemm2_kernel + lora_gemm_kernel (all projections of the step)",
+            "roofline": {"bound": "tensor", "kernel": "lora_gemm2_kernel + lora_gemm_kernel (all projections of the step; the dx launches of the LoRA "
+                                   "projections include their dA/dB tail phase)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
                          "launches": n_l, "kernel_ms_per_step": g_ms / args.steps,
@@ -214,10 +215,19 @@ def _count_launches(cfg, wl) -> int:
     # forward: 2 norms, 7 GEMMs, operand packs, 3 rope/relayout + 1 inverse relayout, attention (or softmax), swiglu
     # (gate, up and swiglu are one kernel when neither projection has an adapter)
     per_layer_fwd = 2 + (5 if fused_mlp else 8) + n_lora + 4 + 1
-    # backward: 7 GEMMs, packs, dA/dB (gradient + reduce each), swiglu, 2 norms, 4 rope/relayout,
-    # attention (dq + dkv kernels, or one softmax), 2 residual-gradient adds
-    # (dA and dB of an adapter come from one gradient launch plus one partial-sum launch)
-    per_layer_bwd = 7 + n_lora + 2 * n_lora + 1 + 2 + 4 + (2 if fused_attn else 1) + 2
+    # backward: 7 GEMMs, packs, dA/dB, swiglu, 2 norms, 4 rope/relayout, attention (dq + dkv kernels, or one
+    # softmax), 2 residual-gradient adds.  dA and dB of an adapter are accumulated in the tail phase of its dx
+    # GEMM launch and cost one partial-sum launch more; adapters whose dx runs on CTA pairs (out features >= 1536)
+    # or that are wider than 1024 features take a gradient launch of their own as well.
+    out_f = {"q_proj": cfg.hidden_size, "k_proj": cfg.kv_size, "v_proj": cfg.kv_size, "o_proj": cfg.hidden_size,
+             "gate_proj": cfg.intermediate_size, "up_proj": cfg.intermediate_size, "down_proj": cfg.hidden_size}
+    in_f = {"down_proj": cfg.intermediate_size}
+    grad_launches = 0
+    for t in wl["targets"]:
+        o, i = out_f[t], in_f.get(t, cfg.hidden_size)
+        tail = o < 1536 and max(o, i) <= 1024 and o % 64 == 0 and i % 64 == 0
+        grad_launches += 1 if tail else 2
+    per_layer_bwd = 7 + n_lora + grad_launches + 1 + 2 + 4 + (2 if fused_attn else 1) + 2
     tail = 1 + 1 + 1 + 3 + 1 + 1  # embed, norm, lm_head, CE x3, lm_head bwd, norm bwd
     adamw = math.ceil(2 * n_lora * L / 64)
     return L * (per_layer_fwd + per_layer_bwd) + tail + adamw

@@ -84,6 +84,13 @@ CASES = [
     (1280, 1536, 1600, 16),
     (1100, 1792, 1544, 64),
     (1024, 896, 1024, 8),
+    # many CTAs in the backward kernel, whose tail phase (dA, dB) reads rank-intermediate rows written by other
+    # CTAs of the same launch; ragged token count; the narrow k/v projection shape
+    (4224, 896, 896, 16),
+    (5000, 896, 128, 16),
+    (20000, 1024, 512, 32),
+    # the backward kernel is a single CTA: the gradients take their own launch
+    (100, 128, 64, 4),
 ]
 
 
