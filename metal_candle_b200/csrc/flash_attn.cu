@@ -50,10 +50,10 @@ constexpr uint32_t kKBytes = kBK * kD * 2;   // 8 KB
 constexpr uint32_t kPBytes = kBQ * kBK * 2;  // 16 KB
 // shared memory map (from the 1024-aligned base)
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + kQBytes;           // 2 stages
-constexpr uint32_t kOffV = kOffK + 2 * kKBytes;       // 2 stages
-constexpr uint32_t kOffP = kOffV + 2 * kKBytes;
-constexpr uint32_t kOffBar = kOffP + kPBytes;
+constexpr int kFwdStages = 4;                         // K / V ring: a load has three blocks' time to arrive
+constexpr uint32_t kOffK = kOffQ + kQBytes;
+constexpr uint32_t kOffV = kOffK + kFwdStages * kKBytes;
+constexpr uint32_t kOffBar = kOffV + kFwdStages * kKBytes;
 constexpr uint32_t kFwdSmem = kOffBar + 256 + 1024;
 
 struct FwdParams {
@@ -85,16 +85,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   // S is double-buffered in tensor memory (the next block's Q K^T runs under this block's softmax), with one
   // s_full / p_ready barrier per buffer
-  const uint32_t q_full = base + kOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16, s_full0 = kv_empty0 + 16;
-  const uint32_t p_ready0 = s_full0 + 16, o_full = p_ready0 + 16, tmem_slot = o_full + 8, abort_addr = tmem_slot + 4;
+  // and P in shared memory (this block's exponentials are written under the previous block's P V), with one
+  // pv_done barrier per buffer
+  const uint32_t q_full = base + kOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * kFwdStages;
+  const uint32_t s_full0 = kv_empty0 + 8 * kFwdStages, p_ready0 = s_full0 + 16, pv_done0 = p_ready0 + 16;
+  const uint32_t tmem_slot = pv_done0 + 16, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(p_ready0 + 8 * s, 4); }
-    mbar_init(o_full, 1);
+    for (int s = 0; s < kFwdStages; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(p_ready0 + 8 * s, 4); mbar_init(pv_done0 + 8 * s, 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -107,7 +109,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const uint32_t tO = tmem_base + 128;  // S buffers at columns 0 and 64
+  // S buffers at columns 0 and 64, O at 128, the two P buffers (bf16 pairs: 32 columns each) at 192 and 224
+  const uint32_t tO = tmem_base + 128, tP0 = tmem_base + 192;
 
   // heavy (late) query blocks first
   const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
@@ -119,22 +122,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       mbar_expect_tx(q_full, kQBytes);
       tma_load_2d(base + kOffQ, &tmQ, q_full, 0, static_cast<int>(qrow0));
+      int st = 0;
+      uint32_t ph = 0;
       for (int j = 0; j < nkb; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag, 71, p.status)) break;
+        if (!mbar_wait(kv_empty0 + 8 * st, ph ^ 1, abort_flag, 71, p.status)) break;
         mbar_expect_tx(kv_full0 + 8 * st, 2 * kKBytes);
         tma_load_2d(base + kOffK + st * kKBytes, &tmK, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
         tma_load_2d(base + kOffV + st * kKBytes, &tmVt, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
+        if (++st == kFwdStages) { st = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);  // M = 128, N = 64 for both products
-      auto issue_s = [&](int j) {   // S_j = Q K_j^T into tensor-memory buffer j & 1
+      auto issue_s = [&](int j, int st) {   // S_j = Q K_j^T into tensor-memory buffer j & 1
         const uint32_t tS = tmem_base + (j & 1) * 64;
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + (j & 1) * kKBytes + k4 * 32), idesc,
+          umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + st * kKBytes + k4 * 32), idesc,
                     k4 != 0 ? 1u : 0u);
         umma_commit(s_full0 + 8 * (j & 1));
       };
@@ -142,28 +147,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) ok = mbar_wait(kv_full0, 0, abort_flag, 73, p.status);
       if (ok) {
         tcgen05_fence_after();
-        issue_s(0);
+        issue_s(0, 0);
       }
+      int st = 0;          // ring stage of block j
+      uint32_t ph = 0;     // and the phase of its barriers
       for (int j = 0; ok && j < nkb; ++j) {
-        const int st = j & 1;
+        int st1 = st + 1;  // stage and phase of block j + 1
+        uint32_t ph1 = ph;
+        if (st1 == kFwdStages) { st1 = 0; ph1 ^= 1; }
         if (j + 1 < nkb) {
           // buffer (j+1)&1 of S was last read by the softmax of block j-1, whose p_ready this thread has waited for
-          ok = mbar_wait(kv_full0 + 8 * (st ^ 1), ((j + 1) >> 1) & 1, abort_flag, 75, p.status);
+          ok = mbar_wait(kv_full0 + 8 * st1, ph1, abort_flag, 75, p.status);
           if (!ok) break;
           tcgen05_fence_after();
-          issue_s(j + 1);
+          issue_s(j + 1, st1);
         }
-        ok = mbar_wait(p_ready0 + 8 * st, (j >> 1) & 1, abort_flag, 74, p.status);
+        ok = mbar_wait(p_ready0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, 74, p.status);
         if (!ok) break;
         tcgen05_fence_after();
-        // O += P_j V_j   (A = P [128 x 64 keys] K-major; B = the V tile as it lies, [64 keys x 64 d]: N-major,
-        // 16 keys further = two 8-row groups of 1024 bytes)
+        // O += P_j V_j   (A = P [128 x 64 keys] in tensor memory, 16 keys = 8 columns; B = the V tile as it lies,
+        // [64 keys x 64 d]: N-major, 16 keys further = two 8-row groups of 1024 bytes)
 #pragma unroll
         for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tO, desc_sw128(base + kOffP + k4 * 32), desc_sw128_mn(base + kOffV + st * kKBytes + k4 * 2048, kKBytes, 1024),
-                    idesc | (1u << 16), (j | k4) != 0 ? 1u : 0u);
-        umma_commit(o_full);
+          umma_bf16_ts(tO, tP0 + (j & 1) * 32 + k4 * 8,
+                       desc_sw128_mn(base + kOffV + st * kKBytes + k4 * 2048, kKBytes, 1024), idesc | (1u << 16),
+                       (j | k4) != 0 ? 1u : 0u);
+        umma_commit(pv_done0 + 8 * (j & 1));
         umma_commit(kv_empty0 + 8 * st);
+        st = st1;
+        ph = ph1;
       }
     }
   } else {
@@ -175,8 +187,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int row = quad * 32 + lane;
     const int qpos = qb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* prow = gen_base + kOffP + row * 128;
-    const int sw = row & 7;
     float m = -INFINITY, l = 0.0f;   // m: the maximum in use (base-2 logits)
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
@@ -209,15 +219,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_true = fmaxf(m, mx * p.sc);  // key 0 is never masked, so this is finite from block 0 on
       const bool raise = m_true > m + 8.0f;       // block 0: m = -inf, always
-      if (j > 0) {
-        // the previous P V product must have landed before O is rescaled or P overwritten
-        ok = __all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1, abort_flag, 77, p.status));
+      if (j >= 2) {
+        // the P V product of block j-2 has read the P buffer that this block overwrites
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * (j & 1), ((j - 2) >> 1) & 1, abort_flag, 77, p.status));
         if (!ok) break;
-        tcgen05_fence_after();
       }
       if (__any_sync(0xffffffffu, raise)) {
         const float alpha = ex2(m - m_true);   // rows that did not ask get alpha <= 1 as well and move their maximum
         if (j > 0) {
+          // every P V product so far must have landed before O is rescaled
+          ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, 79, p.status));
+          if (!ok) break;
+          tcgen05_fence_after();
 #pragma unroll
           for (int c = 0; c < kD; c += 16) {
             uint32_t v[16];
@@ -232,30 +245,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l *= alpha;
         m = m_true;
       }
-      // P = 2^(s*sc - m) (masked scores are -inf and give 0), row sum, bf16 into the swizzled operand buffer
+      // P = 2^(s*sc - m) (masked scores are -inf and give 0), row sum, bf16 pairs into this block's P buffer in
+      // tensor memory (the A operand of the P V product: no trip through shared memory)
       float ls0 = 0.0f, ls1 = 0.0f;
+      const uint32_t tP = tP0 + lane_addr + (j & 1) * 32;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t w[8];
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t w[16];
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(sv[c4][e]), p.sc, -m));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[c4][e + 1]), p.sc, -m));
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c2 + (e >> 4)][e & 15]), p.sc, -m));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + (e >> 4)][(e & 15) + 1]), p.sc, -m));
           ls0 += p0;
           ls1 += p1;
           w[e >> 1] = pack_bf16(p0, p1);
         }
-        const int cc = c4 * 2;  // 16-byte chunk index of columns 16*c4 .. 16*c4+7
-        *reinterpret_cast<uint4*>(prow + (((cc) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(prow + (((cc + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        tmem_st_x16(tP + 16 * c2, w);
       }
+      tmem_st_wait();
       l += ls0 + ls1;
       tcgen05_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready0 + 8 * (j & 1));
     }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, (nkb - 1) & 1, abort_flag, 78, p.status));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * ((nkb - 1) & 1), ((nkb - 1) >> 1) & 1, abort_flag, 78, p.status));
     if (ok) {
       tcgen05_fence_after();
       const float inv = 1.0f / l;

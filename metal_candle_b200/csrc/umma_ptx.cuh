@@ -95,6 +95,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand in tensor memory: row i of A in lane i, its K elements packed two bf16 per 32-bit
+// column from a_tmem on (element 2c in the low half of column c); 16 K elements per instruction = 8 columns.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47).
 //   K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused (=1).
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
