@@ -57,7 +57,7 @@ constexpr uint32_t kOffBar = kOffV + kFwdStages * kKBytes;
 constexpr uint32_t kFwdSmem = kOffBar + 256 + 1024;
 
 struct FwdParams {
-  int S, G;
+  int S, G, NB;
   float sc;  // scale * log2(e)
   __nv_bfloat16* O;
   float* lse;
@@ -69,10 +69,34 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 __device__ __forceinline__ float lg2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Work item t (heavy first): query block qb = nqb-1 - t / (G*nb), then head g and batch*kv-head nb.
+struct FwdTile {
+  int qb, g, nb, nkb;
+  int64_t qrow0;
+};
+__device__ __forceinline__ FwdTile fwd_tile(const FwdParams& p, int t) {
+  FwdTile w;
+  const int per_qb = p.G * p.NB;
+  const int r = t % per_qb;
+  w.qb = p.S / kBQ - 1 - t / per_qb;
+  w.g = r % p.G;
+  w.nb = r / p.G;
+  w.nkb = 2 * w.qb + 2;  // key blocks of 64 up to and including the diagonal
+  w.qrow0 = (static_cast<int64_t>(w.nb) * p.G + w.g) * p.S + static_cast<int64_t>(w.qb) * kBQ;
+  return w;
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -83,20 +107,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // S is double-buffered in tensor memory (the next block's Q K^T runs under this block's softmax), with one
-  // s_full / p_ready barrier per buffer
-  // and P in shared memory (this block's exponentials are written under the previous block's P V), with one
-  // pv_done barrier per buffer
-  const uint32_t q_full = base + kOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * kFwdStages;
+  // Persistent: a CTA walks over work items (128 queries of one head) and carries its rings and barrier phases
+  // from one to the next, so that the next item's Q / K / V loads and first S products run under this item's
+  // last blocks and its write-out.  n below is the running number of a key block over all items of this CTA.
+  // S is double-buffered in tensor memory and runs two blocks ahead of the softmax; P is double-buffered in
+  // tensor memory as well (this block's exponentials are written under the previous block's P V).
+  const uint32_t q_full = base + kOffBar, q_free = q_full + 8, o_free = q_free + 8, kv_full0 = o_free + 8;
+  const uint32_t kv_empty0 = kv_full0 + 8 * kFwdStages;
   const uint32_t s_full0 = kv_empty0 + 8 * kFwdStages, p_ready0 = s_full0 + 16, pv_done0 = p_ready0 + 16;
-  const uint32_t tmem_slot = pv_done0 + 16, abort_addr = tmem_slot + 4;
+  const uint32_t s_free0 = pv_done0 + 16, tmem_slot = s_free0 + 16, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
+    mbar_init(o_free, 4);
     for (int s = 0; s < kFwdStages; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(p_ready0 + 8 * s, 4); mbar_init(pv_done0 + 8 * s, 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(s_full0 + 8 * s, 1); mbar_init(p_ready0 + 8 * s, 4); mbar_init(pv_done0 + 8 * s, 1); mbar_init(s_free0 + 8 * s, 4);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -111,71 +141,83 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot_ptr;
   // S buffers at columns 0 and 64, O at 128, the two P buffers (bf16 pairs: 32 columns each) at 192 and 224
   const uint32_t tO = tmem_base + 128, tP0 = tmem_base + 192;
-
-  // heavy (late) query blocks first
-  const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-  const int g = blockIdx.y, nb = blockIdx.z;
-  const int nkb = 2 * qb + 2;  // key blocks of 64 up to and including the diagonal
-  const int64_t qrow0 = (static_cast<int64_t>(nb) * p.G + g) * p.S + static_cast<int64_t>(qb) * kBQ;
+  const int n_tiles = (p.S / kBQ) * p.G * p.NB;
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, kQBytes);
-      tma_load_2d(base + kOffQ, &tmQ, q_full, 0, static_cast<int>(qrow0));
       int st = 0;
       uint32_t ph = 0;
-      for (int j = 0; j < nkb; ++j) {
-        if (!mbar_wait(kv_empty0 + 8 * st, ph ^ 1, abort_flag, 71, p.status)) break;
-        mbar_expect_tx(kv_full0 + 8 * st, 2 * kKBytes);
-        tma_load_2d(base + kOffK + st * kKBytes, &tmK, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
-        tma_load_2d(base + kOffV + st * kKBytes, &tmVt, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
-        if (++st == kFwdStages) { st = 0; ph ^= 1; }
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++it) {
+        const FwdTile w = fwd_tile(p, t);
+        // the previous item's last S product has read Q
+        if (it > 0) ok = mbar_wait(q_free, (it - 1) & 1, abort_flag, 69, p.status);
+        if (!ok) break;
+        mbar_expect_tx(q_full, kQBytes);
+        tma_load_2d(base + kOffQ, &tmQ, q_full, 0, static_cast<int>(w.qrow0));
+        for (int j = 0; j < w.nkb; ++j) {
+          ok = mbar_wait(kv_empty0 + 8 * st, ph ^ 1, abort_flag, 71, p.status);
+          if (!ok) break;
+          mbar_expect_tx(kv_full0 + 8 * st, 2 * kKBytes);
+          tma_load_2d(base + kOffK + st * kKBytes, &tmK, kv_full0 + 8 * st, 0, w.nb * p.S + j * kBK);
+          tma_load_2d(base + kOffV + st * kKBytes, &tmVt, kv_full0 + 8 * st, 0, w.nb * p.S + j * kBK);
+          if (++st == kFwdStages) { st = 0; ph ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);  // M = 128, N = 64 for both products
-      auto issue_s = [&](int j, int st) {   // S_j = Q K_j^T into tensor-memory buffer j & 1
-        const uint32_t tS = tmem_base + (j & 1) * 64;
+      bool ok = true;
+      int it = 0;
+      uint32_t n0 = 0;            // running number of this item's block 0
+      int sst = 0;                // ring stage and phase of the next block to get its S product
+      uint32_t sph = 0;
+      int pst = 0;                // ring stage of the next block to get its P V product
+      // S_j = Q K_j^T for block j of the current item (running number n) into tensor-memory buffer n & 1; the
+      // buffer is free once the softmax warps have read block n - 2 into registers (s_free)
+      auto issue_s = [&](uint32_t n, bool last) -> bool {
+        if (n >= 2 && !mbar_wait(s_free0 + 8 * (n & 1), ((n - 2) >> 1) & 1, abort_flag, 70, p.status)) return false;
+        if (!mbar_wait(kv_full0 + 8 * sst, sph, abort_flag, 75, p.status)) return false;
+        tcgen05_fence_after();
+        const uint32_t tS = tmem_base + (n & 1) * 64;
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + st * kKBytes + k4 * 32), idesc,
+          umma_bf16(tS, desc_sw128(base + kOffQ + k4 * 32), desc_sw128(base + kOffK + sst * kKBytes + k4 * 32), idesc,
                     k4 != 0 ? 1u : 0u);
-        umma_commit(s_full0 + 8 * (j & 1));
+        umma_commit(s_full0 + 8 * (n & 1));
+        if (last) umma_commit(q_free);   // Q may be replaced by the next item's
+        if (++sst == kFwdStages) { sst = 0; sph ^= 1; }
+        return true;
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag, 72, p.status);
-      if (ok) ok = mbar_wait(kv_full0, 0, abort_flag, 73, p.status);
-      if (ok) {
-        tcgen05_fence_after();
-        issue_s(0, 0);
-      }
-      int st = 0;          // ring stage of block j
-      uint32_t ph = 0;     // and the phase of its barriers
-      for (int j = 0; ok && j < nkb; ++j) {
-        int st1 = st + 1;  // stage and phase of block j + 1
-        uint32_t ph1 = ph;
-        if (st1 == kFwdStages) { st1 = 0; ph1 ^= 1; }
-        if (j + 1 < nkb) {
-          // buffer (j+1)&1 of S was last read by the softmax of block j-1, whose p_ready this thread has waited for
-          ok = mbar_wait(kv_full0 + 8 * st1, ph1, abort_flag, 75, p.status);
+      for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++it) {
+        const FwdTile w = fwd_tile(p, t);
+        ok = mbar_wait(q_full, it & 1, abort_flag, 72, p.status);
+        for (int j = 0; ok && j < 2; ++j) ok = issue_s(n0 + j, j == w.nkb - 1);   // nkb >= 2
+        for (int j = 0; ok && j < w.nkb; ++j) {
+          const uint32_t n = n0 + j;
+          if (j + 2 < w.nkb) {
+            ok = issue_s(n + 2, j + 2 == w.nkb - 1);
+            if (!ok) break;
+          }
+          ok = mbar_wait(p_ready0 + 8 * (n & 1), (n >> 1) & 1, abort_flag, 74, p.status);
+          // the first product of an item overwrites O: the previous item's write-out must have read it
+          if (ok && j == 0 && it > 0) ok = mbar_wait(o_free, (it - 1) & 1, abort_flag, 68, p.status);
           if (!ok) break;
           tcgen05_fence_after();
-          issue_s(j + 1, st1);
-        }
-        ok = mbar_wait(p_ready0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, 74, p.status);
-        if (!ok) break;
-        tcgen05_fence_after();
-        // O += P_j V_j   (A = P [128 x 64 keys] in tensor memory, 16 keys = 8 columns; B = the V tile as it lies,
-        // [64 keys x 64 d]: N-major, 16 keys further = two 8-row groups of 1024 bytes)
+          // O += P_j V_j   (A = P [128 x 64 keys] in tensor memory, 16 keys = 8 columns; B = the V tile as it lies,
+          // [64 keys x 64 d]: N-major, 16 keys further = two 8-row groups of 1024 bytes)
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16_ts(tO, tP0 + (j & 1) * 32 + k4 * 8,
-                       desc_sw128_mn(base + kOffV + st * kKBytes + k4 * 2048, kKBytes, 1024), idesc | (1u << 16),
-                       (j | k4) != 0 ? 1u : 0u);
-        umma_commit(pv_done0 + 8 * (j & 1));
-        umma_commit(kv_empty0 + 8 * st);
-        st = st1;
-        ph = ph1;
+          for (int k4 = 0; k4 < kBK / 16; ++k4)
+            umma_bf16_ts(tO, tP0 + (n & 1) * 32 + k4 * 8,
+                         desc_sw128_mn(base + kOffV + pst * kKBytes + k4 * 2048, kKBytes, 1024), idesc | (1u << 16),
+                         (j | k4) != 0 ? 1u : 0u);
+          umma_commit(pv_done0 + 8 * (n & 1));
+          umma_commit(kv_empty0 + 8 * pst);
+          if (++pst == kFwdStages) pst = 0;
+        }
+        n0 += static_cast<uint32_t>(w.nkb);
       }
     }
   } else {
@@ -185,107 +227,128 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // warp rescales its 32 rows of O in tensor memory.  Between such events nothing but S is touched.
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
-    const int qpos = qb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    float m = -INFINITY, l = 0.0f;   // m: the maximum in use (base-2 logits)
     bool ok = true;
-    for (int j = 0; j < nkb; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, 76, p.status));
+    uint32_t n0 = 0;
+    for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+      const FwdTile w = fwd_tile(p, t);
+      const int qpos = w.qb * kBQ + row;
+      float m = -INFINITY, l = 0.0f;   // m: the maximum in use (base-2 logits)
+      for (int j = 0; j < w.nkb; ++j) {
+        const uint32_t n = n0 + j;
+        ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag, 76, p.status));
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tS = tmem_base + (n & 1) * 64;
+        const int key0 = j * kBK;
+        const bool diag = key0 + kBK - 1 > w.qb * kBQ;  // some element of this block may lie above the diagonal
+        // the row's 64 scores of this block, read from tensor memory once (four loads in flight, one wait)
+        uint32_t sv[4][16];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tS + lane_addr + 16 * c4, sv[c4]);
+        tmem_ld_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free0 + 8 * (n & 1));   // the buffer may take block n + 2
+        if (diag) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (key0 + 16 * c4 + e > qpos) sv[c4][e] = 0xff800000u;   // -inf
+        }
+        // row maximum: four independent chains of three-input maxima (8 instructions each)
+        float mxc[4];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          float tmx = fmaxf(__uint_as_float(sv[c4][0]), __uint_as_float(sv[c4][1]));
+#pragma unroll
+          for (int e = 2; e < 16; e += 2) tmx = fmax3(tmx, __uint_as_float(sv[c4][e]), __uint_as_float(sv[c4][e + 1]));
+          mxc[c4] = tmx;
+        }
+        const float mx = fmaxf(fmax3(mxc[0], mxc[1], mxc[2]), mxc[3]);
+        const float m_true = fmaxf(m, mx * p.sc);  // key 0 is never masked, so this is finite from block 0 on
+        const bool raise = m_true > m + 8.0f;       // block 0: m = -inf, always
+        if (n >= 2) {
+          // the P V product of block n-2 has read the P buffer that this block overwrites
+          ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * (n & 1), ((n - 2) >> 1) & 1, abort_flag, 77, p.status));
+          if (!ok) break;
+        }
+        if (__any_sync(0xffffffffu, raise)) {
+          const float alpha = ex2(m - m_true);   // rows that did not ask get alpha <= 1 as well and move their maximum
+          if (j > 0) {
+            // every P V product so far must have landed before O is rescaled
+            ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1, abort_flag, 79, p.status));
+            if (!ok) break;
+            tcgen05_fence_after();
+#pragma unroll
+            for (int c = 0; c < kD; c += 16) {
+              uint32_t v[16];
+              tmem_ld_x16(tO + lane_addr + c, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+              tmem_st_x16(tO + lane_addr + c, v);
+            }
+            tmem_st_wait();
+          }
+          l *= alpha;
+          m = m_true;
+        }
+        // P = 2^(s*sc - m) (masked scores are -inf and give 0), row sum, bf16 pairs into this block's P buffer in
+        // tensor memory (the A operand of the P V product: no trip through shared memory)
+        // (packed two-wide FMA and add: the special-function unit's 64 exponentials are the only per-element work)
+        float2 lsa = f2(0.0f, 0.0f), lsb = f2(0.0f, 0.0f);
+        const float2 sc2 = f2(p.sc, p.sc), nm2 = f2(-m, -m);
+        const uint32_t tP = tP0 + lane_addr + (n & 1) * 32;
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t pw[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const uint32_t* q4 = &sv[2 * c2 + (e >> 4)][e & 15];
+            const float2 ta = __ffma2_rn(f2(__uint_as_float(q4[0]), __uint_as_float(q4[1])), sc2, nm2);
+            const float2 tb = __ffma2_rn(f2(__uint_as_float(q4[2]), __uint_as_float(q4[3])), sc2, nm2);
+            const float2 pa = f2(ex2(ta.x), ex2(ta.y)), pb = f2(ex2(tb.x), ex2(tb.y));
+            lsa = __fadd2_rn(lsa, pa);
+            lsb = __fadd2_rn(lsb, pb);
+            pw[e >> 1] = pack_bf16(pa.x, pa.y);
+            pw[(e >> 1) + 1] = pack_bf16(pb.x, pb.y);
+          }
+          tmem_st_x16(tP + 16 * c2, pw);
+        }
+        tmem_st_wait();
+        l += (lsa.x + lsa.y) + (lsb.x + lsb.y);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready0 + 8 * (n & 1));
+      }
+      if (!ok) break;
+      // write-out: the item's last P V product has landed
+      const uint32_t nl = n0 + static_cast<uint32_t>(w.nkb) - 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * (nl & 1), (nl >> 1) & 1, abort_flag, 78, p.status));
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t tS = tmem_base + (j & 1) * 64;
-      const int key0 = j * kBK;
-      const bool diag = key0 + kBK - 1 > qb * kBQ;  // some element of this block may lie above the diagonal
-      // the row's 64 scores of this block, read from tensor memory once (four loads in flight, one wait)
-      uint32_t sv[4][16];
+      const float inv = 1.0f / l;
+      __nv_bfloat16* orow = p.O + (w.qrow0 + row) * kD;
+      uint32_t ov[4][16];
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tS + lane_addr + 16 * c4, sv[c4]);
+      for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tO + lane_addr + 16 * c4, ov[c4]);
       tmem_ld_wait();
-      if (diag) {
-#pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4)
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            if (key0 + 16 * c4 + e > qpos) sv[c4][e] = 0xff800000u;   // -inf
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        mx0 = fmaxf(mx0, __uint_as_float(sv[0][e]));
-        mx1 = fmaxf(mx1, __uint_as_float(sv[1][e]));
-        mx2 = fmaxf(mx2, __uint_as_float(sv[2][e]));
-        mx3 = fmaxf(mx3, __uint_as_float(sv[3][e]));
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float m_true = fmaxf(m, mx * p.sc);  // key 0 is never masked, so this is finite from block 0 on
-      const bool raise = m_true > m + 8.0f;       // block 0: m = -inf, always
-      if (j >= 2) {
-        // the P V product of block j-2 has read the P buffer that this block overwrites
-        ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * (j & 1), ((j - 2) >> 1) & 1, abort_flag, 77, p.status));
-        if (!ok) break;
-      }
-      if (__any_sync(0xffffffffu, raise)) {
-        const float alpha = ex2(m - m_true);   // rows that did not ask get alpha <= 1 as well and move their maximum
-        if (j > 0) {
-          // every P V product so far must have landed before O is rescaled
-          ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, 79, p.status));
-          if (!ok) break;
-          tcgen05_fence_after();
-#pragma unroll
-          for (int c = 0; c < kD; c += 16) {
-            uint32_t v[16];
-            tmem_ld_x16(tO + lane_addr + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-            tmem_st_x16(tO + lane_addr + c, v);
-          }
-          tmem_st_wait();
-        }
-        l *= alpha;
-        m = m_true;
-      }
-      // P = 2^(s*sc - m) (masked scores are -inf and give 0), row sum, bf16 pairs into this block's P buffer in
-      // tensor memory (the A operand of the P V product: no trip through shared memory)
-      float ls0 = 0.0f, ls1 = 0.0f;
-      const uint32_t tP = tP0 + lane_addr + (j & 1) * 32;
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        uint32_t w[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(sv[2 * c2 + (e >> 4)][e & 15]), p.sc, -m));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[2 * c2 + (e >> 4)][(e & 15) + 1]), p.sc, -m));
-          ls0 += p0;
-          ls1 += p1;
-          w[e >> 1] = pack_bf16(p0, p1);
-        }
-        tmem_st_x16(tP + 16 * c2, w);
-      }
-      tmem_st_wait();
-      l += ls0 + ls1;
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready0 + 8 * (j & 1));
-    }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * ((nkb - 1) & 1), ((nkb - 1) >> 1) & 1, abort_flag, 78, p.status));
-    if (ok) {
-      tcgen05_fence_after();
-      const float inv = 1.0f / l;
-      __nv_bfloat16* orow = p.O + (qrow0 + row) * kD;
+      if (lane == 0) mbar_arrive(o_free);   // the next item's products may overwrite O
 #pragma unroll
-      for (int c = 0; c < kD; c += 16) {
-        uint32_t v[16];
-        tmem_ld_x16(tO + lane_addr + c, v);
-        tmem_ld_wait();
-        uint32_t w[8];
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t ow[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2)
-          w[e >> 1] = pack_bf16(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
-        *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+          ow[e >> 1] = pack_bf16(__uint_as_float(ov[c4][e]) * inv, __uint_as_float(ov[c4][e + 1]) * inv);
+        *reinterpret_cast<uint4*>(orow + 16 * c4) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        *reinterpret_cast<uint4*>(orow + 16 * c4 + 8) = make_uint4(ow[4], ow[5], ow[6], ow[7]);
       }
-      if (p.lse != nullptr) p.lse[qrow0 + row] = (m + lg2(l)) * kLn2;
+      if (p.lse != nullptr) p.lse[w.qrow0 + row] = (m + lg2(l)) * kLn2;
+      n0 += static_cast<uint32_t>(w.nkb);
     }
   }
 
@@ -817,10 +880,13 @@ extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void
   if (int rc = encode(ds, &tmK, k, kD, nb * seq, kBK, "K")) return rc;
   if (int rc = encode(ds, &tmVt, v, kD, nb * seq, kBK, "V")) return rc;
   FwdParams p;
-  p.S = static_cast<int>(seq); p.G = static_cast<int>(groups);
+  p.S = static_cast<int>(seq); p.G = static_cast<int>(groups); p.NB = static_cast<int>(nb);
   p.sc = scale * kLog2e;
   p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = ds->status_word;
-  dim3 grid(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
+  // persistent: two CTAs per SM walk over the (query block, head, batch) items, heavy ones first
+  const int64_t n_tiles = (seq / kBQ) * groups * nb;
+  const int64_t slots = 2 * static_cast<int64_t>(ds->sm_count);
+  const unsigned grid = static_cast<unsigned>(n_tiles < slots ? n_tiles : slots);
   attn_fwd_kernel<<<grid, kThreads, kFwdSmem, st>>>(tmQ, tmK, tmVt, p);
   MCB_CHECK_LAUNCH("attn_fwd_kernel");
   return MCB_OK;
