@@ -370,15 +370,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // ---------------------------------------------------------------------------------------------------------
 constexpr uint32_t kDqOffQ = 0;
 constexpr uint32_t kDqOffDO = kDqOffQ + kQBytes;
-constexpr int kDqStages = 3;
+constexpr int kDqStages = 4;
 constexpr uint32_t kDqOffStage = kDqOffDO + kQBytes;     // stages of a K and a V tile (8 KB each)
 constexpr uint32_t kDqStageBytes = 2 * kKBytes;
-constexpr uint32_t kDqOffDS = kDqOffStage + kDqStages * kDqStageBytes;
-constexpr uint32_t kDqOffBar = kDqOffDS + kPBytes;
+constexpr uint32_t kDqOffBar = kDqOffStage + kDqStages * kDqStageBytes;
 constexpr uint32_t kDqSmem = kDqOffBar + 256 + 1024;
 
 struct BwdParams {
-  int S, G;
+  int S, G, NB;
   float sc;     // scale * log2(e)
   float scale;
   const __nv_bfloat16* O;
@@ -392,6 +391,11 @@ struct BwdParams {
   int* status;
 };
 
+// Persistent like the forward: a CTA walks over (query block, head, batch) items, heavy first, and carries its
+// rings and barrier phases along (n = running number of a key block over all items of the CTA).
+// Tensor memory (256 columns): S double-buffered at 0 and 64 (the next blocks' Q K^T run under this block's
+// arithmetic), dP at 128, dQ at 192.  dS (bf16 pairs, 32 columns) is written over the first half of dP, which has
+// been read by then, and is the A operand of dQ += dS K straight from tensor memory.
 __global__ void __launch_bounds__(kThreads, 2)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
@@ -400,18 +404,22 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t q_full = base + kDqOffBar, kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * kDqStages;
-  const uint32_t sdp_full = kv_empty0 + 8 * kDqStages;
-  const uint32_t ds_ready = sdp_full + 8, dq_full = ds_ready + 8, tmem_slot = dq_full + 8, abort_addr = tmem_slot + 4;
+  const uint32_t q_full = base + kDqOffBar, q_free = q_full + 8, dq_full = q_free + 8, dq_free = dq_full + 8;
+  const uint32_t kv_full0 = dq_free + 8, kv_empty0 = kv_full0 + 8 * kDqStages;
+  const uint32_t s_full0 = kv_empty0 + 8 * kDqStages, s_free0 = s_full0 + 16;
+  const uint32_t dp_full = s_free0 + 16, ds_ready = dp_full + 8, tmem_slot = ds_ready + 8, abort_addr = tmem_slot + 4;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kDqStages; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 4);
+    mbar_init(q_free, 1);
     mbar_init(dq_full, 1);
+    mbar_init(dq_free, 4);
+    for (int s = 0; s < kDqStages; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(s_free0 + 8 * s, 4); }
+    mbar_init(dp_full, 1);
+    mbar_init(ds_ready, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -424,144 +432,201 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
-
-  const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-  const int g = blockIdx.y, nb = blockIdx.z;
-  const int nkb = 2 * qb + 2;
-  const int64_t qrow0 = (static_cast<int64_t>(nb) * p.G + g) * p.S + static_cast<int64_t>(qb) * kBQ;
+  const uint32_t tDP = tmem_base + 128, tDQ = tmem_base + 192;
+  FwdParams tp;   // the item order of the forward
+  tp.S = p.S; tp.G = p.G; tp.NB = p.NB;
+  const int n_tiles = (p.S / kBQ) * p.G * p.NB;
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * kQBytes);
-      tma_load_2d(base + kDqOffQ, &tmQ, q_full, 0, static_cast<int>(qrow0));
-      tma_load_2d(base + kDqOffDO, &tmdO, q_full, 0, static_cast<int>(qrow0));
-      for (int j = 0; j < nkb; ++j) {
-        const int st = j % kDqStages;
-        if (!mbar_wait(kv_empty0 + 8 * st, ((j / kDqStages) & 1) ^ 1, abort_flag, 81, p.status)) break;
-        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
-        mbar_expect_tx(kv_full0 + 8 * st, kDqStageBytes);
-        tma_load_2d(sb, &tmK, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
-        tma_load_2d(sb + kKBytes, &tmV, kv_full0 + 8 * st, 0, nb * p.S + j * kBK);
+      int st = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++it) {
+        const FwdTile w = fwd_tile(tp, t);
+        // the previous item's last S and dP products have read Q and dO
+        if (it > 0) ok = mbar_wait(q_free, (it - 1) & 1, abort_flag, 80, p.status);
+        if (!ok) break;
+        mbar_expect_tx(q_full, 2 * kQBytes);
+        tma_load_2d(base + kDqOffQ, &tmQ, q_full, 0, static_cast<int>(w.qrow0));
+        tma_load_2d(base + kDqOffDO, &tmdO, q_full, 0, static_cast<int>(w.qrow0));
+        for (int j = 0; j < w.nkb; ++j) {
+          ok = mbar_wait(kv_empty0 + 8 * st, ph ^ 1, abort_flag, 81, p.status);
+          if (!ok) break;
+          const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
+          mbar_expect_tx(kv_full0 + 8 * st, kDqStageBytes);
+          tma_load_2d(sb, &tmK, kv_full0 + 8 * st, 0, w.nb * p.S + j * kBK);
+          tma_load_2d(sb + kKBytes, &tmV, kv_full0 + 8 * st, 0, w.nb * p.S + j * kBK);
+          if (++st == kDqStages) { st = 0; ph ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);
-      auto issue_sdp = [&](int st) {
-        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
+      bool ok = true;
+      int it = 0;
+      uint32_t n0 = 0;
+      int sst = 0;                // ring stage and phase of the next block to get its S product
+      uint32_t sph = 0;
+      int dst = 0;                // ring stage of the next block to get its dP and dQ products
+      auto issue_s = [&](uint32_t n) -> bool {
+        if (n >= 2 && !mbar_wait(s_free0 + 8 * (n & 1), ((n - 2) >> 1) & 1, abort_flag, 82, p.status)) return false;
+        if (!mbar_wait(kv_full0 + 8 * sst, sph, abort_flag, 83, p.status)) return false;
+        tcgen05_fence_after();
+        const uint32_t sb = base + kDqOffStage + sst * kDqStageBytes;
 #pragma unroll
         for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tS, desc_sw128(base + kDqOffQ + k4 * 32), desc_sw128(sb + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tDP, desc_sw128(base + kDqOffDO + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
-        umma_commit(sdp_full);
+          umma_bf16(tmem_base + (n & 1) * 64, desc_sw128(base + kDqOffQ + k4 * 32), desc_sw128(sb + k4 * 32), idesc,
+                    k4 != 0 ? 1u : 0u);
+        umma_commit(s_full0 + 8 * (n & 1));
+        if (++sst == kDqStages) { sst = 0; sph ^= 1; }
+        return true;
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag, 82, p.status);
-      if (ok) ok = mbar_wait(kv_full0, 0, abort_flag, 83, p.status);
-      if (ok) {
-        tcgen05_fence_after();
-        issue_sdp(0);
-      }
-      for (int j = 0; ok && j < nkb; ++j) {
-        const int st = j % kDqStages;
-        ok = mbar_wait(ds_ready, j & 1, abort_flag, 84, p.status);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t sb = base + kDqOffStage + st * kDqStageBytes;
-        // dQ += dS_j K_j   (A = dS [128 x 64 keys] K-major; B = the K tile as it lies, [64 keys x 64 d]: N-major)
+      for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++it) {
+        const FwdTile w = fwd_tile(tp, t);
+        ok = mbar_wait(q_full, it & 1, abort_flag, 84, p.status);
+        for (int j = 0; ok && j < 2; ++j) ok = issue_s(n0 + j);   // nkb >= 2
+        for (int j = 0; ok && j < w.nkb; ++j) {
+          const uint32_t n = n0 + j;
+          const uint32_t sb = base + kDqOffStage + dst * kDqStageBytes;
+          // dP_j = dO V_j^T.  Its buffer (and the dS written over it) was last read by the dQ product of block
+          // n - 1, issued before this point (the tensor core runs them in order); the V tile arrived with the K
+          // tile that S_j has waited for.
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDQ, desc_sw128(base + kDqOffDS + k4 * 32), desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024),
-                    idesc | (1u << 16), (j | k4) != 0 ? 1u : 0u);
-        umma_commit(kv_empty0 + 8 * st);
-        if (j + 1 < nkb) {
-          const int s2 = (j + 1) % kDqStages;
-          ok = mbar_wait(kv_full0 + 8 * s2, ((j + 1) / kDqStages) & 1, abort_flag, 85, p.status);
+          for (int k4 = 0; k4 < kD / 16; ++k4)
+            umma_bf16(tDP, desc_sw128(base + kDqOffDO + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+          umma_commit(dp_full);
+          if (j == w.nkb - 1) umma_commit(q_free);   // Q and dO may be replaced by the next item's
+          if (j + 2 < w.nkb) {
+            ok = issue_s(n + 2);
+            if (!ok) break;
+          }
+          ok = mbar_wait(ds_ready, n & 1, abort_flag, 86, p.status);
+          // the first product of an item overwrites dQ: the previous item's write-out must have read it
+          if (ok && j == 0 && it > 0) ok = mbar_wait(dq_free, (it - 1) & 1, abort_flag, 87, p.status);
           if (!ok) break;
           tcgen05_fence_after();
-          issue_sdp(s2);
-        } else {
-          umma_commit(dq_full);
+          // dQ += dS_j K_j   (A = dS [128 x 64 keys] in tensor memory; B = the K tile as it lies: N-major)
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 16; ++k4)
+            umma_bf16_ts(tDQ, tDP + k4 * 8, desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024), idesc | (1u << 16),
+                         (j | k4) != 0 ? 1u : 0u);
+          umma_commit(kv_empty0 + 8 * dst);
+          if (j == w.nkb - 1) umma_commit(dq_full);
+          if (++dst == kDqStages) dst = 0;
         }
+        n0 += static_cast<uint32_t>(w.nkb);
       }
     }
   } else {
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
-    const int qpos = qb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* dsrow = gen_base + kDqOffDS + row * 128;
-    const int sw = row & 7;
-    // delta = sum_d dO * O of this row, straight from global memory (once per CTA)
-    float delta = 0.0f;
-    {
-      const uint4* o4 = reinterpret_cast<const uint4*>(p.O + (qrow0 + row) * kD);
-      const uint4* d4 = reinterpret_cast<const uint4*>(p.dO + (qrow0 + row) * kD);
+    bool ok = true;
+    uint32_t n0 = 0;
+    int it = 0;
+    for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++it) {
+      const FwdTile w = fwd_tile(tp, t);
+      const int qpos = w.qb * kBQ + row;
+      // delta = sum_d dO * O of this row, straight from global memory (once per item)
+      float delta = 0.0f;
+      {
+        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + (w.qrow0 + row) * kD);
+        const uint4* d4 = reinterpret_cast<const uint4*>(p.dO + (w.qrow0 + row) * kD);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 a = o4[c], b = d4[c];
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        for (int c = 0; c < 8; ++c) {
+          const uint4 a = o4[c], b = d4[c];
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          delta = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(bw[e] << 16), delta);
-          delta = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(bw[e] & 0xffff0000u), delta);
+          for (int e = 0; e < 4; ++e) {
+            delta = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(bw[e] << 16), delta);
+            delta = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(bw[e] & 0xffff0000u), delta);
+          }
         }
       }
-    }
-    const float lse2 = p.lse[qrow0 + row] * kLog2e;
-    p.delta[qrow0 + row] = delta;
-    p.lse2[qrow0 + row] = lse2;
-    bool ok = true;
-    for (int j = 0; j < nkb; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, j & 1, abort_flag, 86, p.status));
+      const float lse2 = p.lse[w.qrow0 + row] * kLog2e;
+      p.delta[w.qrow0 + row] = delta;
+      p.lse2[w.qrow0 + row] = lse2;
+      const float2 sc2 = f2(p.sc, p.sc), nl2 = f2(-lse2, -lse2), nd2 = f2(-delta, -delta);
+      for (int j = 0; j < w.nkb; ++j) {
+        const uint32_t n = n0 + j;
+        ok = __all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag, 88, p.status));
+        if (!ok) break;
+        tcgen05_fence_after();
+        const int key0 = j * kBK;
+        const bool diag = key0 + kBK - 1 > w.qb * kBQ;
+        // the row's 64 scores, read once; P = 2^(s*sc - lse2) takes their place in the registers
+        uint32_t sv[4][16];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tmem_base + (n & 1) * 64 + lane_addr + 16 * c4, sv[c4]);
+        tmem_ld_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free0 + 8 * (n & 1));   // the buffer may take block n + 2
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float2 tt = __ffma2_rn(f2(__uint_as_float(sv[c4][e]), __uint_as_float(sv[c4][e + 1])), sc2, nl2);
+            float p0 = ex2(tt.x), p1 = ex2(tt.y);
+            if (diag) {
+              if (key0 + 16 * c4 + e > qpos) p0 = 0.0f;
+              if (key0 + 16 * c4 + e + 1 > qpos) p1 = 0.0f;
+            }
+            sv[c4][e] = __float_as_uint(p0);
+            sv[c4][e + 1] = __float_as_uint(p1);
+          }
+        }
+        // dS = P (dP - delta), bf16 pairs written over the half of dP already read
+        ok = __all_sync(0xffffffffu, mbar_wait(dp_full, n & 1, abort_flag, 89, p.status));
+        if (!ok) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t vd[2][16];
+          tmem_ld_x16(tDP + lane_addr + 32 * h, vd[0]);
+          tmem_ld_x16(tDP + lane_addr + 32 * h + 16, vd[1]);
+          tmem_ld_wait();
+          uint32_t dw[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const uint32_t* pv = &sv[2 * h + (e >> 4)][e & 15];
+            const uint32_t* dv = &vd[e >> 4][e & 15];
+            const float2 d2 = __fadd2_rn(f2(__uint_as_float(dv[0]), __uint_as_float(dv[1])), nd2);
+            const float2 r2 = __fmul2_rn(f2(__uint_as_float(pv[0]), __uint_as_float(pv[1])), d2);
+            dw[e >> 1] = pack_bf16(r2.x, r2.y);
+          }
+          tmem_st_x16(tDP + lane_addr + 16 * h, dw);
+        }
+        tmem_st_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_ready);
+      }
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, 90, p.status));
       if (!ok) break;
       tcgen05_fence_after();
-      const int key0 = j * kBK;
-      const bool diag = key0 + kBK - 1 > qb * kBQ;
+      uint32_t qv[4][16];
 #pragma unroll
-      for (int c = 0; c < kBK; c += 16) {
-        uint32_t vs[16], vd[16];
-        tmem_ld_x16(tS + lane_addr + c, vs);
-        tmem_ld_x16(tDP + lane_addr + c, vd);
-        tmem_ld_wait();
-        uint32_t w[8];
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(vs[e]), p.sc, -lse2));
-          float p1 = ex2(fmaf(__uint_as_float(vs[e + 1]), p.sc, -lse2));
-          if (diag) {
-            if (key0 + c + e > qpos) p0 = 0.0f;
-            if (key0 + c + e + 1 > qpos) p1 = 0.0f;
-          }
-          w[e >> 1] = pack_bf16(p0 * (__uint_as_float(vd[e]) - delta), p1 * (__uint_as_float(vd[e + 1]) - delta));
-        }
-        const int cc = c >> 3;
-        *reinterpret_cast<uint4*>(dsrow + ((cc ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(dsrow + (((cc + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-      }
+      for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tDQ + lane_addr + 16 * c4, qv[c4]);
+      tmem_ld_wait();
       tcgen05_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
-    }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(dq_full, 0, abort_flag, 87, p.status));
-    if (ok) {
-      tcgen05_fence_after();
-      __nv_bfloat16* orow = p.dQ + (qrow0 + row) * kD;
+      if (lane == 0) mbar_arrive(dq_free);   // the next item's products may overwrite dQ
+      __nv_bfloat16* orow = p.dQ + (w.qrow0 + row) * kD;
 #pragma unroll
-      for (int c = 0; c < kD; c += 16) {
-        uint32_t v[16];
-        tmem_ld_x16(tDQ + lane_addr + c, v);
-        tmem_ld_wait();
-        uint32_t w[8];
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t ow[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2)
-          w[e >> 1] = pack_bf16(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale);
-        *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+          ow[e >> 1] = pack_bf16(__uint_as_float(qv[c4][e]) * p.scale, __uint_as_float(qv[c4][e + 1]) * p.scale);
+        *reinterpret_cast<uint4*>(orow + 16 * c4) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        *reinterpret_cast<uint4*>(orow + 16 * c4 + 8) = make_uint4(ow[4], ow[5], ow[6], ow[7]);
       }
+      n0 += static_cast<uint32_t>(w.nkb);
     }
   }
 
@@ -930,13 +995,16 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   if (int rc = encode(ds, &tmQ64, q, kD, nb * groups * seq, kBK, "Q step")) return rc;
   if (int rc = encode(ds, &tmdO64, dout, kD, nb * groups * seq, kBK, "dO step")) return rc;
   BwdParams p;
-  p.S = static_cast<int>(seq); p.G = static_cast<int>(groups);
+  p.S = static_cast<int>(seq); p.G = static_cast<int>(groups); p.NB = static_cast<int>(nb);
   p.sc = scale * kLog2e; p.scale = scale;
   p.O = static_cast<const __nv_bfloat16*>(o); p.dO = static_cast<const __nv_bfloat16*>(dout); p.lse = lse;
   p.delta = delta; p.lse2 = lse2;
   p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk); p.dV = static_cast<__nv_bfloat16*>(dv);
   p.status = ds->status_word;
-  dim3 gq(static_cast<unsigned>(seq / kBQ), static_cast<unsigned>(groups), static_cast<unsigned>(nb));
+  // persistent: two CTAs per SM walk over the (query block, head, batch) items, heavy ones first
+  const int64_t n_tiles = (seq / kBQ) * groups * nb;
+  const int64_t slots = 2 * static_cast<int64_t>(ds->sm_count);
+  const unsigned gq = static_cast<unsigned>(n_tiles < slots ? n_tiles : slots);
   attn_dq_kernel<<<gq, kThreads, kDqSmem, st>>>(tmQ128, tmdO128, tmK64, tmV64, p);
   MCB_CHECK_LAUNCH("attn_dq_kernel");
   dim3 gk(static_cast<unsigned>(nb), static_cast<unsigned>(seq / kBQ));
