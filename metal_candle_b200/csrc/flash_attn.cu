@@ -647,8 +647,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 // ---------------------------------------------------------------------------------------------------------
 // One CTA per SM: 2 control warps + 8 element-wise warps (two per tensor-memory lane quadrant, 32 of the 64 query
 // columns each; no row reductions are needed here because the log-sum-exp is known).  Loads are double-buffered,
-// S^T / dP^T are double-buffered in tensor memory and P^T / dS^T in shared memory, so the tensor core computes
-// the next step's S^T, dP^T while the element-wise warps work on the current one.
+// S^T / dP^T are double-buffered in tensor memory and so are P^T / dS^T (bf16 pairs, handed to the dV / dK products
+// as tensor-memory A operands), so the tensor core computes the next step's S^T, dP^T while the element-wise
+// warps work on the current one.
 constexpr int kKvThreads = 320;
 constexpr uint32_t kKvOffK = 0;                       // K block [128 keys x 64]
 constexpr uint32_t kKvOffV = kKvOffK + kQBytes;
@@ -656,9 +657,7 @@ constexpr int kKvStages = 4;
 constexpr uint32_t kKvOffStage = kKvOffV + kQBytes;   // per stage: Q and dO tiles (8 KB each), then lse2 and delta (256 B each)
 constexpr uint32_t kKvStageBytes = 2 * kKBytes + 512;
 constexpr uint32_t kKvStageStride = 2 * kKBytes + 1024;
-constexpr uint32_t kKvOffP = kKvOffStage + kKvStages * kKvStageStride;   // two buffers of P^T, then two of dS^T
-constexpr uint32_t kKvOffDS = kKvOffP + 2 * kPBytes;
-constexpr uint32_t kKvOffBar = kKvOffDS + 2 * kPBytes;
+constexpr uint32_t kKvOffBar = kKvOffStage + kKvStages * kKvStageStride;
 constexpr uint32_t kKvSmem = kKvOffBar + 256 + 1024;
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -698,8 +697,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  // columns: S^T buffers at 0 and 128, dP^T at 64 and 192, dV at 256, dK at 320
-  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 320;
+  // columns: S^T buffers at 0 and 128, dP^T at 64 and 192, dV at 256, dK at 320, then per buffer P^T (32 columns
+  // of bf16 pairs) and dS^T (32): 384 / 416 and 448 / 480
+  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 320, tPT0 = tmem_base + 384;
 
   const int kb = blockIdx.y, nb = blockIdx.x;   // all kv heads of key block 0 (the most query steps) start first
   const int nq = p.S / kBK;                      // query steps of 64 per head
@@ -728,17 +728,21 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kBK);
+      // descriptors of the resident K / V block and of stage 0's Q / dO tiles (K-major for S^T and dP^T, as N-major
+      // B operands for dV and dK), built once; a stage or a K slice further is one add
+      const uint64_t dK = desc_sw128(base + kKvOffK), dV = desc_sw128(base + kKvOffV);
+      const uint64_t dQk = desc_sw128(base + kKvOffStage), dQn = desc_sw128_mn(base + kKvOffStage, kKBytes, 1024);
       // S^T = K Q^T, dP^T = V dO^T of step t into tensor-memory buffer t & 1
       auto issue_sdp = [&](int t) {
         const int st = t & 1;
-        const uint32_t sb = base + kKvOffStage + (t % kKvStages) * kKvStageStride;
+        const uint32_t so = static_cast<uint32_t>(t % kKvStages) * kKvStageStride;
         const uint32_t tS = tmem_base + st * 128, tDP = tS + 64;
+        // the two accumulation chains are independent: interleaved, one product's latency hides the other's
 #pragma unroll
-        for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tS, desc_sw128(base + kKvOffK + k4 * 32), desc_sw128(sb + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k4 = 0; k4 < kD / 16; ++k4)
-          umma_bf16(tDP, desc_sw128(base + kKvOffV + k4 * 32), desc_sw128(sb + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+        for (int k4 = 0; k4 < kD / 16; ++k4) {
+          umma_bf16(tS, desc_advance(dK, k4 * 32), desc_advance(dQk, so + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+          umma_bf16(tDP, desc_advance(dV, k4 * 32), desc_advance(dQk, so + kKBytes + k4 * 32), idesc, k4 != 0 ? 1u : 0u);
+        }
         umma_commit(sdp_full0 + 8 * st);
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, 92, p.status);
@@ -761,17 +765,18 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         if (!ok) break;
         tcgen05_fence_after();
         const int ls = t % kKvStages;
-        const uint32_t sb = base + kKvOffStage + ls * kKvStageStride;
-        // dV += P^T dO, dK += dS^T Q   (A = P^T / dS^T [128 keys x 64 queries] K-major; B = the dO / Q tile as it
-        // lies, [64 queries x 64 d]: N-major, 16 queries further = two 8-row groups of 1024 bytes)
+        const uint32_t so = static_cast<uint32_t>(ls) * kKvStageStride;
+        // dV += P^T dO, dK += dS^T Q   (A = P^T / dS^T [128 keys x 64 queries] in tensor memory, 16 queries = 8
+        // columns; B = the dO / Q tile as it lies, [64 queries x 64 d]: N-major, 16 queries further = two 8-row
+        // groups of 1024 bytes)
+        const uint32_t acc = t != 0 ? 1u : 0u;
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDV, desc_sw128(base + kKvOffP + st * kPBytes + k4 * 32), desc_sw128_mn(sb + kKBytes + k4 * 2048, kKBytes, 1024),
-                    idesc | (1u << 16), (t | k4) != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)
-          umma_bf16(tDK, desc_sw128(base + kKvOffDS + st * kPBytes + k4 * 32), desc_sw128_mn(sb + k4 * 2048, kKBytes, 1024),
-                    idesc | (1u << 16), (t | k4) != 0 ? 1u : 0u);
+        for (int k4 = 0; k4 < kBK / 16; ++k4) {
+          umma_bf16_ts(tDV, tPT0 + st * 64 + k4 * 8, desc_advance(dQn, so + kKBytes + k4 * 2048), idesc | (1u << 16),
+                       k4 != 0 ? 1u : acc);
+          umma_bf16_ts(tDK, tPT0 + st * 64 + 32 + k4 * 8, desc_advance(dQn, so + k4 * 2048), idesc | (1u << 16),
+                       k4 != 0 ? 1u : acc);
+        }
         umma_commit(ld_empty0 + 8 * ls);
         if (t + 1 == nsteps) umma_commit(out_full);
       }
@@ -782,7 +787,6 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     const int row = quad * 32 + lane;
     const int key = kb * kBQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const int sw = row & 7;
     bool ok = true;
     for (int t = 0; t < nsteps; ++t) {
       const int st = t & 1;
@@ -791,8 +795,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t tS = tmem_base + st * 128 + lane_addr, tDP = tS + 64;
-      uint8_t* prow = gen_base + kKvOffP + st * kPBytes + row * 128;
-      uint8_t* dsrow = gen_base + kKvOffDS + st * kPBytes + row * 128;
+      // this warp's 32 query columns are 16 packed columns of each of P^T and dS^T
+      const uint32_t tPT = tPT0 + st * 64 + lane_addr + half * 16;
+      uint32_t wp[16], wd[16];
       const float* st_lse2 = reinterpret_cast<const float*>(gen_base + kKvOffStage + (t % kKvStages) * kKvStageStride + 2 * kKBytes);
       const float* st_delta = st_lse2 + 64;
       const int q0 = i * kBK;
@@ -812,7 +817,6 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           dl[e] = b.x; dl[e + 1] = b.y; dl[e + 2] = b.z; dl[e + 3] = b.w;
         }
         tmem_ld_wait();
-        uint32_t wp[8], wd[8];
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
           float p0 = ex2(fmaf(__uint_as_float(vs[e]), p.sc, -l2[e]));
@@ -821,17 +825,14 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
             if (key > q0 + c + e) p0 = 0.0f;
             if (key > q0 + c + e + 1) p1 = 0.0f;
           }
-          wp[e >> 1] = pack_bf16(p0, p1);
-          wd[e >> 1] = pack_bf16(p0 * (__uint_as_float(vd[e]) - dl[e]), p1 * (__uint_as_float(vd[e + 1]) - dl[e + 1]));
+          wp[(cb + e) >> 1] = pack_bf16(p0, p1);
+          wd[(cb + e) >> 1] = pack_bf16(p0 * (__uint_as_float(vd[e]) - dl[e]), p1 * (__uint_as_float(vd[e + 1]) - dl[e + 1]));
         }
-        const int cc = c >> 3;
-        *reinterpret_cast<uint4*>(prow + ((cc ^ sw) << 4)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-        *reinterpret_cast<uint4*>(prow + (((cc + 1) ^ sw) << 4)) = make_uint4(wp[4], wp[5], wp[6], wp[7]);
-        *reinterpret_cast<uint4*>(dsrow + ((cc ^ sw) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
-        *reinterpret_cast<uint4*>(dsrow + (((cc + 1) ^ sw) << 4)) = make_uint4(wd[4], wd[5], wd[6], wd[7]);
       }
+      tmem_st_x16(tPT, wp);
+      tmem_st_x16(tPT + 32, wd);
+      tmem_st_wait();
       tcgen05_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_ready0 + 8 * (t & 1));
     }

@@ -207,6 +207,12 @@ __device__ __forceinline__ uint64_t desc_sw128_mn(uint32_t saddr, uint32_t lbo, 
   return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo >> 4) << 16) |
          (static_cast<uint64_t>(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
+// A descriptor moved by `bytes` (a multiple of 16) within shared memory: one 32-bit add on its low word.  Lets the
+// issuing thread build the descriptors of a tile once and step through stages and K slices cheaply.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) {
+  const uint32_t lo = static_cast<uint32_t>(d) + (bytes >> 4);
+  return (d & 0xFFFFFFFF00000000ull) | lo;
+}
 // Instruction descriptor with the A operand MN-major (bit 15) and B K-major.
 __host__ __device__ constexpr uint32_t make_idesc_a_mn(int n) { return make_idesc(n) | (1u << 15); }
 
