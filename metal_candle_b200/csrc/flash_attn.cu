@@ -7,23 +7,24 @@
 //   K, V  [nb, S, 64]
 //   LSE [nb, G*S] float32: log-sum-exp of the scaled scores of a row (natural log), kept for the backward
 //
-// Forward: one CTA per (128 queries, head); key blocks of 64.  Warp 0 streams K / V tiles by TMA into a
-// two-stage ring, warp 1 issues the tensor-core MMAs (S = Q K^T into tensor memory, then O_blk = P V),
-// warps 2-5 do the online softmax with one query row per thread: read S from tensor memory (once), rescale, write
-// P (bf16) into shared memory in the 128-byte-swizzled K-major operand layout; O accumulates in tensor
-// memory and is rescaled there (tcgen05.ld / tcgen05.st) only when a row maximum has grown by more than
-// 2^8.  S is double-buffered in tensor memory, so the next block's Q K^T runs under this block's softmax;
-// two CTAs per SM.
+// Forward: persistent CTAs (two per SM) walk over (128 queries, head) items, heavy ones first; key blocks of 64.
+// Warp 0 streams K / V tiles by TMA into a four-stage ring, warp 1 issues the tensor-core MMAs (S = Q K^T into
+// one of two tensor-memory buffers, two blocks ahead of the softmax; then O += P V with P read from tensor
+// memory), warps 2-5 do the online softmax with one query row per thread: read S from tensor memory (once),
+// write P (bf16 pairs) back into tensor memory; O accumulates in tensor memory and is rescaled there
+// (tcgen05.ld / tcgen05.st) only when a row maximum has grown by more than 2^8.
 //
 // Backward: two kernels, each recomputes the probabilities from Q, K and the saved log-sum-exp, so that no
 // [S, S] tensor is ever stored and nothing is accumulated with atomics:
-//   dq kernel   one CTA per (128 queries, head), key blocks of 64, one query row per thread:
-//               S = Q K^T and dP = dO V^T into tensor memory, P = exp(scale*S - lse), dS = P (dP - delta) with
-//               delta = rowsum(dO * O), dS (bf16) through shared memory, dQ += dS K accumulated in tensor memory.
+//   dq kernel   persistent like the forward, key blocks of 64, one query row per thread:
+//               S = Q K^T (double-buffered, ahead) and dP = dO V^T into tensor memory, P = exp(scale*S - lse),
+//               dS = P (dP - delta) with delta = rowsum(dO * O), dS (bf16 pairs) written over the half of dP already
+//               read, dQ += dS K accumulated in tensor memory with dS as a tensor-memory A operand.
 //               It also writes delta and lse*log2(e) for the second kernel.
 //   dkv kernel  one CTA per (128 keys, kv head), steps of 64 queries over the heads of the group, one key row
-//               per thread pair: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T through shared memory, dV += P^T dO and
-//               dK += dS^T Q accumulated in tensor memory over all steps (which also sums over the group).
+//               per thread pair: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T back into tensor memory (A operands),
+//               dV += P^T dO and dK += dS^T Q accumulated in tensor memory over all steps (which also sums over
+//               the group).
 // Operands whose reduction index is the slow one in memory (V in P V, K in dS K, dO and Q in the dK / dV
 // products) are used as they lie, as N-major B operands (instruction-descriptor bit 16); nothing is transposed.
 // Every wait is bounded; on expiry the CTA records a code in the device status word and leaves.
