@@ -116,8 +116,17 @@ def device_status() -> int:
     return out.value
 
 
+_profiling = False
+
+
 def profile_enable(on: bool) -> None:
+    global _profiling
     check(load().mcb_profile_enable(int(on)))
+    _profiling = bool(on)
+
+
+def profile_enabled() -> bool:
+    return _profiling
 
 
 def profile_summary(kind: int):

@@ -76,6 +76,21 @@ class _Linear:
         return self.lora.lora_a, self.lora.lora_b, self.lora.config.scaling()
 
 
+class CapturedStep:
+    """forward_backward of a fixed shape as a CUDA graph (Qwen.capture_forward_backward)."""
+
+    def __init__(self, graph, ids, targets, loss, grads):
+        self.graph, self.ids, self.targets, self.loss, self.grads = graph, ids, targets, loss, grads
+
+    def __call__(self, input_ids: torch.Tensor, target_ids: torch.Tensor):
+        """Copies the batch into the graph's input buffers (device to device, or from pinned host memory) and
+        replays; returns (loss, grads) like Qwen.forward_backward - the same tensors on every call."""
+        self.ids.copy_(input_ids, non_blocking=True)
+        self.targets.copy_(target_ids, non_blocking=True)
+        self.graph.replay()
+        return self.loss, self.grads
+
+
 class Qwen:
     """Random-init weights N(0, 0.02^2) for embedding and projections, norm weights 1, biases 0."""
 
@@ -325,6 +340,30 @@ class Qwen:
             if self.layer_done_hook is not None:
                 self.layer_done_hook(idx)
         return loss[:1], self._grad_views
+
+    def capture_forward_backward(self, batch: int, seq: int) -> "CapturedStep":
+        """Records forward_backward for one (batch, seq) shape into a CUDA graph.  The step is some thousand
+        short launches; replayed from a graph they run back to back without the host in the loop.  Call it
+        after at least one eager forward_backward of the same shape (kernel attributes and cached workspaces
+        are set up on first use, which must not happen during capture).  The adapter's tensors are read in
+        place, so optimizer updates between replays are seen; inputs go into the returned object's `ids` and
+        `targets` buffers."""
+        if self.lora_adapter is None:
+            raise TrainingError("capture_forward_backward needs an adapter (apply_adapter)")
+        ids = torch.zeros(batch, seq, dtype=torch.int32, device=self.device)
+        targets = torch.full((batch, seq), -1, dtype=torch.int32, device=self.device)
+        hook, self.layer_done_hook = self.layer_done_hook, None   # no host callbacks inside a graph
+        was_profiling = _lib.profile_enabled()
+        _lib.profile_enable(False)                                # per-launch events cannot be recorded either
+        graph = torch.cuda.CUDAGraph()
+        try:
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                loss, grads = self.forward_backward(ids, targets)
+        finally:
+            self.layer_done_hook = hook
+            _lib.profile_enable(was_profiling)
+        return CapturedStep(graph, ids, targets, loss, grads)
 
     def _layer_bwd(self, dh3, L, sv, idx, B, S, accumulate):
         c = self.config

@@ -58,6 +58,11 @@ def _worker(rank, world, port, out):
             want = torch.arange(model.flat.numel(), dtype=torch.float32) * sum(r + 1 for r in range(world))
             assert torch.equal(model.flat, want)
             assert dp.pending == []
+        # the graph-replay path: no per-layer callbacks, one all-reduce of the whole buffer afterwards
+        model.layer_done_hook = None
+        model.backward(rank)
+        dp.reduce_all()
+        assert torch.equal(model.flat, want)
         out.put((rank, "ok"))
     except Exception as e:  # report instead of hanging the parent
         out.put((rank, repr(e)))

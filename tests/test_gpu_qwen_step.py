@@ -193,3 +193,42 @@ def test_gradient_accumulation_matches_one_big_batch(cuda_device):
     _, g_acc = model.forward_backward(torch.from_numpy(ids[2:]).to(dev), torch.from_numpy(tg[2:]).to(dev), accumulate=True)
     for a, b in zip(g_all, g_acc):
         assert torch.allclose(a, 0.5 * b, rtol=1e-4, atol=1e-7)
+
+
+def test_captured_step_matches_eager(cuda_device):
+    """forward_backward replayed from a CUDA graph gives bit-for-bit the loss and gradients of the eager call
+    (the kernels are deterministic), for the capture batch and for a different batch copied in afterwards, and
+    sees optimizer updates made between replays."""
+    from metal_candle_b200 import _lib
+    from metal_candle_b200.training import AdamW, AdamWConfig, TrainingStep
+
+    cfg, model, adapter = build(cuda_device, torch.bfloat16, all_targets(), cfg=fused_attention_config())
+    seq = 128
+    batches = []
+    for seed in (11, 12):
+        ids, tg = batch(seed, 2, seq, cfg.vocab_size)
+        tg = np.where(tg == R.IGNORE_INDEX, -1, tg)
+        batches.append((torch.from_numpy(ids).to(cuda_device).to(torch.int32),
+                        torch.from_numpy(tg).to(cuda_device).to(torch.int32)))
+    eager = []
+    for ids, tg in batches:
+        loss, grads = model.forward_backward(ids, tg)
+        eager.append((loss.clone(), [g.clone() for g in grads]))
+    step = model.capture_forward_backward(2, seq)
+    for (ids, tg), (want_loss, want_grads) in zip(batches, eager):
+        loss, grads = step(ids, tg)
+        torch.cuda.synchronize()
+        assert torch.equal(loss, want_loss)
+        for g, w in zip(grads, want_grads):
+            assert torch.equal(g, w)
+    # an optimizer step changes the adapter in place; the next replay must use the new values
+    opt = AdamW(AdamWConfig(learning_rate=1e-2))
+    opt.step_vars(TrainingStep.collect_trainable_vars(adapter), step.grads)
+    want_loss, want_grads = model.forward_backward(*batches[0])
+    want_loss, want_grads = want_loss.clone(), [g.clone() for g in want_grads]
+    loss, grads = step(*batches[0])
+    torch.cuda.synchronize()
+    assert torch.equal(loss, want_loss) and not torch.equal(loss, eager[0][0])
+    for g, w in zip(grads, want_grads):
+        assert torch.equal(g, w)
+    assert _lib.device_status() == 0
