@@ -10,7 +10,8 @@ namespace mcb {
 namespace umma {
 
 constexpr int BM = 128;  // rows of every accumulator tile (tensor-memory lanes)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // waits on global-memory flags (rare, long)
+constexpr long long kWaitLimitCycles = 4000000000ll;          // waits on mbarriers: about two seconds of SM cycles
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -40,15 +41,20 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).  The limit is counted
+// on the SM's own cycle counter, read (like the abort flag) only every 16th poll: the global nanosecond timer is
+// slow to read, and a wait that has to poll at all must not pay for that on the critical path of a handshake.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                           int* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  while (true) {
+  long long t0 = 0;
+  for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 15u) != 0) continue;
     if (*abort_flag != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    const long long now = clock64();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > kWaitLimitCycles) {
       *abort_flag = code;
       atomicCAS(status, 0, code);
       return false;
