@@ -96,7 +96,10 @@ int mcb_lora_linear_fwd(const void* x, const void* W, const void* bias, const fl
  *   W      [K,N] (w_layout MCB_W_IN_OUT) for bf16; either layout for f32
  *   h_save from the forward; null makes the call recompute it
  *   dx     [M,K] dtype, or null to skip;  dA [K,r], dB [r,N] float32, or both null to skip
- *   accumulate != 0 adds into dA/dB instead of overwriting (gradient accumulation). */
+ *   accumulate != 0 adds into dA/dB instead of overwriting (gradient accumulation).
+ * bf16: with h_save given, both gradients asked for and K, N multiples of 64 up to 1024 (and N < 1536), the token
+ * reductions for dA and dB run in the same kernel launch as dx, as its tail phase; a small kernel then sums
+ * the per-CTA partials in a fixed order (results do not depend on which form ran beyond float32 summation order). */
 int mcb_lora_linear_bwd(const void* x, const void* W, const float* A, const float* B, const void* dy,
                         const void* h_save, void* dx, float* dA, float* dB, int accumulate,
                         int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
