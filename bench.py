@@ -12,7 +12,7 @@ Kernel micro-benchmarks (one JSON line per case; used for the roofline sweeps an
     python bench.py --micro rmsnorm --rows 114688 --D 896  [--dtype bf16|f32]
     python bench.py --micro softmax --rows 114688 --D 1024 [--dtype bf16|f32]
     python bench.py --micro adamw   --n 67108864
-    python bench.py --sweep c2 | c3          the BASELINE row-kernel / LoRA-GEMM sweeps
+    python bench.py --sweep c2 | c3          the row-kernel / LoRA-GEMM sweeps of the benchmark configurations
 
 All inputs are synthetic (seeded torch generators on the device; shapes and value distributions of the
 benchmark configurations).  Kernel timings use CUDA events on the launching stream and rotate through

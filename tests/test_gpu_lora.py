@@ -66,7 +66,7 @@ def run_case(dev, dtype, M, K, N, r, seed=11, with_bias=True, save_h=True):
     assert _lib.device_status() == 0
 
 
-# BASELINE config 1 (M = 4*128, 768 -> 768, r = 8) first, then Qwen2.5-0.5B projection shapes, ragged
+# The reference benchmark shape (M = 4*128, 768 -> 768, r = 8) first, then Qwen2.5-0.5B projection shapes, ragged
 # sizes (M, N, K not multiples of the tiles), and the rank range of tests/custom_ops_correctness.rs.
 CASES = [
     (512, 768, 768, 8),
