@@ -159,6 +159,14 @@ int mcb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, floa
                     int64_t rows, int64_t D, float eps, int dtype,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same with one more operand fused into the store: dx = (gradient through the norm) + dx_residual, where
+ * dx_residual [rows,D] dtype is the gradient that reaches the same tensor along the residual connection
+ * (src/models/qwen.rs:121,140: the block input feeds both the norm and the skip path).  Null means none.
+ * dx may be the dx_residual buffer itself when rows are whole, 16-byte aligned vectors. */
+int mcb_rmsnorm_bwd_ex(const void* x, const void* w, const void* dy, const void* dx_residual, void* dx,
+                       float* dw, int accumulate, int64_t rows, int64_t D, float eps, int dtype,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* The same reverse pass for callers that cannot allocate device memory at all -- for example a host
  * runtime that has already handed every byte of the GPU to its own memory pool, or a service thread that
  * must never hit the device-wide synchronisation an allocation implies -- and so can neither cudaMalloc a

@@ -57,6 +57,7 @@ SIGNATURES = {
     "mcb_rmsnorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
     "mcb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "mcb_rmsnorm_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
+    "mcb_rmsnorm_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp, _sz, _vp]),
     "mcb_rmsnorm_bwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _f32, _i32, _vp]),
     "mcb_softmax_fwd": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
     "mcb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),

@@ -303,19 +303,31 @@ def rms_norm_fused(x: torch.Tensor, eps: float, weight: torch.Tensor | None = No
     return (y, rstd) if return_rstd else y
 
 
-def rms_norm_backward(x, weight, dy, eps, need_dw=True, grad_w=None, accumulate=False):
+def rms_norm_backward(x, weight, dy, eps, need_dw=True, grad_w=None, accumulate=False, dx_residual=None):
+    """dx (and dw) of rms_norm_fused.  `dx_residual`, if given, is added to dx inside the kernel (the gradient that
+    reaches the same tensor along the residual connection)."""
     rows, D = _rows(x, "rms_norm_backward")
-    _require_cuda(x, weight, dy, grad_w)
+    _require_cuda(x, weight, dy, grad_w, dx_residual)
     lib = _lib_for(x)
-    dx = torch.empty_like(x)
+    if dx_residual is not None:
+        if dx_residual.shape != x.shape or dx_residual.dtype != x.dtype or not dx_residual.is_contiguous():
+            raise ValueError("rms_norm_backward: dx_residual must match x in shape, dtype and be contiguous")
+        dx = torch.empty_like(x)   # (the kernel could write over dx_residual; shapes it declines could not)
+    else:
+        dx = torch.empty_like(x)
     if need_dw and grad_w is None:
         grad_w = torch.empty(D, dtype=torch.float32, device=x.device)
         accumulate = False
     nws = lib.mcb_rmsnorm_bwd_workspace_bytes(rows, D) if need_dw else 0
     ws = workspace(x.device, nws)
-    _lib.check(lib.mcb_rmsnorm_bwd(_ptr(x), _ptr(weight), _ptr(dy), _ptr(dx), _ptr(grad_w) if need_dw else None,
-                                   int(bool(accumulate)), rows, D, float(eps), _dtype_code(x), _ptr(ws), ws.numel(),
-                                   _stream()))
+    if dx_residual is not None:
+        _lib.check(lib.mcb_rmsnorm_bwd_ex(_ptr(x), _ptr(weight), _ptr(dy), _ptr(dx_residual), _ptr(dx),
+                                          _ptr(grad_w) if need_dw else None, int(bool(accumulate)), rows, D, float(eps),
+                                          _dtype_code(x), _ptr(ws), ws.numel(), _stream()))
+    else:
+        _lib.check(lib.mcb_rmsnorm_bwd(_ptr(x), _ptr(weight), _ptr(dy), _ptr(dx), _ptr(grad_w) if need_dw else None,
+                                       int(bool(accumulate)), rows, D, float(eps), _dtype_code(x), _ptr(ws), ws.numel(),
+                                       _stream()))
     return dx, (grad_w if need_dw else None)
 
 

@@ -20,7 +20,7 @@ enum Op { kRmsFwd = 0, kRmsBwd = 1, kSmFwd = 2, kSmBwd = 3 };
 template <typename T>
 int try_launch(int op, const void* in0, const void* in1, const void* w, void* out, float* rstd, float* dw_part,
                int* dw_blocks, int64_t rows, int64_t D, float eps, int causal_seq, float scale, const DeviceState* ds,
-               cudaStream_t st);
+               cudaStream_t st, const void* res = nullptr);
 }  // namespace rowpipe
 namespace {
 
@@ -573,7 +573,7 @@ int bwd_blocks(int64_t rows, int tpr, int sm_count, bool need_dw, int elem_bytes
 template <typename T>
 int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
                   int64_t rows, int64_t D, float eps, void* ws, size_t ws_bytes, cudaStream_t st,
-                  const DeviceState* ds) {
+                  const DeviceState* ds, const void* res = nullptr) {
   if (dw != nullptr && ws_bytes < mcb_rmsnorm_bwd_workspace_bytes(rows, D))
     return fail(MCB_ERR_WORKSPACE, "rmsnorm_bwd: workspace %zu < %zu bytes", ws_bytes,
                 mcb_rmsnorm_bwd_workspace_bytes(rows, D));
@@ -581,7 +581,7 @@ int rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, float*
   {
     int blocks = 0;
     const int rc = rowpipe::try_launch<T>(rowpipe::kRmsBwd, x, dy, w, dx, nullptr, dw ? (float*)ws : nullptr, &blocks, rows, D,
-                                          eps, 0, 1.0f, ds, st);
+                                          eps, 0, 1.0f, ds, st, res);
     if (rc == MCB_OK && dw != nullptr) {
       colsum_partials_kernel<<<(unsigned)((D + 31) / 32), 256, 0, st>>>((const float*)ws, dw, blocks, (int)D, accumulate);
       MCB_CHECK_LAUNCH("rmsnorm_dw_reduce");
@@ -707,6 +707,42 @@ extern "C" size_t mcb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t D) {
   size_t partials = static_cast<size_t>(kMaxDwBlocks) * static_cast<size_t>(D) * sizeof(float);
   size_t per_row = static_cast<size_t>(rows) * sizeof(float);
   return partials > per_row ? partials : per_row;
+}
+
+extern "C" int mcb_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
+
+extern "C" int mcb_rmsnorm_bwd_ex(const void* x, const void* w, const void* dy, const void* dx_residual, void* dx,
+                                  float* dw, int accumulate, int64_t rows, int64_t D, float eps, int dtype,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  if (dx_residual == nullptr)
+    return mcb_rmsnorm_bwd(x, w, dy, dx, dw, accumulate, rows, D, eps, dtype, workspace, workspace_bytes, stream);
+  if (!x || !dy || !dx) return fail(MCB_ERR_NULL, "rmsnorm_bwd_ex: x, dy or dx is null");
+  if (int rc = check_rows("rmsnorm_bwd_ex", rows, D, dtype)) return rc;
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  if (ds->sm_count > 256) return fail(MCB_ERR_UNSUPPORTED, "rmsnorm_bwd_ex: more than 256 SMs");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The bulk-copy pipeline adds the residual as it writes dx.  Shapes it declines (rows that are not whole
+  // 16-byte vectors, unaligned operands) take the plain kernels and one more element-wise pass.
+  {
+    int blocks = 0;
+    const bool has_ws = dw == nullptr || (workspace != nullptr && workspace_bytes >= mcb_rmsnorm_bwd_workspace_bytes(rows, D));
+    if (!has_ws) return fail(MCB_ERR_WORKSPACE, "rmsnorm_bwd_ex: workspace %zu < %zu bytes", workspace_bytes,
+                             mcb_rmsnorm_bwd_workspace_bytes(rows, D));
+    const int rc = dtype == MCB_F32
+        ? rowpipe::try_launch<float>(rowpipe::kRmsBwd, x, dy, w, dx, nullptr, dw ? (float*)workspace : nullptr, &blocks,
+                                     rows, D, eps, 0, 1.0f, ds, st, dx_residual)
+        : rowpipe::try_launch<__nv_bfloat16>(rowpipe::kRmsBwd, x, dy, w, dx, nullptr, dw ? (float*)workspace : nullptr,
+                                             &blocks, rows, D, eps, 0, 1.0f, ds, st, dx_residual);
+    if (rc == MCB_OK && dw != nullptr) {
+      colsum_partials_kernel<<<(unsigned)((D + 31) / 32), 256, 0, st>>>((const float*)workspace, dw, blocks, (int)D, accumulate);
+      MCB_CHECK_LAUNCH("rmsnorm_dw_reduce");
+    }
+    if (rc != 1) return rc;
+  }
+  if (dx == dx_residual) return fail(MCB_ERR_UNSUPPORTED, "rmsnorm_bwd_ex: dx may alias dx_residual only for rows of whole, aligned 16-byte vectors");
+  if (int rc = mcb_rmsnorm_bwd(x, w, dy, dx, dw, accumulate, rows, D, eps, dtype, workspace, workspace_bytes, stream)) return rc;
+  return mcb_add(dx, dx_residual, dx, rows * D, dtype, stream);
 }
 
 extern "C" int mcb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,

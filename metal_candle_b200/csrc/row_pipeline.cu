@@ -33,6 +33,7 @@ struct Params {
   const void* in1;   // dy (backward ops) or null
   const void* w;     // rmsnorm weight or null
   void* out;         // y / dx
+  const void* res;   // rms bwd: [rows, D] added to dx (a second gradient of the same tensor), or null
   float* rstd;       // rms fwd, optional
   float* dw_part;    // rms bwd with dw: [gridDim.x][D] partial sums
   int64_t rows;
@@ -294,9 +295,12 @@ rowpipe_kernel(const Params p) {
           const float c = gx * rinv * inv_d;
           const float2 r2 = f2(rinv, rinv), nc2 = f2(-c, -c);
           // pass 2: dx = rinv * (dy*w - xhat*c), dw += dy*xhat
+          const T* rrow = p.res != nullptr ? static_cast<const T*>(p.res) + row * p.D : nullptr;
           auto body = [&](int vi, float* dw_slot) {
-            V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            V a, b, rr; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
             b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
+            // the residual comes straight from global memory (read once, streaming), issued ahead of the arithmetic
+            if (rrow != nullptr) rr.raw = __ldcs(reinterpret_cast<const decltype(rr.raw)*>(rrow) + vi);
             float x[N], g[N], o[N]; a.to_float(x); b.to_float(g);
 #pragma unroll
             for (int j = 0; j < N; j += 2) {
@@ -310,6 +314,12 @@ rowpipe_kernel(const Params p) {
               if (wsm != nullptr) gw = __fmul2_rn(gg, *reinterpret_cast<const float2*>(wsm + vi * N + j));
               const float2 u = __fmul2_rn(__ffma2_rn(xh, nc2, gw), r2);
               o[j] = u.x; o[j + 1] = u.y;
+            }
+            if (rrow != nullptr) {
+              float rf[N];
+              rr.to_float(rf);
+#pragma unroll
+              for (int j = 0; j < N; ++j) o[j] += rf[j];
             }
             a.from_float(o);
             __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
@@ -557,9 +567,10 @@ int launch_w(int W, const Params& p, int grid, size_t smem, cudaStream_t st) {
 template <typename T>
 int try_launch(int op, const void* in0, const void* in1, const void* w, void* out, float* rstd, float* dw_part,
                int* dw_blocks, int64_t rows, int64_t D, float eps, int causal_seq, float scale, const DeviceState* ds,
-               cudaStream_t st) {
+               cudaStream_t st, const void* res) {
   constexpr int N = Vec16<T>::N;
   if (D % N != 0 || D > (1 << 20)) return 1;
+  if (res != nullptr && (op != kRmsBwd || !aligned16(res))) return 1;
   if (!aligned16(in0) || !aligned16(out) || (in1 && !aligned16(in1)) || (w && !aligned16(w))) return 1;
   const int n_streams = (op == kRmsBwd || op == kSmBwd) ? 2 : 1;
   const int64_t row_bytes = D * static_cast<int64_t>(sizeof(T));
@@ -612,7 +623,7 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
     if (static_cast<int64_t>(R) * D * 4 > static_cast<int64_t>(stages) * R * row_bytes * n_streams) return 1;
   }
   Params p;
-  p.in0 = in0; p.in1 = in1; p.w = w; p.out = out; p.rstd = rstd; p.dw_part = dw_part;
+  p.in0 = in0; p.in1 = in1; p.w = w; p.out = out; p.res = res; p.rstd = rstd; p.dw_part = dw_part;
   p.rows = rows; p.D = static_cast<int>(D); p.nvec = nvec; p.row_bytes = static_cast<int>(row_bytes);
   p.stages = stages; p.n_streams = n_streams; p.wpr = wpr; p.causal_seq = causal_seq; p.eps = eps; p.scale = scale;
   p.status = ds->status_word;
@@ -664,9 +675,9 @@ int try_launch(int op, const void* in0, const void* in1, const void* w, void* ou
 }
 
 template int try_launch<float>(int, const void*, const void*, const void*, void*, float*, float*, int*, int64_t, int64_t,
-                               float, int, float, const DeviceState*, cudaStream_t);
+                               float, int, float, const DeviceState*, cudaStream_t, const void*);
 template int try_launch<__nv_bfloat16>(int, const void*, const void*, const void*, void*, float*, float*, int*, int64_t,
-                                       int64_t, float, int, float, const DeviceState*, cudaStream_t);
+                                       int64_t, float, int, float, const DeviceState*, cudaStream_t, const void*);
 
 }  // namespace rowpipe
 }  // namespace mcb

@@ -198,11 +198,6 @@ class Qwen:
                                               int(rotate), int(inverse), self.dt, _stream()))
         return out
 
-    def _add(self, a, b, out=None):
-        out = torch.empty_like(a) if out is None else out
-        _lib.check(self.lib.mcb_add(_ptr(a), _ptr(b), _ptr(out), a.numel(), self.dt, _stream()))
-        return out
-
     def _embed(self, ids32: torch.Tensor) -> torch.Tensor:
         M = ids32.numel()
         out = torch.empty(M, self.config.hidden_size, dtype=self.dtype, device=self.device)
@@ -376,8 +371,9 @@ class Qwen:
         del dact
         dn2 = self._lin_bwd(sv["n2"], L["gate_proj"], gt, sv["hg"], key("gate_proj"), accumulate)
         dn2 = self._lin_bwd(sv["n2"], L["up_proj"], up, sv["hu"], key("up_proj"), accumulate, dx_residual=dn2)
-        dx2, _ = backend.rms_norm_backward(sv["h2"], L["post_attention_layernorm"], dn2, c.rms_norm_eps, need_dw=False)
-        dh2 = self._add(dh3, dx2, out=dx2)
+        # gradient through the norm plus the one along the residual connection, added inside the norm's kernel
+        dh2, _ = backend.rms_norm_backward(sv["h2"], L["post_attention_layernorm"], dn2, c.rms_norm_eps, need_dw=False,
+                                           dx_residual=dh3)
         # attention
         do = self._lin_bwd(sv["o"], L["o_proj"], dh2, sv["ho"], key("o_proj"), accumulate)
         dO = self._rope(do, c.num_attention_heads, B, S, False, False)
@@ -391,5 +387,6 @@ class Qwen:
         dn1 = self._lin_bwd(n1, L["q_proj"], dq, sv["hq"], key("q_proj"), accumulate)
         dn1 = self._lin_bwd(n1, L["k_proj"], dk, sv["hk"], key("k_proj"), accumulate, dx_residual=dn1)
         dn1 = self._lin_bwd(n1, L["v_proj"], dv, sv["hv"], key("v_proj"), accumulate, dx_residual=dn1)
-        dx1, _ = backend.rms_norm_backward(sv["h"], L["input_layernorm"], dn1, c.rms_norm_eps, need_dw=False)
-        return self._add(dh2, dx1, out=dx1)
+        dh, _ = backend.rms_norm_backward(sv["h"], L["input_layernorm"], dn1, c.rms_norm_eps, need_dw=False,
+                                          dx_residual=dh2)
+        return dh

@@ -55,6 +55,29 @@ def test_rmsnorm_fwd_bwd(cuda_device, dtype, rows, D, weighted):
         assert R.max_abs_normalised(back(dw), (dy.astype(np.float64) * xh).sum(0)) <= 1e-4
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,D", [(300, 896), (33, 2048), (16, 4096), (5, 1024), (3, 8192), (9, 24), (4, 50)])
+@pytest.mark.parametrize("need_dw", [False, True])
+def test_rmsnorm_bwd_with_residual(cuda_device, dtype, rows, D, need_dw):
+    """dx = (gradient through the norm) + dx_residual in one kernel (rows that are not whole 16-byte vectors take
+    the plain kernels plus an add): against the oracle's dx plus the residual; dw is unaffected."""
+    from metal_candle_b200 import backend as B
+
+    c = S.rmsnorm_case(4321, rows, D)
+    x, w, dy = (as_input(c[k], dtype) for k in ("x", "w", "dy"))
+    res = as_input(S.rmsnorm_case(99, rows, D)["dy"], dtype)
+    eps = 1e-6
+    xd, wd, dyd = to_dev(x, dtype, cuda_device), to_dev(w, dtype, cuda_device), to_dev(dy, dtype, cuda_device)
+    resd = to_dev(res, dtype, cuda_device)
+    dx, dw = B.rms_norm_backward(xd, wd, dyd, eps, need_dw=need_dw, dx_residual=resd)
+    wdx, wdw = R.rms_norm_backward(x, w, eps, dy)
+    assert R.max_abs_normalised(back(dx), wdx + res) <= TOL[dtype]
+    if need_dw:
+        assert R.max_abs_normalised(back(dw), wdw) <= 1e-4
+    else:
+        assert dw is None
+
+
 def test_rmsnorm_known_answers(cuda_device):
     """The reference's own known-answer values (tests/executor_direct.rs:480-496,
     src/backend/tensor.rs:321-336,382-397)."""
