@@ -228,6 +228,20 @@ int mcb_attention_causal_bwd(const void* q, const void* k, const void* v, const 
                              int64_t seq, int64_t head_dim, float scale, int dtype, void* workspace,
                              size_t workspace_bytes, void* stream);
 
+/* The same two calls with O (forward output) and dO (backward input) optionally token-major,
+ * [batch*seq, kv_heads*groups*head_dim] with head kvh*groups + g at column offset (kvh*groups + g)*head_dim: the layout
+ * of the o_proj input (src/models/transformer.rs:283-285 transposes and reshapes the per-head output into it), so
+ * that no relayout pass stands between the attention kernels and the projection.  nb = batch*kv_heads with the kv
+ * head varying fastest.  o_token_major == 0 gives the calls above. */
+int mcb_attention_causal_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
+                                int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
+                                int64_t kv_heads, int o_token_major, void* workspace, size_t workspace_bytes,
+                                void* stream);
+int mcb_attention_causal_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
+                                int64_t seq, int64_t head_dim, float scale, int dtype, int64_t kv_heads,
+                                int o_token_major, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- AdamW -------------------------------------------------------------------------------- */
 
 typedef struct {

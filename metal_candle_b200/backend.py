@@ -229,32 +229,41 @@ def attention_supported(q: torch.Tensor, seq: int) -> bool:
     return q.dtype == torch.bfloat16 and q.shape[-1] == 64 and seq % 128 == 0
 
 
-def attention_causal_forward(q, k, v, groups: int, scale: float):
+def attention_causal_forward(q, k, v, groups: int, scale: float, kv_heads: int = 0):
     """Attention::forward's core (src/models/transformer.rs:257-285) in one kernel.  q [nb, groups*S, d]
-    (row g*S + s), k and v [nb, S, d].  Returns (o like q, lse [nb, groups*S] float32)."""
+    (row g*S + s), k and v [nb, S, d].  Returns (o, lse [nb, groups*S] float32); o is laid out like q, or, with
+    kv_heads > 0 (nb = batch*kv_heads), token-major [batch*S, kv_heads*groups*d] - the o_proj input as it is."""
     _require_cuda(q, k, v)
     nb, S, d = k.shape
     if q.shape != (nb, groups * S, d) or v.shape != k.shape:
         raise TrainingError(f"attention: q {list(q.shape)}, k {list(k.shape)}, v {list(v.shape)} do not fit groups={groups}")
+    if kv_heads and nb % kv_heads != 0:
+        raise TrainingError(f"attention: nb={nb} is not a multiple of kv_heads={kv_heads}")
     lib = _lib_for(q)
-    o = torch.empty_like(q)
+    o = (torch.empty((nb // kv_heads) * S, kv_heads * groups * d, dtype=q.dtype, device=q.device) if kv_heads
+         else torch.empty_like(q))
     lse = torch.empty(nb, groups * S, dtype=torch.float32, device=q.device)
     ws = workspace(q.device, lib.mcb_attention_workspace_bytes(nb, groups, S, d))
-    _lib.check(lib.mcb_attention_causal_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), nb, groups, S, d, float(scale),
-                                            _dtype_code(q), _ptr(ws), ws.numel(), _stream()))
+    _lib.check(lib.mcb_attention_causal_fwd_ex(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), nb, groups, S, d, float(scale),
+                                               _dtype_code(q), int(kv_heads), int(bool(kv_heads)), _ptr(ws), ws.numel(),
+                                               _stream()))
     return o, lse
 
 
-def attention_causal_backward(q, k, v, o, lse, dout, groups: int, scale: float):
-    """Gradients of `attention_causal_forward`: (dq like q, dk and dv like k, summed over the group)."""
+def attention_causal_backward(q, k, v, o, lse, dout, groups: int, scale: float, kv_heads: int = 0):
+    """Gradients of `attention_causal_forward`: (dq like q, dk and dv like k, summed over the group).  With
+    kv_heads > 0, o and dout are token-major as returned by the forward."""
     _require_cuda(q, k, v, o, lse, dout)
     nb, S, d = k.shape
+    want = ((nb // kv_heads) * S, kv_heads * groups * d) if kv_heads else tuple(q.shape)
+    if tuple(o.shape) != want or tuple(dout.shape) != want:
+        raise TrainingError(f"attention backward: o {list(o.shape)} / dout {list(dout.shape)}, expected {list(want)}")
     lib = _lib_for(q)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     ws = workspace(q.device, lib.mcb_attention_workspace_bytes(nb, groups, S, d))
-    _lib.check(lib.mcb_attention_causal_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(dout), _ptr(lse), _ptr(dq), _ptr(dk),
-                                            _ptr(dv), nb, groups, S, d, float(scale), _dtype_code(q), _ptr(ws), ws.numel(),
-                                            _stream()))
+    _lib.check(lib.mcb_attention_causal_bwd_ex(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(dout), _ptr(lse), _ptr(dq), _ptr(dk),
+                                               _ptr(dv), nb, groups, S, d, float(scale), _dtype_code(q), int(kv_heads),
+                                               int(bool(kv_heads)), _ptr(ws), ws.numel(), _stream()))
     return dq, dk, dv
 
 

@@ -59,6 +59,7 @@ constexpr uint32_t kFwdSmem = kOffBar + 256 + 1024;
 
 struct FwdParams {
   int S, G, NB;
+  int HKV, o_tok;   // o_tok != 0: O is token-major [batch*S, HKV*G*64] (nb = batch*HKV + kv head), else like Q
   float sc;  // scale * log2(e)
   __nv_bfloat16* O;
   float* lse;
@@ -98,6 +99,20 @@ __device__ __forceinline__ FwdTile fwd_tile(const FwdParams& p, int t) {
   w.nkb = 2 * w.qb + 2;  // key blocks of 64 up to and including the diagonal
   w.qrow0 = (static_cast<int64_t>(w.nb) * p.G + w.g) * p.S + static_cast<int64_t>(w.qb) * kBQ;
   return w;
+}
+
+// Where the 64 values of (kv-head index nb, head g of its group, position s) start in O / dO, in elements, and the
+// two tile coordinates (column, row) of the same place for a tiled copy.
+__device__ __forceinline__ int64_t o_offset(int S, int G, int HKV, int o_tok, int nb, int g, int s) {
+  if (!o_tok) return ((static_cast<int64_t>(nb) * G + g) * S + s) * kD;
+  const int b = nb / HKV, kvh = nb - b * HKV;
+  return ((static_cast<int64_t>(b) * S + s) * (HKV * G) + kvh * G + g) * kD;
+}
+__device__ __forceinline__ void o_coords(int S, int G, int HKV, int o_tok, int nb, int g, int s, int& col, int& row) {
+  if (!o_tok) { col = 0; row = (nb * G + g) * S + s; return; }
+  const int b = nb / HKV, kvh = nb - b * HKV;
+  col = (kvh * G + g) * kD;
+  row = b * S + s;
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -331,7 +346,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;
       tcgen05_fence_after();
       const float inv = 1.0f / l;
-      __nv_bfloat16* orow = p.O + (w.qrow0 + row) * kD;
+      __nv_bfloat16* orow = p.O + o_offset(p.S, p.G, p.HKV, p.o_tok, w.nb, w.g, w.qb * kBQ + row);
       uint32_t ov[4][16];
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) tmem_ld_x16(tO + lane_addr + 16 * c4, ov[c4]);
@@ -379,6 +394,7 @@ constexpr uint32_t kDqSmem = kDqOffBar + 256 + 1024;
 
 struct BwdParams {
   int S, G, NB;
+  int HKV, o_tok;   // o_tok != 0: O and dO are token-major [batch*S, HKV*G*64], else laid out like Q
   float sc;     // scale * log2(e)
   float scale;
   const __nv_bfloat16* O;
@@ -451,7 +467,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (!ok) break;
         mbar_expect_tx(q_full, 2 * kQBytes);
         tma_load_2d(base + kDqOffQ, &tmQ, q_full, 0, static_cast<int>(w.qrow0));
-        tma_load_2d(base + kDqOffDO, &tmdO, q_full, 0, static_cast<int>(w.qrow0));
+        int dcol, drow;
+        o_coords(p.S, p.G, p.HKV, p.o_tok, w.nb, w.g, w.qb * kBQ, dcol, drow);
+        tma_load_2d(base + kDqOffDO, &tmdO, q_full, dcol, drow);
         for (int j = 0; j < w.nkb; ++j) {
           ok = mbar_wait(kv_empty0 + 8 * st, ph ^ 1, abort_flag, 81, p.status);
           if (!ok) break;
@@ -534,8 +552,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // delta = sum_d dO * O of this row, straight from global memory (once per item)
       float delta = 0.0f;
       {
-        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + (w.qrow0 + row) * kD);
-        const uint4* d4 = reinterpret_cast<const uint4*>(p.dO + (w.qrow0 + row) * kD);
+        const int64_t ooff = o_offset(p.S, p.G, p.HKV, p.o_tok, w.nb, w.g, w.qb * kBQ + row);
+        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + ooff);
+        const uint4* d4 = reinterpret_cast<const uint4*>(p.dO + ooff);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const uint4 a = o4[c], b = d4[c];
@@ -721,7 +740,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         const uint32_t sb = base + kKvOffStage + st * kKvStageStride, fb = ld_full0 + 8 * st;
         mbar_expect_tx(fb, kKvStageBytes);
         tma_load_2d(sb, &tmQ, fb, 0, static_cast<int>(qrow));
-        tma_load_2d(sb + kKBytes, &tmdO, fb, 0, static_cast<int>(qrow));
+        int dcol, drow;
+        o_coords(p.S, p.G, p.HKV, p.o_tok, nb, g, i * kBK, dcol, drow);
+        tma_load_2d(sb + kKBytes, &tmdO, fb, dcol, drow);
         bulk_load_1d(sb + 2 * kKBytes, p.lse2 + qrow, 256, fb);
         bulk_load_1d(sb + 2 * kKBytes + 256, p.delta + qrow, 256, fb);
       }
@@ -926,12 +947,15 @@ extern "C" size_t mcb_attention_workspace_bytes(int64_t nb, int64_t groups, int6
   return 2 * up1k(rows) + 1024;
 }
 
-extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
-                                        int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
-                                        void* workspace, size_t workspace_bytes, void* stream) {
+extern "C" int mcb_attention_causal_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
+                                           int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
+                                           int64_t kv_heads, int o_token_major, void* workspace, size_t workspace_bytes,
+                                           void* stream) {
   using namespace mcb::attn;
   if (!q || !k || !v || !o) return fail(MCB_ERR_NULL, "attention_causal_fwd: q, k, v or o is null");
   if (int rc = check_shape("attention_causal_fwd", nb, groups, seq, head_dim, dtype)) return rc;
+  if (o_token_major && (kv_heads <= 0 || nb % kv_heads != 0))
+    return fail(MCB_ERR_SHAPE, "attention_causal_fwd: nb=%lld is not a multiple of kv_heads=%lld", (long long)nb, (long long)kv_heads);
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(MCB_ERR_ALIGN, "attention_causal_fwd: 16-byte alignment");
   (void)workspace; (void)workspace_bytes;  // the forward needs no scratch memory
   DeviceState* ds = current_device_state();
@@ -948,6 +972,7 @@ extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void
   if (int rc = encode(ds, &tmVt, v, kD, nb * seq, kBK, "V")) return rc;
   FwdParams p;
   p.S = static_cast<int>(seq); p.G = static_cast<int>(groups); p.NB = static_cast<int>(nb);
+  p.HKV = o_token_major ? static_cast<int>(kv_heads) : 1; p.o_tok = o_token_major ? 1 : 0;
   p.sc = scale * kLog2e;
   p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = ds->status_word;
   // persistent: two CTAs per SM walk over the (query block, head, batch) items, heavy ones first
@@ -959,11 +984,20 @@ extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void
   return MCB_OK;
 }
 
-extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                                        const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
-                                        int64_t seq, int64_t head_dim, float scale, int dtype, void* workspace,
-                                        size_t workspace_bytes, void* stream) {
+extern "C" int mcb_attention_causal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t nb,
+                                        int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  return mcb_attention_causal_fwd_ex(q, k, v, o, lse, nb, groups, seq, head_dim, scale, dtype, 1, 0, workspace,
+                                     workspace_bytes, stream);
+}
+
+extern "C" int mcb_attention_causal_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                           const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
+                                           int64_t seq, int64_t head_dim, float scale, int dtype, int64_t kv_heads,
+                                           int o_token_major, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace mcb::attn;
+  if (o_token_major && (kv_heads <= 0 || nb % kv_heads != 0))
+    return fail(MCB_ERR_SHAPE, "attention_causal_bwd: nb=%lld is not a multiple of kv_heads=%lld", (long long)nb, (long long)kv_heads);
   if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv)
     return fail(MCB_ERR_NULL, "attention_causal_bwd: a required pointer is null");
   if (int rc = check_shape("attention_causal_bwd", nb, groups, seq, head_dim, dtype)) return rc;
@@ -989,15 +1023,19 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   float* lse2 = reinterpret_cast<float*>(w);
   CUtensorMap tmQ128, tmdO128, tmK64, tmV64, tmK128, tmV128, tmQ64, tmdO64;
   if (int rc = encode(ds, &tmQ128, q, kD, nb * groups * seq, kBQ, "Q")) return rc;
-  if (int rc = encode(ds, &tmdO128, dout, kD, nb * groups * seq, kBQ, "dO")) return rc;
+  // dO either like Q ([rows, 64]) or token-major ([batch*S, heads*64]: a head's tile is a column offset)
+  const int64_t do_inner = o_token_major ? kv_heads * groups * kD : kD;
+  const int64_t do_outer = o_token_major ? (nb / kv_heads) * seq : nb * groups * seq;
+  if (int rc = encode(ds, &tmdO128, dout, do_inner, do_outer, kBQ, "dO")) return rc;
   if (int rc = encode(ds, &tmK64, k, kD, nb * seq, kBK, "K")) return rc;
   if (int rc = encode(ds, &tmV64, v, kD, nb * seq, kBK, "V")) return rc;
   if (int rc = encode(ds, &tmK128, k, kD, nb * seq, kBQ, "K block")) return rc;
   if (int rc = encode(ds, &tmV128, v, kD, nb * seq, kBQ, "V block")) return rc;
   if (int rc = encode(ds, &tmQ64, q, kD, nb * groups * seq, kBK, "Q step")) return rc;
-  if (int rc = encode(ds, &tmdO64, dout, kD, nb * groups * seq, kBK, "dO step")) return rc;
+  if (int rc = encode(ds, &tmdO64, dout, do_inner, do_outer, kBK, "dO step")) return rc;
   BwdParams p;
   p.S = static_cast<int>(seq); p.G = static_cast<int>(groups); p.NB = static_cast<int>(nb);
+  p.HKV = o_token_major ? static_cast<int>(kv_heads) : 1; p.o_tok = o_token_major ? 1 : 0;
   p.sc = scale * kLog2e; p.scale = scale;
   p.O = static_cast<const __nv_bfloat16*>(o); p.dO = static_cast<const __nv_bfloat16*>(dout); p.lse = lse;
   p.delta = delta; p.lse2 = lse2;
@@ -1013,4 +1051,12 @@ extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void
   attn_dkv_kernel<<<gk, kKvThreads, kKvSmem, st>>>(tmK128, tmV128, tmQ64, tmdO64, p);
   MCB_CHECK_LAUNCH("attn_dkv_kernel");
   return MCB_OK;
+}
+
+extern "C" int mcb_attention_causal_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                        const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
+                                        int64_t seq, int64_t head_dim, float scale, int dtype, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  return mcb_attention_causal_bwd_ex(q, k, v, o, dout, lse, dq, dk, dv, nb, groups, seq, head_dim, scale, dtype, 1, 0,
+                                     workspace, workspace_bytes, stream);
 }

@@ -226,8 +226,9 @@ class Qwen:
         c = self.config
         Hk, G, d = c.num_key_value_heads, c.num_attention_heads // c.num_key_value_heads, c.head_dim
         if backend.attention_supported(Qr, S):
+            # the fused kernel writes its output token-major, [B*S, hidden]: the o_proj input as it is
             O, lse = backend.attention_causal_forward(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d),
-                                                      Vr.view(B * Hk, S, d), G, 1.0 / math.sqrt(d))
+                                                      Vr.view(B * Hk, S, d), G, 1.0 / math.sqrt(d), kv_heads=Hk)
             return None, O, lse
         scores = torch.bmm(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d).transpose(1, 2))  # [B*Hk, G*S, S]
         rows = scores.numel() // S
@@ -239,10 +240,12 @@ class Qwen:
     def _attention_bwd(self, Qr, Kr, Vr, P, O, lse, dO, B, S):
         c = self.config
         Hk, G, d = c.num_key_value_heads, c.num_attention_heads // c.num_key_value_heads, c.head_dim
-        dO3 = dO.view(B * Hk, G * S, d)
         if P is None:
+            # fused: O and dO are token-major [B*S, hidden] (o_proj's input and its gradient as they are)
             return backend.attention_causal_backward(Qr.view(B * Hk, G * S, d), Kr.view(B * Hk, S, d),
-                                                     Vr.view(B * Hk, S, d), O, lse, dO3, G, 1.0 / math.sqrt(d))
+                                                     Vr.view(B * Hk, S, d), O, lse, dO, G, 1.0 / math.sqrt(d),
+                                                     kv_heads=Hk)
+        dO3 = dO.view(B * Hk, G * S, d)
         dV = torch.bmm(P.transpose(1, 2), dO3)                       # [B*Hk, S, d], summed over the group
         dP = torch.bmm(dO3, Vr.view(B * Hk, S, d).transpose(1, 2))   # [B*Hk, G*S, S]
         rows = dP.numel() // S
@@ -264,9 +267,9 @@ class Qwen:
         Vr = self._rope(v, c.num_key_value_heads, B, S, False, False)
         del q, k, v
         P, O, lse = self._attention_fwd(Qr, Kr, Vr, B, S)
-        o = self._rope(O, c.num_attention_heads, B, S, False, True)   # back to [M, hidden]
-        if not save or P is not None:
-            O = None   # only the fused backward needs the per-head output again
+        # [M, hidden] for o_proj: the fused kernel's output already is; the unfused one goes through a relayout
+        o = O if P is None else self._rope(O, c.num_attention_heads, B, S, False, True)
+        O = None   # the fused backward takes the saved o_proj input as the attention output
         h2, ho = self._lin(o, L["o_proj"], save, residual=h)   # residual connection fused into the epilogue
         n2 = self._norm(h2, L["post_attention_layernorm"])
         w_gu = self._gate_up_weight(L)
@@ -376,9 +379,10 @@ class Qwen:
                                            dx_residual=dh3)
         # attention
         do = self._lin_bwd(sv["o"], L["o_proj"], dh2, sv["ho"], key("o_proj"), accumulate)
-        dO = self._rope(do, c.num_attention_heads, B, S, False, False)
+        fused = sv["P"] is None
+        dO = do if fused else self._rope(do, c.num_attention_heads, B, S, False, False)
         del do
-        dQ, dK, dV = self._attention_bwd(sv["Qr"], sv["Kr"], sv["Vr"], sv["P"], sv["O"], sv["lse"], dO, B, S)
+        dQ, dK, dV = self._attention_bwd(sv["Qr"], sv["Kr"], sv["Vr"], sv["P"], sv["o"] if fused else None, sv["lse"], dO, B, S)
         dq = self._rope(dQ, c.num_attention_heads, B, S, True, True)
         dk = self._rope(dK, c.num_key_value_heads, B, S, True, True)
         dv = self._rope(dV, c.num_key_value_heads, B, S, False, True)

@@ -244,9 +244,10 @@ def _count_launches(cfg, wl) -> int:
     n_lora = len(wl["targets"])
     fused_attn = cfg.head_dim == 64 and wl["seq"] % 128 == 0   # else the scores are materialised (cuBLAS + row softmax)
     fused_mlp = (cfg.intermediate_size % 128 == 0 and "gate_proj" not in wl["targets"] and "up_proj" not in wl["targets"])
-    # forward: 2 norms, 7 GEMMs, operand packs, 3 rope/relayout + 1 inverse relayout, attention (or softmax), swiglu
+    # forward: 2 norms, 7 GEMMs, operand packs, 3 rope/relayout (+ 1 inverse relayout unless the fused attention
+    # writes the o_proj layout itself), attention (or softmax), swiglu
     # (gate, up and swiglu are one kernel when neither projection has an adapter)
-    per_layer_fwd = 2 + (5 if fused_mlp else 8) + n_lora + 4 + 1
+    per_layer_fwd = 2 + (5 if fused_mlp else 8) + n_lora + (3 if fused_attn else 4) + 1
     # backward: 7 GEMMs, packs, dA/dB, swiglu, 2 norms (each adds the residual-path gradient as it writes dx),
     # 4 rope/relayout, attention (dq + dkv kernels, or one softmax).  dA and dB of an adapter are accumulated in the tail phase of its dx
     # GEMM launch and cost one partial-sum launch more; adapters whose dx runs on CTA pairs (out features >= 1536)
@@ -259,7 +260,7 @@ def _count_launches(cfg, wl) -> int:
         o, i = out_f[t], in_f.get(t, cfg.hidden_size)
         tail = o < 1536 and max(o, i) <= 1024 and o % 64 == 0 and i % 64 == 0
         grad_launches += 1 if tail else 2
-    per_layer_bwd = 7 + n_lora + grad_launches + 1 + 2 + 4 + (2 if fused_attn else 1)
+    per_layer_bwd = 7 + n_lora + grad_launches + 1 + 2 + (3 if fused_attn else 4) + (2 if fused_attn else 1)
     tail = 1 + 1 + 1 + 3 + 1 + 1  # embed, norm, lm_head, CE x3, lm_head bwd, norm bwd
     adamw = math.ceil(2 * n_lora * L / 64)
     return L * (per_layer_fwd + per_layer_bwd) + tail + adamw

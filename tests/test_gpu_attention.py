@@ -58,6 +58,36 @@ def test_attention_backward(cuda_device, nb, G, seq):
     assert _lib.device_status() == 0
 
 
+def _token_major(a, batch, hkv, G, seq):
+    """[batch*hkv, G, seq, d] (kv head fastest in the first index) -> [batch*seq, hkv*G*d], head kvh*G + g."""
+    d = a.shape[-1]
+    return np.ascontiguousarray(a.reshape(batch, hkv, G, seq, d).transpose(0, 3, 1, 2, 4).reshape(batch * seq, hkv * G * d))
+
+
+@pytest.mark.parametrize("batch,hkv,G,seq", [(1, 1, 1, 128), (2, 2, 2, 256), (2, 2, 7, 384), (3, 1, 3, 256)])
+def test_attention_token_major_output(cuda_device, batch, hkv, G, seq):
+    """O written, and O / dO read, in the o_proj layout [batch*seq, heads*d]: forward against the oracle's output
+    permuted into that layout; backward (with O and dO token-major) against the oracle's gradients."""
+    from metal_candle_b200 import _lib, backend as B
+
+    nb = batch * hkv
+    q, k, v, do = _case(79, nb, G, seq)
+    scale = 1.0 / math.sqrt(64)
+    want_o, want_lse, _ = R.causal_gqa_attention(q, k, v, scale)
+    wdq, wdk, wdv = R.causal_gqa_attention_backward(q, k, v, scale, do)
+    qd, kd, vd = _dev(q.reshape(nb, G * seq, 64), cuda_device), _dev(k, cuda_device), _dev(v, cuda_device)
+    o, lse = B.attention_causal_forward(qd, kd, vd, G, scale, kv_heads=hkv)
+    assert tuple(o.shape) == (batch * seq, hkv * G * 64)
+    assert R.max_abs_normalised(o.float().cpu().numpy(), _token_major(want_o, batch, hkv, G, seq)) <= 2e-2
+    assert np.abs(lse.cpu().numpy().reshape(nb, G, seq) - want_lse).max() <= 2e-2
+    dod = _dev(_token_major(do, batch, hkv, G, seq), cuda_device)
+    dq, dk, dv = B.attention_causal_backward(qd, kd, vd, o, lse, dod, G, scale, kv_heads=hkv)
+    assert R.max_abs_normalised(dq.float().cpu().numpy().reshape(nb, G, seq, 64), wdq) <= 2e-2, "dq"
+    assert R.max_abs_normalised(dk.float().cpu().numpy(), wdk) <= 2e-2, "dk"
+    assert R.max_abs_normalised(dv.float().cpu().numpy(), wdv) <= 2e-2, "dv"
+    assert _lib.device_status() == 0
+
+
 def test_attention_rejects_unsupported_shapes(cuda_device):
     from metal_candle_b200 import backend as B
     from metal_candle_b200._lib import McbError
