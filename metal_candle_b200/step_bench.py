@@ -160,9 +160,18 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
     gemm = _lib.profile_summary(0)
     grad = _lib.profile_summary(1)
     prof_steps = 1
+    capture_note = None
     if not getattr(args, "no_graph", False):
-        model.layer_done_hook = None
-        captured["fb"] = model.capture_forward_backward(B, S)
+        hook = model.layer_done_hook
+        try:
+            model.layer_done_hook = None
+            captured["fb"] = model.capture_forward_backward(B, S)
+        except Exception as e:  # the eager path stays valid; say why the graph is not used
+            captured["fb"] = None
+            model.layer_done_hook = hook
+            capture_note = f"{type(e).__name__}: {e}"[:200]
+            print(f"bench: CUDA-graph capture failed, timing eager launches instead ({capture_note})", file=sys.stderr)
+            torch.cuda.synchronize()
         for i in range(args.warmup):
             one_step(*dev_batches[i % len(dev_batches)])
     barrier()
@@ -212,7 +221,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
                        "lora_rank": wl["rank"], "lora_targets": list(wl["targets"]), "parallelism": f"dp{world}",
                        "optimizer": "AdamW lr 1e-4 warmup-cosine",
                        "execution": ("forward+loss+backward replayed from a CUDA graph, then gradient all-reduce and AdamW"
-                                     if captured["fb"] is not None else "eager launches"),
+                                     if captured["fb"] is not None else
+                                     "eager launches" + (f" (graph capture failed: {capture_note})" if capture_note else "")),
                        "l2": "inputs larger than L2 (activations of one "
                        "step are tens of GB)", "loss_last": last},
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 4,
