@@ -172,6 +172,14 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             capture_note = f"{type(e).__name__}: {e}"[:200]
             print(f"bench: CUDA-graph capture failed, timing eager launches instead ({capture_note})", file=sys.stderr)
             torch.cuda.synchronize()
+        if dist is not None:
+            # every rank must exchange gradients the same way: the graph is used only if all of them captured it
+            okf = torch.tensor([1 if captured["fb"] is not None else 0], device=device, dtype=torch.int32)
+            dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+            if int(okf.item()) == 0 and captured["fb"] is not None:
+                captured["fb"] = None
+                model.layer_done_hook = hook
+                capture_note = "another rank could not capture"
         for i in range(args.warmup):
             one_step(*dev_batches[i % len(dev_batches)])
     barrier()
