@@ -324,11 +324,39 @@ rowpipe_kernel(const Params p) {
             a.from_float(o);
             __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
           };
+          auto body_res = [&](int vi, const V& rr) {
+            V a, b; a.raw = reinterpret_cast<const decltype(a.raw)*>(s0)[vi];
+            b.raw = reinterpret_cast<const decltype(b.raw)*>(s1)[vi];
+            float x[N], g[N], o[N], rf[N]; a.to_float(x); b.to_float(g); rr.to_float(rf);
+#pragma unroll
+            for (int j = 0; j < N; j += 2) {
+              const float2 xh = __fmul2_rn(f2(x[j], x[j + 1]), r2);
+              float2 gw = f2(g[j], g[j + 1]);
+              if (wsm != nullptr) gw = __fmul2_rn(gw, *reinterpret_cast<const float2*>(wsm + vi * N + j));
+              const float2 u = __ffma2_rn(__ffma2_rn(xh, nc2, gw), r2, f2(rf[j], rf[j + 1]));
+              o[j] = u.x; o[j + 1] = u.y;
+            }
+            a.from_float(o);
+            __stcs(reinterpret_cast<decltype(a.raw)*>(orow) + vi, a.raw);
+          };
           if constexpr (kDw) {
 #pragma unroll
             for (int k = 0; k < KMAX; ++k) {
               const int vi = v_begin + lane + 32 * k;
               if (vi < v_end) body(vi, dwa[k]);
+            }
+          } else if (rrow != nullptr) {
+            // the residual vectors of the whole row segment are requested before pass 2 touches the first one,
+            // so that their global-memory latency is paid once per row, not once per vector
+            constexpr int kRes = 2;
+            for (int v0 = v_begin + lane; v0 < v_end; v0 += 32 * kRes) {
+              V rr[kRes];
+#pragma unroll
+              for (int k = 0; k < kRes; ++k)
+                if (v0 + 32 * k < v_end) rr[k].raw = __ldcs(reinterpret_cast<const decltype(rr[k].raw)*>(rrow) + v0 + 32 * k);
+#pragma unroll
+              for (int k = 0; k < kRes; ++k)
+                if (v0 + 32 * k < v_end) body_res(v0 + 32 * k, rr[k]);
             }
           } else {
             for (int vi = v_begin + lane; vi < v_end; vi += 32) body(vi, nullptr);
