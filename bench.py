@@ -358,6 +358,7 @@ def cpu_baseline(wl: dict, steps: int, warmup: int):
 
     from metal_candle_b200.qwen import ModelConfig
 
+    torch.set_num_threads(_host_threads())
     cfg = ModelConfig.qwen25_05b()
     S = 512
     g = torch.Generator().manual_seed(0)
@@ -401,15 +402,30 @@ def cpu_baseline(wl: dict, steps: int, warmup: int):
             "ms_per_step": dt / steps * 1e3}
 
 
+def _host_threads() -> int:
+    """Host threads this process may use: all the cores it is allowed on, divided among the ranks a launcher
+    started on this node (torchrun exports OMP_NUM_THREADS=1 to every rank, which would otherwise leave the CPU
+    arm on one core)."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    return max(1, cores)
+
+
 def run_reference(args):
-    """`--impl reference`: the reference's CPU path (its torch-CPU restatement) on the host cores."""
+    """`--impl reference`: the reference's CPU path (its torch-CPU restatement) on the host cores.  Under a
+    multi-rank launch only rank 0 works, so it takes every core of the box."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import torch
+
     from metal_candle_b200.step_bench import WORKLOADS
 
+    torch.set_num_threads(_host_threads())
     wl = WORKLOADS[args.workload]
-    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
     cb = cpu_baseline(wl, steps=steps, warmup=warmup)
     line = {"impl": "reference", "metric": "LoRA fwd+bwd tokens/s, Qwen2.5-0.5B shape", "value": cb["value"],
             "unit": "tokens/s", "n_gpus": max(1, args.gpus), "steps": steps, "warmup": warmup,
@@ -419,6 +435,27 @@ def run_reference(args):
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def kernel_numbers(torch):
+    """Driver-run numbers for the kernels the targets name, measured in the same process as the headline: the row
+    kernels of benchmark configuration 2 at 114 688 rows (bf16) and the fused LoRA linear forward+backward of
+    configuration 3 at M = 32768 for the 0.5B model's 896-wide projection and a 4096-wide one (r = 16)."""
+    out = {"note": "graph replay, inputs rotated through > 2x L2, CUDA events; fractions of the measured peaks "
+                   "(copy bandwidth for the row kernels, cuBLAS bf16 burst for the GEMM)"}
+    rows = {}
+    for op, D in (("rmsnorm", 896), ("rmsnorm", 4096), ("softmax", 1024)):
+        for r in micro_rows(torch, op, 114688, D, "bf16", 20, 5):
+            rows[f"{r['metric']} D={D}"] = {"GBps": round(r["value"], 1), "frac": round(r["roofline"]["frac"], 3),
+                                            "ms": round(r["ms"], 4)}
+    out["rows_bf16_114688"] = rows
+    lora = {}
+    for K, N in ((896, 896), (4096, 4096)):
+        r = micro_lora(torch, 32768, K, N, 16, "bf16", "both", 20, 5)
+        lora[f"{K}x{N} r16 M=32768 fwd+bwd"] = {"TFLOPs": round(r["value"], 1), "frac": round(r["roofline"]["frac"], 3),
+                                                 "ms": round(r["ms"], 4), "bound": r["roofline"]["bound"]}
+    out["lora_linear"] = lora
+    return out
 
 
 C3_SHAPES = [(896, 896), (896, 128), (2048, 2048), (4096, 4096), (4096, 14336)]
@@ -492,6 +529,13 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup-iters", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--comm", default="mcb", choices=["mcb", "mcb-blocking", "torch"],
+                    help="gradient exchange: the library's communicator (default), the same with a blocking NCCL "
+                         "communicator, or torch.distributed")
+    ap.add_argument("--grad-tail", default="auto", choices=["auto", "on", "off"],
+                    help="dA/dB in the tail phase of the dx launch (auto: on with one GPU, off beside a collective)")
+    ap.add_argument("--no-dp-check", action="store_true", help="skip the data-parallel arithmetic check at N > 1")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel numbers at N = 1")
     args = ap.parse_args()
     global NO_GRAPH
     NO_GRAPH = args.no_graph
@@ -501,7 +545,7 @@ def main():
         return run_reference(args)
     from metal_candle_b200 import step_bench  # the Qwen-shaped training-step benchmark
 
-    return step_bench.run_b200(args, ClockSampler, measured_peaks, cpu_baseline)
+    return step_bench.run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers)
 
 
 if __name__ == "__main__":

@@ -33,7 +33,11 @@ extern "C" {
 #define MCB_ERR_UNSUPPORTED (-4)   /* dtype / layout / rank combination the kernel does not implement */
 #define MCB_ERR_WORKSPACE (-5)     /* workspace missing or too small */
 #define MCB_ERR_NOT_INIT (-6)      /* mcb_init was not called for the current device */
-#define MCB_ERR_DEVICE_TIMEOUT 100001 /* a bounded device-side wait ran out (see mcb_device_status) */
+#define MCB_ERR_DEVICE_TIMEOUT 100001 /* a bounded device-side wait ran out (mcb_check_device, mcb_device_status) */
+#define MCB_ERR_COMM_TIMEOUT 100002   /* a collective or the rendezvous passed its host deadline; communicator aborted */
+#define MCB_ERR_COMM_DEAD 100003      /* the communicator was aborted earlier and takes no more work */
+#define MCB_ERR_COMM_UNAVAILABLE 100004 /* no NCCL library could be bound at run time */
+#define MCB_ERR_COMM_BASE 200000      /* + ncclResult_t: an error reported by NCCL */
 
 /* Element types.  MCB_F32 is the validation path (CUDA-core FMA, matches the reference's f32 CPU
  * arithmetic to <=1e-4); MCB_BF16 is the production path (tcgen05 tensor cores, fp32 accumulate). */
@@ -57,10 +61,34 @@ int mcb_version(void);
  * bounded wait that gave up.  Synchronises the device. */
 int mcb_device_status(int* status_out);
 
+/* mcb_device_status as a status: synchronises the device, returns MCB_OK when no bounded wait has run out since the
+ * last check and MCB_ERR_DEVICE_TIMEOUT (message naming the wait's code) otherwise; clears the word.  This is the
+ * library's failure detection for its own kernels: a wait on an mbarrier or a flag that runs out does not trap or
+ * hang, the kernel records a code and returns, and the results of that launch are invalid.  No counterpart in the
+ * reference (its kernels have no waits). */
+int mcb_check_device(void);
+/* Makes a bounded wait run out on purpose: one warp waits on a barrier that nothing arrives at, for at most
+ * `limit_cycles` SM cycles (1 .. 2e9), records MCB_WAIT_CODE_SELFTEST in the status word and returns normally.
+ * Synchronises `stream`.  Returns MCB_OK when the wait gave up as designed (the next mcb_check_device then reports
+ * MCB_ERR_DEVICE_TIMEOUT once); waited_cycles_out, if not null, receives the cycles spent.  Test support. */
+#define MCB_WAIT_CODE_SELFTEST 90
+int mcb_selftest_wait_timeout(int64_t limit_cycles, int64_t* waited_cycles_out, void* stream);
+
+/* Library switches.  MCB_OPT_GRAD_TAIL (default 1): mcb_lora_linear_bwd may accumulate dA and dB in the tail phase
+ * of the dx launch.  That phase makes CTAs wait for rows other CTAs of the same launch write, so it needs the whole
+ * grid (one CTA per SM) resident at once; the library checks the device's occupancy itself, but a caller that runs
+ * other kernels beside the backward pass (a collective on a second stream), or a context limited to a share of the
+ * SMs, should set it to 0: the gradients then take their own launch, which waits for nothing. */
+#define MCB_OPT_GRAD_TAIL 0
+#define MCB_OPT_COUNT_ 1
+int mcb_set_option(int option_id, int value);
+int mcb_get_option(int option_id, int* value_out);
+
 /* Per-kernel timing for roofline reports.  While enabled, every launch of the tensor-core kernels is
  * bracketed by CUDA events on its own stream and tagged with its algorithmic work; mcb_profile_summary
- * synchronises the device, sums the finished records of one kind (0 = the fused LoRA GEMM, 1 = the LoRA
- * weight-gradient kernel) and forgets them.  No counterpart in the reference. */
+ * synchronises the device, sums the finished records of one kind (0 = GEMM launches without a rank path: the frozen
+ * projections; 1 = the stand-alone LoRA weight-gradient kernel; 2 = GEMM launches with a rank path: the fused LoRA
+ * linear forward and backward, the backward including its dA/dB tail phase) and forgets them.  No counterpart in the reference. */
 int mcb_profile_enable(int on);
 int mcb_profile_summary(int kind, int64_t* launches, double* total_ms, double* total_flops, double* total_bytes);
 
@@ -179,7 +207,8 @@ int mcb_rmsnorm_bwd_ex(const void* x, const void* w, const void* dy, const void*
  * that first call before starting any stream capture.  All calls on a device share the one array, which
  * keeps whatever the previous call left in it (each call overwrites the part it reads, nothing has to
  * be cleared): two calls whose kernels overlap on the GPU -- different streams, or different host threads
- * -- race on it, so serialise them. */
+ * -- race on it, so serialise them.  The first call per device also writes the library's host-side cache of the
+ * array's address; make that first call from one host thread. */
 int mcb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
                             int64_t rows, int64_t D, float eps, int dtype, void* stream);
 
@@ -241,6 +270,36 @@ int mcb_attention_causal_bwd_ex(const void* q, const void* k, const void* v, con
                                 const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
                                 int64_t seq, int64_t head_dim, float scale, int dtype, int64_t kv_heads,
                                 int o_token_major, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- data-parallel exchange ------------------------------------------------------------------- */
+
+/* The reference trains on one device and has no communication layer; these calls are the one exchange step of the
+ * batch-data-parallel training step: a float32 sum all-reduce of the LoRA gradient buckets (NCCL over NVLink), one
+ * communicator rank per GPU and process.  NCCL is bound at run time: the copy the process already carries
+ * (PyTorch's), else libnccl.so.2 from the loader path, else the file MCB_NCCL_LIBRARY names.
+ * Failure handling: communicators are non-blocking; the rendezvous, every enqueue and mcb_comm_wait poll
+ * ncclCommGetAsyncError against a host deadline (timeout_ms; 0 = none).  On a deadline or an asynchronous NCCL
+ * error the communicator is aborted (ncclCommAbort) and marked dead; the call returns MCB_ERR_COMM_TIMEOUT or
+ * MCB_ERR_COMM_BASE + the NCCL result, and later calls return MCB_ERR_COMM_DEAD instead of hanging. */
+#define MCB_COMM_ID_BYTES 128
+typedef struct mcb_comm mcb_comm;
+/* Rank 0 creates the id and hands its 128 bytes to every rank by any host channel. */
+int mcb_comm_unique_id(void* id_out);
+/* Joins the communicator as `rank` of `nranks` on the CURRENT device.  flags: 0, or MCB_COMM_BLOCKING for a
+ * blocking communicator (NCCL then works inside the calling thread and the rendezvous has no deadline; the
+ * deadline of mcb_comm_wait and the asynchronous-error checks stay). */
+#define MCB_COMM_BLOCKING 1
+int mcb_comm_init_rank(mcb_comm** comm_out, int nranks, int rank, const void* id, int timeout_ms, int flags);
+/* In-place sum over ranks of buf[0..count) float32, enqueued on `stream` (may be captured into a CUDA graph). */
+int mcb_comm_allreduce_bucket(mcb_comm* comm, float* buf, int64_t count, void* stream);
+/* Waits, on the host and at most timeout_ms, until the communicator's enqueued work and `stream` have finished
+ * (MCB_COMM_NO_STREAM: the communicator's own state only).  A peer that never joined a collective shows up here. */
+#define MCB_COMM_NO_STREAM ((void*)(intptr_t)-1)
+int mcb_comm_wait(mcb_comm* comm, void* stream, int timeout_ms);
+int mcb_comm_abort(mcb_comm* comm);
+int mcb_comm_info(const mcb_comm* comm, int* nranks, int* rank, int* dead, int* nccl_version);
+/* Finalizes (within the communicator's deadline) and frees; also frees a dead communicator. */
+int mcb_comm_destroy(mcb_comm* comm);
 
 /* ---- AdamW -------------------------------------------------------------------------------- */
 

@@ -11,6 +11,13 @@ LIB_PATH = Path(__file__).resolve().parent / "libmetal_candle_b200.so"
 
 MCB_F32, MCB_BF16 = 0, 1
 MCB_W_OUT_IN, MCB_W_IN_OUT = 0, 1
+MCB_ERR_DEVICE_TIMEOUT, MCB_ERR_COMM_TIMEOUT, MCB_ERR_COMM_DEAD, MCB_ERR_COMM_UNAVAILABLE = 100001, 100002, 100003, 100004
+MCB_ERR_COMM_BASE = 200000
+MCB_OPT_GRAD_TAIL = 0
+MCB_WAIT_CODE_SELFTEST = 90
+MCB_COMM_ID_BYTES = 128
+MCB_COMM_BLOCKING = 1
+MCB_COMM_NO_STREAM = C.c_void_p(-1 & 0xFFFFFFFFFFFFFFFF)
 
 
 class McbError(RuntimeError):
@@ -34,6 +41,17 @@ SIGNATURES = {
     "mcb_last_error": (C.c_char_p, []),
     "mcb_version": (_i32, []),
     "mcb_device_status": (_i32, [C.POINTER(C.c_int)]),
+    "mcb_check_device": (_i32, []),
+    "mcb_selftest_wait_timeout": (_i32, [_i64, C.POINTER(C.c_int64), _vp]),
+    "mcb_set_option": (_i32, [_i32, _i32]),
+    "mcb_get_option": (_i32, [_i32, C.POINTER(C.c_int)]),
+    "mcb_comm_unique_id": (_i32, [_vp]),
+    "mcb_comm_init_rank": (_i32, [C.POINTER(_vp), _i32, _i32, _vp, _i32, _i32]),
+    "mcb_comm_allreduce_bucket": (_i32, [_vp, _vp, _i64, _vp]),
+    "mcb_comm_wait": (_i32, [_vp, _vp, _i32]),
+    "mcb_comm_abort": (_i32, [_vp]),
+    "mcb_comm_info": (_i32, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "mcb_comm_destroy": (_i32, [_vp]),
     "mcb_profile_enable": (_i32, [_i32]),
     "mcb_profile_summary": (_i32, [_i32, C.POINTER(C.c_int64), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                    C.POINTER(C.c_double)]),

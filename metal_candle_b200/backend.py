@@ -68,6 +68,13 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return buf
 
 
+def workspace_refs(device: torch.device):
+    """The scratch buffer currently cached for `device` (a list of zero or one tensors).  Whoever bakes its address
+    into something replayable (a CUDA graph) keeps these references for as long as that thing lives."""
+    buf = _ws_cache.get((device.type, device.index))
+    return [] if buf is None else [buf]
+
+
 # ---------------------------------------------------------------------------------------------
 # LoRA
 # ---------------------------------------------------------------------------------------------

@@ -70,7 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 raise RuntimeError(f"nvcc failed for {cmd[-3]}")
     objs = [OBJ / (s.stem + ".o") for s in sources()]
     if force or jobs or _stale(OUT, objs):
-        cmd = [nvcc, "-shared", "-o", str(OUT), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+        cmd = [nvcc, "-shared", "-o", str(OUT), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

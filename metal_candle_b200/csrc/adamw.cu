@@ -102,6 +102,7 @@ using namespace mcb;
 
 extern "C" int mcb_adamw_multi(const mcb_adamw_tensor* tensors, int n_tensors, float lr, float beta1, float beta2,
                                float eps, float weight_decay, float grad_scale, void* stream) {
+  MCB_NVTX_RANGE("mcb_adamw_multi");
   if (n_tensors < 0) return fail(MCB_ERR_SHAPE, "adamw_multi: n_tensors=%d", n_tensors);
   if (n_tensors == 0) return MCB_OK;
   if (!tensors) return fail(MCB_ERR_NULL, "adamw_multi: tensors is null");

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/mcb200.h"
 
 namespace mcb {
@@ -20,16 +22,30 @@ struct DeviceState {
   bool ready = false;
   int sm_count = 0;
   int* status_word = nullptr;  // device int: 0, or the code of a bounded wait that gave up
+  long long* selftest_out = nullptr;  // three device words behind the status word (mcb_selftest_wait_timeout)
   void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled resolved through the runtime
 };
 DeviceState* current_device_state();  // null (and error set) when mcb_init was not called
 
 // Optional per-kernel timing (mcb_profile_enable): CUDA events recorded on the launching stream right
 // around one kernel launch, tagged with the launch's algorithmic work.
-enum ProfileKind { kProfGemm = 0, kProfGrad = 1, kProfKinds = 2 };
+enum ProfileKind { kProfGemm = 0, kProfGrad = 1, kProfGemmLora = 2, kProfKinds = 3 };
 bool profile_on();
 void profile_begin(int kind, double flops, double bytes, cudaStream_t st);
 void profile_end(cudaStream_t st);
+
+// Library switches (mcb_set_option).
+int option(int which);
+
+// An NVTX range around the body of an entry point: shows each call (and the kernels it enqueues) by name on a
+// profiler's timeline; costs a pointer test when no tool is attached.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+#define MCB_NVTX_RANGE(name) mcb::NvtxRange mcb_nvtx_range_(name)
 
 #define MCB_CHECK_CUDA(expr)                                   \
   do {                                                         \

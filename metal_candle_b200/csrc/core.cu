@@ -114,8 +114,9 @@ extern "C" int mcb_init(int device) {
                 device, prop.major, prop.minor);
   DeviceState st;
   st.sm_count = prop.multiProcessorCount;
-  MCB_CHECK_CUDA(cudaMalloc(&st.status_word, sizeof(int)));
-  MCB_CHECK_CUDA(cudaMemset(st.status_word, 0, sizeof(int)));
+  MCB_CHECK_CUDA(cudaMalloc(&st.status_word, 64));
+  MCB_CHECK_CUDA(cudaMemset(st.status_word, 0, 64));
+  st.selftest_out = reinterpret_cast<long long*>(reinterpret_cast<char*>(st.status_word) + 16);
   cudaDriverEntryPointQueryResult qres;
   void* fn = nullptr;
   MCB_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -184,6 +185,7 @@ __global__ void transpose_kernel(const T* __restrict__ src, T* __restrict__ dst,
 using mcb_detail::transpose_kernel;
 
 extern "C" int mcb_transpose_2d(const void* src, void* dst, int64_t rows, int64_t cols, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_transpose_2d");
   if (!src || !dst) return fail(MCB_ERR_NULL, "transpose_2d: null pointer");
   if (rows <= 0 || cols <= 0) return fail(MCB_ERR_SHAPE, "transpose_2d: rows=%lld cols=%lld", (long long)rows, (long long)cols);
   if (!current_device_state()) return MCB_ERR_NOT_INIT;

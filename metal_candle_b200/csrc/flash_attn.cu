@@ -951,6 +951,7 @@ extern "C" int mcb_attention_causal_fwd_ex(const void* q, const void* k, const v
                                            int64_t groups, int64_t seq, int64_t head_dim, float scale, int dtype,
                                            int64_t kv_heads, int o_token_major, void* workspace, size_t workspace_bytes,
                                            void* stream) {
+  MCB_NVTX_RANGE("mcb_attention_causal_fwd_ex");
   using namespace mcb::attn;
   if (!q || !k || !v || !o) return fail(MCB_ERR_NULL, "attention_causal_fwd: q, k, v or o is null");
   if (int rc = check_shape("attention_causal_fwd", nb, groups, seq, head_dim, dtype)) return rc;
@@ -995,6 +996,7 @@ extern "C" int mcb_attention_causal_bwd_ex(const void* q, const void* k, const v
                                            const float* lse, void* dq, void* dk, void* dv, int64_t nb, int64_t groups,
                                            int64_t seq, int64_t head_dim, float scale, int dtype, int64_t kv_heads,
                                            int o_token_major, void* workspace, size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_attention_causal_bwd_ex");
   using namespace mcb::attn;
   if (o_token_major && (kv_heads <= 0 || nb % kv_heads != 0))
     return fail(MCB_ERR_SHAPE, "attention_causal_bwd: nb=%lld is not a multiple of kv_heads=%lld", (long long)nb, (long long)kv_heads);

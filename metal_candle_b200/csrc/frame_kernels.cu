@@ -234,6 +234,7 @@ cross_entropy_kernel(T* __restrict__ logits, const int32_t* __restrict__ targets
       float vm = f[0];
 #pragma unroll
       for (int j = 1; j < NV; ++j) vm = fmaxf(vm, f[j]);
+      if (vm == -INFINITY) continue;  // a wholly masked vector adds nothing (and exp(-inf - -inf) would be NaN)
       if (vm > m) { s *= __expf(m - vm); m = vm; }
 #pragma unroll
       for (int j = 0; j < NV; ++j) s += __expf(f[j] - m);
@@ -241,7 +242,7 @@ cross_entropy_kernel(T* __restrict__ logits, const int32_t* __restrict__ targets
   } else {
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
       const float v = to_f32(lr[c]);
-      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else if (v != -INFINITY) { s += __expf(v - m); }
     }
   }
 #pragma unroll
@@ -334,6 +335,7 @@ using namespace mcb;
 
 extern "C" int mcb_embedding_fwd(const int32_t* ids, const void* table, void* out, int64_t M, int64_t H, int64_t vocab,
                                  int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_embedding_fwd");
   if (!ids || !table || !out) return fail(MCB_ERR_NULL, "embedding_fwd: null pointer");
   if (M <= 0 || H <= 0 || vocab <= 0 || M > 0x7fffffff) return fail(MCB_ERR_SHAPE, "embedding_fwd: bad shape");
   if (!current_device_state()) return MCB_ERR_NOT_INIT;
@@ -345,6 +347,7 @@ extern "C" int mcb_embedding_fwd(const int32_t* ids, const void* table, void* ou
 
 extern "C" int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
                                  int rotate, int inverse, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_rope_relayout");
   if (!src || !dst) return fail(MCB_ERR_NULL, "rope_relayout: null pointer");
   if (B <= 0 || S <= 0 || H <= 0 || d <= 0 || d % 2 != 0) return fail(MCB_ERR_SHAPE, "rope_relayout: bad shape (head_dim must be even)");
   DeviceState* ds = current_device_state();
@@ -364,6 +367,7 @@ extern "C" int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t 
 }
 
 extern "C" int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_swiglu_fwd");
   if (!gate || !up || !out) return fail(MCB_ERR_NULL, "swiglu_fwd: null pointer");
   if (n <= 0 || n % 8 != 0) return fail(MCB_ERR_SHAPE, "swiglu_fwd: element count must be a positive multiple of 8");
   if (!aligned16(gate) || !aligned16(up) || !aligned16(out)) return fail(MCB_ERR_ALIGN, "swiglu_fwd: 16-byte alignment");
@@ -378,6 +382,7 @@ extern "C" int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64
 
 extern "C" int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup, int64_t n,
                               int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_swiglu_bwd");
   if (!gate || !up || !dout || !dgate || !dup) return fail(MCB_ERR_NULL, "swiglu_bwd: null pointer");
   if (n <= 0 || n % 8 != 0) return fail(MCB_ERR_SHAPE, "swiglu_bwd: element count must be a positive multiple of 8");
   if (!aligned16(gate) || !aligned16(up) || !aligned16(dout) || !aligned16(dgate) || !aligned16(dup))
@@ -392,6 +397,7 @@ extern "C" int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout
 }
 
 extern "C" int mcb_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_add");
   if (!a || !b || !out) return fail(MCB_ERR_NULL, "add: null pointer");
   if (n <= 0) return fail(MCB_ERR_SHAPE, "add: element count must be positive");
   DeviceState* ds = current_device_state();
@@ -408,6 +414,7 @@ extern "C" int mcb_add(const void* a, const void* b, void* out, int64_t n, int d
 }
 
 extern "C" int mcb_mul(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_mul");
   if (!a || !b || !out) return fail(MCB_ERR_NULL, "mul: null pointer");
   if (n <= 0) return fail(MCB_ERR_SHAPE, "mul: element count must be positive");
   DeviceState* ds = current_device_state();
@@ -420,6 +427,7 @@ extern "C" int mcb_mul(const void* a, const void* b, void* out, int64_t n, int d
 }
 
 extern "C" int mcb_mul_scalar(const void* a, void* out, int64_t n, float value, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_mul_scalar");
   if (!a || !out) return fail(MCB_ERR_NULL, "mul_scalar: null pointer");
   if (n <= 0) return fail(MCB_ERR_SHAPE, "mul_scalar: element count must be positive");
   DeviceState* ds = current_device_state();
@@ -433,6 +441,7 @@ extern "C" int mcb_mul_scalar(const void* a, void* out, int64_t n, float value, 
 
 extern "C" int mcb_cross_entropy(void* logits, const int32_t* targets, float* nll, int32_t* count, float* loss,
                                  int64_t M, int64_t V, int write_grad, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_cross_entropy");
   if (!logits || !targets || !nll || !count || !loss) return fail(MCB_ERR_NULL, "cross_entropy: null pointer");
   if (M <= 0 || V <= 0 || M > 0x7fffffff || V > 0x7fffffff) return fail(MCB_ERR_SHAPE, "cross_entropy: bad shape");
   if (!current_device_state()) return MCB_ERR_NOT_INIT;

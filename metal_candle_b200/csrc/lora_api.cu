@@ -37,6 +37,7 @@ extern "C" size_t mcb_lora_workspace_bytes(int64_t M, int64_t K, int64_t N, int6
 extern "C" int mcb_lora_delta_fwd(const void* x, const float* A, const float* B, void* out, int64_t M, int64_t K,
                                   int64_t N, int64_t r, float scale, int dtype, void* workspace, size_t workspace_bytes,
                                   void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_delta_fwd");
   if (!x || !A || !B || !out) return fail(MCB_ERR_NULL, "lora_delta_fwd: null pointer");
   if (int rc = check_dims("lora_delta_fwd", M, K, N, r, dtype, true)) return rc;
   DeviceState* ds = current_device_state();
@@ -52,6 +53,7 @@ extern "C" int mcb_lora_delta_fwd(const void* x, const float* A, const float* B,
 extern "C" int mcb_lora_linear_fwd_ex(const void* x, const void* W, const void* bias, const float* A, const float* B,
                                       const void* residual, void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
                                    int w_layout, void* workspace, size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_linear_fwd_ex");
   if (!x || !W || !y) return fail(MCB_ERR_NULL, "lora_linear_fwd: x, W or y is null");
   if (r > 0 && (!A || !B)) return fail(MCB_ERR_NULL, "lora_linear_fwd: rank %lld but A or B is null", (long long)r);
   if (int rc = check_dims("lora_linear_fwd", M, K, N, r, dtype, false)) return rc;
@@ -70,6 +72,7 @@ extern "C" int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float*
                                       const void* h_save, const void* dx_residual, void* dx, float* dA, float* dB, int accumulate, int64_t M,
                                    int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout, void* workspace,
                                    size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_linear_bwd_ex");
   if (!dy) return fail(MCB_ERR_NULL, "lora_linear_bwd: dy is null");
   if (dx && !W) return fail(MCB_ERR_NULL, "lora_linear_bwd: dx wanted but W is null");
   if (r > 0 && (!A || !B)) return fail(MCB_ERR_NULL, "lora_linear_bwd: rank %lld but A or B is null", (long long)r);
@@ -95,6 +98,7 @@ extern "C" size_t mcb_matmul_workspace_bytes(int64_t K, int64_t N, int dtype) {
 
 extern "C" int mcb_matmul(const void* a, const void* b, void* out, int64_t M, int64_t K, int64_t N, int dtype,
                           void* workspace, size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_matmul");
   if (!a || !b || !out) return fail(MCB_ERR_NULL, "matmul: null pointer");
   if (M <= 0 || K <= 0 || N <= 0) return fail(MCB_ERR_SHAPE, "matmul: M=%lld K=%lld N=%lld must be positive", (long long)M, (long long)K, (long long)N);
   DeviceState* ds = current_device_state();
@@ -112,6 +116,7 @@ extern "C" int mcb_matmul(const void* a, const void* b, void* out, int64_t M, in
 
 extern "C" int mcb_linear_swiglu_fwd(const void* x, const void* w_gate_up, void* gate, void* up, void* act, int64_t M,
                                      int64_t K, int64_t F, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_linear_swiglu_fwd");
   if (!x || !w_gate_up || !gate || !up || !act) return fail(MCB_ERR_NULL, "linear_swiglu_fwd: null pointer");
   if (M <= 0 || K <= 0 || F <= 0) return fail(MCB_ERR_SHAPE, "linear_swiglu_fwd: M=%lld K=%lld F=%lld must be positive", (long long)M, (long long)K, (long long)F);
   if (dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "linear_swiglu_fwd: bfloat16 only (use two mcb_lora_linear_fwd calls and mcb_swiglu_fwd)");

@@ -692,6 +692,7 @@ using namespace mcb;
 
 extern "C" int mcb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t rows, int64_t D,
                                float eps, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_rmsnorm_fwd");
   if (!x || !y) return fail(MCB_ERR_NULL, "rmsnorm_fwd: x or y is null");
   if (int rc = check_rows("rmsnorm_fwd", rows, D, dtype)) return rc;
   DeviceState* ds = current_device_state();
@@ -714,6 +715,7 @@ extern "C" int mcb_add(const void* a, const void* b, void* out, int64_t n, int d
 extern "C" int mcb_rmsnorm_bwd_ex(const void* x, const void* w, const void* dy, const void* dx_residual, void* dx,
                                   float* dw, int accumulate, int64_t rows, int64_t D, float eps, int dtype,
                                   void* workspace, size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_add");
   if (dx_residual == nullptr)
     return mcb_rmsnorm_bwd(x, w, dy, dx, dw, accumulate, rows, D, eps, dtype, workspace, workspace_bytes, stream);
   if (!x || !dy || !dx) return fail(MCB_ERR_NULL, "rmsnorm_bwd_ex: x, dy or dx is null");
@@ -761,6 +763,7 @@ extern "C" int mcb_rmsnorm_bwd(const void* x, const void* w, const void* dy, voi
 }
 
 extern "C" int mcb_softmax_fwd(const void* x, void* y, int64_t rows, int64_t D, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_softmax_fwd");
   if (!x || !y) return fail(MCB_ERR_NULL, "softmax_fwd: x or y is null");
   if (int rc = check_rows("softmax_fwd", rows, D, dtype)) return rc;
   DeviceState* ds = current_device_state();
@@ -772,6 +775,7 @@ extern "C" int mcb_softmax_fwd(const void* x, void* y, int64_t rows, int64_t D, 
 
 extern "C" int mcb_softmax_causal_fwd(const void* x, void* y, int64_t rows, int64_t D, int64_t seq, float scale, int dtype,
                                       void* stream) {
+  MCB_NVTX_RANGE("mcb_softmax_causal_fwd");
   if (!x || !y) return fail(MCB_ERR_NULL, "softmax_causal_fwd: x or y is null");
   if (int rc = check_rows("softmax_causal_fwd", rows, D, dtype)) return rc;
   if (seq <= 0 || seq > 0x7fffffff || rows % seq != 0)
@@ -785,6 +789,7 @@ extern "C" int mcb_softmax_causal_fwd(const void* x, void* y, int64_t rows, int6
 
 extern "C" int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int dtype,
                                void* stream) {
+  MCB_NVTX_RANGE("mcb_softmax_bwd");
   if (!y || !dy || !dx) return fail(MCB_ERR_NULL, "softmax_bwd: y, dy or dx is null");
   if (int rc = check_rows("softmax_bwd", rows, D, dtype)) return rc;
   DeviceState* ds = current_device_state();
@@ -796,6 +801,7 @@ extern "C" int mcb_softmax_bwd(const void* y, const void* dy, void* dx, int64_t 
 
 extern "C" int mcb_softmax_causal_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t D, int64_t seq,
                                       float scale, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_softmax_causal_bwd");
   if (!y || !dy || !dx) return fail(MCB_ERR_NULL, "softmax_causal_bwd: y, dy or dx is null");
   if (int rc = check_rows("softmax_causal_bwd", rows, D, dtype)) return rc;
   if (seq < 0 || seq > 0x7fffffff || (seq > 0 && rows % seq != 0))
@@ -855,6 +861,7 @@ int rmsnorm_bwd_noalloc_t(const void* x, const void* w, const void* dy, void* dx
 
 extern "C" int mcb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, int accumulate,
                                        int64_t rows, int64_t D, float eps, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_rmsnorm_bwd_noalloc");
   using namespace mcb;
   if (!x || !dy || !dx) return fail(MCB_ERR_NULL, "rmsnorm_bwd_noalloc: x, dy or dx is null");
   if (int rc = check_rows("rmsnorm_bwd_noalloc", rows, D, dtype)) return rc;

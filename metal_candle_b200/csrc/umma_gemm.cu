@@ -571,7 +571,22 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   // the weight gradients as a tail phase: the same CTAs, the stage ring re-cut for token rows
   GradPlan tail;
   memset(&tail.p, 0, sizeof(tail.p));
-  bool tail_on = c.grads != nullptr;
+  // The tail phase makes CTAs wait for rank-intermediate rows that OTHER CTAs of this launch write, which is only
+  // safe when the whole grid is resident at once (a CTA that has not started cannot be waited for by CTAs that hold
+  // every SM).  One CTA fits an SM, so the grid must not exceed what the occupancy query says the device can hold;
+  // a context restricted to fewer SMs than it reports, or a caller that runs other kernels beside this one (a
+  // collective overlapping the backward pass), switches the tail off with MCB_OPT_GRAD_TAIL = 0 and gets the
+  // separate gradient launch, which waits for nothing.
+  bool tail_on = c.grads != nullptr && option(MCB_OPT_GRAD_TAIL) != 0;
+  if (tail_on) {
+    static int occ_cached = -1;
+    if (occ_cached < 0) {
+      int occ = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, lora_gemm_kernel, kThreads, kSmemBudget + 1024) != cudaSuccess) occ = 0;
+      occ_cached = occ;
+    }
+    if (static_cast<long long>(occ_cached) * ds->sm_count < grid) tail_on = false;
+  }
   if (tail_on) {
     const uint32_t budget = p.bar_off < static_cast<uint32_t>(kGradSmemBudget) ? p.bar_off : static_cast<uint32_t>(kGradSmemBudget);
     if (int rc = plan_grad2(*c.grads, c.M, c.rp, grid, budget, ds, &tail)) return rc;
@@ -593,7 +608,7 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
       flops += 2.0 * m * (c.grads->C[0] + c.grads->C[1]) * c.r_true;
       bytes += 2.0 * m * (c.grads->C[0] + c.grads->C[1]) + 4.0 * m * c.rp;
     }
-    profile_begin(kProfGemm, flops, bytes, st);
+    profile_begin(c.rp > 0 ? kProfGemmLora : kProfGemm, flops, bytes, st);
   }
   lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, tail.tmX[0], tail.tmH[0], tail.tmX[1],
                                                                 tail.tmH[1], p, tail.p);

@@ -521,7 +521,7 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   const bool prof = profile_on();
   if (prof) {
     const double m = static_cast<double>(M), n = static_cast<double>(N), k = static_cast<double>(K);
-    profile_begin(kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
+    profile_begin(c.rp > 0 ? kProfGemmLora : kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
                   2.0 * (m * k + n * k + m * n) + 2.0 * c.rp * (k + n), st);
   }
   lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, tmY, tmY, p);

@@ -44,8 +44,8 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).  The limit is counted
 // on the SM's own cycle counter, read (like the abort flag) only every 16th poll: the global nanosecond timer is
 // slow to read, and a wait that has to poll at all must not pay for that on the critical path of a handshake.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          int* status) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                                int* status, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
   for (uint32_t spins = 1;; ++spins) {
@@ -54,12 +54,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (*abort_flag != 0) return false;
     const long long now = clock64();
     if (t0 == 0) t0 = now;
-    if (now - t0 > kWaitLimitCycles) {
+    if (now - t0 > limit_cycles) {
       *abort_flag = code;
       atomicCAS(status, 0, code);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          int* status) {
+  return mbar_wait_limit(bar, parity, abort_flag, code, status, kWaitLimitCycles);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(

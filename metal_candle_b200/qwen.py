@@ -79,8 +79,13 @@ class _Linear:
 class CapturedStep:
     """forward_backward of a fixed shape as a CUDA graph (Qwen.capture_forward_backward)."""
 
-    def __init__(self, graph, ids, targets, loss, grads):
+    def __init__(self, graph, ids, targets, loss, grads, keepalive=()):
         self.graph, self.ids, self.targets, self.loss, self.grads = graph, ids, targets, loss, grads
+        # The graph's kernels carry the ADDRESSES of the scratch buffers that were current at capture time (GEMM
+        # operand packs, partial sums, attention and RMSNorm scratch).  The per-device scratch buffer is replaced
+        # when a later call needs a larger one; holding the captured ones here keeps their memory from being handed
+        # to another tensor while this graph can still be replayed.
+        self._keepalive = list(keepalive)
 
     def __call__(self, input_ids: torch.Tensor, target_ids: torch.Tensor):
         """Copies the batch into the graph's input buffers (device to device, or from pinned host memory) and
@@ -126,6 +131,7 @@ class Qwen:
         self._grad_views: List[torch.Tensor] = []
         self._grad_slices: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
         self.layer_done_hook = None  # called as hook(layer_idx) when a layer's LoRA gradients are final
+        self.backward_done_hook = None  # called once at the end of forward_backward (joins side-stream work)
 
     # -- adapter management (Qwen::apply_adapter / remove_adapter, src/models/qwen.rs:150-175) --
     def apply_adapter(self, adapter: LoRAAdapter) -> None:
@@ -337,31 +343,39 @@ class Qwen:
             saved[idx] = None
             if self.layer_done_hook is not None:
                 self.layer_done_hook(idx)
+        if self.backward_done_hook is not None:
+            self.backward_done_hook()
         return loss[:1], self._grad_views
 
-    def capture_forward_backward(self, batch: int, seq: int) -> "CapturedStep":
+    def capture_forward_backward(self, batch: int, seq: int, keep_hooks: bool = False, pool=None) -> "CapturedStep":
         """Records forward_backward for one (batch, seq) shape into a CUDA graph.  The step is some thousand
         short launches; replayed from a graph they run back to back without the host in the loop.  Call it
         after at least one eager forward_backward of the same shape (kernel attributes and cached workspaces
         are set up on first use, which must not happen during capture).  The adapter's tensors are read in
         place, so optimizer updates between replays are seen; inputs go into the returned object's `ids` and
-        `targets` buffers."""
+        `targets` buffers.  `keep_hooks` leaves `layer_done_hook` / `backward_done_hook` installed during the
+        capture: only for hooks that enqueue stream work which a graph can record (the C-ABI communicator's
+        all-reduce on a side stream that forks from and joins the capturing stream), never host-side work.
+        `pool` (another capture's `graph.pool()`) lets graphs that are never replayed concurrently share memory."""
         if self.lora_adapter is None:
             raise TrainingError("capture_forward_backward needs an adapter (apply_adapter)")
         ids = torch.zeros(batch, seq, dtype=torch.int32, device=self.device)
         targets = torch.full((batch, seq), -1, dtype=torch.int32, device=self.device)
-        hook, self.layer_done_hook = self.layer_done_hook, None   # no host callbacks inside a graph
+        hook, done_hook = self.layer_done_hook, self.backward_done_hook
+        if not keep_hooks:
+            self.layer_done_hook = self.backward_done_hook = None   # no host callbacks inside a graph
         was_profiling = _lib.profile_enabled()
         _lib.profile_enable(False)                                # per-launch events cannot be recorded either
         graph = torch.cuda.CUDAGraph()
+        keep = backend.workspace_refs(self.device)   # the scratch buffer the first captured kernels will point at
         try:
             torch.cuda.synchronize(self.device)
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            with torch.cuda.graph(graph, pool=pool, capture_error_mode="thread_local"):
                 loss, grads = self.forward_backward(ids, targets)
         finally:
-            self.layer_done_hook = hook
+            self.layer_done_hook, self.backward_done_hook = hook, done_hook
             _lib.profile_enable(was_profiling)
-        return CapturedStep(graph, ids, targets, loss, grads)
+        return CapturedStep(graph, ids, targets, loss, grads, keepalive=keep + backend.workspace_refs(self.device))
 
     def _layer_bwd(self, dh3, L, sv, idx, B, S, accumulate):
         c = self.config

@@ -6,16 +6,18 @@ Workloads (synthetic token ids uniform in [0, vocab), next-token targets, random
   c4            batch 8 x seq 1024, LoRA rank 8 (alpha 16) on q_proj and v_proj
 
 Data parallelism: weights and LoRA parameters are replicated (same seed on every rank); each rank takes
-its own rows of the global batch; the only exchange is a float32 sum all-reduce (NCCL) of the LoRA
-gradients, issued per group of layers from the backward pass as soon as the group is final so that it
-overlaps the rest of the backward; AdamW then runs identically everywhere with gradients scaled by
-1/world.
+its own rows of the global batch; the only exchange is a float32 sum all-reduce of the LoRA gradients, issued
+per group of layers from the backward pass as soon as the group is final, on a side stream, so that it overlaps
+the rest of the backward; AdamW then runs identically everywhere with gradients scaled by 1/world.  The
+all-reduce goes through the library's own communicator (mcb_comm_*, NCCL bound at run time); because it is plain
+stream work it is recorded into the CUDA graph of the step together with the kernels it overlaps.
 """
 from __future__ import annotations
 
 import json
 import math
 import os
+import statistics
 import sys
 import time
 
@@ -28,13 +30,32 @@ WORKLOADS = {
 N_BUCKETS = 4
 
 
+class DataParallelError(RuntimeError):
+    """The gradient exchange failed (a peer left, a deadline passed); the step's gradients are not valid."""
+
+
 class DataParallelLoRA:
-    """Bucketed, overlapped all-reduce of the flat LoRA-gradient buffer."""
+    """Bucketed, overlapped all-reduce of the flat LoRA-gradient buffer.
 
-    def __init__(self, model, world: int):
-        import torch.distributed as dist
+    With `comm` (a `metal_candle_b200.comm.Communicator`) every bucket is enqueued on a side stream that waits for
+    the backward pass up to that point; `finish` makes the current stream wait for the side stream.  Nothing in
+    it is host-synchronous, so it can be recorded into a CUDA graph.  Without `comm` the exchange goes through
+    torch.distributed (any backend; what the CPU tests use with gloo)."""
 
-        self.model, self.world, self.dist = model, world, dist
+    def __init__(self, model, world: int, comm=None):
+        self.model, self.world, self.comm = model, world, comm
+        self.dist = None
+        self.side = None
+        self.inflight = False
+        if comm is None and world > 1:
+            import torch.distributed as dist
+
+            self.dist = dist
+        if comm is not None and world > 1:
+            import torch
+
+            self.torch = torch
+            self.side = torch.cuda.Stream(priority=-1)
         L = model.num_layers()
         per = math.ceil(L / N_BUCKETS)
         self.buckets = {}  # lowest layer of the bucket -> (lo, hi) element range
@@ -44,23 +65,50 @@ class DataParallelLoRA:
             self.buckets[b] = (lo, hi)
         self.pending = []
         model.layer_done_hook = self.on_layer_done if world > 1 else None
+        model.backward_done_hook = self.finish if (world > 1 and comm is not None) else None
+
+    def _issue(self, lo: int, hi: int, async_op: bool):
+        flat = self.model.grad_flat()
+        if self.comm is not None:
+            cur = self.torch.cuda.current_stream()
+            self.side.wait_stream(cur)     # the bucket's gradients are final on the current stream
+            self.comm.allreduce_bucket(flat.data_ptr() + 4 * lo, hi - lo, self.side.cuda_stream)
+            self.inflight = True
+            return None
+        try:
+            return self.dist.all_reduce(flat[lo:hi], op=self.dist.ReduceOp.SUM, async_op=async_op)
+        except RuntimeError as e:
+            raise DataParallelError(f"gradient all-reduce failed: {e}") from e
 
     def on_layer_done(self, idx: int) -> None:
         rng = self.buckets.get(idx)
         if rng is not None:
-            flat = self.model.grad_flat()
-            self.pending.append(self.dist.all_reduce(flat[rng[0]:rng[1]], op=self.dist.ReduceOp.SUM, async_op=True))
+            w = self._issue(rng[0], rng[1], async_op=True)
+            if w is not None:
+                self.pending.append(w)
 
     def finish(self) -> None:
-        for w in self.pending:
-            w.wait()
-        self.pending = []
+        if self.comm is not None:
+            if self.inflight:
+                self.torch.cuda.current_stream().wait_stream(self.side)
+                self.inflight = False
+            return
+        try:
+            for w in self.pending:
+                w.wait()
+        except RuntimeError as e:
+            raise DataParallelError(f"gradient all-reduce failed: {e}") from e
+        finally:
+            self.pending = []
 
     def reduce_all(self) -> None:
-        """The whole flat buffer in one all-reduce: what follows a step replayed from a CUDA graph, which
-        cannot call back per layer (the buffer is a few MB; there is nothing worth overlapping)."""
+        """The whole flat buffer in one all-reduce on the current stream (no overlap)."""
         if self.world > 1:
-            self.dist.all_reduce(self.model.grad_flat(), op=self.dist.ReduceOp.SUM)
+            n = self.model.grad_flat().numel()
+            if self.comm is not None:
+                self.comm.allreduce_bucket(self.model.grad_flat().data_ptr(), n, self.torch.cuda.current_stream().cuda_stream)
+            else:
+                self._issue(0, n, async_op=False)
 
 
 def _build(torch, wl, device, seed=0):
@@ -94,9 +142,85 @@ def _host_batches(torch, n, B, S, vocab, seed):
     return out
 
 
-def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
-    """`ClockSampler`, `measured_peaks` and `cpu_baseline` are supplied by the repo-root bench.py (the CPU
-    baseline is the one leg that may touch the oracle, so it lives outside this package)."""
+def dp_check(torch, model, adapter, dp, world, rank, B, S, vocab, device, steps=3):
+    """The data-parallel arithmetic checked on the GPUs themselves: `steps` optimizer steps data-parallel (each
+    rank its own micro-batch, bucketed all-reduce, AdamW on gradients / world) against the same steps on ONE rank's
+    arithmetic, accumulating the `world` micro-batches before each optimizer step.  Every rank computes the
+    second form redundantly from the same seeds.  Returns the largest relative differences of the loss sequence
+    and of the parameter updates; leaves the adapter as it found it."""
+    import torch.distributed as dist
+
+    from .training import AdamW, AdamWConfig, LRScheduler, TrainingStep
+
+    variables = TrainingStep.collect_trainable_vars(adapter)
+    snapshot = [v.clone() for v in variables]
+    sched = LRScheduler.warmup_cosine(5, 50, 1e-4, 1e-6)
+    micro = {r: _host_batches(torch, steps, B, S, vocab, seed=777 + r) for r in range(world)}
+
+    def restore():
+        with torch.no_grad():
+            for v, s0 in zip(variables, snapshot):
+                v.copy_(s0)
+
+    # (1) data parallel
+    opt = AdamW(AdamWConfig(learning_rate=1e-4))
+    dp_losses = []
+    for s in range(steps):
+        ids, tg = micro[rank][s]
+        loss, grads = model.forward_backward(ids.to(device), tg.to(device))
+        dp.finish()
+        opt.set_lr(sched.get_lr(s))
+        opt.step_vars(variables, grads, grad_scale=1.0 / world)
+        l = loss.detach().clone().double()
+        dist.all_reduce(l, op=dist.ReduceOp.SUM)       # every micro-batch keeps the same number of tokens
+        dp_losses.append(float(l) / world)
+    p_dp = [v.clone() for v in variables]
+    restore()
+    # (2) one rank's arithmetic: accumulate the micro-batches of all ranks, then one optimizer step
+    hook, done = model.layer_done_hook, model.backward_done_hook
+    model.layer_done_hook = model.backward_done_hook = None
+    opt = AdamW(AdamWConfig(learning_rate=1e-4))
+    acc_losses = []
+    try:
+        for s in range(steps):
+            tot = 0.0
+            for r in range(world):
+                ids, tg = micro[r][s]
+                loss, grads = model.forward_backward(ids.to(device), tg.to(device), accumulate=(r > 0))
+                tot += float(loss)
+            opt.set_lr(sched.get_lr(s))
+            opt.step_vars(variables, grads, grad_scale=1.0 / world)
+            acc_losses.append(tot / world)
+    finally:
+        model.layer_done_hook, model.backward_done_hook = hook, done
+    rel_loss = max(abs(a - b) / max(abs(b), 1e-30) for a, b in zip(dp_losses, acc_losses))
+    num = max(float(((a - s0) - (b - s0)).abs().max()) for a, b, s0 in zip(p_dp, variables, snapshot))
+    den = max(float((b - s0).abs().max()) for b, s0 in zip(variables, snapshot))
+    rel_param = max(float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30) for a, b in zip(p_dp, variables))
+    restore()
+    torch.cuda.synchronize()
+    out = {"steps": steps, "max_rel_loss_diff": rel_loss, "max_rel_update_diff": num / max(den, 1e-30),
+           "max_rel_param_diff": rel_param, "loss_dp": dp_losses, "loss_accumulated": acc_losses,
+           "tolerance": {"loss": 1e-5, "update": 2e-3}}
+    out["ok"] = bool(rel_loss <= 1e-5 and out["max_rel_update_diff"] <= 2e-3)
+    return out
+
+
+def _median_ms(torch, fn, reps):
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=None):
+    """`ClockSampler`, `measured_peaks`, `cpu_baseline` and `kernel_numbers` are supplied by the repo-root bench.py
+    (the CPU baseline is the one leg that may touch the oracle, so it lives outside this package)."""
     import torch
 
     from . import _lib
@@ -111,29 +235,45 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    lib = _lib.init(local)
     dist = None
+    comm = None
+    comm_mode = getattr(args, "comm", "mcb")
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
+        if comm_mode != "torch":
+            from . import comm as C
+
+            comm = C.Communicator(world, rank, C.broadcast_id(rank), timeout_ms=120_000,
+                                  blocking=(comm_mode == "mcb-blocking"))
+    # the backward's tail phase needs its whole grid resident; with a collective running beside it, it is off
+    tail = getattr(args, "grad_tail", "auto")
+    tail_on = (tail == "on") or (tail == "auto" and world == 1)
+    _lib.check(lib.mcb_set_option(_lib.MCB_OPT_GRAD_TAIL, int(tail_on)))
     wl = WORKLOADS[args.workload]
     B, S = wl["batch"], wl["seq"]
     cfg, model, adapter, opt, sched = _build(torch, wl, device)
-    dp = DataParallelLoRA(model, world)
+    dp = DataParallelLoRA(model, world, comm=comm)
     variables = TrainingStep.collect_trainable_vars(adapter)
+    check = None
+    if world > 1 and not getattr(args, "no_dp_check", False):
+        check = dp_check(torch, model, adapter, dp, world, rank, B, S, cfg.vocab_size, device)
     n_steps = args.warmup + 2 * args.steps
     host = _host_batches(torch, min(n_steps, 8), B, S, cfg.vocab_size, seed=1234 + rank)
     dev_batches = [(i.to(device), t.to(device)) for i, t in host]
     ids_dev = torch.empty(B, S, dtype=torch.int32, device=device)
     tg_dev = torch.empty(B, S, dtype=torch.int32, device=device)
     state = {"step": 0}
-
-    captured = {"fb": None}
+    captured = {"fb": None, "fb_nocomm": None}
+    graph_has_comm = comm is not None
 
     def one_step(ids, tg):
         if captured["fb"] is not None:
-            loss, grads = captured["fb"](ids, tg)   # forward + loss + backward replayed from a CUDA graph
-            dp.reduce_all()
+            loss, grads = captured["fb"](ids, tg)   # forward + loss + backward (+ the exchange) replayed from a CUDA graph
+            if not graph_has_comm:
+                dp.reduce_all()
         else:
             loss, grads = model.forward_backward(ids, tg)
             dp.finish()
@@ -147,8 +287,9 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # Warm-up: eager steps first (kernel attributes, workspaces), the last of them with per-launch CUDA events on
-    # the GEMM launches for the roofline object; then the step is captured into a CUDA graph and warmed up again.
+    # Warm-up: eager steps first (kernel attributes, workspaces, NCCL connections), the last of them with per-launch
+    # CUDA events on the GEMM launches for the roofline object; then the step is captured into a CUDA graph and
+    # warmed up again.
     n_eager = max(2, args.warmup)
     for i in range(n_eager):
         if i == n_eager - 1:
@@ -157,18 +298,21 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
         one_step(*dev_batches[i % len(dev_batches)])
     torch.cuda.synchronize()
     _lib.profile_enable(False)
-    gemm = _lib.profile_summary(0)
+    plain = _lib.profile_summary(0)
     grad = _lib.profile_summary(1)
-    prof_steps = 1
+    lora = _lib.profile_summary(2)
     capture_note = None
     if not getattr(args, "no_graph", False):
-        hook = model.layer_done_hook
+        hooks = (model.layer_done_hook, model.backward_done_hook)
         try:
-            model.layer_done_hook = None
-            captured["fb"] = model.capture_forward_backward(B, S)
+            if not graph_has_comm:
+                model.layer_done_hook = model.backward_done_hook = None
+            captured["fb"] = model.capture_forward_backward(B, S, keep_hooks=graph_has_comm)
+            if graph_has_comm:   # the same step without the exchange, sharing the first graph's memory: for comm.exposed_ms
+                captured["fb_nocomm"] = model.capture_forward_backward(B, S, keep_hooks=False, pool=captured["fb"].graph.pool())
         except Exception as e:  # the eager path stays valid; say why the graph is not used
-            captured["fb"] = None
-            model.layer_done_hook = hook
+            captured["fb"] = captured["fb_nocomm"] = None
+            model.layer_done_hook, model.backward_done_hook = hooks
             capture_note = f"{type(e).__name__}: {e}"[:200]
             print(f"bench: CUDA-graph capture failed, timing eager launches instead ({capture_note})", file=sys.stderr)
             torch.cuda.synchronize()
@@ -177,8 +321,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             okf = torch.tensor([1 if captured["fb"] is not None else 0], device=device, dtype=torch.int32)
             dist.all_reduce(okf, op=dist.ReduceOp.MIN)
             if int(okf.item()) == 0 and captured["fb"] is not None:
-                captured["fb"] = None
-                model.layer_done_hook = hook
+                captured["fb"] = captured["fb_nocomm"] = None
+                model.layer_done_hook, model.backward_done_hook = hooks
                 capture_note = "another rank could not capture"
         for i in range(args.warmup):
             one_step(*dev_batches[i % len(dev_batches)])
@@ -195,6 +339,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler is not None else None
+    if captured["fb"] is not None and int(model.last_count.item()) == 0:
+        raise SystemExit("bench: every target of the last batch was ignored; the loss is undefined")
     # ---- end to end: pinned host ids -> device, step, loss back to the host, every step ----
     barrier()
     t0 = time.perf_counter()
@@ -209,18 +355,80 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             last = float(one_step(ids_dev, tg_dev).item())
     barrier()
     e2e_s = time.perf_counter() - t0
+    own_ms = ms
+    comm_info = None
     if dist is not None:
         t = torch.tensor([ms, e2e_s], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s = float(t[0]), float(t[1])
+        per_rank = [torch.zeros(1, device=device, dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(per_rank, torch.tensor([own_ms], device=device, dtype=torch.float64))
+        per_rank = [float(x) / args.steps for x in per_rank]
+        # ---- the exchange on its own, and how much of it the step does not hide ----
+        nbytes = model.grad_flat().numel() * 4
+        scratch = torch.zeros_like(model.grad_flat())
+
+        def exchange_alone():
+            for lo, hi in dp.buckets.values():
+                if comm is not None:
+                    comm.allreduce_bucket(scratch.data_ptr() + 4 * lo, hi - lo, torch.cuda.current_stream().cuda_stream)
+                else:
+                    dist.all_reduce(scratch[lo:hi])
+
+        barrier()
+        exchange_alone()
+        alone_ms = _median_ms(torch, exchange_alone, 5)
+        exposed = None
+        if captured["fb_nocomm"] is not None:
+            ids0, tg0 = dev_batches[0]
+            barrier()
+            with_ms = _median_ms(torch, lambda: captured["fb"](ids0, tg0), 5)
+            barrier()
+            without_ms = _median_ms(torch, lambda: captured["fb_nocomm"](ids0, tg0), 5)
+            exposed = with_ms - without_ms
+        t = torch.tensor([alone_ms, exposed if exposed is not None else -1e9], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        alone_ms = float(t[0])
+        exposed = float(t[1]) if exposed is not None else None
+        comm_info = {"backend": ("mcb_comm (NCCL through the C ABI, " + ("blocking" if comm_mode == "mcb-blocking" else "non-blocking") + ")")
+                     if comm is not None else "torch.distributed nccl",
+                     "nccl_version": comm.info()["nccl_version"] if comm is not None else None,
+                     "bytes_per_step": nbytes, "buckets": len(dp.buckets),
+                     "overlapped": bool(comm is not None or captured["fb"] is None),
+                     "in_graph": bool(graph_has_comm and captured["fb"] is not None),
+                     "exposed_ms": exposed,
+                     "exposed_how": "step graph with the exchange minus the same graph without it (median of 5 replays each, max over ranks)"
+                     if exposed is not None else None,
+                     "allreduce_alone_ms": alone_ms,
+                     "bus_GBps": 2.0 * (world - 1) / world * nbytes / (alone_ms * 1e-3) / 1e9 if alone_ms > 0 else None,
+                     "rank_ms_per_step": {"min": min(per_rank), "max": max(per_rank)}}
     status = _lib.device_status()
+    if dist is not None:
+        t = torch.tensor([status], device=device, dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        status = int(t.item())
+    if status != 0:
+        print(f"bench: a bounded device-side wait ran out (code {status}); the run's results are invalid", file=sys.stderr)
+        if dist is not None:
+            dist.destroy_process_group()
+        raise SystemExit(3)
+    if comm is not None:
+        comm.destroy()
+    if dist is not None:
+        dist.destroy_process_group()
     if rank == 0:
         tokens = B * S * world * args.steps
         pk = measured_peaks()
-        n_l, g_ms, g_fl, g_by = gemm
-        achieved = g_fl / g_ms / 1e9 if g_ms > 0 else 0.0
         peak = pk["bf16_tflops_sustained"]
-        per_step_launches = _count_launches(cfg, wl)
+
+        def klass(rec):
+            n_l, g_ms, g_fl, g_by = rec
+            ach = g_fl / g_ms / 1e9 if g_ms > 0 else 0.0
+            return {"launches": n_l, "ms_per_step": g_ms, "flop_per_step": g_fl, "achieved": ach, "frac": ach / peak}
+
+        both_ms, both_fl = plain[1] + lora[1], plain[2] + lora[2]
+        achieved = both_fl / both_ms / 1e9 if both_ms > 0 else 0.0
+        per_step_launches = _count_launches(cfg, wl, tail_on)
         line = {
             "metric": "LoRA fwd+bwd tokens/s, Qwen2.5-0.5B shape", "value": tokens / (ms / 1e3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
@@ -228,7 +436,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
             "config": {"workload": wl["name"], "per_gpu_batch": B, "seq_len": S, "global_batch": B * world,
                        "lora_rank": wl["rank"], "lora_targets": list(wl["targets"]), "parallelism": f"dp{world}",
                        "optimizer": "AdamW lr 1e-4 warmup-cosine",
-                       "execution": ("forward+loss+backward replayed from a CUDA graph, then gradient all-reduce and AdamW"
+                       "execution": (("forward+loss+backward" + (" with the bucketed gradient all-reduce overlapped on a side stream" if graph_has_comm and world > 1 else "")
+                                      + " replayed from a CUDA graph, then " + ("" if graph_has_comm or world == 1 else "gradient all-reduce and ") + "AdamW")
                                      if captured["fb"] is not None else
                                      "eager launches" + (f" (graph capture failed: {capture_note})" if capture_note else "")),
                        "l2": "inputs larger than L2 (activations of one "
@@ -237,26 +446,39 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline):
                     "d2h_bytes_per_step": 4},
             "gpu_launches": per_step_launches * args.steps,
             "roofline": {"bound": "tensor", "kernel": "lora_gemm2_kernel + lora_gemm_kernel (all projections of the step; the dx launches of the LoRA "
-                                   "projections include their dA/dB tail phase)",
+                                   "projections include their dA/dB tail phase when it is on)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
+                         "traffic": 79.3e6,
+                         "traffic_source": "ncu, one launch: fused LoRA forward 32768x896x896 r16 (dram read 60.5 MB + write 18.8 MB; "
+                                           "algorithmic 119.1 MB, the rest of the output was still in L2) - profiles/lora_gemm_kernel.md; "
+                                           "the step as a whole is too large to capture",
+                         "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
                          "measured_in": "per-launch CUDA events in the last eager warm-up step of this run"
                                         + (" (the timed steps replay a CUDA graph)" if captured["fb"] is not None else ""),
-                         "launches": n_l, "kernel_ms_per_step": g_ms / prof_steps,
-                         "share_of_step": (g_ms / prof_steps) / (ms / args.steps) if ms > 0 else None,
-                         "lora_grad_kernel": {"launches": grad[0], "ms_per_step": grad[1] / prof_steps,
+                         "launches": plain[0] + lora[0], "kernel_ms_per_step": both_ms,
+                         "share_of_step": both_ms / (ms / args.steps) if ms > 0 else None,
+                         "classes": {"lora": dict(klass(lora), what="launches with a rank path: the fused LoRA linear forward and "
+                                                  "backward of the adapted projections (dA/dB tail phase included when on)"),
+                                     "plain": dict(klass(plain), what="frozen projections without an adapter (MLP, lm_head, ...)")},
+                         "lora_grad_kernel": {"launches": grad[0], "ms_per_step": grad[1],
                                               "achieved_GBps": grad[3] / grad[1] / 1e6 if grad[1] > 0 else None,
                                               "hbm_peak_GBps": pk["hbm_gbs"]}},
             "clocks": clocks, "device_status": status,
         }
+        if comm_info is not None:
+            line["comm"] = comm_info
+        if check is not None:
+            line["dp_check"] = check
         if world == 1:
-            line["cpu_baseline"] = cpu_baseline(WORKLOADS[args.workload], steps=1, warmup=0)
+            if kernel_numbers is not None and not getattr(args, "no_kernels", False):
+                del model, adapter, opt, dp, captured, dev_batches
+                torch.cuda.empty_cache()
+                line["kernels"] = kernel_numbers(torch)
+            line["cpu_baseline"] = cpu_baseline(WORKLOADS[args.workload], steps=2, warmup=1)
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
 
 
-def _count_launches(cfg, wl) -> int:
+def _count_launches(cfg, wl, tail_on=True) -> int:
     """Kernels of this library launched per training step (counted from the step's structure)."""
     L = cfg.num_hidden_layers
     n_lora = len(wl["targets"])
@@ -276,7 +498,7 @@ def _count_launches(cfg, wl) -> int:
     grad_launches = 0
     for t in wl["targets"]:
         o, i = out_f[t], in_f.get(t, cfg.hidden_size)
-        tail = o < 1536 and max(o, i) <= 1024 and o % 64 == 0 and i % 64 == 0
+        tail = tail_on and o < 1536 and max(o, i) <= 1024 and o % 64 == 0 and i % 64 == 0
         grad_launches += 1 if tail else 2
     per_layer_bwd = 7 + n_lora + grad_launches + 1 + 2 + (3 if fused_attn else 4) + (2 if fused_attn else 1)
     tail = 1 + 1 + 1 + 3 + 1 + 1  # embed, norm, lm_head, CE x3, lm_head bwd, norm bwd

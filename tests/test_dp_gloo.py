@@ -101,3 +101,82 @@ def test_single_process_installs_no_hook():
     model.backward(0)
     dp.finish()
     assert sorted(dp.buckets) == [0, 2, 4]
+
+
+# ---- failure detection on the host: a rank that leaves between steps, a rank that never joins --------------------
+
+def _leaver_worker(rank, world, port, out):
+    """Rank 1 completes step 0 and then exits (between steps, with nothing in flight).  Rank 0 goes on to step 1:
+    its exchange must end with an error within the process group's timeout instead of blocking."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from metal_candle_b200.step_bench import DataParallelError, DataParallelLoRA
+
+    model = FakeModel(n_layers=8)
+    dp = DataParallelLoRA(model, world)
+    model.backward(rank)
+    dp.finish()
+    ok0 = bool(torch.equal(model.flat, torch.arange(model.flat.numel(), dtype=torch.float32) * 3))
+    if rank == 1:
+        out.put((rank, "left" if ok0 else "bad step 0"))
+        out.close()
+        out.join_thread()      # the message is on its way before the process disappears
+        os._exit(0)            # gone: no further collective, no clean shutdown
+    t0 = time.perf_counter()
+    try:
+        model.backward(rank)
+        dp.finish()
+        out.put((rank, "no error"))
+    except DataParallelError as e:
+        out.put((rank, ("error", ok0, time.perf_counter() - t0, str(e)[:80])))
+    out.close()
+    out.join_thread()
+    os._exit(0)
+
+
+@pytest.mark.timeout(120)
+def test_rank_that_leaves_between_steps_gives_the_survivor_an_error():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(out.get(timeout=100) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert results[1] == "left"
+    kind, ok0, waited, msg = results[0]
+    assert kind == "error" and ok0, results
+    assert waited < 60.0, f"the survivor waited {waited:.1f} s"
+
+
+def _lonely_worker(port, out):
+    """World size 2, but the second rank is never started: the rendezvous must time out on the host."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK="0", WORLD_SIZE="2")
+    t0 = time.perf_counter()
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        out.put("joined")
+    except Exception as e:
+        out.put(("error", time.perf_counter() - t0, type(e).__name__))
+    out.close()
+    out.join_thread()
+    os._exit(0)
+
+
+@pytest.mark.timeout(120)
+def test_rank_that_never_joins_times_out_on_the_host():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(_free_port(), out))
+    p.start()
+    res = out.get(timeout=100)
+    p.join(timeout=30)
+    assert res[0] == "error" and res[1] < 60.0, res

@@ -5,7 +5,8 @@ already taken the whole GPU, or a thread that must not trigger the device-wide s
 allocation brings -- so they cannot hand mcb_rmsnorm_bwd a workspace.  This variant keeps the dw partial
 sums in an array built into the library.  The test calls it through the C ABI twice in a row (the array
 keeps the first call's contents, which the second call must not be confused by) and compares with the
-workspace-taking entry point; it also checks that sizes past the built-in limit are refused.
+workspace-taking entry point and with the CPU oracle's RMSNorm reverse pass; it also checks that sizes past the
+built-in limit are refused.
 
 Collected last on purpose: a run that stops at the first failure has then already run everything else.
 """
@@ -37,6 +38,16 @@ def _call_pair(lib, dev, rows, D, dtype, seed, weighted=True):
     _lib.check(lib.mcb_rmsnorm_bwd_noalloc(x.data_ptr(), w.data_ptr() if weighted else None, dy.data_ptr(),
                                            dx.data_ptr(), dw.data_ptr(), 0, rows, D, 1e-6, code, st))
     torch.cuda.synchronize()
+    # the CPU oracle on the same (already rounded) inputs: both entry points share kernels, so agreeing with each
+    # other is not enough
+    from oracle import reference_ops as R
+
+    xw = x.float().cpu().numpy()
+    ww = w.float().cpu().numpy() if weighted else np.ones(D, dtype=np.float32)
+    odx, odw = R.rms_norm_backward(xw, ww, 1e-6, dy.float().cpu().numpy())
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert _close(dx.float().cpu().numpy(), odx, tol), "dx against the oracle"
+    assert _close(dw.cpu().numpy(), odw, tol if dtype == torch.float32 else 1e-3), "dw against the oracle"
     return dx.float().cpu().numpy(), dw.cpu().numpy(), dx_ref.float().cpu().numpy(), dw_ref.cpu().numpy()
 
 
@@ -68,6 +79,20 @@ def test_noalloc_accumulate_and_no_weight(cuda_device):
     lib = _lib.init(0)
     dx, dw, dx_ref, dw_ref = _call_pair(lib, cuda_device, 257, 2048, torch.float32, 7, weighted=False)
     assert _close(dx, dx_ref, 1e-4) and _close(dw, dw_ref, 1e-4)
+    dx, dw, dx_ref, dw_ref = _call_pair(lib, cuda_device, 700, 896, torch.bfloat16, 8, weighted=False)
+    assert _close(dx, dx_ref, 2e-2) and _close(dw, dw_ref, 1e-4)
+    # dw not wanted: dx alone, against the oracle
+    from oracle import reference_ops as R
+
+    g = torch.Generator(device=cuda_device).manual_seed(9)
+    x = torch.randn(300, 1024, device=cuda_device, generator=g)
+    dy = torch.randn(300, 1024, device=cuda_device, generator=g)
+    w = 1 + 0.1 * torch.randn(1024, device=cuda_device, generator=g)
+    dx_only = torch.empty_like(x)
+    _lib.check(lib.mcb_rmsnorm_bwd_noalloc(x.data_ptr(), w.data_ptr(), dy.data_ptr(), dx_only.data_ptr(), None, 0, 300, 1024,
+                                           1e-6, _lib.MCB_F32, torch.cuda.current_stream().cuda_stream))
+    odx, _ = R.rms_norm_backward(x.cpu().numpy(), w.cpu().numpy(), 1e-6, dy.cpu().numpy())
+    assert _close(dx_only.cpu().numpy(), odx, 1e-4)
     dev = cuda_device
     x = torch.randn(64, 256, device=dev)
     dy = torch.randn(64, 256, device=dev)
