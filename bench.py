@@ -182,11 +182,23 @@ def micro_lora(torch, M, K, N, r, dtype, which, iters=20, warmup=5):
         fwd(i)
         bwd(i)
 
+    lib = B._lib_for(xs[0])
+    dxbuf = torch.empty(M, K, device=dev, dtype=dt)
+    ws = B.workspace(dev, lib.mcb_lora_workspace_bytes(M, K, N, r, B._dtype_code(xs[0])))
+
+    def bwd_dx(i):   # dx alone (no dA / dB): what the rank path costs the backward GEMM by itself
+        from metal_candle_b200 import _lib as L
+        L.check(lib.mcb_lora_linear_bwd(xs[i % nv].data_ptr(), Wt.data_ptr(), A.data_ptr() if r else None,
+                                        Bm.data_ptr() if r else None, dys[i % nv].data_ptr(), None, dxbuf.data_ptr(), None, None,
+                                        0, M, K, N, r, scale, B._dtype_code(xs[0]), L.MCB_W_IN_OUT, ws.data_ptr(), ws.numel(),
+                                        torch.cuda.current_stream().cuda_stream))
+
     fl_f = 2 * M * K * N + 2 * M * r * (K + N)
     fl_b = 2 * M * K * N + 4 * M * r * (K + N)
     by_f = e * (M * K + K * N + M * N) + e * r * (K + N)
     by_b = e * (M * N + K * N + 2 * M * K) + 6 * r * (K + N)
-    fn, fl, by = {"fwd": (fwd, fl_f, by_f), "bwd": (bwd, fl_b, by_b), "both": (both, fl_f + fl_b, by_f + by_b)}[which]
+    fn, fl, by = {"fwd": (fwd, fl_f, by_f), "bwd": (bwd, fl_b, by_b), "both": (both, fl_f + fl_b, by_f + by_b),
+                  "bwd_dx": (bwd_dx, fl_f, by_f)}[which]
     med, mn = _time_kernel(torch, fn, nv, iters, warmup)
     pk = measured_peaks()
     tf = fl / med / 1e9
@@ -468,7 +480,10 @@ def run_micro(args):
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
-    _lib.init(0)
+    lib = _lib.init(0)
+    for kv in args.opt:
+        k, v = kv.split("=")
+        _lib.check(lib.mcb_set_option(int(k), int(v)))
     if args.sweep == "c2":
         for dtype in ("bf16", "f32"):
             for D in (896, 2048, 4096):
@@ -525,7 +540,7 @@ def main():
     ap.add_argument("--n", type=int, default=1 << 26)
     ap.add_argument("--tensors", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
-    ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both"])
+    ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both", "bwd_dx"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup-iters", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true")
@@ -534,6 +549,8 @@ def main():
                          "communicator, or torch.distributed")
     ap.add_argument("--grad-tail", default="auto", choices=["auto", "on", "off"],
                     help="dA/dB in the tail phase of the dx launch (auto: on with one GPU, off beside a collective)")
+    ap.add_argument("--opt", action="append", default=[], metavar="ID=VALUE",
+                    help="library switch for this run (mcb_set_option), e.g. --opt 1=512")
     ap.add_argument("--no-dp-check", action="store_true", help="skip the data-parallel arithmetic check at N > 1")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel numbers at N = 1")
     args = ap.parse_args()

@@ -80,7 +80,15 @@ int mcb_selftest_wait_timeout(int64_t limit_cycles, int64_t* waited_cycles_out, 
  * other kernels beside the backward pass (a collective on a second stream), or a context limited to a share of the
  * SMs, should set it to 0: the gradients then take their own launch, which waits for nothing. */
 #define MCB_OPT_GRAD_TAIL 0
-#define MCB_OPT_COUNT_ 1
+/* Smallest reduction length (in features) from which a linear WITH a rank path runs on CTA pairs instead of the
+ * one-CTA kernel (default 1536; linears without a rank path always take the pair kernel when large enough). */
+#define MCB_OPT_PAIR_MIN_K 1
+/* 1 (default): the small operand-pack and partial-sum kernels around the fused LoRA GEMM are chained to it by
+ * programmatic dependent launch, so that each kernel's launch and set-up run under its predecessor's tail; 0: plain
+ * stream order. */
+#define MCB_OPT_PDL 2
+#define MCB_OPT_DEBUG_ 3   /* timing experiments; leave 0 */
+#define MCB_OPT_COUNT_ 4
 int mcb_set_option(int option_id, int value);
 int mcb_get_option(int option_id, int* value_out);
 
@@ -298,7 +306,8 @@ int mcb_comm_allreduce_bucket(mcb_comm* comm, float* buf, int64_t count, void* s
 int mcb_comm_wait(mcb_comm* comm, void* stream, int timeout_ms);
 int mcb_comm_abort(mcb_comm* comm);
 int mcb_comm_info(const mcb_comm* comm, int* nranks, int* rank, int* dead, int* nccl_version);
-/* Finalizes (within the communicator's deadline) and frees; also frees a dead communicator. */
+/* Finalizes (within the communicator's deadline) and frees; also frees a dead communicator.  CUDA graphs that
+ * recorded this communicator's collectives must be destroyed first: NCCL waits for them. */
 int mcb_comm_destroy(mcb_comm* comm);
 
 /* ---- AdamW -------------------------------------------------------------------------------- */

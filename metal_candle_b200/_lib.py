@@ -14,6 +14,8 @@ MCB_W_OUT_IN, MCB_W_IN_OUT = 0, 1
 MCB_ERR_DEVICE_TIMEOUT, MCB_ERR_COMM_TIMEOUT, MCB_ERR_COMM_DEAD, MCB_ERR_COMM_UNAVAILABLE = 100001, 100002, 100003, 100004
 MCB_ERR_COMM_BASE = 200000
 MCB_OPT_GRAD_TAIL = 0
+MCB_OPT_PAIR_MIN_K = 1
+MCB_OPT_PDL = 2
 MCB_WAIT_CODE_SELFTEST = 90
 MCB_COMM_ID_BYTES = 128
 MCB_COMM_BLOCKING = 1

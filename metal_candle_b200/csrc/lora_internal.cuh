@@ -61,6 +61,9 @@ struct GemmCall {
   // Weight-gradient problems to run as a tail phase of the same launch (one-CTA kernel only), or null.  Problem 0
   // reads the H this call writes.
   const GradRequest* grads = nullptr;
+  // The launch directly before this call's GEMM on the same stream is the operand-pack kernel of this call (the
+  // GEMM may then be launched as its programmatic dependent).
+  bool after_pack = false;
 };
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a, const DeviceState* ds);

@@ -61,6 +61,7 @@ struct GemmParams {
   int M, N, K;
   int BN, rp, has_w, stages;
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;
+  int pdl_wait;       // 1: launched as a programmatic dependent of the operand-pack kernel: wait for it before loading
   float scale;
   __nv_bfloat16* Y;
   const __nv_bfloat16* bias;
@@ -142,6 +143,8 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // a partial-sum kernel chained behind this launch may be set up now; it waits for this grid before it reads
+  if (threadIdx.x == 0) grid_launch_dependents();
 
   const int nkb = p.num_k_blocks;
 
@@ -152,6 +155,8 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       int i = 0;
+      // everything up to here (barriers, tensor memory) ran under the tail of the operand-pack kernel
+      if (p.pdl_wait) grid_dependency_wait();
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++i) {
         int mt, nt;
         tile_coords(p, t, mt, nt);
@@ -449,6 +454,7 @@ lora_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 __global__ void pack_lora_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                  __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Q, int K, int N, int r,
                                  int rp, int mode, int* __restrict__ flags, int n_flags) {
+  grid_launch_dependents();   // the GEMM chained behind this kernel may start its set-up; it waits before it loads P / Q
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   // the per-tile counters of the backward kernel's tail phase start from zero in every call
   for (int64_t i = tid; i < n_flags; i += static_cast<int64_t>(gridDim.x) * blockDim.x) flags[i] = 0;
@@ -610,8 +616,14 @@ int launch_gemm(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     }
     profile_begin(c.rp > 0 ? kProfGemmLora : kProfGemm, flops, bytes, st);
   }
-  lora_gemm_kernel<<<grid, kThreads, kSmemBudget + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, tail.tmX[0], tail.tmH[0], tail.tmX[1],
-                                                                tail.tmH[1], p, tail.p);
+  // with a rank path the launch directly before this one is the operand-pack kernel
+  const bool pdl = c.after_pack && !prof && option(MCB_OPT_PDL) != 0;
+  p.pdl_wait = pdl ? 1 : 0;
+  {
+    const cudaError_t le = launch_kernel(lora_gemm_kernel, dim3(grid), dim3(kThreads), kSmemBudget + 1024, st, pdl, tmX, tmW, tmP, tmQ,
+                                         tmY, tail.tmX[0], tail.tmH[0], tail.tmX[1], tail.tmH[1], p, tail.p);
+    if (le != cudaSuccess) return cuda_fail(le, "lora_gemm_kernel launch");
+  }
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm_kernel");
   if (tail_on) return launch_grad_reduce(tail, st);
@@ -685,6 +697,7 @@ int delta_fwd(const LoraArgs& a, const DeviceState* ds) {
   Workspace w = carve(a.ws, a.M, a.K, a.N, a.r);
   if (int rc = pack(a, w, 0)) return rc;
   GemmCall c;
+  c.after_pack = true;
   c.X = static_cast<const __nv_bfloat16*>(a.x);
   c.P = w.P; c.Q = w.Q;
   c.Y = static_cast<__nv_bfloat16*>(a.y);
@@ -709,6 +722,7 @@ int linear_fwd(const LoraArgs& a, const DeviceState* ds) {
   if (a.r > 0) {
     Workspace w = carve(a.ws, a.M, a.K, a.N, a.r);
     if (int rc = pack(a, w, 0)) return rc;
+    c.after_pack = true;
     c.P = w.P; c.Q = w.Q;
     c.H = static_cast<__nv_bfloat16*>(a.h_save);
     c.h_pitch = h_pitch(a.M);
@@ -744,6 +758,7 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
     c.R = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.residual) : nullptr;
     c.M = a.M; c.N = a.K; c.K = a.N;
     if (a.r > 0) {
+      c.after_pack = true;   // pack(a, w, 1) above is the launch directly before the GEMM
       c.P = w.P; c.Q = w.Q;
       c.H = (a.dA != nullptr) ? w.H1 : nullptr;
       c.h_pitch = h_pitch(a.M);
@@ -776,6 +791,7 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
       // P/Q of the backward are still needed by nothing after the GEMM above, so they can be repacked
       if (int rc = pack(f, wf, 0)) return rc;
       GemmCall c;
+      c.after_pack = true;
       c.X = static_cast<const __nv_bfloat16*>(a.x);
       c.P = wf.P; c.Q = wf.Q;
       c.H = w.H2;

@@ -47,6 +47,7 @@ constexpr int kEpiBufs = kEpiBufsMax;
 struct Gemm2Params {
   int M, N, K;
   int BN, stages, rp;
+  int pdl_wait; // 1: launched as a programmatic dependent of the operand-pack kernel
   int swiglu;   // 1: the tile is [128 gate columns | 128 up columns]; the epilogue also writes silu(gate) * up
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;  // m tiles of 256 rows
   float scale;
@@ -175,6 +176,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       int i = 0;
+      if (p.pdl_wait) grid_dependency_wait();   // the operand-pack kernel has finished
       for (int t = pair; ok && t < p.num_tiles; t += npairs, ++i) {
         int mt, nt;
         tile_coords2(p, t, mt, nt);
@@ -462,12 +464,13 @@ int init_gemm2_kernel() {
 // most 64 and a long enough reduction.
 bool gemm2_eligible(const GemmCall& c) {
   if (c.W == nullptr || c.Y == nullptr || c.M < 1024 || c.N < 128 || c.K < 64) return false;
+  if (option(MCB_OPT_DEBUG_) & 8) return false;
   if (c.rp == 0) return true;
   // Short reductions stay on the one-CTA kernel.  Alone, the pair is a little ahead even there once the rank
   // update is issued between the next tile's k-blocks (32768x896x896 r16 forward 953 against 922 TFLOP/s), but
   // inside the training step, with its k/v projections of 128 outputs and its backward calls, the one-CTA kernel
   // measured 1-2 % faster per step on the same box (116.1-118.5 against 118.4-119.5 ms).
-  return c.rp % 16 == 0 && c.rp <= 64 && c.K >= 1536;
+  return c.rp % 16 == 0 && c.rp <= 64 && c.K >= option(MCB_OPT_PAIR_MIN_K);
 }
 
 int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
@@ -524,7 +527,13 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
     profile_begin(c.rp > 0 ? kProfGemmLora : kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
                   2.0 * (m * k + n * k + m * n) + 2.0 * c.rp * (k + n), st);
   }
-  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmP, tmQ, tmY, tmY, tmY, p);
+  const bool pdl = c.after_pack && c.rp > 0 && !prof && option(MCB_OPT_PDL) != 0;
+  p.pdl_wait = pdl ? 1 : 0;
+  {
+    const cudaError_t le = launch_kernel(lora_gemm2_kernel, dim3(2 * pairs), dim3(kThreads2), kSmem2 + 1024, st, pdl, tmX, tmW, tmP,
+                                         tmQ, tmY, tmY, tmY, p);
+    if (le != cudaSuccess) return cuda_fail(le, "lora_gemm2_kernel launch");
+  }
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm2_kernel");
   return MCB_OK;

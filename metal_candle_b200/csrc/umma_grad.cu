@@ -64,6 +64,7 @@ lora_grad_umma_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_con
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  if (threadIdx.x == 0) grid_launch_dependents();   // the partial-sum kernel may be set up; it waits for this grid
   GradShared sh;
   sh.base = base; sh.full0 = full0; sh.empty0 = empty0; sh.done_bar = done_bar; sh.tmem_base = tmem_base;
   sh.abort_flag = abort_flag;
@@ -92,6 +93,7 @@ struct ReduceProblem {
 __global__ void __launch_bounds__(256)
 lora_grad_reduce_kernel(ReduceProblem a, ReduceProblem b, int blocks_a, int r, int rp, int accumulate) {
   __shared__ float red[8][32];
+  grid_dependency_wait();   // launched as a programmatic dependent of the kernel that writes the partials
   const bool second = static_cast<int>(blockIdx.x) >= blocks_a;
   const ReduceProblem q = second ? b : a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -411,6 +413,7 @@ int plan_grad2(const GradRequest& rq, int64_t M, int rp, int max_ctas, uint32_t 
   p.status = ds->status_word;
   p.h_flags = rq.h_flags;
   for (int i = 0; i < np; ++i) plan_groups(rq.C[i], rp, &p.pr[i]);
+  for (int i = 0; i < np; ++i) { p.xptr[i] = (option(MCB_OPT_DEBUG_) & 16) ? nullptr : rq.X[i]; p.row_bytes[i] = static_cast<uint32_t>(rq.C[i] * 2); }
   // tokens per stage, per problem: as many (a multiple of 16, at most 256) as keep a stage near 48 KB, so that
   // narrow problems have as many bytes in flight as wide ones
   for (int i = 0; i < np; ++i) {
@@ -464,7 +467,11 @@ int launch_grad_reduce(const GradPlan& plan, cudaStream_t st) {
                       rq.transposed[1]};
   const int blocks_a = static_cast<int>((rq.C[0] * p.rp + 31) / 32);
   const int blocks_b = two ? static_cast<int>((rq.C[1] * p.rp + 31) / 32) : 0;
-  lora_grad_reduce_kernel<<<static_cast<unsigned>(blocks_a + blocks_b), 256, 0, st>>>(ra, rb, blocks_a, rq.r, p.rp, rq.accumulate);
+  {
+    const cudaError_t le = launch_kernel(lora_grad_reduce_kernel, dim3(static_cast<unsigned>(blocks_a + blocks_b)), dim3(256), 0, st,
+                                         option(MCB_OPT_PDL) != 0 && !profile_on(), ra, rb, blocks_a, rq.r, p.rp, rq.accumulate);
+    if (le != cudaSuccess) return cuda_fail(le, "lora_grad_reduce launch");
+  }
   MCB_CHECK_LAUNCH("lora_grad_reduce");
   return MCB_OK;
 }

@@ -79,8 +79,9 @@ class _Linear:
 class CapturedStep:
     """forward_backward of a fixed shape as a CUDA graph (Qwen.capture_forward_backward)."""
 
-    def __init__(self, graph, ids, targets, loss, grads, keepalive=()):
+    def __init__(self, graph, ids, targets, loss, grads, keepalive=(), count=None):
         self.graph, self.ids, self.targets, self.loss, self.grads = graph, ids, targets, loss, grads
+        self.count = count   # int32 [1]: targets of the last replayed batch that were not ignored
         # The graph's kernels carry the ADDRESSES of the scratch buffers that were current at capture time (GEMM
         # operand packs, partial sums, attention and RMSNorm scratch).  The per-device scratch buffer is replaced
         # when a later call needs a larger one; holding the captured ones here keeps their memory from being handed
@@ -375,7 +376,8 @@ class Qwen:
         finally:
             self.layer_done_hook, self.backward_done_hook = hook, done_hook
             _lib.profile_enable(was_profiling)
-        return CapturedStep(graph, ids, targets, loss, grads, keepalive=keep + backend.workspace_refs(self.device))
+        return CapturedStep(graph, ids, targets, loss, grads, keepalive=keep + backend.workspace_refs(self.device),
+                            count=self.last_count)
 
     def _layer_bwd(self, dh3, L, sv, idx, B, S, accumulate):
         c = self.config

@@ -246,7 +246,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
         if comm_mode != "torch":
             from . import comm as C
 
-            comm = C.Communicator(world, rank, C.broadcast_id(rank), timeout_ms=120_000,
+            comm = C.Communicator(world, rank, C.broadcast_id(rank), timeout_ms=30_000,
                                   blocking=(comm_mode == "mcb-blocking"))
     # the backward's tail phase needs its whole grid resident; with a collective running beside it, it is off
     tail = getattr(args, "grad_tail", "auto")
@@ -339,7 +339,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler is not None else None
-    if captured["fb"] is not None and int(model.last_count.item()) == 0:
+    if captured["fb"] is not None and int(captured["fb"].count.item()) == 0:
         raise SystemExit("bench: every target of the last batch was ignored; the loss is undefined")
     # ---- end to end: pinned host ids -> device, step, loss back to the host, every step ----
     barrier()
@@ -402,6 +402,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                      "allreduce_alone_ms": alone_ms,
                      "bus_GBps": 2.0 * (world - 1) / world * nbytes / (alone_ms * 1e-3) / 1e9 if alone_ms > 0 else None,
                      "rank_ms_per_step": {"min": min(per_rank), "max": max(per_rank)}}
+    used_graph = captured["fb"] is not None
     status = _lib.device_status()
     if dist is not None:
         t = torch.tensor([status], device=device, dtype=torch.int32)
@@ -413,7 +414,14 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
             dist.destroy_process_group()
         raise SystemExit(3)
     if comm is not None:
-        comm.destroy()
+        # NCCL keeps a communicator alive for as long as a CUDA graph that recorded its collectives exists, and
+        # finalizing it waits for those graphs: let go of them first
+        captured["fb"] = captured["fb_nocomm"] = None
+        torch.cuda.synchronize()
+        try:
+            comm.destroy()
+        except Exception as e:   # a communicator that will not shut down must not cost the run its result
+            print(f"bench: communicator shutdown: {e}", file=sys.stderr)
     if dist is not None:
         dist.destroy_process_group()
     if rank == 0:
@@ -438,7 +446,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                        "optimizer": "AdamW lr 1e-4 warmup-cosine",
                        "execution": (("forward+loss+backward" + (" with the bucketed gradient all-reduce overlapped on a side stream" if graph_has_comm and world > 1 else "")
                                       + " replayed from a CUDA graph, then " + ("" if graph_has_comm or world == 1 else "gradient all-reduce and ") + "AdamW")
-                                     if captured["fb"] is not None else
+                                     if used_graph else
                                      "eager launches" + (f" (graph capture failed: {capture_note})" if capture_note else "")),
                        "l2": "inputs larger than L2 (activations of one "
                        "step are tens of GB)", "loss_last": last},
@@ -454,7 +462,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                                            "the step as a whole is too large to capture",
                          "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
                          "measured_in": "per-launch CUDA events in the last eager warm-up step of this run"
-                                        + (" (the timed steps replay a CUDA graph)" if captured["fb"] is not None else ""),
+                                        + (" (the timed steps replay a CUDA graph)" if used_graph else ""),
                          "launches": plain[0] + lora[0], "kernel_ms_per_step": both_ms,
                          "share_of_step": both_ms / (ms / args.steps) if ms > 0 else None,
                          "classes": {"lora": dict(klass(lora), what="launches with a rank path: the fused LoRA linear forward and "

