@@ -153,6 +153,11 @@ int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float* A, const f
                            int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* out[N,K] = W[N,K] + scale * (A B)^T: the adapter folded into a base weight stored [out, in]
+ * (LoRAAdapter::merge_weights, src/training/adapter.rs:315-354).  A [K,r], B [r,N] float32; W, out `dtype`; out may be W. */
+int mcb_lora_merge_weights(const void* W, const float* A, const float* B, void* out, int64_t K, int64_t N, int64_t r,
+                           float scale, int dtype, void* stream);
+
 /* Rank rounded up to the tensor-core K granule (16): the row count of h_save. */
 int64_t mcb_lora_rank_padded(int64_t r);
 /* Row pitch of h_save in elements: the token count rounded up to 64. */
@@ -354,6 +359,16 @@ int mcb_add(const void* a, const void* b, void* out, int64_t n, int dtype, void*
  * d loss / d logits. */
 int mcb_cross_entropy(void* logits, const int32_t* targets, float* nll, int32_t* count, float* loss,
                       int64_t M, int64_t V, int write_grad, int dtype, void* stream);
+/* The same loss a chunk of tokens at a time, for a caller that produces the logits chunk by chunk (lm_head on a
+ * slice of the tokens), turns each chunk into its gradient in place and feeds that straight to the lm_head backward,
+ * so that the [tokens, vocabulary] matrix of the whole batch never exists (the reference materialises it, and walks
+ * it with a host loop: src/training/loss.rs:109-186).  _count: count[0] = targets inside [0, V) over ALL M tokens
+ * (the mean's denominator, needed by every chunk's gradient).  _chunk: rows of one chunk -> nll[rows] and, with
+ * write_grad, d loss / d logits in place.  _finish: loss[0] = sum(nll) / count, loss[1] = sum(nll) over all M. */
+int mcb_cross_entropy_count(const int32_t* targets, int32_t* count, int64_t M, int64_t V, void* stream);
+int mcb_cross_entropy_chunk(void* logits, const int32_t* targets, float* nll, const int32_t* count, int64_t rows,
+                            int64_t V, int write_grad, int dtype, void* stream);
+int mcb_cross_entropy_finish(const float* nll, const int32_t* count, float* loss, int64_t M, void* stream);
 
 #ifdef __cplusplus
 }

@@ -67,6 +67,7 @@ SIGNATURES = {
                                       _vp, _sz, _vp]),
     "mcb_lora_linear_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
                                       _f32, _i32, _i32, _vp, _sz, _vp]),
+    "mcb_lora_merge_weights": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
     "mcb_lora_rank_padded": (_i64, [_i64]),
     "mcb_lora_h_pitch": (_i64, [_i64]),
     "mcb_transpose_2d": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
@@ -98,6 +99,9 @@ SIGNATURES = {
     "mcb_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "mcb_add": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "mcb_cross_entropy": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "mcb_cross_entropy_count": (_i32, [_vp, _vp, _i64, _i64, _vp]),
+    "mcb_cross_entropy_chunk": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "mcb_cross_entropy_finish": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "mcb_adamw_multi": (_i32, [C.POINTER(AdamWTensor), _i32, _f32, _f32, _f32, _f32, _f32, _f32, _vp]),
 }
 

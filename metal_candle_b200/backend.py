@@ -165,7 +165,7 @@ def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=Tr
 
 
 def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, need_dx=True, grad_a=None,
-                         grad_b=None, accumulate=False, weight_layout=MCB_W_IN_OUT, dx_residual=None):
+                         grad_b=None, accumulate=False, weight_layout=MCB_W_IN_OUT, dx_residual=None, dx_out=None):
     """Reverse of `lora_linear_forward`.  `weight_t` is the [in, out] copy of the frozen weight (for
     float32 either layout works, say which with `weight_layout`).  Returns (dx, dA, dB)."""
     N = dy.shape[-1]
@@ -177,7 +177,14 @@ def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, 
     M = dy.numel() // N
     lib = _lib_for(dy)
     dt = _dtype_code(dy)
-    dx = torch.empty(*dy.shape[:-1], K, dtype=dy.dtype, device=dy.device) if need_dx else None
+    dx = None
+    if need_dx:
+        if dx_out is not None:
+            if tuple(dx_out.shape) != (*dy.shape[:-1], K) or dx_out.dtype != dy.dtype or not dx_out.is_contiguous():
+                raise TrainingError(f"lora_linear_backward: dx_out must be a contiguous {list((*dy.shape[:-1], K))} {dy.dtype} tensor")
+            dx = dx_out
+        else:
+            dx = torch.empty(*dy.shape[:-1], K, dtype=dy.dtype, device=dy.device)
     if r and grad_a is None:
         grad_a = torch.empty(K, r, dtype=torch.float32, device=dy.device)
         grad_b = torch.empty(r, N, dtype=torch.float32, device=dy.device)

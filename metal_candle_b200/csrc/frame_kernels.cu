@@ -283,6 +283,37 @@ cross_entropy_kernel(T* __restrict__ logits, const int32_t* __restrict__ targets
   }
 }
 
+// out[n,k] = W[n,k] + scale * sum_j A[k,j] B[j,n]   (LoRAAdapter::merge_weights, src/training/adapter.rs:315-354:
+// base + scaling * (A B)^T for a base weight stored [out, in]).  One thread per 4 consecutive k of one n; A rows
+// and the B column are read through the read-only cache, the product is accumulated in float32.
+template <typename T>
+__global__ void merge_weights_kernel(const T* __restrict__ W, const float* __restrict__ A, const float* __restrict__ B,
+                                     T* __restrict__ out, int K, int N, int r, float scale) {
+  const int64_t total = static_cast<int64_t>(N) * ((K + 3) / 4);
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int kq = static_cast<int>(idx % ((K + 3) / 4));
+    const int n = static_cast<int>(idx / ((K + 3) / 4));
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int j = 0; j < r; ++j) {
+      const float b = __ldg(B + static_cast<int64_t>(j) * N + n);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = kq * 4 + e;
+        if (k < K) acc[e] = fmaf(__ldg(A + static_cast<int64_t>(k) * r + j), b, acc[e]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int k = kq * 4 + e;
+      if (k < K) {
+        const int64_t o = static_cast<int64_t>(n) * K + k;
+        out[o] = from_f32<T>(to_f32(W[o]) + scale * acc[e]);
+      }
+    }
+  }
+}
+
 __global__ void count_valid_kernel(const int32_t* __restrict__ targets, int64_t M, int V, int32_t* __restrict__ count) {
   __shared__ int red[32];
   int c = 0;
@@ -452,5 +483,54 @@ extern "C" int mcb_cross_entropy(void* logits, const int32_t* targets, float* nl
   MCB_CHECK_LAUNCH("cross_entropy");
   reduce_nll_kernel<<<1, 1024, 0, st>>>(nll, M, count, loss);
   MCB_CHECK_LAUNCH("reduce_nll");
+  return MCB_OK;
+}
+
+// The three stages of mcb_cross_entropy as separate calls, so that the logits can be produced, consumed and
+// discarded a chunk of tokens at a time (the [tokens, vocabulary] matrix of the whole batch never exists).
+extern "C" int mcb_cross_entropy_count(const int32_t* targets, int32_t* count, int64_t M, int64_t V, void* stream) {
+  MCB_NVTX_RANGE("mcb_cross_entropy_count");
+  if (!targets || !count) return fail(MCB_ERR_NULL, "cross_entropy_count: null pointer");
+  if (M <= 0 || V <= 0 || M > 0x7fffffff || V > 0x7fffffff) return fail(MCB_ERR_SHAPE, "cross_entropy_count: bad shape");
+  if (!current_device_state()) return MCB_ERR_NOT_INIT;
+  count_valid_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(targets, M, (int)V, count);
+  MCB_CHECK_LAUNCH("count_valid");
+  return MCB_OK;
+}
+
+extern "C" int mcb_cross_entropy_chunk(void* logits, const int32_t* targets, float* nll, const int32_t* count, int64_t rows,
+                                       int64_t V, int write_grad, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_cross_entropy_chunk");
+  if (!logits || !targets || !nll || !count) return fail(MCB_ERR_NULL, "cross_entropy_chunk: null pointer");
+  if (rows <= 0 || V <= 0 || rows > 0x7fffffff || V > 0x7fffffff) return fail(MCB_ERR_SHAPE, "cross_entropy_chunk: bad shape");
+  if (!current_device_state()) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MCB_DTYPE_SWITCH(dtype, (cross_entropy_kernel<T><<<(unsigned)rows, 512, 0, st>>>((T*)logits, targets, nll, count, rows, (int)V, write_grad)));
+  MCB_CHECK_LAUNCH("cross_entropy");
+  return MCB_OK;
+}
+
+extern "C" int mcb_cross_entropy_finish(const float* nll, const int32_t* count, float* loss, int64_t M, void* stream) {
+  MCB_NVTX_RANGE("mcb_cross_entropy_finish");
+  if (!nll || !count || !loss) return fail(MCB_ERR_NULL, "cross_entropy_finish: null pointer");
+  if (M <= 0 || M > 0x7fffffff) return fail(MCB_ERR_SHAPE, "cross_entropy_finish: bad shape");
+  if (!current_device_state()) return MCB_ERR_NOT_INIT;
+  reduce_nll_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(nll, M, count, loss);
+  MCB_CHECK_LAUNCH("reduce_nll");
+  return MCB_OK;
+}
+
+extern "C" int mcb_lora_merge_weights(const void* W, const float* A, const float* B, void* out, int64_t K, int64_t N,
+                                      int64_t r, float scale, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_merge_weights");
+  if (!W || !A || !B || !out) return fail(MCB_ERR_NULL, "lora_merge_weights: null pointer");
+  if (K <= 0 || N <= 0 || r <= 0 || K > 0x7fffffff || N > 0x7fffffff || r > 0x7fffffff)
+    return fail(MCB_ERR_SHAPE, "lora_merge_weights: K=%lld N=%lld r=%lld", (long long)K, (long long)N, (long long)r);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(N * ((K + 3) / 4), 256, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, (merge_weights_kernel<T><<<grid, 256, 0, st>>>((const T*)W, A, B, (T*)out, (int)K, (int)N, (int)r, scale)));
+  MCB_CHECK_LAUNCH("merge_weights");
   return MCB_OK;
 }

@@ -204,15 +204,22 @@ class LoRAAdapter:
         self.set_training(False)
 
     def merge_weights(self, base_weight: torch.Tensor, layer_idx: int, module: TargetModule) -> torch.Tensor:
-        """`W + scaling * (A @ B)^T` for W [out, in] (src/training/adapter.rs:315-354), computed as the
-        fused linear applied to the identity."""
+        """`W + scaling * (A @ B)^T` for W [out, in] (src/training/adapter.rs:315-354): a rank-r update of the
+        base weight, K * N * r multiply-adds in one element-wise kernel."""
         layer = self.get_layer(layer_idx, module)
         if layer is None:
             return base_weight
-        eye = torch.eye(layer.in_features, dtype=base_weight.dtype, device=base_weight.device)
-        y, _ = backend.lora_linear_forward(eye, base_weight.contiguous(), None, layer.lora_a, layer.lora_b,
-                                           layer.config.scaling(), save_hidden=False)
-        return backend.transpose_2d(y)
+        if tuple(base_weight.shape) != (layer.out_features, layer.in_features):
+            raise TrainingError(f"merge_weights: base weight {list(base_weight.shape)} does not match the adapter "
+                                f"[{layer.out_features}, {layer.in_features}]")
+        w = base_weight.contiguous()
+        backend._require_cuda(w)
+        out = torch.empty_like(w)
+        lib = backend._lib_for(w)
+        _lib.check(lib.mcb_lora_merge_weights(w.data_ptr(), layer.lora_a.data_ptr(), layer.lora_b.data_ptr(), out.data_ptr(),
+                                              layer.in_features, layer.out_features, layer.config.rank,
+                                              layer.config.scaling(), backend._dtype_code(w), backend._stream()))
+        return out
 
 
 # ---------------------------------------------------------------------------------------------

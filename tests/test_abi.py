@@ -63,3 +63,18 @@ def test_product_never_imports_oracle():
     for py in (ROOT / "metal_candle_b200").rglob("*.py"):
         src = py.read_text()
         assert "import oracle" not in src and "from oracle" not in src, py
+
+
+def test_rust_sys_crate_source_matches_the_header():
+    """The `-sys` crate a maintainer of the reference would add (metal_candle_b200/sys_crate) is generated from
+    include/mcb200.h: it must be up to date and declare every exported entry point exactly once."""
+    import subprocess
+    import sys
+
+    gen = ROOT / "metal_candle_b200" / "sys_crate" / "generate.py"
+    r = subprocess.run([sys.executable, str(gen), "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    src = (ROOT / "metal_candle_b200" / "sys_crate" / "src" / "lib.rs").read_text()
+    declared = re.findall(r"pub fn (mcb_[a-z0-9_]+)\(", src)
+    assert sorted(declared) == declared_symbols()
+    assert "#[repr(C)]" in src and "pub struct mcb_adamw_tensor" in src

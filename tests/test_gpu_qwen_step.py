@@ -232,3 +232,32 @@ def test_captured_step_matches_eager(cuda_device):
     for g, w in zip(grads, want_grads):
         assert torch.equal(g, w)
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_chunked_lm_head_and_loss_equal_the_unchunked_step(cuda_device, dtype):
+    """forward_backward with the lm_head + cross-entropy stage cut into chunks of tokens (logits of one chunk at a
+    time, never the whole [tokens, vocabulary] matrix) gives bit for bit the loss and gradients of the unchunked
+    step: every row's logits, loss term and gradient are computed by the same arithmetic either way.  Chunk sizes
+    that do not divide the token count, and a chunk of one tile, included; ignored targets fall into several chunks."""
+    from metal_candle_b200 import _lib
+
+    cfg, model, adapter = build(cuda_device, dtype, all_targets(), cfg=fused_attention_config())
+    ids, tg = batch(21, 3, 128, cfg.vocab_size)
+    tg[1, 5:40] = R.IGNORE_INDEX
+    ids_d, tg_d = torch.from_numpy(ids).to(cuda_device), torch.from_numpy(tg).to(cuda_device)
+    model.ce_chunk_tokens = None
+    loss0, g0 = model.forward_backward(ids_d, tg_d)
+    loss0, g0 = loss0.clone(), [g.clone() for g in g0]
+    for chunk in (128, 100, 383):
+        model.ce_chunk_tokens = chunk
+        loss1, g1 = model.forward_backward(ids_d, tg_d)
+        torch.cuda.synchronize()
+        assert torch.equal(loss1, loss0), (chunk, float(loss1), float(loss0))
+        for a, b in zip(g1, g0):
+            assert torch.equal(a, b), chunk
+    # and the oracle agrees (the chunked path is the default for large batches)
+    orc = oracle_of(cfg, model, adapter, dtype == torch.bfloat16)
+    want_loss, _ = orc.loss_and_grads(ids, tg)
+    assert abs(float(loss0) - want_loss) <= (1e-4 if dtype == torch.float32 else 2e-2) * abs(want_loss)
+    assert _lib.device_status() == 0
