@@ -92,6 +92,10 @@ int mcb_selftest_wait_timeout(int64_t limit_cycles, int64_t* waited_cycles_out, 
 int mcb_set_option(int option_id, int value);
 int mcb_get_option(int option_id, int* value_out);
 
+/* Kernels this library has launched (or recorded into a graph being captured) since it was loaded, all devices and
+ * threads together: the difference across a step is the step's launch count. */
+int64_t mcb_launch_count(void);
+
 /* Per-kernel timing for roofline reports.  While enabled, every launch of the tensor-core kernels is
  * bracketed by CUDA events on its own stream and tagged with its algorithmic work; mcb_profile_summary
  * synchronises the device, sums the finished records of one kind (0 = GEMM launches without a rank path: the frozen
@@ -157,6 +161,29 @@ int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float* A, const f
  * (LoRAAdapter::merge_weights, src/training/adapter.rs:315-354).  A [K,r], B [r,N] float32; W, out `dtype`; out may be W. */
 int mcb_lora_merge_weights(const void* W, const float* A, const float* B, void* out, int64_t K, int64_t N, int64_t r,
                            float scale, int dtype, void* stream);
+
+/* Several projections of the SAME input as one linear (the q, k and v projections of an attention block,
+ * src/models/transformer.rs:241-243, each with its own adapter): W is the projections' weights stacked [N, K] (N = sum
+ * of their widths), y / dy hold their outputs / gradients side by side [M, N], and segment i names the adapter of
+ * output columns [n_offset, n_offset + n).  The rank paths run as one block-diagonal update with n_segments * r rank
+ * columns (at most 64), so x is read once for all projections and their input gradients are summed in one pass.
+ * bf16 only.  h_save: [mcb_lora_rank_padded(n_segments * r), mcb_lora_h_pitch(M)], required by the backward.
+ * The backward writes (accumulate: adds to) every segment's dA [K,r] and dB [r,n] (all null: dx only). */
+typedef struct {
+  const float* A;     /* [K, r]  */
+  const float* B;     /* [r, n]  */
+  float* dA;          /* [K, r]  (backward) */
+  float* dB;          /* [r, n]  (backward) */
+  int64_t n_offset;   /* first output column of this projection */
+  int64_t n;          /* its width */
+} mcb_lora_segment;
+size_t mcb_lora_fused_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int n_segments, int dtype);
+int mcb_lora_linear_fused_fwd(const void* x, const void* W, const void* bias, const mcb_lora_segment* segments, int n_segments,
+                              void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype,
+                              void* workspace, size_t workspace_bytes, void* stream);
+int mcb_lora_linear_fused_bwd(const void* x, const void* Wt, const mcb_lora_segment* segments, int n_segments, const void* dy,
+                              const void* h_save, const void* dx_residual, void* dx, int accumulate, int64_t M, int64_t K,
+                              int64_t N, int64_t r, float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Rank rounded up to the tensor-core K granule (16): the row count of h_save. */
 int64_t mcb_lora_rank_padded(int64_t r);
@@ -346,6 +373,11 @@ int mcb_embedding_fwd(const int32_t* ids, const void* table, void* out, int64_t 
  * transposed rotation. */
 int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
                       int rotate, int inverse, int dtype, void* stream);
+/* The same where the [B,S,H,d] side is a column block of wider token rows: rows `token_pitch` elements apart (0 =
+ * H*d), the heads starting at column `col_offset` - the q, k or v part of a fused q/k/v projection's output (forward:
+ * the source) or of the fused gradient buffer (inverse: the destination). */
+int mcb_rope_relayout_ex(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta, int rotate,
+                         int inverse, int64_t token_pitch, int64_t col_offset, int dtype, void* stream);
 /* out = silu(gate) * up and its reverse (MLP::forward, src/models/transformer.rs:389-395). */
 int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
 int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup, int64_t n,

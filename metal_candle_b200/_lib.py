@@ -30,6 +30,11 @@ class McbError(RuntimeError):
         self.code = code
 
 
+class LoraSegment(C.Structure):
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("dA", C.c_void_p), ("dB", C.c_void_p),
+                ("n_offset", C.c_int64), ("n", C.c_int64)]
+
+
 class AdamWTensor(C.Structure):
     _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
                 ("n", C.c_int64), ("t", C.c_int32), ("pad_", C.c_int32)]
@@ -54,6 +59,7 @@ SIGNATURES = {
     "mcb_comm_abort": (_i32, [_vp]),
     "mcb_comm_info": (_i32, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "mcb_comm_destroy": (_i32, [_vp]),
+    "mcb_launch_count": (_i64, []),
     "mcb_profile_enable": (_i32, [_i32]),
     "mcb_profile_summary": (_i32, [_i32, C.POINTER(C.c_int64), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                    C.POINTER(C.c_double)]),
@@ -68,6 +74,11 @@ SIGNATURES = {
     "mcb_lora_linear_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
                                       _f32, _i32, _i32, _vp, _sz, _vp]),
     "mcb_lora_merge_weights": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "mcb_lora_fused_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i32, _i32]),
+    "mcb_lora_linear_fused_fwd": (_i32, [_vp, _vp, _vp, C.POINTER(LoraSegment), _i32, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32,
+                                         _vp, _sz, _vp]),
+    "mcb_lora_linear_fused_bwd": (_i32, [_vp, _vp, C.POINTER(LoraSegment), _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
+                                         _f32, _i32, _vp, _sz, _vp]),
     "mcb_lora_rank_padded": (_i64, [_i64]),
     "mcb_lora_h_pitch": (_i64, [_i64]),
     "mcb_transpose_2d": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
@@ -95,6 +106,7 @@ SIGNATURES = {
                                            _i64, _i32, _vp, _sz, _vp]),
     "mcb_embedding_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "mcb_rope_relayout": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _vp]),
+    "mcb_rope_relayout_ex": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32, _i64, _i64, _i32, _vp]),
     "mcb_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "mcb_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "mcb_add": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),

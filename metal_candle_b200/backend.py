@@ -197,6 +197,69 @@ def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, 
     return dx, grad_a, grad_b
 
 
+def _segment_table(segments, with_grads: bool):
+    arr = (_lib.LoraSegment * len(segments))()
+    for i, sg in enumerate(segments):
+        a, b = sg["A"], sg["B"]
+        arr[i] = _lib.LoraSegment(a.data_ptr(), b.data_ptr(), sg["dA"].data_ptr() if with_grads else None,
+                                  sg["dB"].data_ptr() if with_grads else None, int(sg["offset"]), int(b.shape[1]))
+    return arr
+
+
+def _check_segments(segments, K: int):
+    if not segments:
+        raise TrainingError("fused LoRA linear: no segments")
+    r = segments[0]["A"].shape[1]
+    for sg in segments:
+        a, b = sg["A"], sg["B"]
+        if a.dim() != 2 or b.dim() != 2 or a.shape != (K, r) or b.shape[0] != r:
+            raise TrainingError(f"fused LoRA linear: every segment needs A [{K}, {r}] and B [{r}, n] "
+                                f"(got {list(a.shape)} and {list(b.shape)})")
+        if a.dtype != torch.float32 or b.dtype != torch.float32:
+            raise TrainingError("fused LoRA linear: LoRA matrices are float32 master copies")
+        _require_cuda(a, b, sg.get("dA"), sg.get("dB"))
+    return r
+
+
+def lora_linear_fused_forward(x, weight_cat, bias_cat, segments, scaling, save_hidden=True):
+    """Several projections of the same input as one linear: `weight_cat` [N, K] stacks their weights, segment i =
+    dict(A=[K,r], B=[r,n_i], offset=first output column) is the adapter of columns [offset, offset + n_i).  Returns
+    (y [.., N], h_save): the rank paths run as one block-diagonal update.  bfloat16 only."""
+    K, N = x.shape[-1], weight_cat.shape[0]
+    if weight_cat.dim() != 2 or weight_cat.shape[1] != K:
+        raise TrainingError(f"weight must be [out, in={K}], got {list(weight_cat.shape)}")
+    r = _check_segments(segments, K)
+    _require_cuda(x, weight_cat, bias_cat)
+    M = x.numel() // K
+    lib = _lib_for(x)
+    dt = _dtype_code(x)
+    y = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+    h = torch.empty(lib.mcb_lora_rank_padded(r * len(segments)), lib.mcb_lora_h_pitch(M), dtype=x.dtype, device=x.device)
+    ws = workspace(x.device, lib.mcb_lora_fused_workspace_bytes(M, K, N, r, len(segments), dt))
+    _lib.check(lib.mcb_lora_linear_fused_fwd(_ptr(x), _ptr(weight_cat), _ptr(bias_cat), _segment_table(segments, False),
+                                             len(segments), _ptr(y), _ptr(h), M, K, N, r, float(scaling), dt, _ptr(ws),
+                                             ws.numel(), _stream()))
+    return y, (h if save_hidden else None)
+
+
+def lora_linear_fused_backward(x, weight_cat_t, segments, scaling, dy, h_save, accumulate=False, dx_residual=None):
+    """Reverse of `lora_linear_fused_forward`: dx, and every segment's gradients written (accumulate: added) into
+    its `dA` [K,r] / `dB` [r,n] tensors.  `weight_cat_t` is the [in, out] copy of the stacked weight."""
+    N = dy.shape[-1]
+    K = weight_cat_t.shape[0]
+    r = _check_segments(segments, K)
+    _require_cuda(x, weight_cat_t, dy, h_save, dx_residual)
+    M = dy.numel() // N
+    lib = _lib_for(dy)
+    dt = _dtype_code(dy)
+    dx = torch.empty(*dy.shape[:-1], K, dtype=dy.dtype, device=dy.device)
+    ws = workspace(dy.device, lib.mcb_lora_fused_workspace_bytes(M, K, N, r, len(segments), dt))
+    _lib.check(lib.mcb_lora_linear_fused_bwd(_ptr(x), _ptr(weight_cat_t), _segment_table(segments, True), len(segments),
+                                             _ptr(dy), _ptr(h_save), _ptr(dx_residual), _ptr(dx), int(bool(accumulate)), M, K, N,
+                                             r, float(scaling), dt, _ptr(ws), ws.numel(), _stream()))
+    return dx
+
+
 def transpose_2d(src: torch.Tensor) -> torch.Tensor:
     _require_cuda(src)
     if src.dim() != 2:

@@ -53,10 +53,13 @@ struct NvtxRange {
     if (e_ != cudaSuccess) return mcb::cuda_fail(e_, #expr);   \
   } while (0)
 
+// Every kernel launch of the library passes through this check; it also counts them (mcb_launch_count).
+void note_launch();
 #define MCB_CHECK_LAUNCH(name)                                 \
   do {                                                         \
     cudaError_t e_ = cudaGetLastError();                       \
     if (e_ != cudaSuccess) return mcb::cuda_fail(e_, name);    \
+    mcb::note_launch();                                        \
   } while (0)
 
 // Kernel launch with or without the programmatic-serialization attribute (see umma_ptx.cuh).

@@ -32,7 +32,7 @@ __global__ void embedding_fwd_kernel(const int32_t* __restrict__ ids, const T* _
 // rotate == 0 only changes the layout (used for V).
 template <typename T>
 __global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int S, int H, int d,
-                                     float theta, int rotate, int inverse) {
+                                     float theta, int rotate, int inverse, int64_t pitch, int64_t offset) {
   // One thread owns a 16-byte chunk of the first half of a head (and the matching chunk of the second
   // half) at one (batch, position), computes its sines and cosines once, and walks over the heads.
   using V = Vec16<T>;
@@ -60,7 +60,8 @@ __global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ 
       }
     }
     for (int h = 0; h < H; ++h) {
-      const int64_t bshd = ((static_cast<int64_t>(b) * S + s) * H + h) * d;   // [B,S,H,d]
+      // [B,S,H,d] side: token rows `pitch` elements apart, the heads starting `offset` elements into a row
+      const int64_t bshd = (static_cast<int64_t>(b) * S + s) * pitch + offset + static_cast<int64_t>(h) * d;
       const int64_t bhsd = ((static_cast<int64_t>(b) * H + h) * S + s) * d;   // [B,H,S,d]
       const int64_t in = inverse ? bhsd : bshd, out = inverse ? bshd : bhsd;
       V a, bb;
@@ -83,7 +84,7 @@ __global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ 
 // Scalar variant for head sizes whose half is not a multiple of the vector width.
 template <typename T>
 __global__ void rope_relayout_scalar_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int S, int H, int d,
-                                            float theta, int rotate, int inverse) {
+                                            float theta, int rotate, int inverse, int64_t pitch, int64_t offset) {
   const int half = d / 2;
   const int64_t total = static_cast<int64_t>(B) * S * H * half;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -93,7 +94,7 @@ __global__ void rope_relayout_scalar_kernel(const T* __restrict__ src, T* __rest
     const int h = static_cast<int>(t % H); t /= H;
     const int s = static_cast<int>(t % S);
     const int b = static_cast<int>(t / S);
-    const int64_t bshd = ((static_cast<int64_t>(b) * S + s) * H + h) * d;
+    const int64_t bshd = (static_cast<int64_t>(b) * S + s) * pitch + offset + static_cast<int64_t>(h) * d;
     const int64_t bhsd = ((static_cast<int64_t>(b) * H + h) * S + s) * d;
     const int64_t in = inverse ? bhsd : bshd, out = inverse ? bshd : bhsd;
     const float x1 = to_f32(src[in + i]), x2 = to_f32(src[in + half + i]);
@@ -376,25 +377,34 @@ extern "C" int mcb_embedding_fwd(const int32_t* ids, const void* table, void* ou
   return MCB_OK;
 }
 
-extern "C" int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
-                                 int rotate, int inverse, int dtype, void* stream) {
+extern "C" int mcb_rope_relayout_ex(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
+                                    int rotate, int inverse, int64_t token_pitch, int64_t col_offset, int dtype, void* stream) {
   MCB_NVTX_RANGE("mcb_rope_relayout");
   if (!src || !dst) return fail(MCB_ERR_NULL, "rope_relayout: null pointer");
   if (B <= 0 || S <= 0 || H <= 0 || d <= 0 || d % 2 != 0) return fail(MCB_ERR_SHAPE, "rope_relayout: bad shape (head_dim must be even)");
+  if (token_pitch == 0) token_pitch = H * d;
+  if (col_offset < 0 || col_offset + H * d > token_pitch)
+    return fail(MCB_ERR_SHAPE, "rope_relayout: %lld heads x %lld at column %lld do not fit a row of %lld", (long long)H, (long long)d,
+                (long long)col_offset, (long long)token_pitch);
   DeviceState* ds = current_device_state();
   if (!ds) return MCB_ERR_NOT_INIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t half = d / 2;
   const int vec_n = dtype == MCB_F32 ? 4 : 8;
-  if (half % vec_n == 0 && aligned16(src) && aligned16(dst)) {
+  if (half % vec_n == 0 && aligned16(src) && aligned16(dst) && token_pitch % vec_n == 0 && col_offset % vec_n == 0) {
     const int grid = grid_for(B * S * (half / vec_n), 128, ds->sm_count);
-    MCB_DTYPE_SWITCH(dtype, (rope_relayout_kernel<T><<<grid, 128, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse)));
+    MCB_DTYPE_SWITCH(dtype, (rope_relayout_kernel<T><<<grid, 128, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse, token_pitch, col_offset)));
   } else {
     const int grid = grid_for(B * S * H * half, 256, ds->sm_count);
-    MCB_DTYPE_SWITCH(dtype, (rope_relayout_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse)));
+    MCB_DTYPE_SWITCH(dtype, (rope_relayout_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, (int)B, (int)S, (int)H, (int)d, theta, rotate, inverse, token_pitch, col_offset)));
   }
   MCB_CHECK_LAUNCH("rope_relayout");
   return MCB_OK;
+}
+
+extern "C" int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta,
+                                 int rotate, int inverse, int dtype, void* stream) {
+  return mcb_rope_relayout_ex(src, dst, B, S, H, d, theta, rotate, inverse, 0, 0, dtype, stream);
 }
 
 extern "C" int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream) {

@@ -143,3 +143,65 @@ extern "C" int mcb_lora_linear_bwd(const void* x, const void* W, const float* A,
   return mcb_lora_linear_bwd_ex(x, W, A, B, dy, h_save, nullptr, dx, dA, dB, accumulate, M, K, N, r, scale, dtype, w_layout,
                                 workspace, workspace_bytes, stream);
 }
+
+// ---- several projections of one input as one linear (block-diagonal rank path) ---------------------------------
+namespace {
+int to_segments(const char* op, const mcb_lora_segment* segs, int n_segments, int64_t N, int64_t r, bool backward, LoraSegments* out) {
+  if (!segs) return fail(MCB_ERR_NULL, "%s: null segment table", op);
+  if (n_segments < 1 || n_segments > kMaxSegments) return fail(MCB_ERR_SHAPE, "%s: %d segments (1..%d)", op, n_segments, kMaxSegments);
+  out->count = n_segments;
+  for (int i = 0; i < n_segments; ++i) {
+    out->A[i] = segs[i].A; out->B[i] = segs[i].B;
+    out->dA[i] = backward ? segs[i].dA : nullptr; out->dB[i] = backward ? segs[i].dB : nullptr;
+    out->n_off[i] = segs[i].n_offset; out->n[i] = segs[i].n;
+    if (r > segs[i].n) return fail(MCB_ERR_SHAPE, "%s: LoRA rank %lld exceeds the width %lld of segment %d", op, (long long)r, (long long)segs[i].n, i);
+  }
+  (void)N;
+  return MCB_OK;
+}
+}  // namespace
+
+extern "C" size_t mcb_lora_fused_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int n_segments, int dtype) {
+  if (M <= 0 || K <= 0 || N <= 0 || r <= 0 || n_segments <= 0 || dtype != MCB_BF16) return 0;
+  return bf16path::fused_workspace_bytes(M, K, N, r, n_segments);
+}
+
+extern "C" int mcb_lora_linear_fused_fwd(const void* x, const void* W, const void* bias, const mcb_lora_segment* segments,
+                                         int n_segments, void* y, void* h_save, int64_t M, int64_t K, int64_t N, int64_t r,
+                                         float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_linear_fused_fwd");
+  if (!x || !W || !y) return fail(MCB_ERR_NULL, "lora_linear_fused_fwd: x, W or y is null");
+  if (int rc = check_dims("lora_linear_fused_fwd", M, K, N, r, dtype, true)) return rc;
+  if (dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_fused_fwd: bfloat16 only (call mcb_lora_linear_fwd per projection for float32)");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  LoraSegments sg;
+  if (int rc = to_segments("lora_linear_fused_fwd", segments, n_segments, N, r, false, &sg)) return rc;
+  LoraArgs a;
+  a.x = x; a.W = W; a.bias = bias; a.y = y; a.h_save = h_save;
+  a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = MCB_W_OUT_IN;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return bf16path::linear_fused_fwd(a, sg, ds);
+}
+
+extern "C" int mcb_lora_linear_fused_bwd(const void* x, const void* Wt, const mcb_lora_segment* segments, int n_segments,
+                                         const void* dy, const void* h_save, const void* dx_residual, void* dx, int accumulate,
+                                         int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_linear_fused_bwd");
+  if (!x || !dy || !h_save) return fail(MCB_ERR_NULL, "lora_linear_fused_bwd: x, dy or h_save is null");
+  if (dx && !Wt) return fail(MCB_ERR_NULL, "lora_linear_fused_bwd: dx wanted but the weight is null");
+  if (int rc = check_dims("lora_linear_fused_bwd", M, K, N, r, dtype, true)) return rc;
+  if (dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_fused_bwd: bfloat16 only (call mcb_lora_linear_bwd per projection for float32)");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  LoraSegments sg;
+  if (int rc = to_segments("lora_linear_fused_bwd", segments, n_segments, N, r, true, &sg)) return rc;
+  LoraArgs a;
+  a.x = x; a.W = Wt; a.dy = dy; a.h_save = const_cast<void*>(h_save); a.dx = dx; a.residual = dx_residual; a.accumulate = accumulate;
+  a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = MCB_W_IN_OUT;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return bf16path::linear_fused_bwd(a, sg, ds);
+}

@@ -28,6 +28,19 @@ struct LoraArgs {
   cudaStream_t stream = nullptr;
 };
 
+// Several projections that share one input, computed as ONE linear with a block-diagonal rank path: segment i owns
+// output columns [n_off, n_off + n) of the fused output and has its own adapter (A_i [K,r], B_i [r,n]).
+constexpr int kMaxSegments = 4;
+struct LoraSegments {
+  int count = 0;
+  const float* A[kMaxSegments] = {nullptr, nullptr, nullptr, nullptr};
+  const float* B[kMaxSegments] = {nullptr, nullptr, nullptr, nullptr};
+  float* dA[kMaxSegments] = {nullptr, nullptr, nullptr, nullptr};
+  float* dB[kMaxSegments] = {nullptr, nullptr, nullptr, nullptr};
+  int64_t n_off[kMaxSegments] = {0, 0, 0, 0};
+  int64_t n[kMaxSegments] = {0, 0, 0, 0};
+};
+
 inline int64_t rank_padded(int64_t r) { return r <= 0 ? 0 : ((r + 15) / 16) * 16; }
 // Row pitch (in elements) of the saved rank intermediate [rp, pitch]: tokens rounded up to 64.
 inline int64_t h_pitch(int64_t M) { return ((M + 63) / 64) * 64; }
@@ -69,6 +82,10 @@ size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_bwd(const LoraArgs& a, const DeviceState* ds);
+// The same two passes for a fused projection with one adapter of rank a.r per segment (a.A / a.B / a.dA / a.dB unused).
+size_t fused_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int segments);
+int linear_fused_fwd(const LoraArgs& a, const LoraSegments& sg, const DeviceState* ds);
+int linear_fused_bwd(const LoraArgs& a, const LoraSegments& sg, const DeviceState* ds);
 // out[M,N] = a[M,K] bt[N,K]^T (bt is b transposed, both operands K-major)
 int matmul_nt(const void* a, const void* bt, void* out, int64_t M, int64_t K, int64_t N, const DeviceState* ds,
               cudaStream_t st);

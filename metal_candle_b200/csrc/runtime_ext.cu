@@ -10,6 +10,11 @@ namespace {
 std::atomic<int> g_options[MCB_OPT_COUNT_] = {{1}, {1536}, {1}, {0}};   // MCB_OPT_GRAD_TAIL on, MCB_OPT_PAIR_MIN_K 1536, MCB_OPT_PDL on, debug 0
 }
 
+namespace {
+std::atomic<long long> g_launches{0};
+}
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 int option(int which) { return (which >= 0 && which < MCB_OPT_COUNT_) ? g_options[which].load() : 0; }
 
 namespace {
@@ -56,6 +61,8 @@ extern "C" int mcb_get_option(int option_id, int* value_out) {
   *value_out = g_options[option_id].load();
   return MCB_OK;
 }
+
+extern "C" int64_t mcb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int mcb_check_device(void) {
   int st = 0;

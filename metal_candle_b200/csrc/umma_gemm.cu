@@ -479,6 +479,79 @@ __global__ void pack_lora_kernel(const float* __restrict__ A, const float* __res
   }
 }
 
+// The same packing for a fused projection: the adapters of up to kMaxSegments segments side by side.  Rank column
+// jt = segment * r + j.  The A factors are concatenated ([K, r_tot]); the B factors form a block-diagonal
+// [r_tot, N] matrix (segment i's B in its own rows and in the output columns it owns, zero elsewhere), so the one
+// rank update  (x A_cat) B_bd  adds every segment's delta to its own columns only.
+struct SegTable {
+  const float* A[kMaxSegments];
+  const float* B[kMaxSegments];
+  int n_off[kMaxSegments], n[kMaxSegments];
+  int count;
+};
+__global__ void pack_lora_fused_kernel(const SegTable t, __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Q, int K,
+                                       int N, int r, int rp, int mode, int* __restrict__ flags, int n_flags) {
+  grid_launch_dependents();
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (int64_t i = tid; i < n_flags; i += static_cast<int64_t>(gridDim.x) * blockDim.x) flags[i] = 0;
+  const int64_t nP = static_cast<int64_t>(rp) * (mode == 0 ? K : N);
+  const int64_t nQ = static_cast<int64_t>(rp) * (mode == 0 ? N : K);
+  auto a_at = [&](int k, int jt) -> float {     // A_cat[k, jt]
+    const int sg = jt / r, j = jt - sg * r;
+    return sg < t.count ? t.A[sg][static_cast<int64_t>(k) * r + j] : 0.0f;
+  };
+  auto b_at = [&](int jt, int n) -> float {     // B_bd[jt, n]
+    const int sg = jt / r, j = jt - sg * r;
+    if (sg >= t.count || n < t.n_off[sg] || n >= t.n_off[sg] + t.n[sg]) return 0.0f;
+    return t.B[sg][static_cast<int64_t>(j) * t.n[sg] + (n - t.n_off[sg])];
+  };
+  if (tid < nP) {
+    if (mode == 0) {  // P[jt,k] = A_cat[k,jt]
+      P[tid] = __float2bfloat16_rn(a_at(static_cast<int>(tid % K), static_cast<int>(tid / K)));
+    } else {          // P[jt,n] = B_bd[jt,n]
+      P[tid] = __float2bfloat16_rn(b_at(static_cast<int>(tid / N), static_cast<int>(tid % N)));
+    }
+  } else if (tid < nP + nQ) {
+    const int64_t q = tid - nP;
+    const int jt = static_cast<int>(q % rp);
+    const int row = static_cast<int>(q / rp);
+    Q[q] = __float2bfloat16_rn(mode == 0 ? b_at(jt, row) : a_at(row, jt));   // Q[n,jt] = B_bd[jt,n]  /  Q[k,jt] = A_cat[k,jt]
+  }
+}
+
+// The fused gradients dA_cat [K, r_tot] and dB_cat [r_tot, N] hold every segment's dA_i in its own columns and
+// dB_i in its own diagonal block; this writes (or adds) them to the segments' own tensors.
+struct ScatterTable {
+  float* dA[kMaxSegments];
+  float* dB[kMaxSegments];
+  int n_off[kMaxSegments], n[kMaxSegments];
+  int count;
+};
+__global__ void scatter_fused_grads_kernel(const ScatterTable t, const float* __restrict__ dA_cat, const float* __restrict__ dB_cat,
+                                           int K, int N, int r, int accumulate) {
+  const int r_tot = t.count * r;
+  const int64_t nA = static_cast<int64_t>(K) * r_tot;
+  int64_t nB = 0;
+  for (int sg = 0; sg < t.count; ++sg) nB += static_cast<int64_t>(r) * t.n[sg];
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nA + nB;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    if (i < nA) {
+      const int k = static_cast<int>(i / r_tot), jt = static_cast<int>(i % r_tot);
+      const int sg = jt / r, j = jt - sg * r;
+      float* o = t.dA[sg] + static_cast<int64_t>(k) * r + j;
+      *o = accumulate ? *o + dA_cat[i] : dA_cat[i];
+    } else {
+      int64_t e = i - nA;
+      int sg = 0;
+      while (e >= static_cast<int64_t>(r) * t.n[sg]) { e -= static_cast<int64_t>(r) * t.n[sg]; ++sg; }
+      const int j = static_cast<int>(e / t.n[sg]), n = static_cast<int>(e % t.n[sg]);
+      const float v = dB_cat[static_cast<int64_t>(sg * r + j) * N + t.n_off[sg] + n];
+      float* o = t.dB[sg] + e;
+      *o = accumulate ? *o + v : v;
+    }
+  }
+}
+
 // ---- host side -----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -815,6 +888,135 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
                         static_cast<int>(a.r), rp, a.accumulate, ds, a.stream);
   return launch_grad2(xb, hs, a.N, a.dB, 1, nullptr, nullptr, 0, nullptr, 0, h_pitch(a.M), w.part, a.M, static_cast<int>(a.r), rp,
                       a.accumulate, ds, a.stream);
+}
+
+// ---- fused projections (several adapters, one GEMM) ----------------------------------------------------------
+namespace {
+struct FusedWorkspace {
+  Workspace w;
+  float *dA_cat, *dB_cat;
+  size_t total;
+};
+FusedWorkspace carve_fused(void* ws, int64_t M, int64_t K, int64_t N, int64_t r_tot) {
+  FusedWorkspace f;
+  f.w = carve(ws, M, K, N, r_tot);
+  size_t off = f.w.total;
+  uint8_t* b = static_cast<uint8_t*>(ws);
+  auto take = [&](size_t bytes) { uint8_t* q = b ? b + off : nullptr; off += align_up(bytes, 1024); return q; };
+  f.dA_cat = reinterpret_cast<float*>(take(static_cast<size_t>(K) * r_tot * sizeof(float)));
+  f.dB_cat = reinterpret_cast<float*>(take(static_cast<size_t>(N) * r_tot * sizeof(float)));
+  f.total = off;
+  return f;
+}
+int pack_fused(const LoraArgs& a, const LoraSegments& sg, const Workspace& w, int rp, int mode) {
+  SegTable t;
+  memset(&t, 0, sizeof(t));
+  t.count = sg.count;
+  for (int i = 0; i < sg.count; ++i) {
+    t.A[i] = sg.A[i]; t.B[i] = sg.B[i];
+    t.n_off[i] = static_cast<int>(sg.n_off[i]); t.n[i] = static_cast<int>(sg.n[i]);
+  }
+  const int64_t n = static_cast<int64_t>(rp) * (a.K + a.N);
+  pack_lora_fused_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, a.stream>>>(
+      t, w.P, w.Q, static_cast<int>(a.K), static_cast<int>(a.N), static_cast<int>(a.r), rp, mode,
+      mode == 1 ? w.flags : nullptr, mode == 1 ? static_cast<int>((a.M + BM - 1) / BM) : 0);
+  MCB_CHECK_LAUNCH("pack_lora_fused");
+  return MCB_OK;
+}
+int check_fused(const LoraArgs& a, const LoraSegments& sg, const char* op) {
+  if (sg.count < 1 || sg.count > kMaxSegments) return fail(MCB_ERR_SHAPE, "%s: %d segments (1..%d)", op, sg.count, kMaxSegments);
+  if (a.r < 1 || a.r * sg.count > 64) return fail(MCB_ERR_UNSUPPORTED, "%s: rank %lld x %d segments exceeds 64 rank columns", op, (long long)a.r, sg.count);
+  int64_t end = 0;
+  for (int i = 0; i < sg.count; ++i) {
+    if (!sg.A[i] || !sg.B[i]) return fail(MCB_ERR_NULL, "%s: segment %d has no adapter", op, i);
+    if (sg.n[i] <= 0 || sg.n_off[i] < end || sg.n_off[i] + sg.n[i] > a.N)
+      return fail(MCB_ERR_SHAPE, "%s: segment %d covers columns [%lld, %lld) of %lld (segments must be ascending and disjoint)", op, i,
+                  (long long)sg.n_off[i], (long long)(sg.n_off[i] + sg.n[i]), (long long)a.N);
+    end = sg.n_off[i] + sg.n[i];
+  }
+  const size_t need = fused_workspace_bytes(a.M, a.K, a.N, a.r, sg.count);
+  if (!a.ws || a.ws_bytes < need) return fail(MCB_ERR_WORKSPACE, "%s: workspace %zu < %zu bytes", op, a.ws_bytes, need);
+  if ((reinterpret_cast<uintptr_t>(a.ws) & 1023u) != 0) return fail(MCB_ERR_ALIGN, "%s: workspace must be 1024-byte aligned", op);
+  return MCB_OK;
+}
+}  // namespace
+
+size_t fused_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int segments) {
+  if (r <= 0 || segments <= 0) return 0;
+  return carve_fused(nullptr, M, K, N, r * segments).total;
+}
+
+int linear_fused_fwd(const LoraArgs& a, const LoraSegments& sg, const DeviceState* ds) {
+  if (a.w_layout != MCB_W_OUT_IN) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_fused_fwd(bf16) needs W as [out,in]");
+  if (int rc = check_fused(a, sg, "lora_linear_fused_fwd")) return rc;
+  const int64_t r_tot = a.r * sg.count;
+  const int rp = static_cast<int>(rank_padded(r_tot));
+  FusedWorkspace f = carve_fused(a.ws, a.M, a.K, a.N, r_tot);
+  if (int rc = pack_fused(a, sg, f.w, rp, 0)) return rc;
+  GemmCall c;
+  c.after_pack = true;
+  c.X = static_cast<const __nv_bfloat16*>(a.x);
+  c.W = static_cast<const __nv_bfloat16*>(a.W);
+  c.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  c.R = static_cast<const __nv_bfloat16*>(a.residual);
+  c.Y = static_cast<__nv_bfloat16*>(a.y);
+  c.M = a.M; c.N = a.N; c.K = a.K;
+  c.P = f.w.P; c.Q = f.w.Q;
+  c.H = static_cast<__nv_bfloat16*>(a.h_save);
+  c.h_pitch = h_pitch(a.M);
+  c.rp = rp;
+  c.r_true = static_cast<int>(r_tot);
+  c.scale = a.scale;
+  return launch_gemm(c, ds, a.stream);
+}
+
+int linear_fused_bwd(const LoraArgs& a, const LoraSegments& sg, const DeviceState* ds) {
+  if (a.dx != nullptr && a.w_layout != MCB_W_IN_OUT) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_fused_bwd(bf16) needs W as [in,out]");
+  if (int rc = check_fused(a, sg, "lora_linear_fused_bwd")) return rc;
+  if (a.h_save == nullptr) return fail(MCB_ERR_NULL, "lora_linear_fused_bwd: the forward's h_save is required");
+  bool want_grads = false;
+  for (int i = 0; i < sg.count; ++i) {
+    if ((sg.dA[i] == nullptr) != (sg.dB[i] == nullptr) || (i > 0 && (sg.dA[i] == nullptr) != (sg.dA[0] == nullptr)))
+      return fail(MCB_ERR_NULL, "lora_linear_fused_bwd: pass dA and dB for every segment, or for none");
+    want_grads = want_grads || sg.dA[i] != nullptr;
+  }
+  const int64_t r_tot = a.r * sg.count;
+  const int rp = static_cast<int>(rank_padded(r_tot));
+  FusedWorkspace f = carve_fused(a.ws, a.M, a.K, a.N, r_tot);
+  if (int rc = pack_fused(a, sg, f.w, rp, 1)) return rc;
+  GemmCall c;
+  c.after_pack = true;
+  c.X = static_cast<const __nv_bfloat16*>(a.dy);
+  c.W = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.W) : nullptr;
+  c.Y = static_cast<__nv_bfloat16*>(a.dx);
+  c.R = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.residual) : nullptr;
+  c.M = a.M; c.N = a.K; c.K = a.N;
+  c.P = f.w.P; c.Q = f.w.Q;
+  c.H = want_grads ? f.w.H1 : nullptr;
+  c.h_pitch = h_pitch(a.M);
+  c.rp = rp;
+  c.r_true = static_cast<int>(r_tot);
+  c.scale = a.scale;
+  if (int rc = launch_gemm(c, ds, a.stream)) return rc;
+  if (!want_grads) return MCB_OK;
+  // dA_cat = x^T (scale dy B_bd^T), dB_cat = (scale x A_cat)^T dy: one launch, then the segments' own blocks go out
+  if (int rc = launch_grad2(static_cast<const __nv_bfloat16*>(a.x), f.w.H1, a.K, f.dA_cat, 0,
+                            static_cast<const __nv_bfloat16*>(a.dy), static_cast<const __nv_bfloat16*>(a.h_save), a.N, f.dB_cat, 1,
+                            h_pitch(a.M), f.w.part, a.M, static_cast<int>(r_tot), rp, 0, ds, a.stream))
+    return rc;
+  ScatterTable t;
+  memset(&t, 0, sizeof(t));
+  t.count = sg.count;
+  int64_t elems = a.K * r_tot;
+  for (int i = 0; i < sg.count; ++i) {
+    t.dA[i] = sg.dA[i]; t.dB[i] = sg.dB[i];
+    t.n_off[i] = static_cast<int>(sg.n_off[i]); t.n[i] = static_cast<int>(sg.n[i]);
+    elems += a.r * sg.n[i];
+  }
+  scatter_fused_grads_kernel<<<static_cast<unsigned>((elems + 255) / 256), 256, 0, a.stream>>>(
+      t, f.dA_cat, f.dB_cat, static_cast<int>(a.K), static_cast<int>(a.N), static_cast<int>(a.r), a.accumulate);
+  MCB_CHECK_LAUNCH("scatter_fused_grads");
+  return MCB_OK;
 }
 
 int matmul_nt(const void* a, const void* bt, void* out, int64_t M, int64_t K, int64_t N, const DeviceState* ds,

@@ -136,6 +136,9 @@ class Qwen:
         # next chunk starts, so only [chunk, vocabulary] is ever resident (2.5 GB at 8192 tokens instead of 10 GB for
         # 32768; measured on the 16 x 2048 step: peak 35.7 -> 28.3 GB and 107.9 -> 106.1 ms, 4096 tokens: 27.0 GB, 107.3 ms).
         self.ce_chunk_tokens: Optional[int] = 8192
+        # q, k and v projections of a layer as one fused linear with a block-diagonal rank path (bf16, adapters of
+        # equal rank): the normed input is read once and the three input gradients are summed in one pass
+        self.fuse_qkv = True
         self.layer_done_hook = None  # called as hook(layer_idx) when a layer's LoRA gradients are final
         self.backward_done_hook = None  # called once at the end of forward_backward (joins side-stream work)
 
@@ -203,12 +206,41 @@ class Qwen:
                                                 accumulate=accumulate, dx_residual=dx_residual)
         return dx
 
-    def _rope(self, x, heads: int, B: int, S: int, rotate: bool, inverse: bool):
+    def _rope(self, x, heads: int, B: int, S: int, rotate: bool, inverse: bool, pitch: int = 0, offset: int = 0, out=None):
+        """Rotary embedding + head relayout.  `pitch` / `offset` place the token-major side inside wider rows (a
+        column block of the fused q/k/v buffer); for the inverse direction `out` is that buffer."""
         d = self.config.head_dim
-        out = torch.empty((B, heads, S, d) if not inverse else (B * S, heads * d), dtype=x.dtype, device=x.device)
-        _lib.check(self.lib.mcb_rope_relayout(_ptr(x), _ptr(out), B, S, heads, d, float(self.config.rope_theta),
-                                              int(rotate), int(inverse), self.dt, _stream()))
+        if out is None:
+            out = torch.empty((B, heads, S, d) if not inverse else (B * S, heads * d), dtype=x.dtype, device=x.device)
+        _lib.check(self.lib.mcb_rope_relayout_ex(_ptr(x), _ptr(out), B, S, heads, d, float(self.config.rope_theta),
+                                                 int(rotate), int(inverse), int(pitch), int(offset), self.dt, _stream()))
         return out
+
+    def _qkv_fused(self, L):
+        """The q, k and v projections as one linear (they read the same normed input): the stacked weight [q;k;v]
+        in both majors, the stacked bias, and one segment per adapted projection; or None when this does not
+        apply (float32, no adapter on any of the three, adapters of different rank or scaling).  Cached per layer
+        and rebuilt when a weight or bias tensor has been written to."""
+        if self.dtype != torch.bfloat16 or not self.fuse_qkv:
+            return None
+        lins = [L["q_proj"], L["k_proj"], L["v_proj"]]
+        loras = [l.lora for l in lins if l.lora is not None]
+        if not loras:
+            return None
+        r, sc = loras[0].config.rank, loras[0].config.scaling()
+        if any(l.config.rank != r or l.config.scaling() != sc for l in loras) or r * len(loras) > 64:
+            return None
+        ver = tuple((l.weight._version, l.weight.data_ptr(), l.bias._version) for l in lins)
+        cached = L.get("_qkv")
+        if cached is None or cached[0] != ver:
+            w = torch.cat([l.weight for l in lins], 0).contiguous()
+            cached = (ver, w, backend.transpose_2d(w), torch.cat([l.bias for l in lins], 0).contiguous())
+            L["_qkv"] = cached
+        offs, off = [], 0
+        for l in lins:
+            offs.append(off)
+            off += l.out_f
+        return dict(w=cached[1], wt=cached[2], bias=cached[3], scale=sc, offsets=offs, width=off, lins=lins)
 
     def _embed(self, ids32: torch.Tensor) -> torch.Tensor:
         M = ids32.numel()
@@ -271,13 +303,25 @@ class Qwen:
     def _layer_fwd(self, h, L, B, S, save: bool):
         c = self.config
         n1 = self._norm(h, L["input_layernorm"])
-        q, hq = self._lin(n1, L["q_proj"], save)
-        k, hk = self._lin(n1, L["k_proj"], save)
-        v, hv = self._lin(n1, L["v_proj"], save)
-        Qr = self._rope(q, c.num_attention_heads, B, S, True, False)
-        Kr = self._rope(k, c.num_key_value_heads, B, S, True, False)
-        Vr = self._rope(v, c.num_key_value_heads, B, S, False, False)
-        del q, k, v
+        fq = self._qkv_fused(L)
+        hqkv = None
+        if fq is not None:
+            segs = [dict(A=l.lora.lora_a, B=l.lora.lora_b, offset=o) for l, o in zip(fq["lins"], fq["offsets"]) if l.lora is not None]
+            qkv, hqkv = backend.lora_linear_fused_forward(n1, fq["w"], fq["bias"], segs, fq["scale"], save_hidden=save)
+            W3, o = fq["width"], fq["offsets"]
+            Qr = self._rope(qkv, c.num_attention_heads, B, S, True, False, pitch=W3, offset=o[0])
+            Kr = self._rope(qkv, c.num_key_value_heads, B, S, True, False, pitch=W3, offset=o[1])
+            Vr = self._rope(qkv, c.num_key_value_heads, B, S, False, False, pitch=W3, offset=o[2])
+            del qkv
+            hq = hk = hv = None
+        else:
+            q, hq = self._lin(n1, L["q_proj"], save)
+            k, hk = self._lin(n1, L["k_proj"], save)
+            v, hv = self._lin(n1, L["v_proj"], save)
+            Qr = self._rope(q, c.num_attention_heads, B, S, True, False)
+            Kr = self._rope(k, c.num_key_value_heads, B, S, True, False)
+            Vr = self._rope(v, c.num_key_value_heads, B, S, False, False)
+            del q, k, v
         P, O, lse = self._attention_fwd(Qr, Kr, Vr, B, S)
         # [M, hidden] for o_proj: the fused kernel's output already is; the unfused one goes through a relayout
         o = O if P is None else self._rope(O, c.num_attention_heads, B, S, False, True)
@@ -300,7 +344,7 @@ class Qwen:
         keep_n2 = L["gate_proj"].lora is not None or L["up_proj"].lora is not None
         keep_act = L["down_proj"].lora is not None
         saved = dict(h=h, n1=n1, Qr=Qr, Kr=Kr, Vr=Vr, P=P, O=O, lse=lse, o=o, h2=h2, n2=n2 if keep_n2 else None, gate=gt, up=up,
-                     act=act if keep_act else None, hq=hq, hk=hk, hv=hv, ho=ho, hg=hg, hu=hu, hd=hd)
+                     act=act if keep_act else None, hq=hq, hk=hk, hv=hv, ho=ho, hg=hg, hu=hu, hd=hd, hqkv=hqkv)
         return h3, saved
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -419,14 +463,30 @@ class Qwen:
         dO = do if fused else self._rope(do, c.num_attention_heads, B, S, False, False)
         del do
         dQ, dK, dV = self._attention_bwd(sv["Qr"], sv["Kr"], sv["Vr"], sv["P"], sv["o"] if fused else None, sv["lse"], dO, B, S)
-        dq = self._rope(dQ, c.num_attention_heads, B, S, True, True)
-        dk = self._rope(dK, c.num_key_value_heads, B, S, True, True)
-        dv = self._rope(dV, c.num_key_value_heads, B, S, False, True)
-        del dQ, dK, dV, dO
         n1 = sv["n1"]
-        dn1 = self._lin_bwd(n1, L["q_proj"], dq, sv["hq"], key("q_proj"), accumulate)
-        dn1 = self._lin_bwd(n1, L["k_proj"], dk, sv["hk"], key("k_proj"), accumulate, dx_residual=dn1)
-        dn1 = self._lin_bwd(n1, L["v_proj"], dv, sv["hv"], key("v_proj"), accumulate, dx_residual=dn1)
+        fq = self._qkv_fused(L) if sv["hqkv"] is not None else None
+        if fq is not None:
+            W3, o = fq["width"], fq["offsets"]
+            dqkv = torch.empty(B * S, W3, dtype=self.dtype, device=self.device)
+            self._rope(dQ, c.num_attention_heads, B, S, True, True, pitch=W3, offset=o[0], out=dqkv)
+            self._rope(dK, c.num_key_value_heads, B, S, True, True, pitch=W3, offset=o[1], out=dqkv)
+            self._rope(dV, c.num_key_value_heads, B, S, False, True, pitch=W3, offset=o[2], out=dqkv)
+            del dQ, dK, dV, dO
+            segs = []
+            for l, off, m in zip(fq["lins"], fq["offsets"], ("q_proj", "k_proj", "v_proj")):
+                if l.lora is not None:
+                    ga, gb = self._grad_slices[key(m)]
+                    segs.append(dict(A=l.lora.lora_a, B=l.lora.lora_b, dA=ga, dB=gb, offset=off))
+            dn1 = backend.lora_linear_fused_backward(n1, fq["wt"], segs, fq["scale"], dqkv, sv["hqkv"], accumulate=accumulate)
+            del dqkv
+        else:
+            dq = self._rope(dQ, c.num_attention_heads, B, S, True, True)
+            dk = self._rope(dK, c.num_key_value_heads, B, S, True, True)
+            dv = self._rope(dV, c.num_key_value_heads, B, S, False, True)
+            del dQ, dK, dV, dO
+            dn1 = self._lin_bwd(n1, L["q_proj"], dq, sv["hq"], key("q_proj"), accumulate)
+            dn1 = self._lin_bwd(n1, L["k_proj"], dk, sv["hk"], key("k_proj"), accumulate, dx_residual=dn1)
+            dn1 = self._lin_bwd(n1, L["v_proj"], dv, sv["hv"], key("v_proj"), accumulate, dx_residual=dn1)
         dh, _ = backend.rms_norm_backward(sv["h"], L["input_layernorm"], dn1, c.rms_norm_eps, need_dw=False,
                                           dx_residual=dh2)
         return dh

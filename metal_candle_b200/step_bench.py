@@ -291,11 +291,14 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
     # CUDA events on the GEMM launches for the roofline object; then the step is captured into a CUDA graph and
     # warmed up again.
     n_eager = max(2, args.warmup)
+    launches_before = 0
     for i in range(n_eager):
         if i == n_eager - 1:
             torch.cuda.synchronize()
             _lib.profile_enable(True)
+            launches_before = lib.mcb_launch_count()
         one_step(*dev_batches[i % len(dev_batches)])
+    per_step_launches = lib.mcb_launch_count() - launches_before   # this library's kernels in one step (AdamW included)
     torch.cuda.synchronize()
     _lib.profile_enable(False)
     plain = _lib.profile_summary(0)
@@ -436,7 +439,6 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
 
         both_ms, both_fl = plain[1] + lora[1], plain[2] + lora[2]
         achieved = both_fl / both_ms / 1e9 if both_ms > 0 else 0.0
-        per_step_launches = _count_launches(cfg, wl, tail_on)
         line = {
             "metric": "LoRA fwd+bwd tokens/s, Qwen2.5-0.5B shape", "value": tokens / (ms / 1e3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
@@ -484,31 +486,3 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                 line["kernels"] = kernel_numbers(torch)
             line["cpu_baseline"] = cpu_baseline(WORKLOADS[args.workload], steps=2, warmup=1)
         print(json.dumps(line), flush=True)
-
-
-def _count_launches(cfg, wl, tail_on=True) -> int:
-    """Kernels of this library launched per training step (counted from the step's structure)."""
-    L = cfg.num_hidden_layers
-    n_lora = len(wl["targets"])
-    fused_attn = cfg.head_dim == 64 and wl["seq"] % 128 == 0   # else the scores are materialised (cuBLAS + row softmax)
-    fused_mlp = (cfg.intermediate_size % 128 == 0 and "gate_proj" not in wl["targets"] and "up_proj" not in wl["targets"])
-    # forward: 2 norms, 7 GEMMs, operand packs, 3 rope/relayout (+ 1 inverse relayout unless the fused attention
-    # writes the o_proj layout itself), attention (or softmax), swiglu
-    # (gate, up and swiglu are one kernel when neither projection has an adapter)
-    per_layer_fwd = 2 + (5 if fused_mlp else 8) + n_lora + (3 if fused_attn else 4) + 1
-    # backward: 7 GEMMs, packs, dA/dB, swiglu, 2 norms (each adds the residual-path gradient as it writes dx),
-    # 4 rope/relayout, attention (dq + dkv kernels, or one softmax).  dA and dB of an adapter are accumulated in the tail phase of its dx
-    # GEMM launch and cost one partial-sum launch more; adapters whose dx runs on CTA pairs (out features >= 1536)
-    # or that are wider than 1024 features take a gradient launch of their own as well.
-    out_f = {"q_proj": cfg.hidden_size, "k_proj": cfg.kv_size, "v_proj": cfg.kv_size, "o_proj": cfg.hidden_size,
-             "gate_proj": cfg.intermediate_size, "up_proj": cfg.intermediate_size, "down_proj": cfg.hidden_size}
-    in_f = {"down_proj": cfg.intermediate_size}
-    grad_launches = 0
-    for t in wl["targets"]:
-        o, i = out_f[t], in_f.get(t, cfg.hidden_size)
-        tail = tail_on and o < 1536 and max(o, i) <= 1024 and o % 64 == 0 and i % 64 == 0
-        grad_launches += 1 if tail else 2
-    per_layer_bwd = 7 + n_lora + grad_launches + 1 + 2 + (3 if fused_attn else 4) + (2 if fused_attn else 1)
-    tail = 1 + 1 + 1 + 3 + 1 + 1  # embed, norm, lm_head, CE x3, lm_head bwd, norm bwd
-    adamw = math.ceil(2 * n_lora * L / 64)
-    return L * (per_layer_fwd + per_layer_bwd) + tail + adamw

@@ -21,6 +21,7 @@ OUT = HERE / "src" / "lib.rs"
 TYPES = {
     "void": None, "int": "c_int", "float": "f32", "double": "f64", "int64_t": "i64", "int32_t": "i32",
     "size_t": "usize", "char": "c_char", "mcb_adamw_tensor": "mcb_adamw_tensor", "mcb_comm": "mcb_comm",
+    "mcb_lora_segment": "mcb_lora_segment",
 }
 
 
@@ -103,6 +104,18 @@ def render(consts, funcs) -> str:
         "    pub n: i64,",
         "    pub t: i32,",
         "    pub pad_: i32,",
+        "}",
+        "",
+        "/// One projection of a fused linear (`mcb_lora_linear_fused_*`; a HOST array of these is passed).",
+        "#[repr(C)]",
+        "#[derive(Debug, Clone, Copy)]",
+        "pub struct mcb_lora_segment {",
+        "    pub A: *const f32,",
+        "    pub B: *const f32,",
+        "    pub dA: *mut f32,",
+        "    pub dB: *mut f32,",
+        "    pub n_offset: i64,",
+        "    pub n: i64,",
         "}",
         "",
         "/// Opaque communicator handle (`mcb_comm_*`).",

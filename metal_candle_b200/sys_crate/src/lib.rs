@@ -49,6 +49,18 @@ pub struct mcb_adamw_tensor {
     pub pad_: i32,
 }
 
+/// One projection of a fused linear (`mcb_lora_linear_fused_*`; a HOST array of these is passed).
+#[repr(C)]
+#[derive(Debug, Clone, Copy)]
+pub struct mcb_lora_segment {
+    pub A: *const f32,
+    pub B: *const f32,
+    pub dA: *mut f32,
+    pub dB: *mut f32,
+    pub n_offset: i64,
+    pub n: i64,
+}
+
 /// Opaque communicator handle (`mcb_comm_*`).
 #[repr(C)]
 pub struct mcb_comm {
@@ -65,6 +77,7 @@ extern "C" {
     pub fn mcb_selftest_wait_timeout(limit_cycles: i64, waited_cycles_out: *mut i64, stream: *mut c_void) -> c_int;
     pub fn mcb_set_option(option_id: c_int, value: c_int) -> c_int;
     pub fn mcb_get_option(option_id: c_int, value_out: *mut c_int) -> c_int;
+    pub fn mcb_launch_count() -> i64;
     pub fn mcb_profile_enable(on: c_int) -> c_int;
     pub fn mcb_profile_summary(kind: c_int, launches: *mut i64, total_ms: *mut f64, total_flops: *mut f64, total_bytes: *mut f64) -> c_int;
     pub fn mcb_lora_delta_fwd(x: *const c_void, A: *const f32, B: *const f32, out: *mut c_void, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
@@ -74,6 +87,9 @@ extern "C" {
     pub fn mcb_lora_linear_fwd_ex(x: *const c_void, W: *const c_void, bias: *const c_void, A: *const f32, B: *const f32, residual: *const c_void, y: *mut c_void, h_save: *mut c_void, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, w_layout: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_linear_bwd_ex(x: *const c_void, W: *const c_void, A: *const f32, B: *const f32, dy: *const c_void, h_save: *const c_void, dx_residual: *const c_void, dx: *mut c_void, dA: *mut f32, dB: *mut f32, accumulate: c_int, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, w_layout: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_merge_weights(W: *const c_void, A: *const f32, B: *const f32, out: *mut c_void, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, stream: *mut c_void) -> c_int;
+    pub fn mcb_lora_fused_workspace_bytes(M: i64, K: i64, N: i64, r: i64, n_segments: c_int, dtype: c_int) -> usize;
+    pub fn mcb_lora_linear_fused_fwd(x: *const c_void, W: *const c_void, bias: *const c_void, segments: *const mcb_lora_segment, n_segments: c_int, y: *mut c_void, h_save: *mut c_void, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
+    pub fn mcb_lora_linear_fused_bwd(x: *const c_void, Wt: *const c_void, segments: *const mcb_lora_segment, n_segments: c_int, dy: *const c_void, h_save: *const c_void, dx_residual: *const c_void, dx: *mut c_void, accumulate: c_int, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_rank_padded(r: i64) -> i64;
     pub fn mcb_lora_h_pitch(M: i64) -> i64;
     pub fn mcb_transpose_2d(src: *const c_void, dst: *mut c_void, rows: i64, cols: i64, dtype: c_int, stream: *mut c_void) -> c_int;
@@ -106,6 +122,7 @@ extern "C" {
     pub fn mcb_adamw_multi(tensors: *const mcb_adamw_tensor, n_tensors: c_int, lr: f32, beta1: f32, beta2: f32, eps: f32, weight_decay: f32, grad_scale: f32, stream: *mut c_void) -> c_int;
     pub fn mcb_embedding_fwd(ids: *const i32, table: *const c_void, out: *mut c_void, M: i64, H: i64, vocab: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_rope_relayout(src: *const c_void, dst: *mut c_void, B: i64, S: i64, H: i64, d: i64, theta: f32, rotate: c_int, inverse: c_int, dtype: c_int, stream: *mut c_void) -> c_int;
+    pub fn mcb_rope_relayout_ex(src: *const c_void, dst: *mut c_void, B: i64, S: i64, H: i64, d: i64, theta: f32, rotate: c_int, inverse: c_int, token_pitch: i64, col_offset: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_swiglu_fwd(gate: *const c_void, up: *const c_void, out: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_swiglu_bwd(gate: *const c_void, up: *const c_void, dout: *const c_void, dgate: *mut c_void, dup: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_add(a: *const c_void, b: *const c_void, out: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;

@@ -263,3 +263,68 @@ def test_lora_rejects_bad_arguments(cuda_device):
     xb = torch.zeros(4, 20, device=dev, dtype=torch.bfloat16)
     with pytest.raises(B.TrainingError):
         B.lora_forward_fused(xb, torch.zeros(20, 2, device=dev), torch.zeros(2, 8, device=dev), 1.0)
+
+
+@pytest.mark.parametrize("M,r,which", [(300, 16, (0, 1, 2)), (1300, 8, (0, 2)), (4224, 16, (0, 1, 2)), (256, 4, (1,))])
+def test_fused_projections_with_block_diagonal_rank_path(cuda_device, M, r, which):
+    """mcb_lora_linear_fused_fwd / _bwd: the q, k and v projections of the 0.5B model (896 -> 896, 128, 128) as one
+    linear with one adapter per listed projection.  Every projection's output, the summed input gradient and every
+    adapter's dA / dB against the CPU oracle applied projection by projection; then once more accumulating."""
+    from metal_candle_b200 import _lib
+    from metal_candle_b200 import backend as B
+
+    dev, K, widths, scale = cuda_device, 896, (896, 128, 128), 2.0
+    offs = (0, 896, 1024)
+    cases = [S.lora_linear_case(30 + i, M, K, n, r) for i, n in enumerate(widths)]
+    x64 = S.bf16_round(cases[0]["x"])
+    xd = dev_t(x64, torch.bfloat16, dev)
+    Ws = [S.bf16_round(c["W"]) for c in cases]
+    biases = [S.bf16_round(S.normal(40 + i, "bias", (n,), 0.0, 0.1)) for i, n in enumerate(widths)]
+    dys = [S.bf16_round(c["dy"]) for c in cases]
+    Wcat = dev_t(np.concatenate(Ws, 0), torch.bfloat16, dev)
+    bcat = dev_t(np.concatenate(biases, 0), torch.bfloat16, dev)
+    dycat = dev_t(np.concatenate(dys, 1), torch.bfloat16, dev)
+    segs = []
+    for i in which:
+        segs.append(dict(A=dev_t(cases[i]["A"], torch.float32, dev), B=dev_t(cases[i]["B"], torch.float32, dev), offset=offs[i],
+                         dA=torch.full((K, r), 7.0, device=dev), dB=torch.full((r, widths[i]), 7.0, device=dev)))
+    y, h = B.lora_linear_fused_forward(xd, Wcat, bcat, segs, scale)
+    dx = B.lora_linear_fused_backward(xd, B.transpose_2d(Wcat), segs, scale, dycat, h)
+    want_dx = 0.0
+    for i, n in enumerate(widths):
+        A = S.bf16_round(cases[i]["A"]) if i in which else np.zeros((K, r))
+        Bm = S.bf16_round(cases[i]["B"]) if i in which else np.zeros((r, n))
+        wy, _ = R.lora_linear_forward(x64, Ws[i], biases[i], A, Bm, scale)
+        assert R.max_abs_normalised(back(y)[:, offs[i]:offs[i] + n], wy) <= 2e-2, f"y of projection {i}"
+        wdx, wdA, wdB = R.lora_linear_backward(x64, Ws[i], A, Bm, scale, dys[i])
+        want_dx = want_dx + wdx
+        if i in which:
+            sg = segs[which.index(i)]
+            assert R.max_abs_normalised(back(sg["dA"]), wdA) <= 2e-2, f"dA of projection {i}"
+            assert R.max_abs_normalised(back(sg["dB"]), wdB) <= 2e-2, f"dB of projection {i}"
+    assert R.max_abs_normalised(back(dx), want_dx) <= 2e-2, "dx"
+    # accumulate: a second backward adds the same gradients once more
+    once = [(sg["dA"].clone(), sg["dB"].clone()) for sg in segs]
+    B.lora_linear_fused_backward(xd, B.transpose_2d(Wcat), segs, scale, dycat, h, accumulate=True)
+    for sg, (a1, b1) in zip(segs, once):
+        assert torch.allclose(sg["dA"], 2 * a1, rtol=1e-6, atol=1e-6) and torch.allclose(sg["dB"], 2 * b1, rtol=1e-6, atol=1e-6)
+    assert _lib.device_status() == 0
+
+
+def test_fused_projections_reject_bad_segments(cuda_device):
+    from metal_candle_b200 import _lib
+    from metal_candle_b200 import backend as B
+
+    dev = cuda_device
+    x = torch.zeros(64, 128, device=dev, dtype=torch.bfloat16)
+    W = torch.zeros(256, 128, device=dev, dtype=torch.bfloat16)
+    mk = lambda n, off: dict(A=torch.zeros(128, 8, device=dev), B=torch.zeros(8, n, device=dev), offset=off)
+    with pytest.raises(_lib.McbError, match="ascending and disjoint"):
+        B.lora_linear_fused_forward(x, W, None, [mk(128, 0), mk(128, 64)], 1.0)
+    with pytest.raises(_lib.McbError, match="ascending and disjoint"):
+        B.lora_linear_fused_forward(x, W, None, [mk(128, 192)], 1.0)
+    with pytest.raises(_lib.McbError, match="bfloat16 only"):
+        B.lora_linear_fused_forward(x.float(), W.float(), None, [mk(128, 0)], 1.0)
+    with pytest.raises(_lib.McbError, match="64 rank columns"):
+        big = lambda off: dict(A=torch.zeros(128, 32, device=dev), B=torch.zeros(32, 64, device=dev), offset=off)
+        B.lora_linear_fused_forward(x, W, None, [big(0), big(64), big(128)], 1.0)

@@ -261,3 +261,21 @@ def test_chunked_lm_head_and_loss_equal_the_unchunked_step(cuda_device, dtype):
     want_loss, _ = orc.loss_and_grads(ids, tg)
     assert abs(float(loss0) - want_loss) <= (1e-4 if dtype == torch.float32 else 2e-2) * abs(want_loss)
     assert _lib.device_status() == 0
+
+
+def test_fused_qkv_step_equals_the_separate_projections(cuda_device):
+    """The layer's q, k and v projections as one fused linear (the default in bf16) against three separate fused
+    LoRA linears: same loss and logits bit for bit (zero blocks of the block-diagonal rank path add nothing), LoRA
+    gradients within the bf16 bound of each other (the fused input gradient is summed in one pass, unrounded)."""
+    cfg, model, adapter = build(cuda_device, torch.bfloat16, all_targets(), cfg=fused_attention_config())
+    ids, tg = batch(31, 2, 128, cfg.vocab_size)
+    ids_d, tg_d = torch.from_numpy(ids).to(cuda_device), torch.from_numpy(tg).to(cuda_device)
+    assert model.fuse_qkv and model._qkv_fused(model.layers[0]) is not None
+    loss1, g1 = model.forward_backward(ids_d, tg_d)
+    loss1, g1 = loss1.clone(), [g.clone() for g in g1]
+    model.fuse_qkv = False
+    loss0, g0 = model.forward_backward(ids_d, tg_d)
+    assert torch.equal(loss0, loss1)
+    for a, b in zip(g1, g0):
+        assert R.max_abs_normalised(a.cpu().numpy(), b.cpu().numpy().astype(np.float64)) <= 2e-2
+    model.fuse_qkv = True
