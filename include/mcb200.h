@@ -402,6 +402,71 @@ int mcb_cross_entropy_chunk(void* logits, const int32_t* targets, float* nll, co
                             int64_t V, int write_grad, int dtype, void* stream);
 int mcb_cross_entropy_finish(const float* nll, const int32_t* count, float* loss, int64_t M, void* stream);
 
+/* ---- the training step as one engine ------------------------------------------------------------ */
+
+/* TrainingStep::execute (src/training/trainer.rs:368-414) over Qwen::forward (src/models/qwen.rs:95-143,236-251) for
+ * a host that is not Python: forward, next-token cross-entropy (ignore index = any target outside [0, vocab)),
+ * the written-out backward pass for the LoRA parameters, the optional bucketed gradient all-reduce, and AdamW - all
+ * enqueued on the caller's stream, nothing allocated inside a step, recordable into a CUDA graph.  Adapters sit on
+ * the projections they name and see those projections' true inputs (the reference wires only o_proj / down_proj,
+ * src/models/qwen.rs:106-138).  Production configuration only: bfloat16, head_dim 64, sequence a multiple of 128;
+ * anything else returns MCB_ERR_UNSUPPORTED.
+ * Modules are numbered q 0, k 1, v 2, o 3, gate 4, up 5, down 6 (TargetModule, src/training/adapter.rs:15-62).
+ * All weights are bf16 device tensors in candle's [out, in] layout; the engine keeps the pointers (the caller keeps
+ * the memory) and derives what its kernels want ([in, out] copies, the stacked q/k/v weight, the interleaved
+ * gate/up weight) into the head of `arena`, next to the AdamW moments.  The rest of the arena is re-cut for every
+ * step; mcb_qwen_arena_bytes says how much a (batch, seq) needs. */
+typedef struct {
+  int64_t vocab_size, hidden_size, intermediate_size, num_layers, num_heads, num_kv_heads;
+  float rms_norm_eps, rope_theta;
+} mcb_qwen_config;
+typedef struct {
+  const void* input_layernorm;           /* [hidden] */
+  const void* post_attention_layernorm;  /* [hidden] */
+  const void* weight[7];                 /* by module: [out, in] */
+  const void* bias[3];                   /* q, k, v: [out] or null */
+} mcb_qwen_layer;
+typedef struct {
+  const void* embed_tokens;              /* [vocab, hidden] */
+  const void* final_norm;                /* [hidden] */
+  const void* lm_head;                   /* [vocab, hidden] */
+  const mcb_qwen_layer* layers;          /* HOST array, num_layers entries */
+} mcb_qwen_weights;
+typedef struct {
+  int32_t layer, module;
+  const float* A;   /* [in, r]  float32, trained in place */
+  const float* B;   /* [r, out] */
+  float* dA;        /* gradients, written by every forward_backward (added to with accumulate) */
+  float* dB;
+} mcb_qwen_adapter_entry;
+typedef struct mcb_qwen mcb_qwen;
+
+size_t mcb_qwen_arena_bytes(const mcb_qwen_config* cfg, const mcb_qwen_adapter_entry* adapters, int n_adapters, int rank,
+                            int64_t batch, int64_t seq);
+/* `adapters` (a HOST array) fixes the order in which AdamW visits the tensors: entry order, A before B.  `arena` is
+ * 1024-byte aligned device memory.  The derived weights are written on `stream`. */
+int mcb_qwen_create(mcb_qwen** out, const mcb_qwen_config* cfg, const mcb_qwen_weights* weights,
+                    const mcb_qwen_adapter_entry* adapters, int n_adapters, int rank, float scale, void* arena,
+                    size_t arena_bytes, void* stream);
+/* Data-parallel exchange: with a communicator, forward_backward all-reduces bucket i (elements [lo, hi) of grad_flat,
+ * which must be the buffer the adapters' dA / dB live in) on `side_stream` as soon as layer bucket_first_layer[i] has
+ * finished its backward, and joins the side stream before it returns.  comm = null switches it off. */
+int mcb_qwen_set_exchange(mcb_qwen* q, mcb_comm* comm, void* side_stream, float* grad_flat, const int64_t* bucket_lo,
+                          const int64_t* bucket_hi, const int* bucket_first_layer, int n_buckets);
+/* Tokens per chunk of the lm_head + cross-entropy stage (default 8192; see mcb_cross_entropy_chunk). */
+int mcb_qwen_set_ce_chunk(mcb_qwen* q, int64_t tokens);
+/* ids, targets: int32 [batch, seq] on the device.  loss_out: device float[2] = {mean, sum} of the token losses. */
+int mcb_qwen_forward_backward(mcb_qwen* q, const int32_t* ids, const int32_t* targets, int64_t batch, int64_t seq,
+                              int accumulate, float* loss_out, void* stream);
+/* AdamW::step_var over all adapter tensors (src/training/trainer.rs:398-402) with the reference's shared counter. */
+int mcb_qwen_adamw_step(mcb_qwen* q, float lr, float beta1, float beta2, float eps, float weight_decay, float grad_scale,
+                        void* stream);
+/* forward_backward + adamw_step. */
+int mcb_qwen_train_step(mcb_qwen* q, const int32_t* ids, const int32_t* targets, int64_t batch, int64_t seq, float lr,
+                        float beta1, float beta2, float eps, float weight_decay, float grad_scale, float* loss_out, void* stream);
+int mcb_qwen_info(const mcb_qwen* q, int64_t* adamw_steps, int64_t* persistent_bytes, int32_t** kept_targets_dev);
+int mcb_qwen_destroy(mcb_qwen* q);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,27 @@ class LoraSegment(C.Structure):
                 ("n_offset", C.c_int64), ("n", C.c_int64)]
 
 
+class QwenConfig(C.Structure):
+    _fields_ = [("vocab_size", C.c_int64), ("hidden_size", C.c_int64), ("intermediate_size", C.c_int64),
+                ("num_layers", C.c_int64), ("num_heads", C.c_int64), ("num_kv_heads", C.c_int64),
+                ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float)]
+
+
+class QwenLayer(C.Structure):
+    _fields_ = [("input_layernorm", C.c_void_p), ("post_attention_layernorm", C.c_void_p),
+                ("weight", C.c_void_p * 7), ("bias", C.c_void_p * 3)]
+
+
+class QwenWeights(C.Structure):
+    _fields_ = [("embed_tokens", C.c_void_p), ("final_norm", C.c_void_p), ("lm_head", C.c_void_p),
+                ("layers", C.POINTER(QwenLayer))]
+
+
+class QwenAdapterEntry(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("module", C.c_int32), ("A", C.c_void_p), ("B", C.c_void_p),
+                ("dA", C.c_void_p), ("dB", C.c_void_p)]
+
+
 class AdamWTensor(C.Structure):
     _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
                 ("n", C.c_int64), ("t", C.c_int32), ("pad_", C.c_int32)]
@@ -114,6 +135,16 @@ SIGNATURES = {
     "mcb_cross_entropy_count": (_i32, [_vp, _vp, _i64, _i64, _vp]),
     "mcb_cross_entropy_chunk": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "mcb_cross_entropy_finish": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "mcb_qwen_arena_bytes": (_sz, [C.POINTER(QwenConfig), C.POINTER(QwenAdapterEntry), _i32, _i32, _i64, _i64]),
+    "mcb_qwen_create": (_i32, [C.POINTER(_vp), C.POINTER(QwenConfig), C.POINTER(QwenWeights), C.POINTER(QwenAdapterEntry), _i32, _i32,
+                               _f32, _vp, _sz, _vp]),
+    "mcb_qwen_set_exchange": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int), _i32]),
+    "mcb_qwen_set_ce_chunk": (_i32, [_vp, _i64]),
+    "mcb_qwen_forward_backward": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp]),
+    "mcb_qwen_adamw_step": (_i32, [_vp, _f32, _f32, _f32, _f32, _f32, _f32, _vp]),
+    "mcb_qwen_train_step": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp]),
+    "mcb_qwen_info": (_i32, [_vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(_vp)]),
+    "mcb_qwen_destroy": (_i32, [_vp]),
     "mcb_adamw_multi": (_i32, [C.POINTER(AdamWTensor), _i32, _f32, _f32, _f32, _f32, _f32, _f32, _vp]),
 }
 

@@ -21,7 +21,8 @@ OUT = HERE / "src" / "lib.rs"
 TYPES = {
     "void": None, "int": "c_int", "float": "f32", "double": "f64", "int64_t": "i64", "int32_t": "i32",
     "size_t": "usize", "char": "c_char", "mcb_adamw_tensor": "mcb_adamw_tensor", "mcb_comm": "mcb_comm",
-    "mcb_lora_segment": "mcb_lora_segment",
+    "mcb_lora_segment": "mcb_lora_segment", "mcb_qwen": "mcb_qwen", "mcb_qwen_config": "mcb_qwen_config",
+    "mcb_qwen_weights": "mcb_qwen_weights", "mcb_qwen_adapter_entry": "mcb_qwen_adapter_entry",
 }
 
 
@@ -116,6 +117,56 @@ def render(consts, funcs) -> str:
         "    pub dB: *mut f32,",
         "    pub n_offset: i64,",
         "    pub n: i64,",
+        "}",
+        "",
+        "/// The model's shape (`mcb_qwen_*`).",
+        "#[repr(C)]",
+        "#[derive(Debug, Clone, Copy)]",
+        "pub struct mcb_qwen_config {",
+        "    pub vocab_size: i64,",
+        "    pub hidden_size: i64,",
+        "    pub intermediate_size: i64,",
+        "    pub num_layers: i64,",
+        "    pub num_heads: i64,",
+        "    pub num_kv_heads: i64,",
+        "    pub rms_norm_eps: f32,",
+        "    pub rope_theta: f32,",
+        "}",
+        "",
+        "/// One decoder layer's bf16 device tensors, weights in [out, in] layout, by module q k v o gate up down.",
+        "#[repr(C)]",
+        "#[derive(Debug, Clone, Copy)]",
+        "pub struct mcb_qwen_layer {",
+        "    pub input_layernorm: *const c_void,",
+        "    pub post_attention_layernorm: *const c_void,",
+        "    pub weight: [*const c_void; 7],",
+        "    pub bias: [*const c_void; 3],",
+        "}",
+        "",
+        "#[repr(C)]",
+        "#[derive(Debug, Clone, Copy)]",
+        "pub struct mcb_qwen_weights {",
+        "    pub embed_tokens: *const c_void,",
+        "    pub final_norm: *const c_void,",
+        "    pub lm_head: *const c_void,",
+        "    pub layers: *const mcb_qwen_layer,",
+        "}",
+        "",
+        "#[repr(C)]",
+        "#[derive(Debug, Clone, Copy)]",
+        "pub struct mcb_qwen_adapter_entry {",
+        "    pub layer: i32,",
+        "    pub module: i32,",
+        "    pub A: *const f32,",
+        "    pub B: *const f32,",
+        "    pub dA: *mut f32,",
+        "    pub dB: *mut f32,",
+        "}",
+        "",
+        "/// Opaque training-step engine (`mcb_qwen_*`).",
+        "#[repr(C)]",
+        "pub struct mcb_qwen {",
+        "    _private: [u8; 0],",
         "}",
         "",
         "/// Opaque communicator handle (`mcb_comm_*`).",

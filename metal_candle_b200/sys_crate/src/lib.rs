@@ -61,6 +61,56 @@ pub struct mcb_lora_segment {
     pub n: i64,
 }
 
+/// The model's shape (`mcb_qwen_*`).
+#[repr(C)]
+#[derive(Debug, Clone, Copy)]
+pub struct mcb_qwen_config {
+    pub vocab_size: i64,
+    pub hidden_size: i64,
+    pub intermediate_size: i64,
+    pub num_layers: i64,
+    pub num_heads: i64,
+    pub num_kv_heads: i64,
+    pub rms_norm_eps: f32,
+    pub rope_theta: f32,
+}
+
+/// One decoder layer's bf16 device tensors, weights in [out, in] layout, by module q k v o gate up down.
+#[repr(C)]
+#[derive(Debug, Clone, Copy)]
+pub struct mcb_qwen_layer {
+    pub input_layernorm: *const c_void,
+    pub post_attention_layernorm: *const c_void,
+    pub weight: [*const c_void; 7],
+    pub bias: [*const c_void; 3],
+}
+
+#[repr(C)]
+#[derive(Debug, Clone, Copy)]
+pub struct mcb_qwen_weights {
+    pub embed_tokens: *const c_void,
+    pub final_norm: *const c_void,
+    pub lm_head: *const c_void,
+    pub layers: *const mcb_qwen_layer,
+}
+
+#[repr(C)]
+#[derive(Debug, Clone, Copy)]
+pub struct mcb_qwen_adapter_entry {
+    pub layer: i32,
+    pub module: i32,
+    pub A: *const f32,
+    pub B: *const f32,
+    pub dA: *mut f32,
+    pub dB: *mut f32,
+}
+
+/// Opaque training-step engine (`mcb_qwen_*`).
+#[repr(C)]
+pub struct mcb_qwen {
+    _private: [u8; 0],
+}
+
 /// Opaque communicator handle (`mcb_comm_*`).
 #[repr(C)]
 pub struct mcb_comm {
@@ -130,4 +180,13 @@ extern "C" {
     pub fn mcb_cross_entropy_count(targets: *const i32, count: *mut i32, M: i64, V: i64, stream: *mut c_void) -> c_int;
     pub fn mcb_cross_entropy_chunk(logits: *mut c_void, targets: *const i32, nll: *mut f32, count: *const i32, rows: i64, V: i64, write_grad: c_int, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_cross_entropy_finish(nll: *const f32, count: *const i32, loss: *mut f32, M: i64, stream: *mut c_void) -> c_int;
+    pub fn mcb_qwen_arena_bytes(cfg: *const mcb_qwen_config, adapters: *const mcb_qwen_adapter_entry, n_adapters: c_int, rank: c_int, batch: i64, seq: i64) -> usize;
+    pub fn mcb_qwen_create(out: *mut *mut mcb_qwen, cfg: *const mcb_qwen_config, weights: *const mcb_qwen_weights, adapters: *const mcb_qwen_adapter_entry, n_adapters: c_int, rank: c_int, scale: f32, arena: *mut c_void, arena_bytes: usize, stream: *mut c_void) -> c_int;
+    pub fn mcb_qwen_set_exchange(q: *mut mcb_qwen, comm: *mut mcb_comm, side_stream: *mut c_void, grad_flat: *mut f32, bucket_lo: *const i64, bucket_hi: *const i64, bucket_first_layer: *const c_int, n_buckets: c_int) -> c_int;
+    pub fn mcb_qwen_set_ce_chunk(q: *mut mcb_qwen, tokens: i64) -> c_int;
+    pub fn mcb_qwen_forward_backward(q: *mut mcb_qwen, ids: *const i32, targets: *const i32, batch: i64, seq: i64, accumulate: c_int, loss_out: *mut f32, stream: *mut c_void) -> c_int;
+    pub fn mcb_qwen_adamw_step(q: *mut mcb_qwen, lr: f32, beta1: f32, beta2: f32, eps: f32, weight_decay: f32, grad_scale: f32, stream: *mut c_void) -> c_int;
+    pub fn mcb_qwen_train_step(q: *mut mcb_qwen, ids: *const i32, targets: *const i32, batch: i64, seq: i64, lr: f32, beta1: f32, beta2: f32, eps: f32, weight_decay: f32, grad_scale: f32, loss_out: *mut f32, stream: *mut c_void) -> c_int;
+    pub fn mcb_qwen_info(q: *const mcb_qwen, adamw_steps: *mut i64, persistent_bytes: *mut i64, kept_targets_dev: *mut *mut i32) -> c_int;
+    pub fn mcb_qwen_destroy(q: *mut mcb_qwen) -> c_int;
 }
