@@ -547,6 +547,8 @@ def main():
     ap.add_argument("--comm", default="mcb", choices=["mcb", "mcb-blocking", "torch"],
                     help="gradient exchange: the library's communicator (default), the same with a blocking NCCL "
                          "communicator, or torch.distributed")
+    ap.add_argument("--step-impl", default="engine", choices=["engine", "python"],
+                    help="run the step through the C-ABI engine (mcb_qwen_*) or through the Python mirror of the reference API")
     ap.add_argument("--grad-tail", default="auto", choices=["auto", "on", "off"],
                     help="dA/dB in the tail phase of the dx launch (auto: on with one GPU, off beside a collective)")
     ap.add_argument("--opt", action="append", default=[], metavar="ID=VALUE",

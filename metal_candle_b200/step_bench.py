@@ -142,7 +142,80 @@ def _host_batches(torch, n, B, S, vocab, seed):
     return out
 
 
-def dp_check(torch, model, adapter, dp, world, rank, B, S, vocab, device, steps=3):
+class _CapturedEngineStep:
+    """QwenEngine.forward_backward of a fixed shape as a CUDA graph; called like `CapturedStep`."""
+
+    def __init__(self, torch, eng, batch, seq):
+        self.ids = torch.zeros(batch, seq, dtype=torch.int32, device=eng.model.device)
+        self.targets = torch.full((batch, seq), -1, dtype=torch.int32, device=eng.model.device)
+        self.graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(eng.model.device)
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.loss, self.grads = eng.forward_backward(self.ids, self.targets)
+
+    def __call__(self, input_ids, target_ids):
+        self.ids.copy_(input_ids, non_blocking=True)
+        self.targets.copy_(target_ids, non_blocking=True)
+        self.graph.replay()
+        return self.loss, self.grads
+
+
+class _Step:
+    """The two implementations of the step behind one face: the C-ABI engine (mcb_qwen_*) or the Python mirror
+    (Qwen.forward_backward + AdamW.step_vars).  Both issue the same kernels."""
+
+    def __init__(self, torch, model, adapter, dp, world, comm, use_engine, B, S):
+        from .training import AdamW, AdamWConfig, TrainingStep
+
+        self.torch, self.model, self.dp, self.world, self.comm = torch, model, dp, world, comm
+        self.variables = TrainingStep.collect_trainable_vars(adapter)
+        self.eng = None
+        self.opt = AdamW(AdamWConfig(learning_rate=1e-4))
+        self.B, self.S = B, S
+        if use_engine:
+            from .engine import QwenEngine
+
+            self.eng = QwenEngine(model, B, S)
+            model.layer_done_hook = model.backward_done_hook = None    # the engine issues the exchange itself
+            self.exchange(True)
+
+    def exchange(self, on: bool) -> None:
+        """Engine only: the bucketed all-reduce inside forward_backward on / off."""
+        if self.eng is None:
+            return
+        if on and self.comm is not None and self.world > 1:
+            self.eng.set_exchange(self.comm, self.dp.side, [(layer, lo, hi) for layer, (lo, hi) in self.dp.buckets.items()])
+        else:
+            self.eng.set_exchange(None, None, None)
+
+    def fb(self, ids, tg, accumulate=False, exchange=True):
+        """forward + loss + backward (+ the exchange, finished on the current stream); returns (loss, grads)."""
+        if self.eng is not None:
+            return self.eng.forward_backward(ids, tg, accumulate=accumulate)
+        loss, grads = self.model.forward_backward(ids, tg, accumulate=accumulate)
+        if exchange:
+            self.dp.finish()
+        return loss, grads
+
+    def capture(self, with_exchange: bool, pool=None):
+        if self.eng is not None:
+            self.exchange(with_exchange)
+            try:
+                return _CapturedEngineStep(self.torch, self.eng, self.B, self.S)
+            finally:
+                self.exchange(True)
+        return self.model.capture_forward_backward(self.B, self.S, keep_hooks=with_exchange, pool=pool)
+
+    def adamw(self, lr, grads, opt=None):
+        if self.eng is not None and opt is None:
+            self.eng.adamw_step(lr, grad_scale=1.0 / self.world)
+            return
+        o = self.opt if opt is None else opt
+        o.set_lr(lr)
+        o.step_vars(self.variables, grads, grad_scale=1.0 / self.world)
+
+
+def dp_check(torch, step, adapter, world, rank, B, S, vocab, device, steps=3):
     """The data-parallel arithmetic checked on the GPUs themselves: `steps` optimizer steps data-parallel (each
     rank its own micro-batch, bucketed all-reduce, AdamW on gradients / world) against the same steps on ONE rank's
     arithmetic, accumulating the `world` micro-batches before each optimizer step.  Every rank computes the
@@ -150,9 +223,9 @@ def dp_check(torch, model, adapter, dp, world, rank, B, S, vocab, device, steps=
     and of the parameter updates; leaves the adapter as it found it."""
     import torch.distributed as dist
 
-    from .training import AdamW, AdamWConfig, LRScheduler, TrainingStep
+    from .training import AdamW, AdamWConfig, LRScheduler
 
-    variables = TrainingStep.collect_trainable_vars(adapter)
+    variables = step.variables
     snapshot = [v.clone() for v in variables]
     sched = LRScheduler.warmup_cosine(5, 50, 1e-4, 1e-6)
     micro = {r: _host_batches(torch, steps, B, S, vocab, seed=777 + r) for r in range(world)}
@@ -167,18 +240,18 @@ def dp_check(torch, model, adapter, dp, world, rank, B, S, vocab, device, steps=
     dp_losses = []
     for s in range(steps):
         ids, tg = micro[rank][s]
-        loss, grads = model.forward_backward(ids.to(device), tg.to(device))
-        dp.finish()
-        opt.set_lr(sched.get_lr(s))
-        opt.step_vars(variables, grads, grad_scale=1.0 / world)
+        loss, grads = step.fb(ids.to(device), tg.to(device))
+        step.adamw(sched.get_lr(s), grads, opt=opt)
         l = loss.detach().clone().double()
         dist.all_reduce(l, op=dist.ReduceOp.SUM)       # every micro-batch keeps the same number of tokens
         dp_losses.append(float(l) / world)
     p_dp = [v.clone() for v in variables]
     restore()
     # (2) one rank's arithmetic: accumulate the micro-batches of all ranks, then one optimizer step
+    model = step.model
     hook, done = model.layer_done_hook, model.backward_done_hook
     model.layer_done_hook = model.backward_done_hook = None
+    step.exchange(False)
     opt = AdamW(AdamWConfig(learning_rate=1e-4))
     acc_losses = []
     try:
@@ -186,13 +259,13 @@ def dp_check(torch, model, adapter, dp, world, rank, B, S, vocab, device, steps=
             tot = 0.0
             for r in range(world):
                 ids, tg = micro[r][s]
-                loss, grads = model.forward_backward(ids.to(device), tg.to(device), accumulate=(r > 0))
+                loss, grads = step.fb(ids.to(device), tg.to(device), accumulate=(r > 0), exchange=False)
                 tot += float(loss)
-            opt.set_lr(sched.get_lr(s))
-            opt.step_vars(variables, grads, grad_scale=1.0 / world)
+            step.adamw(sched.get_lr(s), grads, opt=opt)
             acc_losses.append(tot / world)
     finally:
         model.layer_done_hook, model.backward_done_hook = hook, done
+        step.exchange(True)
     rel_loss = max(abs(a - b) / max(abs(b), 1e-30) for a, b in zip(dp_losses, acc_losses))
     num = max(float(((a - s0) - (b - s0)).abs().max()) for a, b, s0 in zip(p_dp, variables, snapshot))
     den = max(float((b - s0).abs().max()) for b, s0 in zip(variables, snapshot))
@@ -256,10 +329,11 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
     B, S = wl["batch"], wl["seq"]
     cfg, model, adapter, opt, sched = _build(torch, wl, device)
     dp = DataParallelLoRA(model, world, comm=comm)
-    variables = TrainingStep.collect_trainable_vars(adapter)
+    use_engine = getattr(args, "step_impl", "engine") == "engine" and (world == 1 or comm is not None)
+    step = _Step(torch, model, adapter, dp, world, comm, use_engine, B, S)
     check = None
     if world > 1 and not getattr(args, "no_dp_check", False):
-        check = dp_check(torch, model, adapter, dp, world, rank, B, S, cfg.vocab_size, device)
+        check = dp_check(torch, step, adapter, world, rank, B, S, cfg.vocab_size, device)
     n_steps = args.warmup + 2 * args.steps
     host = _host_batches(torch, min(n_steps, 8), B, S, cfg.vocab_size, seed=1234 + rank)
     dev_batches = [(i.to(device), t.to(device)) for i, t in host]
@@ -275,10 +349,12 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
             if not graph_has_comm:
                 dp.reduce_all()
         else:
-            loss, grads = model.forward_backward(ids, tg)
-            dp.finish()
-        opt.set_lr(sched.get_lr(state["step"]))
-        opt.step_vars(variables, grads, grad_scale=1.0 / world)
+            if step.eng is not None and not ids.is_cuda:
+                ids_dev.copy_(ids, non_blocking=True)
+                tg_dev.copy_(tg, non_blocking=True)
+                ids, tg = ids_dev, tg_dev
+            loss, grads = step.fb(ids, tg)
+        step.adamw(sched.get_lr(state["step"]), grads)
         state["step"] += 1
         return loss
 
@@ -310,9 +386,9 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
         try:
             if not graph_has_comm:
                 model.layer_done_hook = model.backward_done_hook = None
-            captured["fb"] = model.capture_forward_backward(B, S, keep_hooks=graph_has_comm)
+            captured["fb"] = step.capture(graph_has_comm)
             if graph_has_comm:   # the same step without the exchange, sharing the first graph's memory: for comm.exposed_ms
-                captured["fb_nocomm"] = model.capture_forward_backward(B, S, keep_hooks=False, pool=captured["fb"].graph.pool())
+                captured["fb_nocomm"] = step.capture(False, pool=captured["fb"].graph.pool())
         except Exception as e:  # the eager path stays valid; say why the graph is not used
             captured["fb"] = captured["fb_nocomm"] = None
             model.layer_done_hook, model.backward_done_hook = hooks
@@ -342,7 +418,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler is not None else None
-    if captured["fb"] is not None and int(captured["fb"].count.item()) == 0:
+    if captured["fb"] is not None and getattr(captured["fb"], "count", None) is not None and int(captured["fb"].count.item()) == 0:
         raise SystemExit("bench: every target of the last batch was ignored; the loss is undefined")
     # ---- end to end: pinned host ids -> device, step, loss back to the host, every step ----
     barrier()
@@ -446,6 +522,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
             "config": {"workload": wl["name"], "per_gpu_batch": B, "seq_len": S, "global_batch": B * world,
                        "lora_rank": wl["rank"], "lora_targets": list(wl["targets"]), "parallelism": f"dp{world}",
                        "optimizer": "AdamW lr 1e-4 warmup-cosine",
+                       "step_through": "the C-ABI engine (mcb_qwen_forward_backward, mcb_qwen_adamw_step)" if use_engine
+                       else "the Python mirror (Qwen.forward_backward, AdamW.step_vars)",
                        "execution": (("forward+loss+backward" + (" with the bucketed gradient all-reduce overlapped on a side stream" if graph_has_comm and world > 1 else "")
                                       + " replayed from a CUDA graph, then " + ("" if graph_has_comm or world == 1 else "gradient all-reduce and ") + "AdamW")
                                      if used_graph else
@@ -481,7 +559,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
             line["dp_check"] = check
         if world == 1:
             if kernel_numbers is not None and not getattr(args, "no_kernels", False):
-                del model, adapter, opt, dp, captured, dev_batches
+                step.eng = None
+                del model, adapter, opt, dp, captured, dev_batches, step
                 torch.cuda.empty_cache()
                 line["kernels"] = kernel_numbers(torch)
             line["cpu_baseline"] = cpu_baseline(WORKLOADS[args.workload], steps=2, warmup=1)
