@@ -8,6 +8,7 @@ Headline (the line the driver reads):
 
 Kernel micro-benchmarks (one JSON line per case; used for the roofline sweeps and for ncu captures):
     python bench.py --micro lora    --M 32768 --K 896 --N 896 --r 16 [--dtype bf16|f32] [--pass fwd|bwd|both]
+    python bench.py --micro lora_qkv --M 32768 --r 16 [--pass fwd|bwd|both]     (q, k, v projections as one fused linear)
     python bench.py --micro attention --nb 32 --G 7 --S 2048 [--pass fwd|bwd|both]
     python bench.py --micro rmsnorm --rows 114688 --D 896  [--dtype bf16|f32]
     python bench.py --micro softmax --rows 114688 --D 1024 [--dtype bf16|f32]
@@ -214,6 +215,55 @@ def micro_lora(torch, M, K, N, r, dtype, which, iters=20, warmup=5):
             "dtype": dtype, "config": {"workload": "lora_linear", "M": M, "K": K, "N": N, "r": r, "pass": which,
                                        "input_sets": nv, "l2": "inputs rotated through >2x L2"},
             "flop_per_byte": fl / by, "roofline": roof}
+
+
+def micro_lora_qkv(torch, M, r, which, iters=20, warmup=5):
+    """The 0.5B model's q, k and v projections (896 -> 896 + 128 + 128) as one fused linear with three adapters of
+    rank r (mcb_lora_linear_fused_*).  Algorithmic FLOP = the three projections' own 2MKN + 2Mr(K+N) forward and
+    2MKN + 4Mr(K+N) backward (the zero blocks of the block-diagonal rank path are not counted)."""
+    from metal_candle_b200 import backend as B
+
+    dev = torch.device("cuda", 0)
+    K, widths = 896, (896, 128, 128)
+    N = sum(widths)
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    nv = max(2, min(8, _variants((M * K + M * N) * 2)))
+    xs = [torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16) for _ in range(nv)]
+    dys = [torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16) for _ in range(nv)]
+    W = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    Wt = B.transpose_2d(W)
+    bias = torch.zeros(N, device=dev, dtype=torch.bfloat16)
+    segs, off = [], 0
+    for n in widths:
+        segs.append(dict(A=(torch.rand(K, r, device=dev, generator=g) * 2 - 1) / math.sqrt(K), B=torch.randn(r, n, device=dev, generator=g) * 0.02,
+                         dA=torch.zeros(K, r, device=dev), dB=torch.zeros(r, n, device=dev), offset=off))
+        off += n
+    hs = [B.lora_linear_fused_forward(xs[i], W, bias, segs, 2.0)[1] for i in range(nv)]
+
+    def fwd(i):
+        B.lora_linear_fused_forward(xs[i % nv], W, bias, segs, 2.0)
+
+    def bwd(i):
+        B.lora_linear_fused_backward(xs[i % nv], Wt, segs, 2.0, dys[i % nv], hs[i % nv])
+
+    def both(i):
+        fwd(i)
+        bwd(i)
+
+    fl_f = sum(2 * M * K * n + 2 * M * r * (K + n) for n in widths)
+    fl_b = sum(2 * M * K * n + 4 * M * r * (K + n) for n in widths)
+    by_f = 2 * (M * K + K * N + M * N) + sum(2 * r * (K + n) for n in widths)
+    by_b = 2 * (M * N + K * N + 2 * M * K) + sum(6 * r * (K + n) for n in widths)
+    fn, fl, by = {"fwd": (fwd, fl_f, by_f), "bwd": (bwd, fl_b, by_b), "both": (both, fl_f + fl_b, by_f + by_b)}[which]
+    med, mn = _time_kernel(torch, fn, nv, iters, warmup)
+    pk = measured_peaks()
+    tf = fl / med / 1e9
+    return {"metric": f"fused q/k/v LoRA linear {which}", "value": tf, "unit": "TFLOP/s", "ms": med, "ms_min": mn, "dtype": "bf16",
+            "config": {"workload": "lora_linear_qkv", "M": M, "K": K, "N": list(widths), "r": r, "pass": which, "input_sets": nv,
+                       "l2": "inputs rotated through >2x L2"},
+            "flop_per_byte": fl / by,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / pk["bf16_tflops"],
+                         "traffic": None, "peak_source": pk["source"]}}
 
 
 def micro_attention(torch, nb, G, S, which, iters=20, warmup=5):
@@ -466,6 +516,9 @@ def kernel_numbers(torch):
         r = micro_lora(torch, 32768, K, N, 16, "bf16", "both", 20, 5)
         lora[f"{K}x{N} r16 M=32768 fwd+bwd"] = {"TFLOPs": round(r["value"], 1), "frac": round(r["roofline"]["frac"], 3),
                                                  "ms": round(r["ms"], 4), "bound": r["roofline"]["bound"]}
+    r = micro_lora_qkv(torch, 32768, 16, "both", 20, 5)
+    lora["q/k/v fused (896 -> 896+128+128) r16 M=32768 fwd+bwd"] = {"TFLOPs": round(r["value"], 1), "frac": round(r["roofline"]["frac"], 3),
+                                                                    "ms": round(r["ms"], 4), "bound": "tensor"}
     out["lora_linear"] = lora
     return out
 
@@ -507,6 +560,8 @@ def run_micro(args):
     if args.micro == "lora":
         print(json.dumps(micro_lora(torch, args.M, args.K, args.N, args.r, args.dtype, args.which, args.iters,
                                     args.warmup_iters)), flush=True)
+    elif args.micro == "lora_qkv":
+        print(json.dumps(micro_lora_qkv(torch, args.M, args.r, args.which, args.iters, args.warmup_iters)), flush=True)
     elif args.micro == "attention":
         print(json.dumps(micro_attention(torch, args.nb, args.G, args.S, args.which, args.iters, args.warmup_iters)),
               flush=True)
