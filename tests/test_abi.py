@@ -78,3 +78,33 @@ def test_rust_sys_crate_source_matches_the_header():
     declared = re.findall(r"pub fn (mcb_[a-z0-9_]+)\(", src)
     assert sorted(declared) == declared_symbols()
     assert "#[repr(C)]" in src and "pub struct mcb_adamw_tensor" in src
+
+
+def test_host_only_entry_points_work_without_a_gpu():
+    """Switches, the launch counter and the engine's arena sizing are pure host code."""
+    import ctypes as C
+
+    from metal_candle_b200 import _lib
+
+    lib = _lib.load()
+    v = C.c_int(-1)
+    assert lib.mcb_get_option(_lib.MCB_OPT_GRAD_TAIL, C.byref(v)) == 0 and v.value == 1
+    assert lib.mcb_set_option(_lib.MCB_OPT_GRAD_TAIL, 0) == 0
+    assert lib.mcb_get_option(_lib.MCB_OPT_GRAD_TAIL, C.byref(v)) == 0 and v.value == 0
+    assert lib.mcb_set_option(_lib.MCB_OPT_GRAD_TAIL, 1) == 0
+    assert lib.mcb_get_option(_lib.MCB_OPT_PAIR_MIN_K, C.byref(v)) == 0 and v.value == 1536
+    assert lib.mcb_set_option(99, 1) == -2 and lib.mcb_get_option(0, None) == -1
+    assert lib.mcb_launch_count() >= 0
+    # the 0.5B model, rank 16 on q/k/v/o, 16 x 2048 tokens: derived weights + 24 layers of saved activations + scratch
+    cfg = _lib.QwenConfig(151936, 896, 4864, 24, 14, 2, 1e-6, 1e6)
+    entries = (_lib.QwenAdapterEntry * 96)()
+    for i in range(24):
+        for j, m in enumerate((0, 1, 2, 3)):
+            entries[4 * i + j] = _lib.QwenAdapterEntry(i, m, None, None, None, None)
+    big = lib.mcb_qwen_arena_bytes(C.byref(cfg), entries, 96, 16, 16, 2048)
+    small = lib.mcb_qwen_arena_bytes(C.byref(cfg), entries, 96, 16, 1, 128)
+    assert 20e9 < big < 40e9 and 1e9 < small < 3e9 and small < big
+    assert lib.mcb_qwen_arena_bytes(C.byref(cfg), entries, 96, 32, 16, 2048) == 0      # 3 x 32 rank columns > 64
+    bad = _lib.QwenConfig(151936, 896, 4864, 24, 7, 1, 1e-6, 1e6)                      # head_dim 128
+    assert lib.mcb_qwen_arena_bytes(C.byref(bad), entries, 96, 16, 1, 128) == 0
+    assert b"head_dim" in lib.mcb_last_error()
