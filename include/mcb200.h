@@ -87,8 +87,7 @@ int mcb_selftest_wait_timeout(int64_t limit_cycles, int64_t* waited_cycles_out, 
  * programmatic dependent launch, so that each kernel's launch and set-up run under its predecessor's tail; 0: plain
  * stream order. */
 #define MCB_OPT_PDL 2
-#define MCB_OPT_DEBUG_ 3   /* timing experiments; leave 0 */
-#define MCB_OPT_COUNT_ 4
+#define MCB_OPT_COUNT_ 3
 int mcb_set_option(int option_id, int value);
 int mcb_get_option(int option_id, int* value_out);
 

@@ -38,9 +38,6 @@ struct GradParams {
   // Tail-phase use only: problem 0's H is written by other CTAs of the same launch.  h_flags[mt] counts the
   // epilogue warps (4 per tile) that have stored the rows of 128-token tile mt; null when H is already there.
   const int* h_flags;
-  // X as plain memory, for L2 prefetches of whole token rows ahead of the tiled copies
-  const void* xptr[2];
-  uint32_t row_bytes[2];
 };
 
 // What a CTA needs of its surroundings: the aligned shared-memory base of the stage ring, the barrier addresses,
@@ -106,20 +103,7 @@ __device__ __forceinline__ void grad_roles(const GradParams& p, const CUtensorMa
       uint32_t phase = 0;
       const bool flagged = which == 0 && p.h_flags != nullptr;
       int next_mt = (step_begin * T) / BM;    // first 128-token tile not yet known to be written
-      // The tiled copy of a stage gathers 128-byte pieces of T token rows, atom by atom.  When the CTA's group is the
-      // whole row, the rows of a step are one contiguous range: it is requested from L2 as such one ring turn ahead,
-      // so that DRAM sees long sequential reads and the tiled copies find their pieces in L2.
-      const bool whole_rows = q.groups == 1 && p.xptr[which] != nullptr;
-      const char* xbase = static_cast<const char*>(p.xptr[which]);
-      const uint32_t rowb = p.row_bytes[which];
-      auto prefetch_step = [&](int s) {
-        if (!whole_rows || s >= step_end) return;
-        const int tok0 = s * T, ntok = min(T, p.M - tok0);
-        if (ntok > 0) l2_prefetch_bulk(xbase + static_cast<size_t>(tok0) * rowb, static_cast<uint32_t>(ntok) * rowb);
-      };
-      for (int s = step_begin; s < min(step_end, step_begin + n_stages); ++s) prefetch_step(s);
       for (int s = step_begin; s < step_end; ++s) {
-        prefetch_step(s + n_stages);
         if (flagged) {
           const int last_tok = min(p.M, (s + 1) * T) - 1;
           bool ok = true;

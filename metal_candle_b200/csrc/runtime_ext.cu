@@ -7,7 +7,7 @@
 
 namespace mcb {
 namespace {
-std::atomic<int> g_options[MCB_OPT_COUNT_] = {{1}, {1536}, {1}, {0}};   // MCB_OPT_GRAD_TAIL on, MCB_OPT_PAIR_MIN_K 1536, MCB_OPT_PDL on, debug 0
+std::atomic<int> g_options[MCB_OPT_COUNT_] = {{1}, {1536}, {1}};   // MCB_OPT_GRAD_TAIL on, MCB_OPT_PAIR_MIN_K 1536, MCB_OPT_PDL on
 }
 
 namespace {

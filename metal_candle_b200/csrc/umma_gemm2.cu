@@ -464,7 +464,6 @@ int init_gemm2_kernel() {
 // most 64 and a long enough reduction.
 bool gemm2_eligible(const GemmCall& c) {
   if (c.W == nullptr || c.Y == nullptr || c.M < 1024 || c.N < 128 || c.K < 64) return false;
-  if (option(MCB_OPT_DEBUG_) & 8) return false;
   if (c.rp == 0) return true;
   // Short reductions stay on the one-CTA kernel.  Alone, the pair is a little ahead even there once the rank
   // update is issued between the next tile's k-blocks (32768x896x896 r16 forward 953 against 922 TFLOP/s), but

@@ -413,7 +413,6 @@ int plan_grad2(const GradRequest& rq, int64_t M, int rp, int max_ctas, uint32_t 
   p.status = ds->status_word;
   p.h_flags = rq.h_flags;
   for (int i = 0; i < np; ++i) plan_groups(rq.C[i], rp, &p.pr[i]);
-  for (int i = 0; i < np; ++i) { p.xptr[i] = (option(MCB_OPT_DEBUG_) & 16) ? nullptr : rq.X[i]; p.row_bytes[i] = static_cast<uint32_t>(rq.C[i] * 2); }
   // tokens per stage, per problem: as many (a multiple of 16, at most 256) as keep a stage near 48 KB, so that
   // narrow problems have as many bytes in flight as wide ones
   for (int i = 0; i < np; ++i) {
