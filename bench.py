@@ -608,6 +608,7 @@ def main():
                     help="dA/dB in the tail phase of the dx launch (auto: on with one GPU, off beside a collective)")
     ap.add_argument("--opt", action="append", default=[], metavar="ID=VALUE",
                     help="library switch for this run (mcb_set_option), e.g. --opt 1=512")
+    ap.add_argument("--buckets", type=int, default=4, help="gradient buckets of the data-parallel exchange (N > 1)")
     ap.add_argument("--no-dp-check", action="store_true", help="skip the data-parallel arithmetic check at N > 1")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel numbers at N = 1")
     args = ap.parse_args()

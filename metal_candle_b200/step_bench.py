@@ -42,7 +42,7 @@ class DataParallelLoRA:
     it is host-synchronous, so it can be recorded into a CUDA graph.  Without `comm` the exchange goes through
     torch.distributed (any backend; what the CPU tests use with gloo)."""
 
-    def __init__(self, model, world: int, comm=None):
+    def __init__(self, model, world: int, comm=None, n_buckets: int = N_BUCKETS):
         self.model, self.world, self.comm = model, world, comm
         self.dist = None
         self.side = None
@@ -57,7 +57,7 @@ class DataParallelLoRA:
             self.torch = torch
             self.side = torch.cuda.Stream(priority=-1)
         L = model.num_layers()
-        per = math.ceil(L / N_BUCKETS)
+        per = math.ceil(L / max(1, min(L, n_buckets)))
         self.buckets = {}  # lowest layer of the bucket -> (lo, hi) element range
         for b in range(0, L, per):
             lo = model.grad_layer_range(b)[0]
@@ -216,11 +216,20 @@ class _Step:
 
 
 def dp_check(torch, step, adapter, world, rank, B, S, vocab, device, steps=3):
-    """The data-parallel arithmetic checked on the GPUs themselves: `steps` optimizer steps data-parallel (each
-    rank its own micro-batch, bucketed all-reduce, AdamW on gradients / world) against the same steps on ONE rank's
-    arithmetic, accumulating the `world` micro-batches before each optimizer step.  Every rank computes the
-    second form redundantly from the same seeds.  Returns the largest relative differences of the loss sequence
-    and of the parameter updates; leaves the adapter as it found it."""
+    """The data-parallel arithmetic checked on the GPUs themselves.  For `steps` optimizer steps, from the SAME
+    parameters and optimizer state each time: (a) the data-parallel form (this rank's micro-batch, bucketed
+    all-reduce, AdamW on gradients / world) and (b) one rank's arithmetic (the `world` micro-batches accumulated
+    into the gradient buffer, then the same AdamW).  Compared are the mean loss, the summed gradients (they may
+    differ only by the order of the fp32 additions: sequential accumulation against the all-reduce's ring or tree)
+    and the parameter update each gives.  The trajectory then continues from (a).
+
+    The comparison is made step by step rather than between two free-running trajectories on purpose: with four
+    ranks the gradients of the first steps differ by 1.5e-7 (addition order), but B is then a few 1e-5 after
+    AdamW's sign-like first update, its bf16 rounding inside the LoRA GEMM flips for a few elements, and by the
+    third step the two free-running gradients differ by 1 % and AdamW's normalisation turns that into a 10 %
+    difference of single updates -- the sensitivity of this bf16 training step to one ulp, not of the exchange.
+
+    Every rank computes (b) redundantly from the same seeds.  Leaves the adapter as it found it."""
     import torch.distributed as dist
 
     from .training import AdamW, AdamWConfig, LRScheduler
@@ -229,53 +238,72 @@ def dp_check(torch, step, adapter, world, rank, B, S, vocab, device, steps=3):
     snapshot = [v.clone() for v in variables]
     sched = LRScheduler.warmup_cosine(5, 50, 1e-4, 1e-6)
     micro = {r: _host_batches(torch, steps, B, S, vocab, seed=777 + r) for r in range(world)}
-
-    def restore():
-        with torch.no_grad():
-            for v, s0 in zip(variables, snapshot):
-                v.copy_(s0)
-
-    # (1) data parallel
-    opt = AdamW(AdamWConfig(learning_rate=1e-4))
-    dp_losses = []
-    for s in range(steps):
-        ids, tg = micro[rank][s]
-        loss, grads = step.fb(ids.to(device), tg.to(device))
-        step.adamw(sched.get_lr(s), grads, opt=opt)
-        l = loss.detach().clone().double()
-        dist.all_reduce(l, op=dist.ReduceOp.SUM)       # every micro-batch keeps the same number of tokens
-        dp_losses.append(float(l) / world)
-    p_dp = [v.clone() for v in variables]
-    restore()
-    # (2) one rank's arithmetic: accumulate the micro-batches of all ranks, then one optimizer step
     model = step.model
     hook, done = model.layer_done_hook, model.backward_done_hook
-    model.layer_done_hook = model.backward_done_hook = None
-    step.exchange(False)
     opt = AdamW(AdamWConfig(learning_rate=1e-4))
-    acc_losses = []
+
+    def rel(xs, ys):
+        """largest |x - y| over the tensors, relative to the largest |y|"""
+        num = max(float((x - y).abs().max()) for x, y in zip(xs, ys))
+        return num / max(max(float(y.abs().max()) for y in ys), 1e-30)
+
+    def set_values(dst, src):
+        with torch.no_grad():
+            for d, s0 in zip(dst, src):
+                d.copy_(s0)
+
+    dp_losses, acc_losses, grad_diff, update_diff = [], [], [], []
     try:
         for s in range(steps):
+            lr = sched.get_lr(s)
+            # (a) data parallel
+            ids, tg = micro[rank][s]
+            loss, grads = step.fb(ids.to(device), tg.to(device))
+            g_dp = [g.clone() for g in grads]
+            l = loss.detach().clone().double()
+            dist.all_reduce(l, op=dist.ReduceOp.SUM)       # every micro-batch keeps the same number of tokens
+            dp_losses.append(float(l) / world)
+            # (b) one rank, the micro-batches of all ranks accumulated
+            model.layer_done_hook = model.backward_done_hook = None
+            step.exchange(False)
             tot = 0.0
             for r in range(world):
                 ids, tg = micro[r][s]
                 loss, grads = step.fb(ids.to(device), tg.to(device), accumulate=(r > 0), exchange=False)
                 tot += float(loss)
-            step.adamw(sched.get_lr(s), grads, opt=opt)
             acc_losses.append(tot / world)
+            model.layer_done_hook, model.backward_done_hook = hook, done
+            step.exchange(True)
+            grad_diff.append(rel(g_dp, grads))
+            # AdamW from the same parameters and moments with either gradient
+            before = [v.clone() for v in variables]
+            moments = {k: (m.clone(), v.clone()) for k, (m, v) in opt.state.items()}
+            count = opt.step_count
+            step.adamw(lr, grads, opt=opt)
+            upd_acc = [v - b0 for v, b0 in zip(variables, before)]
+            set_values(variables, before)
+            for k, (m, v) in list(opt.state.items()):
+                if k in moments:
+                    m.copy_(moments[k][0]), v.copy_(moments[k][1])
+                else:
+                    m.zero_(), v.zero_()
+            opt.step_count = count
+            step.adamw(lr, g_dp, opt=opt)
+            upd_dp = [v - b0 for v, b0 in zip(variables, before)]
+            update_diff.append(rel(upd_dp, upd_acc) if max(float(u.abs().max()) for u in upd_acc) > 0 else 0.0)
     finally:
         model.layer_done_hook, model.backward_done_hook = hook, done
         step.exchange(True)
+        set_values(variables, snapshot)
+        torch.cuda.synchronize()
     rel_loss = max(abs(a - b) / max(abs(b), 1e-30) for a, b in zip(dp_losses, acc_losses))
-    num = max(float(((a - s0) - (b - s0)).abs().max()) for a, b, s0 in zip(p_dp, variables, snapshot))
-    den = max(float((b - s0).abs().max()) for b, s0 in zip(variables, snapshot))
-    rel_param = max(float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30) for a, b in zip(p_dp, variables))
-    restore()
-    torch.cuda.synchronize()
-    out = {"steps": steps, "max_rel_loss_diff": rel_loss, "max_rel_update_diff": num / max(den, 1e-30),
-           "max_rel_param_diff": rel_param, "loss_dp": dp_losses, "loss_accumulated": acc_losses,
-           "tolerance": {"loss": 1e-5, "update": 2e-3}}
-    out["ok"] = bool(rel_loss <= 1e-5 and out["max_rel_update_diff"] <= 2e-3)
+    tol = {"loss": 1e-5, "grad": 1e-5, "update": 2e-4}
+    out = {"steps": steps, "max_rel_loss_diff": rel_loss, "max_rel_grad_diff": max(grad_diff),
+           "max_rel_update_diff": max(update_diff), "rel_grad_diff_by_step": grad_diff,
+           "rel_update_diff_by_step": update_diff, "loss_dp": dp_losses, "loss_accumulated": acc_losses,
+           "compared": "each step from the same parameters and optimizer state", "tolerance": tol}
+    out["ok"] = bool(rel_loss <= tol["loss"] and out["max_rel_grad_diff"] <= tol["grad"]
+                     and out["max_rel_update_diff"] <= tol["update"])
     return out
 
 
@@ -328,7 +356,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
     wl = WORKLOADS[args.workload]
     B, S = wl["batch"], wl["seq"]
     cfg, model, adapter, opt, sched = _build(torch, wl, device)
-    dp = DataParallelLoRA(model, world, comm=comm)
+    dp = DataParallelLoRA(model, world, comm=comm, n_buckets=getattr(args, "buckets", N_BUCKETS))
     use_engine = getattr(args, "step_impl", "engine") == "engine" and (world == 1 or comm is not None)
     step = _Step(torch, model, adapter, dp, world, comm, use_engine, B, S)
     check = None
