@@ -485,18 +485,22 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
         barrier()
         exchange_alone()
         alone_ms = _median_ms(torch, exchange_alone, 5)
-        exposed = None
+        exposed = rank_spread = None
+        with_ms = without_ms = -1e9
         if captured["fb_nocomm"] is not None:
             ids0, tg0 = dev_batches[0]
             barrier()
             with_ms = _median_ms(torch, lambda: captured["fb"](ids0, tg0), 5)
             barrier()
             without_ms = _median_ms(torch, lambda: captured["fb_nocomm"](ids0, tg0), 5)
-            exposed = with_ms - without_ms
-        t = torch.tensor([alone_ms, exposed if exposed is not None else -1e9], device=device, dtype=torch.float64)
+        # the exchange couples the ranks (every step ends with the slowest one), so compare the SLOWEST rank's step
+        # with and without it; a per-rank difference would read the spread between the GPUs as communication
+        t = torch.tensor([alone_ms, with_ms, without_ms, -without_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         alone_ms = float(t[0])
-        exposed = float(t[1]) if exposed is not None else None
+        if captured["fb_nocomm"] is not None:
+            exposed = float(t[1]) - float(t[2])
+            rank_spread = {"fastest_ms": -float(t[3]), "slowest_ms": float(t[2])}
         comm_info = {"backend": ("mcb_comm (NCCL through the C ABI, " + ("blocking" if comm_mode == "mcb-blocking" else "non-blocking") + ")")
                      if comm is not None else "torch.distributed nccl",
                      "nccl_version": comm.info()["nccl_version"] if comm is not None else None,
@@ -504,8 +508,9 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                      "overlapped": bool(comm is not None or captured["fb"] is None),
                      "in_graph": bool(graph_has_comm and captured["fb"] is not None),
                      "exposed_ms": exposed,
-                     "exposed_how": "step graph with the exchange minus the same graph without it (median of 5 replays each, max over ranks)"
-                     if exposed is not None else None,
+                     "exposed_how": "slowest rank's step graph with the exchange minus the slowest rank's same graph without it "
+                                    "(median of 5 replays each)" if exposed is not None else None,
+                     "step_without_exchange": rank_spread,
                      "allreduce_alone_ms": alone_ms,
                      "bus_GBps": 2.0 * (world - 1) / world * nbytes / (alone_ms * 1e-3) / 1e9 if alone_ms > 0 else None,
                      "rank_ms_per_step": {"min": min(per_rank), "max": max(per_rank)}}
