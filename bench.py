@@ -266,6 +266,51 @@ def micro_lora_qkv(torch, M, r, which, iters=20, warmup=5):
                          "traffic": None, "peak_source": pk["source"]}}
 
 
+def micro_mlp_down_bwd(torch, M, I, H, which, iters=20, warmup=5):
+    """Backward of the MLP's down projection (I -> H, no adapter) up to d gate / d up: `fused` = the SwiGLU backward in
+    the GEMM's epilogue (mcb_lora_linear_bwd_swiglu), `unfused` = mcb_lora_linear_bwd_ex + mcb_swiglu_bwd, `gemm` = the
+    input-gradient GEMM alone.  gate and up are updated in place, so later launches work on earlier results (the
+    timing does not depend on the values).  Algorithmic bytes: dy + W + gate, up read and written once each."""
+    from metal_candle_b200 import _lib, backend as B
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    nv = max(1, min(4, _variants(4 * M * I * 2)))
+    dys = [torch.randn(M, H, device=dev, generator=g).to(torch.bfloat16) for _ in range(nv)]
+    gates = [torch.randn(M, I, device=dev, generator=g).to(torch.bfloat16) for _ in range(nv)]
+    ups = [torch.randn(M, I, device=dev, generator=g).to(torch.bfloat16) for _ in range(nv)]
+    wt = (torch.randn(I, H, device=dev, generator=g) / math.sqrt(I)).to(torch.bfloat16)
+    dact = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+    lib = _lib.load()
+
+    def gemm(i):
+        B.lora_linear_backward(None, wt, None, None, 1.0, dys[i % nv], dx_out=dact)
+
+    def unfused(i):
+        gemm(i)
+        gt, up = gates[i % nv], ups[i % nv]
+        _lib.check(lib.mcb_swiglu_bwd(gt.data_ptr(), up.data_ptr(), dact.data_ptr(), gt.data_ptr(), up.data_ptr(), gt.numel(),
+                                      _lib.MCB_BF16, torch.cuda.current_stream().cuda_stream))
+
+    def fused(i):
+        B.lora_linear_backward_swiglu(None, wt, None, None, 1.0, dys[i % nv], gates[i % nv], ups[i % nv])
+
+    fn = {"gemm": gemm, "unfused": unfused, "fused": fused}[which]
+    med, mn = _time_kernel(torch, fn, nv, iters, warmup)
+    pk = measured_peaks()
+    fl = 2.0 * M * I * H
+    by = 2.0 * (M * H + I * H + (1 if which == "gemm" else 4) * M * I)
+    tf, gbs = fl / med / 1e9, by / med / 1e6
+    return {"metric": f"MLP down projection backward ({which})", "value": med * 1e3, "unit": "us", "ms": med, "ms_min": mn, "dtype": "bf16",
+            "higher_is_better": False, "tflops": tf, "algorithmic_GBps": gbs,
+            "config": {"workload": "mlp_down_bwd", "M": M, "I": I, "H": H, "pass": which, "input_sets": nv,
+                       "l2": "operands larger than L2"},
+            "roofline": {"bound": "hbm" if which != "gemm" else "tensor", "achieved": gbs if which != "gemm" else tf,
+                         "peak": pk["hbm_gbs"] if which != "gemm" else pk["bf16_tflops"], "unit": "GB/s" if which != "gemm" else "TFLOP/s",
+                         "frac": (gbs / pk["hbm_gbs"]) if which != "gemm" else tf / pk["bf16_tflops"], "traffic": None,
+                         "peak_source": pk["source"]}}
+
+
 def micro_attention(torch, nb, G, S, which, iters=20, warmup=5):
     """Fused causal grouped-query attention at one layer's shape (nb = batch * kv heads, G query heads per kv head,
     head_dim 64, bf16).  FLOP counted over the causal half only: forward 4*nb*G*S*S*64/2, backward 2.5x that."""
@@ -562,6 +607,9 @@ def run_micro(args):
                                     args.warmup_iters)), flush=True)
     elif args.micro == "lora_qkv":
         print(json.dumps(micro_lora_qkv(torch, args.M, args.r, args.which, args.iters, args.warmup_iters)), flush=True)
+    elif args.micro == "mlp_down_bwd":
+        which = args.which if args.which in ("fused", "unfused", "gemm") else "fused"
+        print(json.dumps(micro_mlp_down_bwd(torch, args.M, args.I, args.H, which, args.iters, args.warmup_iters)), flush=True)
     elif args.micro == "attention":
         print(json.dumps(micro_attention(torch, args.nb, args.G, args.S, args.which, args.iters, args.warmup_iters)),
               flush=True)
@@ -595,7 +643,9 @@ def main():
     ap.add_argument("--n", type=int, default=1 << 26)
     ap.add_argument("--tensors", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
-    ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both", "bwd_dx"])
+    ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both", "bwd_dx", "fused", "unfused", "gemm"])
+    ap.add_argument("--I", type=int, default=4864)
+    ap.add_argument("--H", type=int, default=896)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup-iters", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true")

@@ -156,6 +156,19 @@ int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float* A, const f
                            int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* mcb_lora_linear_bwd_ex for the down projection of a SwiGLU MLP (down(silu(gate) * up),
+ * src/models/transformer.rs:389-395), with the SwiGLU backward in the epilogue of the input-gradient product.  The input
+ * gradient d act [M,K] is never stored: gate and up [M,K] (the pre-activations the forward saved) are overwritten
+ * with  d gate = d act * up * silu'(gate)  and  d up = d act * silu(gate),  d act taken from the float32 accumulator.
+ * Saves one write and one read of [M,K] against mcb_lora_linear_bwd_ex followed by mcb_swiglu_bwd.  bf16, W as
+ * [in,out].  Runs where mcb_lora_linear_bwd_swiglu_supported returns 1 (host-only query: the product must run on CTA
+ * pairs); elsewhere MCB_ERR_UNSUPPORTED, and the caller uses the two calls. */
+int mcb_lora_linear_bwd_swiglu_supported(int64_t M, int64_t K, int64_t N, int64_t r, int dtype);
+int mcb_lora_linear_bwd_swiglu(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                               const void* h_save, void* gate, void* up, float* dA, float* dB, int accumulate,
+                               int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
 /* out[N,K] = W[N,K] + scale * (A B)^T: the adapter folded into a base weight stored [out, in]
  * (LoRAAdapter::merge_weights, src/training/adapter.rs:315-354).  A [K,r], B [r,N] float32; W, out `dtype`; out may be W. */
 int mcb_lora_merge_weights(const void* W, const float* A, const float* B, void* out, int64_t K, int64_t N, int64_t r,

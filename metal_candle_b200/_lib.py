@@ -94,6 +94,9 @@ SIGNATURES = {
                                       _vp, _sz, _vp]),
     "mcb_lora_linear_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
                                       _f32, _i32, _i32, _vp, _sz, _vp]),
+    "mcb_lora_linear_bwd_swiglu_supported": (_i32, [_i64, _i64, _i64, _i64, _i32]),
+    "mcb_lora_linear_bwd_swiglu": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
+                                          _f32, _i32, _i32, _vp, _sz, _vp]),
     "mcb_lora_merge_weights": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
     "mcb_lora_fused_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i32, _i32]),
     "mcb_lora_linear_fused_fwd": (_i32, [_vp, _vp, _vp, C.POINTER(LoraSegment), _i32, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32,

@@ -197,6 +197,42 @@ def lora_linear_backward(x, weight_t, lora_a, lora_b, scaling, dy, h_save=None, 
     return dx, grad_a, grad_b
 
 
+def lora_linear_backward_swiglu_supported(M: int, K: int, N: int, r: int, dtype=torch.bfloat16) -> bool:
+    """Whether `lora_linear_backward_swiglu` takes a down projection of K inputs, N outputs and rank r over M tokens."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(_lib.load().mcb_lora_linear_bwd_swiglu_supported(int(M), int(K), int(N), int(r), MCB_BF16))
+
+
+def lora_linear_backward_swiglu(x, weight_t, lora_a, lora_b, scaling, dy, gate, up, h_save=None, grad_a=None, grad_b=None,
+                                accumulate=False):
+    """Backward of the down projection of a SwiGLU MLP with the SwiGLU backward in the GEMM's epilogue: `gate` and
+    `up` [.., K] (the saved pre-activations) are overwritten with their gradients; the gradient of the activation
+    itself is never stored.  `weight_t` is the [in, out] copy of the frozen weight.  Returns (dA, dB)."""
+    N = dy.shape[-1]
+    K = weight_t.shape[0]
+    r = 0 if lora_a is None else lora_a.shape[1]
+    if r and x is None:
+        raise TrainingError("lora_linear_backward_swiglu: the layer input x is needed for the LoRA gradients")
+    _require_cuda(x, weight_t, lora_a, lora_b, dy, h_save, grad_a, grad_b, gate, up)
+    M = dy.numel() // N
+    for name, t in (("gate", gate), ("up", up)):
+        if t.numel() != M * K or t.dtype != dy.dtype or not t.is_contiguous():
+            raise TrainingError(f"lora_linear_backward_swiglu: {name} must be a contiguous [{M}, {K}] {dy.dtype} tensor")
+    lib = _lib_for(dy)
+    dt = _dtype_code(dy)
+    if r and grad_a is None:
+        grad_a = torch.empty(K, r, dtype=torch.float32, device=dy.device)
+        grad_b = torch.empty(r, N, dtype=torch.float32, device=dy.device)
+        accumulate = False
+    nws = lib.mcb_lora_workspace_bytes(M, K, N, r, dt)
+    ws = workspace(dy.device, nws)
+    _lib.check(lib.mcb_lora_linear_bwd_swiglu(_ptr(x), _ptr(weight_t), _ptr(lora_a), _ptr(lora_b), _ptr(dy), _ptr(h_save),
+                                           _ptr(gate), _ptr(up), _ptr(grad_a), _ptr(grad_b), int(bool(accumulate)), M, K, N, r,
+                                           float(scaling), dt, MCB_W_IN_OUT, _ptr(ws), ws.numel(), _stream()))
+    return grad_a, grad_b
+
+
 def _segment_table(segments, with_grads: bool):
     arr = (_lib.LoraSegment * len(segments))()
     for i, sg in enumerate(segments):

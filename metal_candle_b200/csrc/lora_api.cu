@@ -91,6 +91,35 @@ extern "C" int mcb_lora_linear_bwd_ex(const void* x, const void* W, const float*
   return dtype == MCB_F32 ? f32path::linear_bwd(a) : bf16path::linear_bwd(a, ds);
 }
 
+extern "C" int mcb_lora_linear_bwd_swiglu_supported(int64_t M, int64_t K, int64_t N, int64_t r, int dtype) {
+  return dtype == MCB_BF16 && bf16path::swiglu_bwd_supported(M, K, N, r) ? 1 : 0;
+}
+
+extern "C" int mcb_lora_linear_bwd_swiglu(const void* x, const void* W, const float* A, const float* B, const void* dy,
+                                          const void* h_save, void* gate, void* up, float* dA, float* dB, int accumulate,
+                                          int64_t M, int64_t K, int64_t N, int64_t r, float scale, int dtype, int w_layout,
+                                          void* workspace, size_t workspace_bytes, void* stream) {
+  MCB_NVTX_RANGE("mcb_lora_linear_bwd_swiglu");
+  if (!dy || !W || !gate || !up) return fail(MCB_ERR_NULL, "lora_linear_bwd_swiglu: dy, W, gate or up is null");
+  if (gate == up) return fail(MCB_ERR_SHAPE, "lora_linear_bwd_swiglu: gate and up are the same buffer");
+  if (r > 0 && (!A || !B)) return fail(MCB_ERR_NULL, "lora_linear_bwd_swiglu: rank %lld but A or B is null", (long long)r);
+  if (r > 0 && (dA || dB) && !x) return fail(MCB_ERR_NULL, "lora_linear_bwd_swiglu: dA/dB wanted but x is null");
+  if ((dA == nullptr) != (dB == nullptr)) return fail(MCB_ERR_NULL, "lora_linear_bwd_swiglu: pass both dA and dB, or neither");
+  if (int rc = check_dims("lora_linear_bwd_swiglu", M, K, N, r, dtype, false)) return rc;
+  if (dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_bwd_swiglu: bfloat16 only (use mcb_lora_linear_bwd_ex and mcb_swiglu_bwd)");
+  if (w_layout != MCB_W_IN_OUT) return fail(MCB_ERR_UNSUPPORTED, "lora_linear_bwd_swiglu: W must be [in,out] (MCB_W_IN_OUT)");
+  if (!aligned16(gate) || !aligned16(up)) return fail(MCB_ERR_ALIGN, "lora_linear_bwd_swiglu: 16-byte alignment");
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  LoraArgs a;
+  a.x = x; a.W = W; a.A = A; a.B = B; a.dy = dy; a.h_save = const_cast<void*>(h_save);
+  a.dx = gate; a.swiglu_up = up; a.dA = dA; a.dB = dB; a.accumulate = accumulate;
+  a.M = M; a.K = K; a.N = N; a.r = r; a.scale = scale; a.w_layout = w_layout;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return bf16path::linear_bwd(a, ds);
+}
+
 extern "C" size_t mcb_matmul_workspace_bytes(int64_t K, int64_t N, int dtype) {
   if (K <= 0 || N <= 0 || dtype != MCB_BF16) return 0;
   return static_cast<size_t>(K) * static_cast<size_t>(N) * 2;

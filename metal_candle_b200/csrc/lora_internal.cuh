@@ -17,6 +17,8 @@ struct LoraArgs {
   void* h_save = nullptr;      // [rp, h_pitch(M)] scale*(x A) transposed, optional
   const void* dy = nullptr;    // [M,N]
   void* dx = nullptr;          // [M,K]
+  void* swiglu_up = nullptr;   // backward, with dx: dx holds gate and this holds up [M,K]; both are replaced by the
+                               // SwiGLU backward of the input gradient, which itself is not stored
   float* dA = nullptr;         // [K,r]
   float* dB = nullptr;         // [r,N]
   int accumulate = 0;
@@ -77,11 +79,16 @@ struct GemmCall {
   // The launch directly before this call's GEMM on the same stream is the operand-pack kernel of this call (the
   // GEMM may then be launched as its programmatic dependent).
   bool after_pack = false;
+  // Y is the gate buffer of a SwiGLU and this its up buffer: the product is d act, and the epilogue replaces gate and
+  // up by d gate and d up instead of storing it (pair kernel only).
+  __nv_bfloat16* swiglu_up = nullptr;
 };
 size_t workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r);
 int delta_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_fwd(const LoraArgs& a, const DeviceState* ds);
 int linear_bwd(const LoraArgs& a, const DeviceState* ds);
+// Whether linear_bwd can run the SwiGLU backward in the epilogue of its input-gradient product (a.swiglu_up).
+bool swiglu_bwd_supported(int64_t M, int64_t K, int64_t N, int64_t r);
 // The same two passes for a fused projection with one adapter of rank a.r per segment (a.A / a.B / a.dA / a.dB unused).
 size_t fused_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t r, int segments);
 int linear_fused_fwd(const LoraArgs& a, const LoraSegments& sg, const DeviceState* ds);

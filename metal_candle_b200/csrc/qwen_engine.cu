@@ -309,9 +309,20 @@ int layer_backward(const mcb_qwen* q, const StepPlan& p, size_t li, const __nv_b
   const float eps = q->cfg.rms_norm_eps, theta = q->cfg.rope_theta;
   const int Hq = static_cast<int>(q->cfg.num_heads), Hk = static_cast<int>(q->cfg.num_kv_heads);
   // MLP
-  __nv_bfloat16* dact = p.t_MI[1];
-  QCHECK(lin_bwd(q, p, s.act, L.wt[kDown], L.ad[kDown], dh3, s.hd, nullptr, dact, accumulate, M, I, H, st));
-  QCHECK(mcb_swiglu_bwd(s.gate, s.up, dact, s.gate, s.up, M * I, MCB_BF16, st));   // in place: gate <- d gate, up <- d up
+  {
+    const Adapter& ad = L.ad[kDown];
+    const int r = ad.A ? q->rank : 0;
+    if (mcb_lora_linear_bwd_swiglu_supported(M, I, H, r, MCB_BF16)) {
+      // the SwiGLU backward runs in the epilogue of the input-gradient GEMM: gate <- d gate, up <- d up, no d act
+      QCHECK(mcb_lora_linear_bwd_swiglu(r ? s.act : nullptr, L.wt[kDown], ad.A, ad.B, dh3, r ? s.hd : nullptr, s.gate, s.up,
+                                        r ? ad.dA : nullptr, r ? ad.dB : nullptr, accumulate, M, I, H, r, q->scale, MCB_BF16,
+                                        MCB_W_IN_OUT, p.ws, p.ws_bytes, st));
+    } else {
+      __nv_bfloat16* dact = p.t_MI[1];
+      QCHECK(lin_bwd(q, p, s.act, L.wt[kDown], ad, dh3, s.hd, nullptr, dact, accumulate, M, I, H, st));
+      QCHECK(mcb_swiglu_bwd(s.gate, s.up, dact, s.gate, s.up, M * I, MCB_BF16, st));   // in place: gate <- d gate, up <- d up
+    }
+  }
   __nv_bfloat16 *dn2a = p.t_MH[1], *dn2 = p.t_MH[2];
   QCHECK(lin_bwd(q, p, s.n2, L.wt[kGate], L.ad[kGate], s.gate, s.hg, nullptr, dn2a, accumulate, M, H, I, st));
   QCHECK(lin_bwd(q, p, s.n2, L.wt[kUp], L.ad[kUp], s.up, s.hu, dn2a, dn2, accumulate, M, H, I, st));

@@ -806,9 +806,21 @@ int linear_fwd(const LoraArgs& a, const DeviceState* ds) {
   return launch_gemm(c, ds, a.stream);
 }
 
+bool swiglu_bwd_supported(int64_t M, int64_t K, int64_t N, int64_t r) {
+  if (M <= 0 || K <= 0 || N <= 0 || r < 0 || K % 8 != 0 || N % 8 != 0) return false;
+  GemmCall c;   // the input-gradient product: [M,N] . [K,N]^T, rank path over N
+  c.X = c.W = c.Y = reinterpret_cast<__nv_bfloat16*>(16);   // placeholders: only their presence is looked at
+  c.M = M; c.N = K; c.K = N;
+  c.rp = static_cast<int>(rank_padded(r));
+  return gemm2_eligible(c);
+}
+
 int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
   if (a.dx != nullptr && a.w_layout != MCB_W_IN_OUT)
     return fail(MCB_ERR_UNSUPPORTED, "lora_linear_bwd(bf16) needs W as [in,out] (MCB_W_IN_OUT); transpose it once with mcb_transpose_2d");
+  if (a.swiglu_up != nullptr && (a.dx == nullptr || a.residual != nullptr || !swiglu_bwd_supported(a.M, a.K, a.N, a.r)))
+    return fail(MCB_ERR_UNSUPPORTED, "lora_linear_bwd_swiglu: M=%lld K=%lld N=%lld r=%lld does not run on CTA pairs; use "
+                "mcb_lora_linear_bwd_ex and mcb_swiglu_bwd", (long long)a.M, (long long)a.K, (long long)a.N, (long long)a.r);
   if (int rc = check_ws(a, "lora_linear_bwd")) return rc;
   const int rp = static_cast<int>(rank_padded(a.r));
   const bool want_grads = a.r > 0 && (a.dA != nullptr || a.dB != nullptr);
@@ -829,6 +841,7 @@ int linear_bwd(const LoraArgs& a, const DeviceState* ds) {
     c.W = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.W) : nullptr;
     c.Y = static_cast<__nv_bfloat16*>(a.dx);
     c.R = a.dx != nullptr ? static_cast<const __nv_bfloat16*>(a.residual) : nullptr;
+    c.swiglu_up = static_cast<__nv_bfloat16*>(a.swiglu_up);
     c.M = a.M; c.N = a.K; c.K = a.N;
     if (a.r > 0) {
       c.after_pack = true;   // pack(a, w, 1) above is the launch directly before the GEMM

@@ -40,6 +40,7 @@ namespace {
 
 constexpr int BK2 = 64;
 constexpr int kThreads2 = 192;
+constexpr int kThreads2Wide = 320;  // SwiGLU-backward form: a second set of four epilogue warps
 constexpr int kMaxStages2 = 8;
 constexpr int kSmem2 = 227 * 1024 - 1024;
 constexpr int kEpiBufs = kEpiBufsMax;
@@ -49,9 +50,13 @@ struct Gemm2Params {
   int BN, stages, rp;
   int pdl_wait; // 1: launched as a programmatic dependent of the operand-pack kernel
   int swiglu;   // 1: the tile is [128 gate columns | 128 up columns]; the epilogue also writes silu(gate) * up
+                // 2: the product is d act of a SwiGLU; the epilogue turns it into d gate and d up (see U) and stores those
+  int epi_bufs; // staging buffers per epilogue warp (kEpiBufs; more in the SwiGLU-backward form)
+  int sw_pairs, sw_ahead;  // SwiGLU backward: buffer pairs per 32 rows, jobs loaded ahead
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;  // m tiles of 256 rows
   float scale;
   __nv_bfloat16* Y;
+  __nv_bfloat16* U;  // swiglu == 2: Y holds gate and U holds up [M,N] on entry, d gate and d up on return
   const __nv_bfloat16* bias;
   const __nv_bfloat16* R;
   __nv_bfloat16* H;  // [rp, h_pitch]: scale * X P^T transposed, or null
@@ -110,6 +115,21 @@ __host__ __device__ constexpr uint32_t make_idesc2(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 }
 
+// One element of the SwiGLU backward: d gate = d u s (1 + g (1 - s)), d up = d g s with s = sigmoid(g), in 12
+// instructions (the epilogue warps are bound by their instruction count): the two approximate special functions
+// flush denormals, so that the compiler adds no range handling around them; their relative error is about 2^-22.
+// g -> -inf gives s = 0 and both results 0; g -> +inf gives s = 1, d gate = d u, d up = d g.
+__device__ __forceinline__ void swiglu_bwd_elem(float d, float g, float u, float& dgate, float& dup) {
+  float e, s;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(1.0f + e));
+  const float t = d * s;
+  dup = t * g;
+  const float q = fmaf(-g, s, g);   // g (1 - s)
+  const float tu = t * u;
+  dgate = fmaf(tu, q, tu);
+}
+
 __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& mt, int& nt) {
   const int per_band = p.group_m * p.num_n_tiles;
   const int band = t / per_band;
@@ -120,11 +140,12 @@ __device__ __forceinline__ void tile_coords2(const Gemm2Params& p, int t, int& m
   mt = m_first + in % gm;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2Wide, 1)
 lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                   const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                   const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmU,
-                  const __grid_constant__ CUtensorMap tmAct, const Gemm2Params p) {
+                  const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmY64,
+                  const __grid_constant__ CUtensorMap tmU64, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -141,6 +162,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const uint32_t q_full0 = h_ready0 + 16;
   const uint32_t tmem_slot = q_full0 + 16;
   const uint32_t abort_addr = tmem_slot + 4;
+  const uint32_t gu_full0 = tmem_slot + 8;   // SwiGLU backward: 4 epilogue warps x 4 buffer pairs, "gate and up have landed"
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_addr - base));
 
@@ -148,11 +170,13 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int a = 0; a < 2; ++a) {
       mbar_init(d1_full0 + 8 * a, 1);
-      mbar_init(acc_empty0 + 8 * a, 8);
+      mbar_init(acc_empty0 + 8 * a, 8 * ((blockDim.x >> 5) > 6 ? 2 : 1));   // every epilogue warp of both CTAs
       mbar_init(d2_full0 + 8 * a, 1);
       mbar_init(h_ready0 + 8 * a, 8);
       mbar_init(q_full0 + 8 * a, 1);
     }
+    if (p.swiglu == 2)
+      for (int b = 0; b < 32; ++b) mbar_init(gu_full0 + 8 * b, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -282,12 +306,67 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       if (ok && pend_a >= 0) ok = finish_pending();
     }
   } else {
-    // ---------------- epilogue (warps 2..5, both CTAs): own 128 rows of the pair's tile ----------------
+    // ---------------- epilogue (warps 2 and up, both CTAs): own 128 rows of the pair's tile ----------------
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t epi_base = base + p.epi_off + static_cast<uint32_t>(quad) * (kEpiBufs * kEpiBufBytes);
+    const uint32_t epi_base = base + p.epi_off + static_cast<uint32_t>(quad * p.epi_bufs) * kEpiBufBytes;
     int sbuf = 0;
+    // SwiGLU backward (swiglu == 2), launched with four more warps: warps 2..5 lead, warps 6..9 help the leader of the
+    // same 32 rows (one warp per scheduler issues an instruction about every fourth cycle on this dependent
+    // arithmetic; two per scheduler hide each other's latencies).  The 64-column pieces of a quad's rows over all its
+    // tiles form one sequence of jobs.  Job j stages 32 rows x 64 columns of gate and of up (128-byte rows: half as
+    // many TMA row requests as 32-column boxes) in the buffer pair j % np by two TMA loads that the leader issues
+    // `ahead` jobs early; leader and helper each turn 32 of the 64 columns into d gate and d up in place, the helper
+    // reports on an mbarrier, and the leader sends the pair off with two TMA stores.  A piece with only 32 columns
+    // left in the tile (or the matrix) uses the 32-column boxes in the same buffers and the leader alone.
+    const bool helper = warp >= 6;
+    const int jw = 64, pair_bufs = 4;   // columns per job; 2-KB buffers per pair (gate 4 KB + up 4 KB)
+    const int cset = (p.BN + jw - 1) / jw;   // jobs per tile
+    const int np = p.sw_pairs, ahead = p.sw_ahead;
+    const int pending = min(2, np - ahead - 1);   // store groups that may still be reading their pair
+    const uint32_t gu_bar0 = gu_full0 + static_cast<uint32_t>(quad * np) * 8;
+    const uint32_t hb_bar0 = gu_full0 + static_cast<uint32_t>(16 + quad * np) * 8;   // per pair: "the helper's half is in place"
+    uint32_t gu_parity = 0, hb_parity = 0;   // bit s: parity of the next completion of pair s's barrier
+    // columns of piece c of a tile at column n0 that exist: 64, 32 (a lone half) or <= 0 (none)
+    auto piece_cols = [&](int n0_, int c) { return min(jw, min(p.BN - c, p.N - (n0_ + c))); };
+    // the load cursor (lane 0) runs `ahead` jobs in front of the consumer; both step through tiles, pieces and
+    // buffer pairs by increments (the tile coordinates, with their divisions, once per tile)
+    int pf_t = pair, pf_k = 0, pf_slot = 0, pf_row0 = 0, pf_n0 = 0;
+    auto pf_tile = [&]() {
+      if (pf_t >= p.num_tiles) return;
+      int mt2, nt2;
+      tile_coords2(p, pf_t, mt2, nt2);
+      pf_row0 = mt2 * 256 + static_cast<int>(rank) * 128 + quad * 32;
+      pf_n0 = nt2 * p.BN;
+    };
+    auto gu_issue_next = [&]() {
+      if (pf_t >= p.num_tiles) return;
+      const int c = pf_k * jw;
+      const int cols = piece_cols(pf_n0, c);
+      if (pf_row0 < p.M && cols > 0) {   // the consumer skips the same jobs
+        const uint32_t buf = epi_base + static_cast<uint32_t>(pair_bufs * pf_slot) * kEpiBufBytes;
+        const uint32_t half = static_cast<uint32_t>(pair_bufs >> 1) * kEpiBufBytes;
+        const uint32_t bar = gu_bar0 + 8 * pf_slot;
+        if (cols > 32) {
+          mbar_expect_tx(bar, 4 * kEpiBufBytes);   // a box clipped at the edges still counts in full
+          tma_load_2d(buf, &tmY64, bar, pf_n0 + c, pf_row0);
+          tma_load_2d(buf + half, &tmU64, bar, pf_n0 + c, pf_row0);
+        } else {
+          mbar_expect_tx(bar, 2 * kEpiBufBytes);
+          tma_load_2d(buf, &tmY, bar, pf_n0 + c, pf_row0);
+          tma_load_2d(buf + half, &tmU, bar, pf_n0 + c, pf_row0);
+        }
+      }
+      if (++pf_slot == np) pf_slot = 0;
+      if (++pf_k == cset) { pf_k = 0; pf_t += npairs; pf_tile(); }
+    };
+    if (p.swiglu == 2 && lane == 0 && !helper) {
+      if (p.pdl_wait) grid_dependency_wait();   // gate and up may come from the kernel before the operand pack
+      pf_tile();
+      for (int j = 0; j < ahead; ++j) gu_issue_next();
+    }
+    int sl = 0;   // the consumer's buffer pair
     bool ok = true;
     int i = 0;
     for (int t = pair; ok && t < p.num_tiles; t += npairs, ++i) {
@@ -298,7 +377,7 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const uint32_t u = static_cast<uint32_t>(i >> 1);
       const int64_t grow = static_cast<int64_t>(m0) + row_in_tile;
       const uint32_t d = tmem_base + lane_addr + a * 256;
-      if (p.rp > 0) {
+      if (p.rp > 0 && !helper) {
         ok = __all_sync(0xffffffffu, mbar_wait(d2_full0 + 8 * a, u & 1, abort_flag, 67, p.status));
         if (!ok) break;
         tcgen05_fence_after();
@@ -337,7 +416,69 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       ok = __all_sync(0xffffffffu, mbar_wait(d1_full0 + 8 * a, u & 1, abort_flag, 64, p.status));
       if (!ok) break;
       tcgen05_fence_after();
-      if (p.swiglu) {
+      if (p.swiglu == 2) {
+        // d gate = d act * up * silu'(gate), d up = d act * silu(gate), d act straight from the float32 accumulator
+        const bool rows_ok = m0 + quad * 32 < p.M;
+        for (int k = 0; k < cset; ++k) {
+          const int c = k * jw, gcol = n0 + c;
+          if (lane == 0 && !helper) {
+            bulk_wait_group_read_n(pending);   // the stores that last used the pair the next load goes into have read it
+            gu_issue_next();
+          }
+          const int cols = piece_cols(n0, c);
+          if (rows_ok && cols > 0) {
+            const bool wide = cols > 32;
+            const uint32_t buf = epi_base + static_cast<uint32_t>(pair_bufs * sl) * kEpiBufBytes;
+            const uint32_t half = static_cast<uint32_t>(pair_bufs >> 1) * kEpiBufBytes;
+            uint8_t* bg = gen_base + (buf - base);
+            uint8_t* bu = bg + half;
+            if (wide || !helper) {
+              const int h = helper ? 1 : 0, cc = c + 32 * h;
+              uint32_t v0[16], v1[16];
+              tmem_ld_x16(d + (cc < half_n ? cc : cc + half_r), v0);
+              tmem_ld_x16(d + (cc + 16 < half_n ? cc + 16 : cc + 16 + half_r), v1);
+              ok = __all_sync(0xffffffffu, mbar_wait(gu_bar0 + 8 * sl, (gu_parity >> sl) & 1u, abort_flag, 68, p.status));
+              if (!ok) break;
+              uint32_t gw[16], uw[16];
+              if (wide) { unstage_half128(bg, lane, h, gw); unstage_half128(bu, lane, h, uw); }
+              else { unstage_row(bg, lane, gw); unstage_row(bu, lane, uw); }
+              tmem_ld_wait();
+              uint32_t wg[16], wu[16];
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const float d0 = __uint_as_float(e < 8 ? v0[2 * e] : v1[2 * e - 16]);
+                const float d1 = __uint_as_float(e < 8 ? v0[2 * e + 1] : v1[2 * e - 15]);
+                float dg0, du0, dg1, du1;
+                swiglu_bwd_elem(d0, __uint_as_float(gw[e] << 16), __uint_as_float(uw[e] << 16), dg0, du0);
+                swiglu_bwd_elem(d1, __uint_as_float(gw[e] & 0xffff0000u), __uint_as_float(uw[e] & 0xffff0000u), dg1, du1);
+                wg[e] = pack_bf16(dg0, dg1);
+                wu[e] = pack_bf16(du0, du1);
+              }
+              if (wide) { stage_half128(bg, lane, h, wg); stage_half128(bu, lane, h, wu); }
+              else { stage_row(bg, lane, wg); stage_row(bu, lane, wu); }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (helper) {
+                if (lane == 0) mbar_arrive(hb_bar0 + 8 * sl);
+              } else {
+                if (wide) {
+                  ok = __all_sync(0xffffffffu, mbar_wait(hb_bar0 + 8 * sl, (hb_parity >> sl) & 1u, abort_flag, 69, p.status));
+                  if (!ok) break;
+                  hb_parity ^= 1u << sl;
+                }
+                if (lane == 0) {
+                  tma_store_2d(wide ? &tmY64 : &tmY, buf, gcol, m0 + quad * 32);
+                  tma_store_2d(wide ? &tmU64 : &tmU, buf + half, gcol, m0 + quad * 32);
+                }
+              }
+            }
+            gu_parity ^= 1u << sl;   // the pair's barrier has completed once more, whether or not this warp waited on it
+          }
+          if (lane == 0 && !helper) bulk_commit_group();   // one group per job, empty or not: the wait above counts groups
+          if (++sl == np) sl = 0;
+        }
+        if (!ok) break;
+      } else if (p.swiglu) {
         // SwiGLU tile: accumulator columns [0, 128) are gate features nt*128.., columns [128, 256) the same
         // features of up.  Per 32 features: gate, up and silu(gate)*up go out through three staging buffers.
         const int F = p.N >> 1;
@@ -493,6 +634,17 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.num_k_blocks = static_cast<int>((K + BK2 - 1) / BK2);
   p.group_m = p.num_m_tiles < 8 ? p.num_m_tiles : 8;
   p.Y = c.Y; p.bias = c.bias; p.R = c.R; p.H = c.H; p.h_pitch = c.h_pitch; p.status = ds->status_word;
+  p.epi_bufs = kEpiBufs;
+  bool helpers = false;   // launch the four helper epilogue warps of the SwiGLU-backward form
+  if (c.swiglu_up != nullptr) {
+    if (c.bias != nullptr || c.R != nullptr)
+      return fail(MCB_ERR_UNSUPPORTED, "pair GEMM: the SwiGLU-backward epilogue takes neither bias nor residual");
+    p.swiglu = 2;
+    p.U = c.swiglu_up;
+    p.sw_pairs = 3; p.sw_ahead = 1;
+    helpers = true;
+    p.epi_bufs = p.sw_pairs * 4;   // per 32 rows: pairs of two buffers of 32 rows x 128 bytes (gate, up)
+  }
   const uint32_t x_bytes = 128 * BK2 * 2, w_bytes = static_cast<uint32_t>(bn / 2) * BK2 * 2;
   const uint32_t p_bytes = static_cast<uint32_t>(c.rp / 2) * BK2 * 2;  // 8-row groups: a multiple of 1024
   p.w_off = x_bytes;
@@ -500,7 +652,7 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.stage_bytes = x_bytes + w_bytes + p_bytes;
   p.q_bytes = static_cast<uint32_t>(bn / 2) * c.rp * 2;
   p.hs_bytes = 128u * c.rp * 2;
-  const uint32_t epi_bytes = 4 * kEpiBufs * kEpiBufBytes;
+  const uint32_t epi_bytes = 4u * static_cast<uint32_t>(p.epi_bufs) * kEpiBufBytes;
   const uint32_t fixed = 2 * p.q_bytes + 2 * p.hs_bytes + epi_bytes + 512;
   int stages = static_cast<int>((kSmem2 - fixed) / p.stage_bytes);
   if (stages > kMaxStages2) stages = kMaxStages2;
@@ -510,8 +662,15 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   p.hs_off = p.q_off + 2 * p.q_bytes;
   p.epi_off = p.hs_off + 2 * p.hs_bytes;  // a multiple of 1024, as the swizzled staging rows need
   p.bar_off = p.epi_off + epi_bytes;
-  CUtensorMap tmX, tmW, tmP, tmQ, tmY;
+  CUtensorMap tmX, tmW, tmP, tmQ, tmY, tmU, tmY64, tmU64;
   if (int rc = make_map2(ds, &tmY, c.Y, N, M, 32, 32, 64, "Y (pair)")) return rc;
+  if (c.swiglu_up != nullptr) {
+    if (int rc = make_map2(ds, &tmU, c.swiglu_up, N, M, 32, 32, 64, "up (pair)")) return rc;
+    if (int rc = make_map2(ds, &tmY64, c.Y, N, M, 64, 32, 128, "gate, 64 columns (pair)")) return rc;
+    if (int rc = make_map2(ds, &tmU64, c.swiglu_up, N, M, 64, 32, 128, "up, 64 columns (pair)")) return rc;
+  } else {
+    tmU = tmY; tmY64 = tmY; tmU64 = tmY;
+  }
   if (int rc = make_map2(ds, &tmX, c.X, K, M, BK2, 128, 128, "X (pair)")) return rc;
   if (int rc = make_map2(ds, &tmW, c.W, K, N, BK2, bn / 2, 128, "W (pair)")) return rc;
   if (c.rp > 0) {
@@ -524,13 +683,13 @@ int launch_gemm2(const GemmCall& c, const DeviceState* ds, cudaStream_t st) {
   if (prof) {
     const double m = static_cast<double>(M), n = static_cast<double>(N), k = static_cast<double>(K);
     profile_begin(c.rp > 0 ? kProfGemmLora : kProfGemm, 2.0 * m * n * k + 2.0 * m * c.r_true * (k + n),
-                  2.0 * (m * k + n * k + m * n) + 2.0 * c.rp * (k + n), st);
+                  2.0 * (m * k + n * k + (c.swiglu_up != nullptr ? 4.0 : 1.0) * m * n) + 2.0 * c.rp * (k + n), st);
   }
   const bool pdl = c.after_pack && c.rp > 0 && !prof && option(MCB_OPT_PDL) != 0;
   p.pdl_wait = pdl ? 1 : 0;
   {
-    const cudaError_t le = launch_kernel(lora_gemm2_kernel, dim3(2 * pairs), dim3(kThreads2), kSmem2 + 1024, st, pdl, tmX, tmW, tmP,
-                                         tmQ, tmY, tmY, tmY, p);
+    const cudaError_t le = launch_kernel(lora_gemm2_kernel, dim3(2 * pairs), dim3(helpers ? kThreads2Wide : kThreads2), kSmem2 + 1024, st, pdl, tmX, tmW, tmP,
+                                         tmQ, tmY, tmU, tmY, tmY64, tmU64, p);
     if (le != cudaSuccess) return cuda_fail(le, "lora_gemm2_kernel launch");
   }
   if (prof) profile_end(st);
@@ -548,6 +707,7 @@ int launch_gemm2_swiglu(const __nv_bfloat16* X, const __nv_bfloat16* Wgu, __nv_b
   memset(&p, 0, sizeof(p));
   p.M = static_cast<int>(M); p.N = static_cast<int>(2 * F); p.K = static_cast<int>(K);
   p.swiglu = 1;
+  p.epi_bufs = kEpiBufs;
   p.BN = 256;
   p.num_m_tiles = static_cast<int>((M + 255) / 256);
   p.num_n_tiles = static_cast<int>(F / 128);
@@ -580,7 +740,7 @@ int launch_gemm2_swiglu(const __nv_bfloat16* X, const __nv_bfloat16* Wgu, __nv_b
     const double m = static_cast<double>(M), n = static_cast<double>(2 * F), k = static_cast<double>(K);
     profile_begin(kProfGemm, 2.0 * m * n * k, 2.0 * (m * k + n * k + 1.5 * m * n), st);
   }
-  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmX, tmX, tmG, tmU, tmA, p);
+  lora_gemm2_kernel<<<2 * pairs, kThreads2, kSmem2 + 1024, st>>>(tmX, tmW, tmX, tmX, tmG, tmU, tmA, tmG, tmG, p);
   if (prof) profile_end(st);
   MCB_CHECK_LAUNCH("lora_gemm2_kernel");
   return MCB_OK;

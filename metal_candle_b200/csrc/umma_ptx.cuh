@@ -214,7 +214,33 @@ __device__ __forceinline__ void stage_row(uint8_t* buf, int lane, const uint32_t
   for (int j = 0; j < 4; ++j)
     *reinterpret_cast<uint4*>(bg + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
 }
-
+// The reverse: this lane's 64-byte row of a staging buffer that a 64-byte-swizzled TMA load has filled.
+__device__ __forceinline__ void unstage_row(const uint8_t* buf, int lane, uint32_t (&w)[16]) {
+  const uint8_t* bg = buf + lane * 64;
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 v = *reinterpret_cast<const uint4*>(bg + ((j ^ sw) << 4));
+    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+  }
+}// Staging buffers with 128-byte rows (64 bf16 columns, CU_TENSOR_MAP_SWIZZLE_128B): 16-byte piece q of row r sits at
+// piece q ^ (r & 7).  This lane's row, half `h` (columns 32h .. 32h + 31).
+__device__ __forceinline__ void stage_half128(uint8_t* buf, int lane, int h, const uint32_t (&w)[16]) {
+  uint8_t* bg = buf + lane * 128;
+  const int sw = lane & 7;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(bg + (((4 * h + j) ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+__device__ __forceinline__ void unstage_half128(const uint8_t* buf, int lane, int h, uint32_t (&w)[16]) {
+  const uint8_t* bg = buf + lane * 128;
+  const int sw = lane & 7;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 v = *reinterpret_cast<const uint4*>(bg + (((4 * h + j) ^ sw) << 4));
+    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+  }
+}
 
 //   MN-major, 128-byte swizzle: the M (or N) index is the contiguous one.  An atom is 64 elements of M
 //   (128 bytes) by 8 rows of K; LBO = byte step between 64-element M atoms, SBO = byte step between

@@ -139,6 +139,8 @@ class Qwen:
         # q, k and v projections of a layer as one fused linear with a block-diagonal rank path (bf16, adapters of
         # equal rank): the normed input is read once and the three input gradients are summed in one pass
         self.fuse_qkv = True
+        # SwiGLU backward inside the epilogue of the down projection's input-gradient GEMM (where the library takes it)
+        self.fuse_swiglu_bwd = True
         self.layer_done_hook = None  # called as hook(layer_idx) when a layer's LoRA gradients are final
         self.backward_done_hook = None  # called once at the end of forward_backward (joins side-stream work)
 
@@ -447,11 +449,21 @@ class Qwen:
         c = self.config
         key = lambda m: f"layers.{idx}.{m}"
         # MLP
-        dact = self._lin_bwd(sv["act"], L["down_proj"], dh3, sv["hd"], key("down_proj"), accumulate)
         gt, up = sv["gate"], sv["up"]
-        _lib.check(self.lib.mcb_swiglu_bwd(_ptr(gt), _ptr(up), _ptr(dact), _ptr(gt), _ptr(up), gt.numel(), self.dt,
-                                           _stream()))  # in place: gate <- d gate, up <- d up
-        del dact
+        down = L["down_proj"]
+        A, Bm, s = down.ab()
+        r = 0 if A is None else A.shape[1]
+        if self.fuse_swiglu_bwd and backend.lora_linear_backward_swiglu_supported(B * S, c.intermediate_size, c.hidden_size, r,
+                                                                                   self.dtype):
+            # the SwiGLU backward runs in the epilogue of the down projection's input-gradient GEMM
+            ga, gb = self._grad_slices[key("down_proj")] if A is not None else (None, None)
+            backend.lora_linear_backward_swiglu(sv["act"], down.weight_t, A, Bm, s, dh3, gt, up, h_save=sv["hd"], grad_a=ga,
+                                                grad_b=gb, accumulate=accumulate)
+        else:
+            dact = self._lin_bwd(sv["act"], down, dh3, sv["hd"], key("down_proj"), accumulate)
+            _lib.check(self.lib.mcb_swiglu_bwd(_ptr(gt), _ptr(up), _ptr(dact), _ptr(gt), _ptr(up), gt.numel(), self.dt,
+                                               _stream()))  # in place: gate <- d gate, up <- d up
+            del dact
         dn2 = self._lin_bwd(sv["n2"], L["gate_proj"], gt, sv["hg"], key("gate_proj"), accumulate)
         dn2 = self._lin_bwd(sv["n2"], L["up_proj"], up, sv["hu"], key("up_proj"), accumulate, dx_residual=dn2)
         # gradient through the norm plus the one along the residual connection, added inside the norm's kernel

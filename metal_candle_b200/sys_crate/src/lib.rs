@@ -136,6 +136,8 @@ extern "C" {
     pub fn mcb_lora_linear_bwd(x: *const c_void, W: *const c_void, A: *const f32, B: *const f32, dy: *const c_void, h_save: *const c_void, dx: *mut c_void, dA: *mut f32, dB: *mut f32, accumulate: c_int, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, w_layout: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_linear_fwd_ex(x: *const c_void, W: *const c_void, bias: *const c_void, A: *const f32, B: *const f32, residual: *const c_void, y: *mut c_void, h_save: *mut c_void, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, w_layout: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_linear_bwd_ex(x: *const c_void, W: *const c_void, A: *const f32, B: *const f32, dy: *const c_void, h_save: *const c_void, dx_residual: *const c_void, dx: *mut c_void, dA: *mut f32, dB: *mut f32, accumulate: c_int, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, w_layout: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
+    pub fn mcb_lora_linear_bwd_swiglu_supported(M: i64, K: i64, N: i64, r: i64, dtype: c_int) -> c_int;
+    pub fn mcb_lora_linear_bwd_swiglu(x: *const c_void, W: *const c_void, A: *const f32, B: *const f32, dy: *const c_void, h_save: *const c_void, gate: *mut c_void, up: *mut c_void, dA: *mut f32, dB: *mut f32, accumulate: c_int, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, w_layout: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_merge_weights(W: *const c_void, A: *const f32, B: *const f32, out: *mut c_void, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_lora_fused_workspace_bytes(M: i64, K: i64, N: i64, r: i64, n_segments: c_int, dtype: c_int) -> usize;
     pub fn mcb_lora_linear_fused_fwd(x: *const c_void, W: *const c_void, bias: *const c_void, segments: *const mcb_lora_segment, n_segments: c_int, y: *mut c_void, h_save: *mut c_void, M: i64, K: i64, N: i64, r: i64, scale: f32, dtype: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;

@@ -18,20 +18,23 @@ def _i32(a, dev):
     return torch.from_numpy(np.where(a == R.IGNORE_INDEX, -1, a)).to(dev).to(torch.int32).contiguous()
 
 
-@pytest.mark.parametrize("which", ["all", "qv"])
-def test_engine_matches_python_step_and_oracle(cuda_device, which):
-    from metal_candle_b200 import _lib
+@pytest.mark.parametrize("which,nb", [("all", 3), ("qv", 3), ("qv", 8)])
+def test_engine_matches_python_step_and_oracle(cuda_device, which, nb):
+    """nb = 8 gives 1024 tokens: from there the MLP's plain linears run on CTA pairs and the SwiGLU backward moves
+    into the epilogue of the down projection's input-gradient GEMM."""
+    from metal_candle_b200 import _lib, backend
     from metal_candle_b200.engine import QwenEngine
     from metal_candle_b200.training import TargetModule
 
     targets = all_targets() if which == "all" else [TargetModule.QProj, TargetModule.VProj]
     cfg, model, adapter = build(cuda_device, torch.bfloat16, targets, cfg=fused_attention_config())
-    ids, tg = batch(41, 3, 128, cfg.vocab_size)
+    ids, tg = batch(41, nb, 128, cfg.vocab_size)
     tg[2, 10:30] = R.IGNORE_INDEX
     ids_d, tg_d = _i32(ids, cuda_device), _i32(tg, cuda_device)
+    assert backend.lora_linear_backward_swiglu_supported(nb * 128, cfg.intermediate_size, cfg.hidden_size, 0) == (nb == 8)
     loss_p, g_p = model.forward_backward(ids_d, tg_d)
     loss_p, g_p = loss_p.clone(), [g.clone() for g in g_p]
-    eng = QwenEngine(model, 3, 128)
+    eng = QwenEngine(model, nb, 128)
     for chunk in (8192, 100):            # one chunk, and several ragged ones
         eng.set_ce_chunk(chunk)
         for g in model._grad_views:

@@ -243,6 +243,63 @@ def test_linear_swiglu_forward(cuda_device, M, K, F):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("M,I,H,r", [(1300, 4864, 896, 0), (2048, 512, 1536, 16), (1100, 360, 896, 0), (4096, 1000, 2048, 8)])
+def test_down_projection_backward_with_swiglu_epilogue(cuda_device, M, I, H, r):
+    """mcb_lora_linear_bwd_swiglu: the input gradient of the MLP's down projection (I -> H, with and without an
+    adapter) goes through the SwiGLU backward inside the GEMM's epilogue and replaces gate and up; against the CPU
+    oracle's linear backward followed by the SwiGLU derivative.  Ragged rows and a width that is not a multiple of
+    the 32-column store chunk included."""
+    from metal_candle_b200 import _lib, backend as B
+
+    dev, scale = cuda_device, 2.0
+    c = S.lora_linear_case(77, M, I, H, max(r, 1))
+    act64, W, dy = S.bf16_round(c["x"]), S.bf16_round(c["W"]), S.bf16_round(c["dy"])
+    gate64 = S.bf16_round(S.normal(78, "gate", (M, I), 0.0, 1.5))
+    up64 = S.bf16_round(S.normal(78, "up", (M, I)))
+    A = S.bf16_round(c["A"]) if r else np.zeros((I, 1))
+    Bm = S.bf16_round(c["B"]) if r else np.zeros((1, H))
+    want_dact, want_dA, want_dB = R.lora_linear_backward(act64, W, A, Bm, scale if r else 0.0, dy)
+    sg = 1.0 / (1.0 + np.exp(-gate64))
+    want_dgate = want_dact * up64 * sg * (1.0 + gate64 * (1.0 - sg))
+    want_dup = want_dact * gate64 * sg
+    assert B.lora_linear_backward_swiglu_supported(M, I, H, r)
+    gate, up = dev_t(gate64, torch.bfloat16, dev), dev_t(up64, torch.bfloat16, dev)
+    wt = B.transpose_2d(dev_t(W, torch.bfloat16, dev))
+    dyd = dev_t(dy, torch.bfloat16, dev)
+    if r:
+        actd = dev_t(act64, torch.bfloat16, dev)
+        Ad, Bd = dev_t(c["A"], torch.float32, dev), dev_t(c["B"], torch.float32, dev)
+        _, h = B.lora_linear_forward(actd, dev_t(W, torch.bfloat16, dev), None, Ad, Bd, scale)
+        dA, dB = B.lora_linear_backward_swiglu(actd, wt, Ad, Bd, scale, dyd, gate, up, h_save=h)
+        assert R.max_abs_normalised(back(dA), want_dA) <= 2e-2
+        assert R.max_abs_normalised(back(dB), want_dB) <= 2e-2
+    else:
+        B.lora_linear_backward_swiglu(None, wt, None, None, 1.0, dyd, gate, up)
+    assert R.max_abs_normalised(back(gate), want_dgate) <= 2e-2, "d gate"
+    assert R.max_abs_normalised(back(up), want_dup) <= 2e-2, "d up"
+    # the unfused pair of calls gives the same result up to the bf16 rounding of the stored activation gradient
+    g2, u2 = dev_t(gate64, torch.bfloat16, dev), dev_t(up64, torch.bfloat16, dev)
+    dact, _, _ = B.lora_linear_backward(actd if r else None, wt, Ad if r else None, Bd if r else None, scale if r else 1.0, dyd,
+                                        h_save=h if r else None)
+    _lib.check(_lib.load().mcb_swiglu_bwd(g2.data_ptr(), u2.data_ptr(), dact.data_ptr(), g2.data_ptr(), u2.data_ptr(), g2.numel(),
+                                          _lib.MCB_BF16, torch.cuda.current_stream().cuda_stream))
+    assert R.max_abs_normalised(back(gate), back(g2)) <= 1e-2 and R.max_abs_normalised(back(up), back(u2)) <= 1e-2
+    assert _lib.device_status() == 0
+
+
+def test_swiglu_epilogue_refuses_what_the_pair_kernel_does_not_take(cuda_device):
+    from metal_candle_b200 import _lib, backend as B
+
+    dev = cuda_device
+    assert not B.lora_linear_backward_swiglu_supported(300, 4864, 896, 0)        # too few rows for CTA pairs
+    assert not B.lora_linear_backward_swiglu_supported(4096, 4864, 896, 16)      # rank path with a short reduction
+    assert not B.lora_linear_backward_swiglu_supported(4096, 4864, 896, 0, torch.float32)
+    g = torch.zeros(300, 256, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(_lib.McbError, match="does not run on CTA pairs"):
+        B.lora_linear_backward_swiglu(None, torch.zeros(256, 128, device=dev, dtype=torch.bfloat16), None, None, 1.0,
+                                      torch.zeros(300, 128, device=dev, dtype=torch.bfloat16), g, torch.zeros_like(g))
+
+
 def test_lora_rejects_bad_arguments(cuda_device):
     from metal_candle_b200 import backend as B
 
