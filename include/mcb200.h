@@ -99,7 +99,9 @@ int64_t mcb_launch_count(void);
  * bracketed by CUDA events on its own stream and tagged with its algorithmic work; mcb_profile_summary
  * synchronises the device, sums the finished records of one kind (0 = GEMM launches without a rank path: the frozen
  * projections; 1 = the stand-alone LoRA weight-gradient kernel; 2 = GEMM launches with a rank path: the fused LoRA
- * linear forward and backward, the backward including its dA/dB tail phase) and forgets them.  No counterpart in the reference. */
+ * linear forward and backward, the backward including its dA/dB tail phase; 3 = GEMM launches whose epilogue runs the
+ * SwiGLU backward, mcb_lora_linear_bwd_swiglu: bound by the gate / up traffic, not by the tensor pipe) and forgets them.
+ * No counterpart in the reference. */
 int mcb_profile_enable(int on);
 int mcb_profile_summary(int kind, int64_t* launches, double* total_ms, double* total_flops, double* total_bytes);
 

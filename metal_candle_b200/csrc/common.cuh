@@ -29,7 +29,7 @@ DeviceState* current_device_state();  // null (and error set) when mcb_init was 
 
 // Optional per-kernel timing (mcb_profile_enable): CUDA events recorded on the launching stream right
 // around one kernel launch, tagged with the launch's algorithmic work.
-enum ProfileKind { kProfGemm = 0, kProfGrad = 1, kProfGemmLora = 2, kProfKinds = 3 };
+enum ProfileKind { kProfGemm = 0, kProfGrad = 1, kProfGemmLora = 2, kProfGemmSwigluBwd = 3, kProfKinds = 4 };
 bool profile_on();
 void profile_begin(int kind, double flops, double bytes, cudaStream_t st);
 void profile_end(cudaStream_t st);

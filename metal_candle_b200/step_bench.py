@@ -408,6 +408,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
     plain = _lib.profile_summary(0)
     grad = _lib.profile_summary(1)
     lora = _lib.profile_summary(2)
+    swig = _lib.profile_summary(3)
     capture_note = None
     if not getattr(args, "no_graph", False):
         hooks = (model.layer_done_hook, model.backward_done_hook)
@@ -546,7 +547,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
             ach = g_fl / g_ms / 1e9 if g_ms > 0 else 0.0
             return {"launches": n_l, "ms_per_step": g_ms, "flop_per_step": g_fl, "achieved": ach, "frac": ach / peak}
 
-        both_ms, both_fl = plain[1] + lora[1], plain[2] + lora[2]
+        both_ms, both_fl = plain[1] + lora[1] + swig[1], plain[2] + lora[2] + swig[2]
         achieved = both_fl / both_ms / 1e9 if both_ms > 0 else 0.0
         line = {
             "metric": "LoRA fwd+bwd tokens/s, Qwen2.5-0.5B shape", "value": tokens / (ms / 1e3), "unit": "tokens/s",
@@ -576,11 +577,17 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                          "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
                          "measured_in": "per-launch CUDA events in the last eager warm-up step of this run"
                                         + (" (the timed steps replay a CUDA graph)" if used_graph else ""),
-                         "launches": plain[0] + lora[0], "kernel_ms_per_step": both_ms,
+                         "launches": plain[0] + lora[0] + swig[0], "kernel_ms_per_step": both_ms,
                          "share_of_step": both_ms / (ms / args.steps) if ms > 0 else None,
                          "classes": {"lora": dict(klass(lora), what="launches with a rank path: the fused LoRA linear forward and "
                                                   "backward of the adapted projections (dA/dB tail phase included when on)"),
-                                     "plain": dict(klass(plain), what="frozen projections without an adapter (MLP, lm_head, ...)")},
+                                     "plain": dict(klass(plain), what="frozen projections without an adapter (MLP, lm_head, ...)"),
+                                     "plain_swiglu_bwd": dict(klass(swig), achieved_GBps=swig[3] / swig[1] / 1e6 if swig[1] > 0 else None,
+                                                              hbm_peak_GBps=pk["hbm_gbs"],
+                                                              what="input-gradient GEMM of the MLP down projection with the SwiGLU "
+                                                              "backward in its epilogue (reads and rewrites gate and up: bound by "
+                                                              "that traffic, not by the tensor pipe; replaces a GEMM launch and an "
+                                                              "element-wise kernel)")},
                          "lora_grad_kernel": {"launches": grad[0], "ms_per_step": grad[1],
                                               "achieved_GBps": grad[3] / grad[1] / 1e6 if grad[1] > 0 else None,
                                               "hbm_peak_GBps": pk["hbm_gbs"]}},
