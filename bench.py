@@ -311,6 +311,35 @@ def micro_mlp_down_bwd(torch, M, I, H, which, iters=20, warmup=5):
                          "peak_source": pk["source"]}}
 
 
+def micro_cross_entropy(torch, rows, V, iters=10, warmup=3):
+    """One chunk of the loss stage: mcb_cross_entropy_chunk over [rows, V] bf16 logits, the gradient written in place
+    (so later launches read earlier gradients: the timing does not depend on the values).  Algorithmic bytes: the
+    logits read once and the gradient written once."""
+    from metal_candle_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0x5EED)
+    nv = max(1, min(3, _variants(rows * V * 2)))
+    logits = [torch.randn(rows, V, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(nv)]
+    targets = torch.randint(0, V, (rows,), device=dev, generator=g, dtype=torch.int32)
+    nll = torch.empty(rows, device=dev, dtype=torch.float32)
+    count = torch.full((1,), rows, device=dev, dtype=torch.int32)
+    lib = _lib.load()
+
+    def fn(i):
+        _lib.check(lib.mcb_cross_entropy_chunk(logits[i % nv].data_ptr(), targets.data_ptr(), nll.data_ptr(), count.data_ptr(),
+                                               rows, V, 1, _lib.MCB_BF16, torch.cuda.current_stream().cuda_stream))
+
+    med, mn = _time_kernel(torch, fn, nv, iters, warmup)
+    pk = measured_peaks()
+    by = 4.0 * rows * V
+    gbs = by / med / 1e6
+    return {"metric": "cross-entropy forward+backward, one chunk", "value": gbs, "unit": "GB/s", "ms": med, "ms_min": mn, "dtype": "bf16",
+            "config": {"workload": "cross_entropy_chunk", "rows": rows, "V": V, "input_sets": nv, "l2": "logits larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                         "traffic": None, "peak_source": pk["source"]}}
+
+
 def micro_attention(torch, nb, G, S, which, iters=20, warmup=5):
     """Fused causal grouped-query attention at one layer's shape (nb = batch * kv heads, G query heads per kv head,
     head_dim 64, bf16).  FLOP counted over the causal half only: forward 4*nb*G*S*S*64/2, backward 2.5x that."""
@@ -610,6 +639,8 @@ def run_micro(args):
     elif args.micro == "mlp_down_bwd":
         which = args.which if args.which in ("fused", "unfused", "gemm") else "fused"
         print(json.dumps(micro_mlp_down_bwd(torch, args.M, args.I, args.H, which, args.iters, args.warmup_iters)), flush=True)
+    elif args.micro == "cross_entropy":
+        print(json.dumps(micro_cross_entropy(torch, min(args.rows, 8192), args.V, args.iters, args.warmup_iters)), flush=True)
     elif args.micro == "attention":
         print(json.dumps(micro_attention(torch, args.nb, args.G, args.S, args.which, args.iters, args.warmup_iters)),
               flush=True)
@@ -644,6 +675,7 @@ def main():
     ap.add_argument("--tensors", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--pass", dest="which", default="both", choices=["fwd", "bwd", "both", "bwd_dx", "fused", "unfused", "gemm"])
+    ap.add_argument("--V", type=int, default=151936)
     ap.add_argument("--I", type=int, default=4864)
     ap.add_argument("--H", type=int, default=896)
     ap.add_argument("--iters", type=int, default=20)
