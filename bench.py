@@ -594,6 +594,15 @@ def kernel_numbers(torch):
     lora["q/k/v fused (896 -> 896+128+128) r16 M=32768 fwd+bwd"] = {"TFLOPs": round(r["value"], 1), "frac": round(r["roofline"]["frac"], 3),
                                                                     "ms": round(r["ms"], 4), "bound": "tensor"}
     out["lora_linear"] = lora
+    frame = {}
+    for which in ("fused", "unfused", "gemm"):
+        r = micro_mlp_down_bwd(torch, 32768, 4864, 896, which, 10, 3)
+        frame[f"MLP down projection backward to d gate / d up, {which} (M=32768, 4864 -> 896)"] = {
+            "us": round(r["value"], 1), "algorithmic_GBps": round(r["algorithmic_GBps"]), "TFLOPs": round(r["tflops"])}
+    r = micro_cross_entropy(torch, 8192, 151936, 10, 3)
+    frame["cross-entropy forward+backward, 8192 x 151936"] = {"ms": round(r["ms"], 3), "GBps": round(r["value"]),
+                                                            "frac": round(r["roofline"]["frac"], 3)}
+    out["frame"] = frame
     return out
 
 

@@ -115,19 +115,24 @@ __host__ __device__ constexpr uint32_t make_idesc2(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 }
 
-// One element of the SwiGLU backward: d gate = d u s (1 + g (1 - s)), d up = d g s with s = sigmoid(g), in 12
-// instructions (the epilogue warps are bound by their instruction count): the two approximate special functions
-// flush denormals, so that the compiler adds no range handling around them; their relative error is about 2^-22.
+// Two neighbouring elements of the SwiGLU backward: d gate = d u s (1 + g (1 - s)), d up = d g s with s = sigmoid(g).
+// The epilogue warps are bound by their instruction count, so: the two approximate special functions flush
+// denormals (the compiler then adds no range handling around them; relative error about 2^-22), products are shared
+// between the two results, and the multiplies and adds run as packed pairs (one instruction for two elements).
 // g -> -inf gives s = 0 and both results 0; g -> +inf gives s = 1, d gate = d u, d up = d g.
-__device__ __forceinline__ void swiglu_bwd_elem(float d, float g, float u, float& dgate, float& dup) {
-  float e, s;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(1.0f + e));
-  const float t = d * s;
-  dup = t * g;
-  const float q = fmaf(-g, s, g);   // g (1 - s)
-  const float tu = t * u;
-  dgate = fmaf(tu, q, tu);
+__device__ __forceinline__ void swiglu_bwd_pair(float2 d, float2 g, float2 u, float2& dgate, float2& dup) {
+  const float2 a = __fmul2_rn(g, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  float2 e, s;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(a.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(a.y));
+  e = __fadd2_rn(e, make_float2(1.0f, 1.0f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s.x) : "f"(e.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s.y) : "f"(e.y));
+  const float2 t = __fmul2_rn(d, s);
+  dup = __fmul2_rn(t, g);
+  const float2 q = __ffma2_rn(make_float2(-g.x, -g.y), s, g);   // g (1 - s)
+  const float2 tu = __fmul2_rn(t, u);
+  dgate = __ffma2_rn(tu, q, tu);
 }
 
 // silu(g) * u with the same two flushing special functions (5 instructions)
@@ -454,13 +459,13 @@ lora_gemm2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               uint32_t wg[16], wu[16];
 #pragma unroll
               for (int e = 0; e < 16; ++e) {
-                const float d0 = __uint_as_float(e < 8 ? v0[2 * e] : v1[2 * e - 16]);
-                const float d1 = __uint_as_float(e < 8 ? v0[2 * e + 1] : v1[2 * e - 15]);
-                float dg0, du0, dg1, du1;
-                swiglu_bwd_elem(d0, __uint_as_float(gw[e] << 16), __uint_as_float(uw[e] << 16), dg0, du0);
-                swiglu_bwd_elem(d1, __uint_as_float(gw[e] & 0xffff0000u), __uint_as_float(uw[e] & 0xffff0000u), dg1, du1);
-                wg[e] = pack_bf16(dg0, dg1);
-                wu[e] = pack_bf16(du0, du1);
+                const float2 dd = make_float2(__uint_as_float(e < 8 ? v0[2 * e] : v1[2 * e - 16]),
+                                              __uint_as_float(e < 8 ? v0[2 * e + 1] : v1[2 * e - 15]));
+                float2 dg, du;
+                swiglu_bwd_pair(dd, make_float2(__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xffff0000u)),
+                                make_float2(__uint_as_float(uw[e] << 16), __uint_as_float(uw[e] & 0xffff0000u)), dg, du);
+                wg[e] = pack_bf16(dg.x, dg.y);
+                wu[e] = pack_bf16(du.x, du.y);
               }
               if (wide) { stage_half128(bg, lane, h, wg); stage_half128(bu, lane, h, wu); }
               else { stage_row(bg, lane, wg); stage_row(bu, lane, wu); }
