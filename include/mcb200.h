@@ -392,6 +392,13 @@ int mcb_rope_relayout(const void* src, void* dst, int64_t B, int64_t S, int64_t 
  * the source) or of the fused gradient buffer (inverse: the destination). */
 int mcb_rope_relayout_ex(const void* src, void* dst, int64_t B, int64_t S, int64_t H, int64_t d, float theta, int rotate,
                          int inverse, int64_t token_pitch, int64_t col_offset, int dtype, void* stream);
+/* The three mcb_rope_relayout_ex calls that split a fused q/k/v projection's output (inverse = 0) or assemble the fused
+ * gradient buffer (inverse = 1), as one launch: the sines and cosines of a position are computed once for the query
+ * and the key heads, and the value heads are only re-laid out (Attention::forward, src/models/transformer.rs:241-257).
+ * fused: token rows `token_pitch` elements apart (0 = (Hq + 2 Hk) * d) holding Hq query heads, then Hk key heads, then
+ * Hk value heads; q [B,Hq,S,d], k and v [B,Hk,S,d].  Results equal those of the three calls bit for bit. */
+int mcb_rope_relayout_qkv(void* fused, void* q, void* k, void* v, int64_t B, int64_t S, int64_t Hq, int64_t Hk, int64_t d,
+                          float theta, int inverse, int64_t token_pitch, int dtype, void* stream);
 /* out = silu(gate) * up and its reverse (MLP::forward, src/models/transformer.rs:389-395). */
 int mcb_swiglu_fwd(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
 int mcb_swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup, int64_t n,

@@ -130,6 +130,7 @@ SIGNATURES = {
                                            _i64, _i32, _vp, _sz, _vp]),
     "mcb_embedding_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "mcb_rope_relayout": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _vp]),
+    "mcb_rope_relayout_qkv": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _i32, _i64, _i32, _vp]),
     "mcb_rope_relayout_ex": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _i32, _i64, _i64, _i32, _vp]),
     "mcb_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "mcb_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp]),

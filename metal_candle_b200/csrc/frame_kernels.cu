@@ -82,6 +82,65 @@ __global__ void rope_relayout_kernel(const T* __restrict__ src, T* __restrict__ 
 }
 
 // Scalar variant for head sizes whose half is not a multiple of the vector width.
+// The same for the query, key and value heads of a fused q/k/v row in one launch: the sines and cosines of a
+// (position, chunk) are computed once and used for the rotated segments (q and k); v is only re-laid out.
+template <typename T>
+struct RopeSegment {
+  T* head_major;    // [B, H, S, d]
+  int H;
+  int64_t offset;   // first column of the segment's heads in a token row
+  int rotate;
+};
+template <typename T>
+__global__ void rope_relayout_qkv_kernel(T* __restrict__ fused, RopeSegment<T> s0, RopeSegment<T> s1, RopeSegment<T> s2, int B, int S,
+                                         int d, float theta, int inverse, int64_t pitch) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  const int half = d / 2;
+  const int chunks = half / N;
+  const int64_t total = static_cast<int64_t>(B) * S * chunks;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % chunks);
+    const int64_t bs = idx / chunks;
+    const int s = static_cast<int>(bs % S);
+    const int b = static_cast<int>(bs / S);
+    float cs[N], sn[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int i = c * N + j;
+      const float inv_freq = 1.0f / powf(theta, static_cast<float>(2 * i) / static_cast<float>(d));
+      sincosf(static_cast<float>(s) * inv_freq, &sn[j], &cs[j]);
+      if (inverse) sn[j] = -sn[j];
+    }
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+      const RopeSegment<T>& sg = g == 0 ? s0 : g == 1 ? s1 : s2;
+      for (int h = 0; h < sg.H; ++h) {
+        const int64_t tok = (static_cast<int64_t>(b) * S + s) * pitch + sg.offset + static_cast<int64_t>(h) * d;
+        const int64_t hm = ((static_cast<int64_t>(b) * sg.H + h) * S + s) * d;
+        const T* in = inverse ? sg.head_major + hm : fused + tok;
+        T* out = inverse ? fused + tok : sg.head_major + hm;
+        V a, bb;
+        a.raw = *reinterpret_cast<const decltype(a.raw)*>(in + c * N);
+        bb.raw = *reinterpret_cast<const decltype(bb.raw)*>(in + half + c * N);
+        if (sg.rotate) {
+          float x1[N], x2[N], o1[N], o2[N];
+          a.to_float(x1); bb.to_float(x2);
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            o1[j] = x1[j] * cs[j] - x2[j] * sn[j];
+            o2[j] = x1[j] * sn[j] + x2[j] * cs[j];
+          }
+          a.from_float(o1); bb.from_float(o2);
+        }
+        *reinterpret_cast<decltype(a.raw)*>(out + c * N) = a.raw;
+        *reinterpret_cast<decltype(bb.raw)*>(out + half + c * N) = bb.raw;
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void rope_relayout_scalar_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int S, int H, int d,
                                             float theta, int rotate, int inverse, int64_t pitch, int64_t offset) {
@@ -422,6 +481,44 @@ extern "C" int mcb_embedding_fwd(const int32_t* ids, const void* table, void* ou
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MCB_DTYPE_SWITCH(dtype, (embedding_fwd_kernel<T><<<(unsigned)M, 128, 0, st>>>(ids, (const T*)table, (T*)out, M, (int)H, (int)vocab)));
   MCB_CHECK_LAUNCH("embedding_fwd");
+  return MCB_OK;
+}
+
+extern "C" int mcb_rope_relayout_qkv(void* fused, void* q, void* k, void* v, int64_t B, int64_t S, int64_t Hq, int64_t Hk, int64_t d,
+                                     float theta, int inverse, int64_t token_pitch, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_rope_relayout_qkv");
+  if (!fused || !q || !k || !v) return fail(MCB_ERR_NULL, "rope_relayout_qkv: null pointer");
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hk <= 0 || d <= 0 || d % 2 != 0)
+    return fail(MCB_ERR_SHAPE, "rope_relayout_qkv: bad shape (head_dim must be even)");
+  const int64_t width = (Hq + 2 * Hk) * d;
+  if (token_pitch == 0) token_pitch = width;
+  if (token_pitch < width)
+    return fail(MCB_ERR_SHAPE, "rope_relayout_qkv: %lld + 2 x %lld heads of %lld do not fit a row of %lld", (long long)Hq, (long long)Hk,
+                (long long)d, (long long)token_pitch);
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  const int64_t half = d / 2;
+  const int vec_n = dtype == MCB_F32 ? 4 : 8;
+  if (dtype != MCB_F32 && dtype != MCB_BF16) return fail(MCB_ERR_UNSUPPORTED, "rope_relayout_qkv: dtype %d", dtype);
+  if (!(half % vec_n == 0 && aligned16(fused) && aligned16(q) && aligned16(k) && aligned16(v) && token_pitch % vec_n == 0)) {
+    // shapes the vector kernel does not take: the three single calls (same arithmetic)
+    const void* src[3] = {inverse ? q : fused, inverse ? k : fused, inverse ? v : fused};
+    void* dst[3] = {inverse ? fused : q, inverse ? fused : k, inverse ? fused : v};
+    const int64_t H[3] = {Hq, Hk, Hk}, off[3] = {0, Hq * d, (Hq + Hk) * d};
+    for (int g = 0; g < 3; ++g)
+      if (int rc = mcb_rope_relayout_ex(src[g], dst[g], B, S, H[g], d, theta, g < 2 ? 1 : 0, inverse, token_pitch, off[g], dtype, stream))
+        return rc;
+    return MCB_OK;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(B * S * (half / vec_n), 128, ds->sm_count);
+  MCB_DTYPE_SWITCH(dtype, ({
+    RopeSegment<T> s0{static_cast<T*>(q), static_cast<int>(Hq), 0, 1};
+    RopeSegment<T> s1{static_cast<T*>(k), static_cast<int>(Hk), Hq * d, 1};
+    RopeSegment<T> s2{static_cast<T*>(v), static_cast<int>(Hk), (Hq + Hk) * d, 0};
+    rope_relayout_qkv_kernel<T><<<grid, 128, 0, st>>>(static_cast<T*>(fused), s0, s1, s2, (int)B, (int)S, (int)d, theta, inverse, token_pitch);
+  }));
+  MCB_CHECK_LAUNCH("rope_relayout_qkv");
   return MCB_OK;
 }
 

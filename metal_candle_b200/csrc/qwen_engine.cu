@@ -279,9 +279,7 @@ int layer_forward(const mcb_qwen* q, const StepPlan& p, size_t li, const __nv_bf
   else
     QCHECK(mcb_lora_linear_fwd_ex(s.n1, L.wqkv, L.bqkv, nullptr, nullptr, nullptr, p.qkv, nullptr, M, H, W3, 0, 1.0f, MCB_BF16,
                                   MCB_W_OUT_IN, p.ws, p.ws_bytes, st));
-  QCHECK(mcb_rope_relayout_ex(p.qkv, s.Qr, B, S, Hq, q->d, theta, 1, 0, W3, 0, MCB_BF16, st));
-  QCHECK(mcb_rope_relayout_ex(p.qkv, s.Kr, B, S, Hk, q->d, theta, 1, 0, W3, H, MCB_BF16, st));
-  QCHECK(mcb_rope_relayout_ex(p.qkv, s.Vr, B, S, Hk, q->d, theta, 0, 0, W3, H + KV, MCB_BF16, st));
+  QCHECK(mcb_rope_relayout_qkv(p.qkv, s.Qr, s.Kr, s.Vr, B, S, Hq, Hk, q->d, theta, 0, W3, MCB_BF16, st));
   const float sc = 1.0f / sqrtf(static_cast<float>(q->d));
   QCHECK(mcb_attention_causal_fwd_ex(s.Qr, s.Kr, s.Vr, s.o, s.lse, B * Hk, q->G, S, q->d, sc, MCB_BF16, Hk, 1, p.attn_ws, p.attn_ws_bytes,
                                      st));
@@ -335,9 +333,7 @@ int layer_backward(const mcb_qwen* q, const StepPlan& p, size_t li, const __nv_b
   QCHECK(mcb_attention_causal_bwd_ex(s.Qr, s.Kr, s.Vr, s.o, d_o, s.lse, p.dQ, p.dK, p.dV, B * Hk, q->G, S, q->d, sc, MCB_BF16, Hk, 1,
                                      p.attn_ws, p.attn_ws_bytes, st));
   __nv_bfloat16* dqkv = p.qkv;
-  QCHECK(mcb_rope_relayout_ex(p.dQ, dqkv, B, S, Hq, q->d, theta, 1, 1, W3, 0, MCB_BF16, st));
-  QCHECK(mcb_rope_relayout_ex(p.dK, dqkv, B, S, Hk, q->d, theta, 1, 1, W3, H, MCB_BF16, st));
-  QCHECK(mcb_rope_relayout_ex(p.dV, dqkv, B, S, Hk, q->d, theta, 0, 1, W3, H + KV, MCB_BF16, st));
+  QCHECK(mcb_rope_relayout_qkv(dqkv, p.dQ, p.dK, p.dV, B, S, Hq, Hk, q->d, theta, 1, W3, MCB_BF16, st));
   __nv_bfloat16* dn1 = p.t_MH[2];
   mcb_lora_segment segs[3];
   const int nseg = qkv_segments(q, L, segs);

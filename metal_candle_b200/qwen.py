@@ -218,6 +218,20 @@ class Qwen:
                                                  int(rotate), int(inverse), int(pitch), int(offset), self.dt, _stream()))
         return out
 
+    def _rope_qkv(self, fused, heads_major, B: int, S: int, pitch: int):
+        """Rotary embedding + head relayout of the q, k and v column blocks of a fused buffer in one launch.
+        `heads_major` None: fused -> (Q, K rotated, V) as [B, heads, S, d]; a (dQ, dK, dV) triple: the reverse
+        pass into `fused`."""
+        c = self.config
+        d, Hq, Hk = c.head_dim, c.num_attention_heads, c.num_key_value_heads
+        inverse = heads_major is not None
+        if not inverse:
+            heads_major = tuple(torch.empty((B, h, S, d), dtype=fused.dtype, device=fused.device) for h in (Hq, Hk, Hk))
+        q, k, v = heads_major
+        _lib.check(self.lib.mcb_rope_relayout_qkv(_ptr(fused), _ptr(q), _ptr(k), _ptr(v), B, S, Hq, Hk, d, float(c.rope_theta),
+                                                  int(inverse), int(pitch), self.dt, _stream()))
+        return heads_major
+
     def _qkv_fused(self, L):
         """The q, k and v projections as one linear (they read the same normed input): the stacked weight [q;k;v]
         in both majors, the stacked bias, and one segment per adapted projection; or None when this does not
@@ -311,9 +325,7 @@ class Qwen:
             segs = [dict(A=l.lora.lora_a, B=l.lora.lora_b, offset=o) for l, o in zip(fq["lins"], fq["offsets"]) if l.lora is not None]
             qkv, hqkv = backend.lora_linear_fused_forward(n1, fq["w"], fq["bias"], segs, fq["scale"], save_hidden=save)
             W3, o = fq["width"], fq["offsets"]
-            Qr = self._rope(qkv, c.num_attention_heads, B, S, True, False, pitch=W3, offset=o[0])
-            Kr = self._rope(qkv, c.num_key_value_heads, B, S, True, False, pitch=W3, offset=o[1])
-            Vr = self._rope(qkv, c.num_key_value_heads, B, S, False, False, pitch=W3, offset=o[2])
+            Qr, Kr, Vr = self._rope_qkv(qkv, None, B, S, W3)
             del qkv
             hq = hk = hv = None
         else:
@@ -480,9 +492,7 @@ class Qwen:
         if fq is not None:
             W3, o = fq["width"], fq["offsets"]
             dqkv = torch.empty(B * S, W3, dtype=self.dtype, device=self.device)
-            self._rope(dQ, c.num_attention_heads, B, S, True, True, pitch=W3, offset=o[0], out=dqkv)
-            self._rope(dK, c.num_key_value_heads, B, S, True, True, pitch=W3, offset=o[1], out=dqkv)
-            self._rope(dV, c.num_key_value_heads, B, S, False, True, pitch=W3, offset=o[2], out=dqkv)
+            self._rope_qkv(dqkv, (dQ, dK, dV), B, S, W3)
             del dQ, dK, dV, dO
             segs = []
             for l, off, m in zip(fq["lins"], fq["offsets"], ("q_proj", "k_proj", "v_proj")):

@@ -175,6 +175,7 @@ extern "C" {
     pub fn mcb_embedding_fwd(ids: *const i32, table: *const c_void, out: *mut c_void, M: i64, H: i64, vocab: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_rope_relayout(src: *const c_void, dst: *mut c_void, B: i64, S: i64, H: i64, d: i64, theta: f32, rotate: c_int, inverse: c_int, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_rope_relayout_ex(src: *const c_void, dst: *mut c_void, B: i64, S: i64, H: i64, d: i64, theta: f32, rotate: c_int, inverse: c_int, token_pitch: i64, col_offset: i64, dtype: c_int, stream: *mut c_void) -> c_int;
+    pub fn mcb_rope_relayout_qkv(fused: *mut c_void, q: *mut c_void, k: *mut c_void, v: *mut c_void, B: i64, S: i64, Hq: i64, Hk: i64, d: i64, theta: f32, inverse: c_int, token_pitch: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_swiglu_fwd(gate: *const c_void, up: *const c_void, out: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_swiglu_bwd(gate: *const c_void, up: *const c_void, dout: *const c_void, dgate: *mut c_void, dup: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_add(a: *const c_void, b: *const c_void, out: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;

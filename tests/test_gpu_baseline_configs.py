@@ -437,3 +437,62 @@ def test_checkpoint_round_trip_with_a_real_adapter(cuda_device, tmp_path):
     tensors, _ = CK.load_file(p)
     assert {"layers.0.q_proj.lora_a", "layers.1.v_proj.lora_b"} <= set(tensors)
     assert tensors["layers.0.v_proj.lora_b"].shape == (4, 32)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# rotary embedding + head relayout, called directly
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("B,Sq,Hq,Hk,d,pad", [(2, 256, 14, 2, 64, 0), (1, 100, 4, 2, 64, 16), (2, 33, 3, 1, 6, 0)])
+def test_rope_relayout_entry_points(cuda_device, dtype, tol, B, Sq, Hq, Hk, d, pad):
+    """mcb_rope_relayout_ex per projection and mcb_rope_relayout_qkv for the three at once, on the q / k / v column
+    blocks of a fused row (the 0.5B model's 14 + 2 + 2 heads of 64; a padded row; a head size the vector kernel does
+    not take): against the oracle's rotary tables (src/models/transformer.rs:47-120) and [B,S,H,d] -> [B,H,S,d]
+    transpose, forward and reverse; the merged call must equal the three single calls bit for bit."""
+    from metal_candle_b200 import _lib
+
+    lib, dev, theta = _lib.init(0), cuda_device, 1.0e6
+    code = _lib.MCB_F32 if dtype == torch.float32 else _lib.MCB_BF16
+    st = torch.cuda.current_stream().cuda_stream
+    width = (Hq + 2 * Hk) * d
+    pitch = width + pad
+    x = S.normal(9, "qkv", (B * Sq, pitch))
+    if dtype == torch.bfloat16:
+        x = S.bf16_round(x)
+    xd = torch.from_numpy(x).to(dev).to(dtype).contiguous()
+    sin, cos = QO._rope_tables(d, Sq, theta, torch.float64)
+    heads, offs, rot = (Hq, Hk, Hk), (0, Hq * d, (Hq + Hk) * d), (1, 1, 0)
+    want = []
+    for H, off, r in zip(heads, offs, rot):
+        blk = torch.from_numpy(x[:, off:off + H * d]).double().reshape(B, Sq, H, d)
+        if r:
+            blk = QO._apply_rope(blk, sin, cos)
+        want.append(blk.permute(0, 2, 1, 3).contiguous().numpy())
+    single = [torch.empty(B, H, Sq, d, device=dev, dtype=dtype) for H in heads]
+    for out, H, off, r in zip(single, heads, offs, rot):
+        _lib.check(lib.mcb_rope_relayout_ex(xd.data_ptr(), out.data_ptr(), B, Sq, H, d, theta, r, 0, pitch, off, code, st))
+    merged = [torch.empty_like(t) for t in single]
+    _lib.check(lib.mcb_rope_relayout_qkv(xd.data_ptr(), *(t.data_ptr() for t in merged), B, Sq, Hq, Hk, d, theta, 0, pitch, code, st))
+    for got, one, w in zip(merged, single, want):
+        assert torch.equal(got, one)
+        assert R.max_abs_normalised(got.float().cpu().numpy().astype(np.float64), w) <= tol
+    # the reverse pass: gradients in [B,H,S,d] back into the fused row with the transposed rotation
+    g = [S.normal(10 + i, "g", (B, H, Sq, d)) for i, H in enumerate(heads)]
+    if dtype == torch.bfloat16:
+        g = [S.bf16_round(a) for a in g]
+    gd = [torch.from_numpy(a).to(dev).to(dtype).contiguous() for a in g]
+    back_single = torch.zeros(B * Sq, pitch, device=dev, dtype=dtype)
+    for t, H, off, r in zip(gd, heads, offs, rot):
+        _lib.check(lib.mcb_rope_relayout_ex(t.data_ptr(), back_single.data_ptr(), B, Sq, H, d, theta, r, 1, pitch, off, code, st))
+    back_merged = torch.zeros_like(back_single)
+    _lib.check(lib.mcb_rope_relayout_qkv(back_merged.data_ptr(), *(t.data_ptr() for t in gd), B, Sq, Hq, Hk, d, theta, 1, pitch, code, st))
+    assert torch.equal(back_merged, back_single)
+    got = back_merged.float().cpu().numpy().astype(np.float64)
+    for a, H, off, r in zip(g, heads, offs, rot):
+        blk = torch.from_numpy(a).double().permute(0, 2, 1, 3)           # [B,S,H,d]
+        if r:
+            blk = QO._apply_rope(blk, -sin, cos)                          # the transpose of a rotation is the rotation by -angle
+        assert R.max_abs_normalised(got[:, off:off + H * d], blk.reshape(B * Sq, H * d).numpy()) <= tol
+    if pad:
+        assert float(back_merged[:, width:].abs().max()) == 0.0           # the padding columns are not touched
+    assert _lib.device_status() == 0
