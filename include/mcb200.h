@@ -474,8 +474,12 @@ int mcb_qwen_create(mcb_qwen** out, const mcb_qwen_config* cfg, const mcb_qwen_w
  * finished its backward, and joins the side stream before it returns.  comm = null switches it off. */
 int mcb_qwen_set_exchange(mcb_qwen* q, mcb_comm* comm, void* side_stream, float* grad_flat, const int64_t* bucket_lo,
                           const int64_t* bucket_hi, const int* bucket_first_layer, int n_buckets);
-/* Tokens per chunk of the lm_head + cross-entropy stage (default 8192; see mcb_cross_entropy_chunk). */
+/* Tokens per chunk of the lm_head + cross-entropy stage (see mcb_cross_entropy_chunk); 0 (the default) lets
+ * mcb_ce_chunk_tokens choose.  The results do not depend on it. */
 int mcb_qwen_set_ce_chunk(mcb_qwen* q, int64_t tokens);
+/* The chunk size (4096 .. 12288 tokens) for which the lm_head backward GEMM of `tokens` rows and `hidden` columns fills
+ * whole waves of CTA pairs best; host-only (assumes 148 SMs before mcb_init). */
+int64_t mcb_ce_chunk_tokens(int64_t tokens, int64_t hidden);
 /* ids, targets: int32 [batch, seq] on the device.  loss_out: device float[2] = {mean, sum} of the token losses. */
 int mcb_qwen_forward_backward(mcb_qwen* q, const int32_t* ids, const int32_t* targets, int64_t batch, int64_t seq,
                               int accumulate, float* loss_out, void* stream);

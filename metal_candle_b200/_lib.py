@@ -143,6 +143,7 @@ SIGNATURES = {
     "mcb_qwen_create": (_i32, [C.POINTER(_vp), C.POINTER(QwenConfig), C.POINTER(QwenWeights), C.POINTER(QwenAdapterEntry), _i32, _i32,
                                _f32, _vp, _sz, _vp]),
     "mcb_qwen_set_exchange": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int), _i32]),
+    "mcb_ce_chunk_tokens": (_i64, [_i64, _i64]),
     "mcb_qwen_set_ce_chunk": (_i32, [_vp, _i64]),
     "mcb_qwen_forward_backward": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp]),
     "mcb_qwen_adamw_step": (_i32, [_vp, _f32, _f32, _f32, _f32, _f32, _f32, _vp]),

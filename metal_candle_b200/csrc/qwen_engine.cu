@@ -79,7 +79,7 @@ struct mcb_qwen {
   std::vector<mcb_qwen_adapter_entry> order;   // adapters in the caller's order (AdamW visits them so)
   uint8_t* arena = nullptr;
   size_t arena_bytes = 0, persistent_bytes = 0;
-  int64_t ce_chunk = 8192;
+  int64_t ce_chunk = 0;   // tokens per lm_head + loss chunk; 0: mcb_ce_chunk_tokens picks it
   int64_t adamw_steps = 0;                      // the shared counter: one tick per tensor update
   // gradient exchange (optional)
   mcb_comm* comm = nullptr;
@@ -226,7 +226,8 @@ void plan_step(const mcb_qwen* q, Bump& b, int64_t M, int64_t B, int64_t S, Step
   p->dQ = b.take_n<__nv_bfloat16>(M * H);
   p->dK = b.take_n<__nv_bfloat16>(M * KV);
   p->dV = b.take_n<__nv_bfloat16>(M * KV);
-  const int64_t chunk = q->ce_chunk < M ? q->ce_chunk : M;
+  const int64_t want = q->ce_chunk > 0 ? q->ce_chunk : mcb_ce_chunk_tokens(M, H);
+  const int64_t chunk = want < M ? want : M;
   p->logits = b.take_n<__nv_bfloat16>(static_cast<size_t>(chunk) * q->V);
 }
 
@@ -449,9 +450,29 @@ extern "C" int mcb_qwen_set_exchange(mcb_qwen* q, mcb_comm* comm, void* side_str
   return MCB_OK;
 }
 
+// The lm_head backward is a GEMM of `tokens` rows by `hidden` columns over a very long reduction (the vocabulary):
+// few tiles (256 tokens x up to 256 columns each), every one as long as the whole vocabulary, so what decides its
+// time is how many WAVES of tiles the CTA pairs need.  Among the chunk sizes of 4096..12288 tokens (multiples of
+// 256) this returns the one with the fewest waves over all `tokens` (the smallest of those): 9472 for 32768 tokens
+// of width 896 on 148 SMs (37 x 4 = 148 tiles = two full waves; 8192 gives 128 tiles, a wave and three quarters).
+extern "C" int64_t mcb_ce_chunk_tokens(int64_t tokens, int64_t hidden) {
+  if (tokens <= 0 || hidden <= 0) return 0;
+  const DeviceState* ds = current_device_state();
+  const int64_t pairs = (ds ? ds->sm_count : 148) / 2;
+  const int64_t nt = (hidden + 255) / 256;
+  auto waves = [&](int64_t rows) { return rows <= 0 ? 0 : (((rows + 255) / 256) * nt + pairs - 1) / pairs; };
+  if (tokens <= 4096) return tokens;
+  int64_t best = 8192, best_waves = -1;
+  for (int64_t c = 4096; c <= 12288; c += 256) {
+    const int64_t w = (tokens / c) * waves(c) + waves(tokens % c);
+    if (best_waves < 0 || w < best_waves) { best = c; best_waves = w; }
+  }
+  return best;
+}
+
 extern "C" int mcb_qwen_set_ce_chunk(mcb_qwen* q, int64_t tokens) {
   if (!q) return fail(MCB_ERR_NULL, "mcb_qwen_set_ce_chunk: null engine");
-  if (tokens <= 0) return fail(MCB_ERR_SHAPE, "mcb_qwen_set_ce_chunk: %lld tokens", (long long)tokens);
+  if (tokens < 0) return fail(MCB_ERR_SHAPE, "mcb_qwen_set_ce_chunk: %lld tokens", (long long)tokens);
   q->ce_chunk = tokens;
   return MCB_OK;
 }
@@ -481,7 +502,8 @@ extern "C" int mcb_qwen_forward_backward(mcb_qwen* q, const int32_t* ids, const 
   QCHECK(mcb_rmsnorm_fwd(p.h_final, q->final_norm, p.nf, nullptr, M, H, q->cfg.rms_norm_eps, MCB_BF16, st));
   // lm_head, loss and lm_head backward, a chunk of tokens at a time
   QCHECK(mcb_cross_entropy_count(targets, q->count, M, V, st));
-  const int64_t chunk = q->ce_chunk < M ? q->ce_chunk : M;
+  const int64_t want = q->ce_chunk > 0 ? q->ce_chunk : mcb_ce_chunk_tokens(M, H);
+  const int64_t chunk = want < M ? want : M;
   for (int64_t c0 = 0; c0 < M; c0 += chunk) {
     const int64_t rows = (M - c0 < chunk) ? M - c0 : chunk;
     QCHECK(mcb_lora_linear_fwd_ex(p.nf + c0 * H, q->lm_head, nullptr, nullptr, nullptr, nullptr, p.logits, nullptr, rows, H, V, 0, 1.0f,

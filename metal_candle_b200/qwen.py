@@ -135,7 +135,7 @@ class Qwen:
         # chunk are produced, turned into their gradient in place and consumed by the lm_head backward before the
         # next chunk starts, so only [chunk, vocabulary] is ever resident (2.5 GB at 8192 tokens instead of 10 GB for
         # 32768; measured on the 16 x 2048 step: peak 35.7 -> 28.3 GB and 107.9 -> 106.1 ms, 4096 tokens: 27.0 GB, 107.3 ms).
-        self.ce_chunk_tokens: Optional[int] = 8192
+        self.ce_chunk_tokens: Optional[int] = 0    # 0: the library picks it (mcb_ce_chunk_tokens), None: one chunk
         # q, k and v projections of a layer as one fused linear with a block-diagonal rank path (bf16, adapters of
         # equal rank): the normed input is read once and the three input gradients are summed in one pass
         self.fuse_qkv = True
@@ -394,6 +394,8 @@ class Qwen:
         count = torch.empty(1, dtype=torch.int32, device=self.device)
         loss = torch.empty(2, dtype=torch.float32, device=self.device)
         chunk = self.ce_chunk_tokens
+        if chunk == 0:
+            chunk = int(self.lib.mcb_ce_chunk_tokens(M, c.hidden_size))
         if chunk is None or chunk >= M:
             logits, _ = self._lin(nf, self.lm_head, False)
             _lib.check(self.lib.mcb_cross_entropy(_ptr(logits), _ptr(tgt32), _ptr(nll), _ptr(count), _ptr(loss), M,

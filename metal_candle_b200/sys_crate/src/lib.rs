@@ -187,6 +187,7 @@ extern "C" {
     pub fn mcb_qwen_create(out: *mut *mut mcb_qwen, cfg: *const mcb_qwen_config, weights: *const mcb_qwen_weights, adapters: *const mcb_qwen_adapter_entry, n_adapters: c_int, rank: c_int, scale: f32, arena: *mut c_void, arena_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_qwen_set_exchange(q: *mut mcb_qwen, comm: *mut mcb_comm, side_stream: *mut c_void, grad_flat: *mut f32, bucket_lo: *const i64, bucket_hi: *const i64, bucket_first_layer: *const c_int, n_buckets: c_int) -> c_int;
     pub fn mcb_qwen_set_ce_chunk(q: *mut mcb_qwen, tokens: i64) -> c_int;
+    pub fn mcb_ce_chunk_tokens(tokens: i64, hidden: i64) -> i64;
     pub fn mcb_qwen_forward_backward(q: *mut mcb_qwen, ids: *const i32, targets: *const i32, batch: i64, seq: i64, accumulate: c_int, loss_out: *mut f32, stream: *mut c_void) -> c_int;
     pub fn mcb_qwen_adamw_step(q: *mut mcb_qwen, lr: f32, beta1: f32, beta2: f32, eps: f32, weight_decay: f32, grad_scale: f32, stream: *mut c_void) -> c_int;
     pub fn mcb_qwen_train_step(q: *mut mcb_qwen, ids: *const i32, targets: *const i32, batch: i64, seq: i64, lr: f32, beta1: f32, beta2: f32, eps: f32, weight_decay: f32, grad_scale: f32, loss_out: *mut f32, stream: *mut c_void) -> c_int;

@@ -105,6 +105,9 @@ def test_host_only_entry_points_work_without_a_gpu():
     small = lib.mcb_qwen_arena_bytes(C.byref(cfg), entries, 96, 16, 1, 128)
     assert 20e9 < big < 40e9 and 1e9 < small < 3e9 and small < big
     assert lib.mcb_qwen_arena_bytes(C.byref(cfg), entries, 96, 32, 16, 2048) == 0      # 3 x 32 rank columns > 64
+    # the loss chunk: whole waves of the lm_head backward's 256-token tiles over 74 CTA pairs (37 x 4 = 148 tiles)
+    assert lib.mcb_ce_chunk_tokens(32768, 896) == 9472 and lib.mcb_ce_chunk_tokens(384, 256) == 384
+    assert 4096 <= lib.mcb_ce_chunk_tokens(100000, 4096) <= 12288 and lib.mcb_ce_chunk_tokens(0, 896) == 0
     bad = _lib.QwenConfig(151936, 896, 4864, 24, 7, 1, 1e-6, 1e6)                      # head_dim 128
     assert lib.mcb_qwen_arena_bytes(C.byref(bad), entries, 96, 16, 1, 128) == 0
     assert b"head_dim" in lib.mcb_last_error()
