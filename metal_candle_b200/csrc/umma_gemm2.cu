@@ -25,7 +25,10 @@
 //   h_ready[a]   in the LEADER: 8 arrivals (epilogue warps of both CTAs) once the bf16 rank operand is in place
 //   q_full[a]    in the LEADER: the Q quarter-tiles of both CTAs have landed
 //   d1_full[a]   in each CTA: same commit, after the rank update (or the last k-block when rp == 0)
-//   acc_empty[a] in the LEADER: 8 arrivals, the 4 epilogue warps of each CTA (the peer's arrive remotely)
+//   acc_empty[a] in the LEADER: 8 arrivals, the 4 epilogue warps of each CTA (the peer's arrive remotely); 16 in the
+//                SwiGLU-backward form, which runs 8 epilogue warps per CTA
+//   gu_full[q][s] in each CTA (SwiGLU-backward form): the gate and up boxes of rows 32q.. have landed in buffer pair s
+//   hb[q][s]     in each CTA (same form): the helper warp of rows 32q.. has written its half of pair s
 // Every wait is bounded; both CTAs always meet at the cluster barrier before tensor memory is released.
 #include <cuda.h>
 #include <string.h>
@@ -51,7 +54,7 @@ struct Gemm2Params {
   int pdl_wait; // 1: launched as a programmatic dependent of the operand-pack kernel
   int swiglu;   // 1: the tile is [128 gate columns | 128 up columns]; the epilogue also writes silu(gate) * up
                 // 2: the product is d act of a SwiGLU; the epilogue turns it into d gate and d up (see U) and stores those
-  int epi_bufs; // staging buffers per epilogue warp (kEpiBufs; more in the SwiGLU-backward form)
+  int epi_bufs; // 2-KB staging buffers per 32 rows of the tile (kEpiBufs; 12 in the SwiGLU-backward form)
   int sw_pairs, sw_ahead;  // SwiGLU backward: buffer pairs per 32 rows, jobs loaded ahead
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks, group_m;  // m tiles of 256 rows
   float scale;
@@ -63,7 +66,7 @@ struct Gemm2Params {
   int64_t h_pitch;
   int* status;
   uint32_t stage_bytes, w_off, p_off, bar_off;
-  uint32_t epi_off;  // output staging: 4 epilogue warps x kEpiBufs buffers of 32 rows x 64 bytes
+  uint32_t epi_off;  // output staging: 4 row groups x epi_bufs buffers of 32 rows x 64 bytes
   uint32_t q_off, q_bytes, hs_off, hs_bytes;  // per CTA and accumulator buffer; q_bytes covers both halves' quarter-tiles
 };
 
