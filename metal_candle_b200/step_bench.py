@@ -506,7 +506,7 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                      if comm is not None else "torch.distributed nccl",
                      "nccl_version": comm.info()["nccl_version"] if comm is not None else None,
                      "bytes_per_step": nbytes, "buckets": len(dp.buckets),
-                     "overlapped": bool(comm is not None or captured["fb"] is None),
+                     "overlapped": bool((comm is not None or captured["fb"] is None) and len(dp.buckets) > 1),
                      "in_graph": bool(graph_has_comm and captured["fb"] is not None),
                      "exposed_ms": exposed,
                      "exposed_how": "slowest rank's step graph with the exchange minus the slowest rank's same graph without it "
@@ -558,7 +558,8 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
                        "optimizer": "AdamW lr 1e-4 warmup-cosine",
                        "step_through": "the C-ABI engine (mcb_qwen_forward_backward, mcb_qwen_adamw_step)" if use_engine
                        else "the Python mirror (Qwen.forward_backward, AdamW.step_vars)",
-                       "execution": (("forward+loss+backward" + (" with the bucketed gradient all-reduce overlapped on a side stream" if graph_has_comm and world > 1 else "")
+                       "execution": (("forward+loss+backward" + ((" with the bucketed gradient all-reduce overlapped on a side stream" if len(dp.buckets) > 1
+                                                                  else " and the gradient all-reduce") if graph_has_comm and world > 1 else "")
                                       + " replayed from a CUDA graph, then " + ("" if graph_has_comm or world == 1 else "gradient all-reduce and ") + "AdamW")
                                      if used_graph else
                                      "eager launches" + (f" (graph capture failed: {capture_note})" if capture_note else "")),
