@@ -226,6 +226,14 @@ int mcb_matmul(const void* a, const void* b, void* out, int64_t M, int64_t K, in
 int mcb_mul(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
 int mcb_mul_scalar(const void* a, void* out, int64_t n, float value, int dtype, void* stream);
 
+/* candle_nn::ops::dropout as LoRALayer::forward applies it to x A in training mode (src/training/lora.rs:325-330):
+ * out[i] = x[i] / (1 - p) where element i is kept, 0 where it is dropped; kept with probability 1 - p.  The mask comes
+ * from a counter-based generator over (seed, offset + i) - element i is kept when the 24 high bits of
+ * splitmix64(seed ^ (offset + i) * 0x9E3779B97F4A7C15), as a fraction of one, are >= p - so the same call on the
+ * upstream gradient is the backward pass.  Not candle's generator: draw by draw the masks differ from the reference's,
+ * their distribution and the inverted scaling are the same.  out may be x. */
+int mcb_dropout(const void* x, void* out, int64_t n, float p, uint64_t seed, uint64_t offset, int dtype, void* stream);
+
 /* ---- RMSNorm ------------------------------------------------------------------------------ */
 
 /* Replaces FusedRMSNormOp / rms_norm_fused (src/backend/custom_ops.rs:443-632, kernels.metal:281-330)

@@ -109,6 +109,7 @@ SIGNATURES = {
     "mcb_matmul_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "mcb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "mcb_mul": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "mcb_dropout": (_i32, [_vp, _vp, _i64, _f32, C.c_uint64, C.c_uint64, _i32, _vp]),
     "mcb_mul_scalar": (_i32, [_vp, _vp, _i64, _f32, _i32, _vp]),
     "mcb_rmsnorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
     "mcb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),

@@ -136,6 +136,39 @@ def lora_forward_fused(x: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tens
     return out
 
 
+def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """`a` [..., k] times `b` [k, n] (Tensor::broadcast_matmul with a 2-D right operand)."""
+    _require_cuda(a, b)
+    if b.dim() != 2 or a.shape[-1] != b.shape[0] or a.dtype != b.dtype:
+        raise TrainingError(f"matmul: {list(a.shape)} @ {list(b.shape)} ({a.dtype}, {b.dtype})")
+    a, b = a.contiguous(), b.contiguous()
+    K, N = b.shape
+    lib, dt = _lib_for(a), _dtype_code(a)
+    out = torch.empty(*a.shape[:-1], N, dtype=a.dtype, device=a.device)
+    ws = workspace(a.device, lib.mcb_matmul_workspace_bytes(K, N, dt))
+    _lib.check(lib.mcb_matmul(_ptr(a), _ptr(b), _ptr(out), a.numel() // K, K, N, dt, _ptr(ws), ws.numel(), _stream()))
+    return out
+
+
+def dropout(x: torch.Tensor, p: float, seed: int, offset: int = 0) -> torch.Tensor:
+    """Inverted dropout with the library's counter-based mask over (seed, offset + element index); applied to the
+    upstream gradient with the same arguments it is its own backward."""
+    _require_cuda(x)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _lib.check(_lib_for(x).mcb_dropout(_ptr(x), _ptr(out), x.numel(), float(p), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                                       int(offset) & 0xFFFFFFFFFFFFFFFF, _dtype_code(x), _stream()))
+    return out
+
+
+def scale(x: torch.Tensor, value: float) -> torch.Tensor:
+    _require_cuda(x)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _lib.check(_lib_for(x).mcb_mul_scalar(_ptr(x), _ptr(out), x.numel(), float(value), _dtype_code(x), _stream()))
+    return out
+
+
 def lora_linear_forward(x, weight, bias, lora_a, lora_b, scaling, save_hidden=True, residual=None):
     """`y = x W^T (+b) + scaling (x A) B` with W [out, in].  Returns (y, h_save or None); h_save is
     `scaling * (x A)` transposed, [rank padded to 16, tokens padded to 64]."""

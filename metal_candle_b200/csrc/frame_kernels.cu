@@ -612,6 +612,39 @@ extern "C" int mcb_mul(const void* a, const void* b, void* out, int64_t n, int d
   return MCB_OK;
 }
 
+// Inverted dropout with a counter-based generator: element i of the call is kept when the 24 high bits of
+// splitmix64(seed, offset + i), read as a fraction of one, are >= p.  The mask depends on (seed, offset + i) only,
+// so the same call on the upstream gradient is the backward pass, whatever the launch shape.
+__device__ __forceinline__ bool dropout_keep(uint64_t seed, uint64_t index, float p) {
+  uint64_t z = seed ^ (index * 0x9E3779B97F4A7C15ull);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  return static_cast<float>(z >> 40) * (1.0f / 16777216.0f) >= p;
+}
+template <typename T>
+__global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, float p, float keep_scale, uint64_t seed,
+                               uint64_t offset) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    out[i] = dropout_keep(seed, offset + static_cast<uint64_t>(i), p) ? from_f32<T>(to_f32(x[i]) * keep_scale) : from_f32<T>(0.0f);
+}
+
+extern "C" int mcb_dropout(const void* x, void* out, int64_t n, float p, uint64_t seed, uint64_t offset, int dtype, void* stream) {
+  MCB_NVTX_RANGE("mcb_dropout");
+  if (!x || !out) return fail(MCB_ERR_NULL, "dropout: null pointer");
+  if (n <= 0) return fail(MCB_ERR_SHAPE, "dropout: element count must be positive");
+  if (!(p >= 0.0f && p < 1.0f)) return fail(MCB_ERR_SHAPE, "dropout: probability %g is not in [0, 1)", static_cast<double>(p));
+  DeviceState* ds = current_device_state();
+  if (!ds) return MCB_ERR_NOT_INIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n, 256, ds->sm_count);
+  const float keep_scale = 1.0f / (1.0f - p);
+  MCB_DTYPE_SWITCH(dtype, (dropout_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)out, n, p, keep_scale, seed, offset)));
+  MCB_CHECK_LAUNCH("dropout");
+  return MCB_OK;
+}
+
 extern "C" int mcb_mul_scalar(const void* a, void* out, int64_t n, float value, int dtype, void* stream) {
   MCB_NVTX_RANGE("mcb_mul_scalar");
   if (!a || !out) return fail(MCB_ERR_NULL, "mul_scalar: null pointer");

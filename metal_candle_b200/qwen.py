@@ -153,6 +153,9 @@ class Qwen:
             if (layer.in_features, layer.out_features) != (lin.in_f, lin.out_f):
                 raise TrainingError(f"adapter {key} is {layer.in_features}x{layer.out_features} but the projection is "
                                     f"{lin.in_f}x{lin.out_f} (size K/V adapters with kv_size={c.kv_size})")
+            if layer.config.dropout > 0.0:
+                raise TrainingError(f"adapter {key} has dropout {layer.config.dropout}: the fused training step applies none "
+                                    "(LoRALayer.forward has the reference's unfused dropout branch); use dropout = 0 here")
             lin.lora = layer
         self.lora_adapter = adapter
         n = sum(l.lora_a.numel() + l.lora_b.numel() for _, l in adapter.layers())

@@ -19,7 +19,7 @@ HEADER = HERE.parent.parent / "include" / "mcb200.h"
 OUT = HERE / "src" / "lib.rs"
 
 TYPES = {
-    "void": None, "int": "c_int", "float": "f32", "double": "f64", "int64_t": "i64", "int32_t": "i32",
+    "void": None, "int": "c_int", "float": "f32", "double": "f64", "int64_t": "i64", "int32_t": "i32", "uint64_t": "u64",
     "size_t": "usize", "char": "c_char", "mcb_adamw_tensor": "mcb_adamw_tensor", "mcb_comm": "mcb_comm",
     "mcb_lora_segment": "mcb_lora_segment", "mcb_qwen": "mcb_qwen", "mcb_qwen_config": "mcb_qwen_config",
     "mcb_qwen_weights": "mcb_qwen_weights", "mcb_qwen_adapter_entry": "mcb_qwen_adapter_entry",

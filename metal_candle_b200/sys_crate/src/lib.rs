@@ -150,6 +150,7 @@ extern "C" {
     pub fn mcb_matmul(a: *const c_void, b: *const c_void, out: *mut c_void, M: i64, K: i64, N: i64, dtype: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn mcb_mul(a: *const c_void, b: *const c_void, out: *mut c_void, n: i64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_mul_scalar(a: *const c_void, out: *mut c_void, n: i64, value: f32, dtype: c_int, stream: *mut c_void) -> c_int;
+    pub fn mcb_dropout(x: *const c_void, out: *mut c_void, n: i64, p: f32, seed: u64, offset: u64, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_rmsnorm_fwd(x: *const c_void, w: *const c_void, y: *mut c_void, rstd: *mut f32, rows: i64, D: i64, eps: f32, dtype: c_int, stream: *mut c_void) -> c_int;
     pub fn mcb_rmsnorm_bwd_workspace_bytes(rows: i64, D: i64) -> usize;
     pub fn mcb_rmsnorm_bwd(x: *const c_void, w: *const c_void, dy: *const c_void, dx: *mut c_void, dw: *mut f32, accumulate: c_int, rows: i64, D: i64, eps: f32, dtype: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;

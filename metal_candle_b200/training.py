@@ -68,6 +68,8 @@ class LoRALayer:
         self.config = LoRAConfig(config.rank, config.alpha, config.dropout)
         self.in_features, self.out_features = in_features, out_features
         self.training = True
+        # dropout stream of this layer: mask element i of a call is drawn from (dropout_seed, dropout_offset + i)
+        self.dropout_seed, self.dropout_offset, self.last_dropout = 0, 0, None
 
     # -- accessors (src/training/lora.rs:441-574) --
     def lora_a_tensor(self) -> torch.Tensor:
@@ -96,8 +98,14 @@ class LoRALayer:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.training and self.config.dropout > 0.0:
-            raise TrainingError("dropout > 0 in training mode is not implemented by the fused kernel; "
-                                "call eval() or use dropout = 0")
+            # LoRALayer::forward's unfused branch (src/training/lora.rs:312-339): hidden = x A, dropout on hidden,
+            # hidden B, then the scaling.  float32 throughout (the rank may be any size); the mask of this call covers
+            # the elements [dropout_offset, dropout_offset + hidden.numel()) of the layer's stream.
+            h = backend.matmul(x.float().contiguous(), self.lora_a)
+            self.last_dropout = (self.dropout_seed, self.dropout_offset)
+            h = backend.dropout(h, self.config.dropout, self.dropout_seed, self.dropout_offset)
+            self.dropout_offset += h.numel()
+            return backend.scale(backend.matmul(h, self.lora_b), self.config.scaling()).to(x.dtype)
         return backend.lora_forward_fused(x, self.lora_a, self.lora_b, self.config.scaling())
 
     def forward_lazy(self, x_lazy):

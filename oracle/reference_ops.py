@@ -386,6 +386,29 @@ def causal_gqa_attention_backward(q, k, v, scale, do, dtype=np.float64):
     return dq, dk, dv
 
 
+def dropout_mask(n, p, seed, offset=0):
+    """The keep mask of the library's dropout (include/mcb200.h, mcb_dropout): element i is kept when the 24 high bits
+    of splitmix64(seed ^ (offset + i) * 0x9E3779B97F4A7C15), as a fraction of one, are >= p.  candle_nn::ops::dropout
+    (used by src/training/lora.rs:325-330) draws from candle's own generator; only the distribution is shared."""
+    with np.errstate(over="ignore"):
+        idx = np.uint64(offset) + np.arange(n, dtype=np.uint64)
+        z = np.uint64(seed) ^ (idx * np.uint64(0x9E3779B97F4A7C15))
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    u = (z >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+    return u >= np.float32(p)
+
+
+def lora_forward_dropout(x, A, B, scaling, p, seed, offset=0, dtype=np.float64):
+    """LoRALayer::forward in training mode with dropout (src/training/lora.rs:312-339): hidden = x A, inverted dropout
+    on hidden, hidden B, scaling."""
+    h = x.astype(dtype) @ A.astype(dtype)
+    keep = dropout_mask(h.size, p, seed, offset).reshape(h.shape)
+    h = np.where(keep, h / (1.0 - np.float32(p)).astype(dtype), 0.0)
+    return (h @ B.astype(dtype)) * dtype(scaling)
+
+
 def matmul(a, b, dtype=np.float64):
     """Operation::Matmul -> broadcast_matmul, src/graph/executor.rs:71-82."""
     return np.asarray(a, dtype=dtype) @ np.asarray(b, dtype=dtype)

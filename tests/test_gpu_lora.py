@@ -385,3 +385,43 @@ def test_fused_projections_reject_bad_segments(cuda_device):
     with pytest.raises(_lib.McbError, match="64 rank columns"):
         big = lambda off: dict(A=torch.zeros(128, 32, device=dev), B=torch.zeros(32, 64, device=dev), offset=off)
         B.lora_linear_fused_forward(x, W, None, [big(0), big(64), big(128)], 1.0)
+
+
+def test_dropout_mask_and_lora_layer_training_forward(cuda_device):
+    """mcb_dropout against the oracle's restatement of its counter-based mask (bit for bit), and LoRALayer.forward in
+    training mode with dropout > 0 (the reference's unfused branch, src/training/lora.rs:312-339) against the oracle
+    with the same mask; eval mode stays on the fused kernel."""
+    from metal_candle_b200 import _lib, backend as B
+    from metal_candle_b200.training import LoRAConfig, LoRALayer
+
+    dev = cuda_device
+    x = S.normal(3, "x", (1000, 37)).astype(np.float32)
+    for dtype, p, seed, off in ((torch.float32, 0.25, 99, 0), (torch.bfloat16, 0.1, 2**40 + 5, 123457), (torch.float32, 0.0, 1, 0)):
+        xd = torch.from_numpy(x).to(dev).to(dtype)
+        got = B.dropout(xd, p, seed, off).float().cpu().numpy()
+        keep = R.dropout_mask(x.size, p, seed, off).reshape(x.shape)
+        ref = xd.float().cpu().numpy()
+        assert np.array_equal(got != 0, keep & (ref != 0))
+        want = np.where(keep, ref / np.float32(1.0 - p), 0.0)
+        assert R.max_abs_normalised(got, want) <= (1e-6 if dtype == torch.float32 else 4e-3)
+        assert abs(keep.mean() - (1.0 - p)) < 5e-3
+    with pytest.raises(_lib.McbError, match="not in"):
+        B.dropout(torch.zeros(8, device=dev), 1.0, 0, 0)
+    # the layer
+    layer = LoRALayer(64, 48, LoRAConfig(rank=8, alpha=16.0, dropout=0.2), dev, generator=torch.Generator(device=dev).manual_seed(5))
+    layer.lora_b.copy_(torch.from_numpy(S.normal(4, "B", (8, 48), 0.0, 0.05)).float())
+    layer.dropout_seed = 4242
+    xin = S.normal(6, "xin", (3, 50, 64)).astype(np.float32)
+    xd = torch.from_numpy(xin).to(dev)
+    A, Bm = layer.lora_a.cpu().numpy(), layer.lora_b.cpu().numpy()
+    y1 = layer.forward(xd).cpu().numpy()
+    assert layer.last_dropout == (4242, 0) and layer.dropout_offset == 3 * 50 * 8
+    want1 = R.lora_forward_dropout(xin.reshape(-1, 64), A, Bm, layer.config.scaling(), 0.2, 4242, 0).reshape(3, 50, 48)
+    assert R.max_abs_normalised(y1, want1) <= 1e-4
+    y2 = layer.forward(xd).cpu().numpy()                     # the next call draws the next part of the stream
+    want2 = R.lora_forward_dropout(xin.reshape(-1, 64), A, Bm, layer.config.scaling(), 0.2, 4242, 3 * 50 * 8).reshape(3, 50, 48)
+    assert R.max_abs_normalised(y2, want2) <= 1e-4 and not np.allclose(y1, y2)
+    layer.eval()
+    y3 = layer.forward(xd).cpu().numpy()
+    assert R.max_abs_normalised(y3, R.lora_forward(xin.reshape(-1, 64), A, Bm, layer.config.scaling())[0].reshape(3, 50, 48)) <= 1e-4
+    assert _lib.device_status() == 0
