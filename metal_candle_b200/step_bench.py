@@ -349,9 +349,10 @@ def run_b200(args, ClockSampler, measured_peaks, cpu_baseline, kernel_numbers=No
 
             comm = C.Communicator(world, rank, C.broadcast_id(rank), timeout_ms=30_000,
                                   blocking=(comm_mode == "mcb-blocking"))
-    # the backward's tail phase needs its whole grid resident; with a collective running beside it, it is off
+    # the backward's tail phase needs its whole grid resident: off where a collective runs beside the backward pass
+    # (more than one exchange bucket); with one bucket the all-reduce starts when the backward pass has finished
     tail = getattr(args, "grad_tail", "auto")
-    tail_on = (tail == "on") or (tail == "auto" and world == 1)
+    tail_on = (tail == "on") or (tail == "auto" and (world == 1 or getattr(args, "buckets", N_BUCKETS) <= 1))
     _lib.check(lib.mcb_set_option(_lib.MCB_OPT_GRAD_TAIL, int(tail_on)))
     wl = WORKLOADS[args.workload]
     B, S = wl["batch"], wl["seq"]
