@@ -138,3 +138,22 @@ def test_from_slice_and_constructors():
     assert LazyTensor.ones((3, 2), torch.float32, "cpu").graph_size() == 1
     with pytest.raises(Exception):
         LazyTensor.from_slice([1.0, 2.0], (3,), "cpu")
+
+
+def test_oracle_dropout_mask_is_a_pure_function_of_seed_and_position():
+    """The restated mask of mcb_dropout: keep rate 1 - p, a call at offset k continues the stream of a call at offset 0,
+    different seeds give different masks, p = 0 keeps everything; the LoRA training-mode forward scales kept entries
+    of x A by 1 / (1 - p) (src/training/lora.rs:325-330 applies candle_nn::ops::dropout to the same tensor)."""
+    import numpy as np
+
+    from oracle import reference_ops as R
+
+    whole = R.dropout_mask(100_000, 0.3, 7, 0)
+    assert abs(whole.mean() - 0.7) < 5e-3
+    assert np.array_equal(R.dropout_mask(1000, 0.3, 7, 5000), whole[5000:6000])
+    assert not np.array_equal(R.dropout_mask(1000, 0.3, 8, 0), whole[:1000])
+    assert R.dropout_mask(1000, 0.0, 7, 0).all()
+    x = np.ones((4, 3)); A = np.ones((3, 2)); B = np.ones((2, 5))
+    y = R.lora_forward_dropout(x, A, B, 2.0, 0.5, 11, 0)
+    keep = R.dropout_mask(8, 0.5, 11, 0).reshape(4, 2)
+    assert np.allclose(y, (np.where(keep, 3.0 / 0.5, 0.0) @ B) * 2.0)
